@@ -1,0 +1,218 @@
+/*
+ * mxb200 — C ABI of the B200 weight-placement data plane.
+ *
+ * Plain C: pointers and sizes only, no C++ or framework types.  Every device
+ * address is a 64-bit integer valid in the calling process (a cudaMalloc'ed
+ * pointer, a peer pointer opened with mxb_ipc_open, or pinned host memory).
+ * All functions return an int32 status (MXB_OK or a negative MXB_ERR_*) unless
+ * stated otherwise; mxb_last_error() gives the text of the last failure on the
+ * calling thread.  Nothing here falls back to the CPU: without a usable CUDA
+ * device the compute entry points return MXB_ERR_CUDA.
+ *
+ * Each entry point cites the reference interface it stands in for, by path
+ * inside the reference project (modelexpress_client/python/modelexpress/...).
+ */
+#ifndef MXB200_H
+#define MXB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MXB_OK 0
+#define MXB_ERR_ARG (-1)     /* null pointer, zero size where one is needed, bad enum */
+#define MXB_ERR_BOUNDS (-2)  /* a descriptor leaves the registered extents */
+#define MXB_ERR_ALIGN (-3)   /* an address breaks an alignment the call requires */
+#define MXB_ERR_CUDA (-4)    /* a CUDA runtime call failed; see mxb_last_error */
+#define MXB_ERR_TIMEOUT (-5) /* a bounded device- or host-side wait ran out */
+#define MXB_ERR_PEER (-6)    /* peer access / IPC mapping unavailable */
+#define MXB_ERR_NOMEM (-7)
+#define MXB_ERR_STATE (-8)   /* object used in the wrong state */
+
+typedef struct mxb_ctx mxb_ctx;
+typedef struct mxb_ring mxb_ring;
+typedef struct mxb_fanout mxb_fanout;
+
+/* One contiguous byte run.  Mirrors ReadDescriptor(session, src_addr, dst_addr,
+ * nbytes) of refit/reshard/transport/base.py:26-35 with the session resolved
+ * to an address the caller can reach. */
+typedef struct {
+    uint64_t src;
+    uint64_t dst;
+    uint64_t nbytes;
+} mxb_run;
+
+/* One strided slice: `rows` runs of `row_bytes`, row r at src + r*src_pitch ->
+ * dst + r*dst_pitch.  This is the closed form of the run list that
+ * refit/reshard/slice_plan.py:259-294 (paired_runs) emits for one TP slice:
+ * a row-parallel shard is one record instead of thousands of runs. */
+typedef struct {
+    uint64_t src;
+    uint64_t dst;
+    uint64_t rows;
+    uint64_t row_bytes;
+    uint64_t src_pitch;
+    uint64_t dst_pitch;
+} mxb_desc2d;
+
+/* One byte range to digest. */
+typedef struct {
+    uint64_t ptr;
+    uint64_t nbytes;
+} mxb_span;
+
+/* Per-span digest record written by mxb_digest. */
+typedef struct {
+    uint64_t nbytes;
+    uint64_t row_sum;        /* sum of 4 KiB row sums (signed int32 words), mod 2^64 */
+    uint64_t row_sum_w;      /* sum of row sums * (1-based row index) */
+    uint64_t tail_sum;       /* words after the last whole row */
+    uint64_t tail_sum_w;     /* ... weighted by 1-based word index */
+    uint64_t ragged_sum;     /* bytes after the last whole word */
+    uint64_t block_hash;     /* 64-bit block hash (MXB_DIGEST_BLOCK64) */
+    uint32_t safe_checksum;  /* 32-bit position-weighted byte sum */
+    uint32_t reserved;
+} mxb_digest_out;
+
+#define MXB_DIGEST_SAFE32 1u  /* tensor_utils.py:27-44 safe_checksum */
+#define MXB_DIGEST_ROWS 2u    /* refit/reshard/verify.py:113-150 scalars of tensor_digest */
+#define MXB_DIGEST_BLOCK64 4u /* 64-bit hash over 4 KiB blocks; no reference counterpart */
+
+/* ---- context ----------------------------------------------------------- */
+
+/* Create a context over `n` CUDA devices of this process and enable peer
+ * access between every pair that supports it.  Replaces the per-worker agent
+ * set-up of nixl_transfer.py:194-254 (NixlTransferManager.initialize). */
+int32_t mxb_ctx_create(const int32_t *device_ids, int32_t n, mxb_ctx **out);
+int32_t mxb_ctx_destroy(mxb_ctx *ctx);
+/* Text of the last error raised on this thread ("" if none). */
+const char *mxb_last_error(void);
+/* ABI version of the loaded library. */
+int32_t mxb_version(void);
+/* Block the host until all work queued by this context on `dev` is done;
+ * returns MXB_ERR_TIMEOUT if a kernel reported a wait that ran out. */
+int32_t mxb_sync(mxb_ctx *ctx, int32_t dev);
+/* Number of this library's kernels launched since the context was created. */
+uint64_t mxb_launch_count(mxb_ctx *ctx);
+
+/* Device memory owned by the library (plain cudaMalloc, so it can be exported
+ * over CUDA IPC).  Replaces refit/reshard/cuda_pool.py:52-108. */
+int32_t mxb_alloc(mxb_ctx *ctx, int32_t dev, uint64_t nbytes, uint64_t *out_ptr);
+int32_t mxb_free(mxb_ctx *ctx, int32_t dev, uint64_t ptr);
+/* Pinned host memory. */
+int32_t mxb_host_alloc(uint64_t nbytes, uint64_t *out_ptr);
+int32_t mxb_host_free(uint64_t ptr);
+
+/* Extents the scatter entry points check destinations (and device sources)
+ * against; with none registered only structural checks run.  Replaces the
+ * registration step of nixl_transfer.py:302-585. */
+int32_t mxb_register_extent(mxb_ctx *ctx, uint64_t base, uint64_t nbytes);
+int32_t mxb_clear_extents(mxb_ctx *ctx);
+
+/* Cross-process peer mapping (one OS process per GPU rank).  `handle` is 64
+ * opaque bytes; `offset` is ptr's distance from its allocation base.
+ * Replaces the metadata exchange of nixl_transfer.py:680-712. */
+int32_t mxb_ipc_export(uint64_t ptr, uint8_t handle[64], uint64_t *offset);
+int32_t mxb_ipc_open(const uint8_t handle[64], uint64_t offset, uint64_t *out_ptr);
+int32_t mxb_ipc_close(uint64_t ptr, uint64_t offset);
+
+/* ---- descriptor compiler (host) ---------------------------------------- */
+
+/* Fold consecutive runs of equal length and constant src/dst stride into 2-D
+ * records, preserving order.  Returns the number of records written (<= cap),
+ * or the negated count needed if cap is too small.  The expansion of the
+ * result is exactly the input run list (refit/reshard/slice_plan.py:297-339). */
+int64_t mxb_coalesce_runs(const mxb_run *runs, uint64_t n, mxb_desc2d *out, uint64_t cap);
+
+/* ---- kernel 1/3: descriptor-driven scatter ----------------------------- */
+
+#define MXB_SCATTER_DEFAULT 0u
+#define MXB_SCATTER_BULK 1u    /* move large 16-byte-aligned rows with cp.async.bulk */
+#define MXB_SCATTER_NO_SYNC 2u /* return after enqueueing on the context stream */
+
+/* One persistent launch on `dev` moves every record of the host table
+ * `descs[0..n)`: sources and destinations may be local HBM, a peer GPU's HBM
+ * or pinned host memory.  Stands in for Transport.read(descriptors)
+ * (refit/reshard/transport/base.py:38-43), for the per-tensor narrow+copy_
+ * loop reached from engines/vllm/adapter.py:316-329 and for the per-tensor
+ * copy loop of engines/vllm/refit/installer.py:419-424. */
+int32_t mxb_scatter(mxb_ctx *ctx, int32_t dev, const mxb_desc2d *descs, uint64_t n,
+                    uint32_t flags);
+/* Same, from a 1-D run list: coalesces, launches and waits.  Direct
+ * equivalent of InMemoryReferenceTransport.read (transport/base.py:46-62). */
+int32_t mxb_read_runs(mxb_ctx *ctx, int32_t dev, const mxb_run *runs, uint64_t n);
+
+/* ---- staging ring: host bytes -> HBM shards ----------------------------- */
+
+typedef struct {
+    uint64_t bytes_placed;
+    uint64_t chunks;
+    uint64_t launches;
+    double seconds_total;   /* wall time of the call */
+    double seconds_gather;  /* summed host gather time (overlaps the copies) */
+    double seconds_device;  /* first H2D start to last scatter end, CUDA events */
+} mxb_place_stats;
+
+#define MXB_PLACE_COPY_ENGINE 0u /* slot -> device staging by cudaMemcpyAsync, then scatter */
+#define MXB_PLACE_ZERO_COPY 1u   /* scatter kernel reads the pinned slot directly */
+
+/* A pinned host ring of `slots` equal slots (ring_bytes in total) plus, for the
+ * copy-engine mode, two device staging buffers of one slot each. */
+int32_t mxb_ring_create(mxb_ctx *ctx, int32_t dev, uint64_t ring_bytes, uint32_t slots,
+                        mxb_ring **out);
+int32_t mxb_ring_destroy(mxb_ring *ring);
+/* Place `n` slices whose sources are ordinary host memory (a checkpoint file
+ * image) and whose destinations are device addresses: host threads gather the
+ * needed bytes of each chunk into a ring slot while the previous slot crosses
+ * PCIe, and one scatter launch per chunk writes the shards.  Replaces the
+ * host-staged path engines/vllm/adapter.py:316-329 and the file->GPU batches of
+ * gds_loader.py:284-331 / gds_transfer.py:142-231. */
+int32_t mxb_place(mxb_ring *ring, const mxb_desc2d *items, uint64_t n, int32_t host_threads,
+                  uint32_t mode, mxb_place_stats *stats);
+
+/* ---- kernel 4: integrity digests ---------------------------------------- */
+
+/* Digest `n` device byte ranges in one launch; `out[i]` receives the record of
+ * `spans[i]` (host memory).  `modes` is a bit set of MXB_DIGEST_*.  Replaces
+ * tensor_utils.py:27-44 (safe_checksum) and the device half of
+ * refit/reshard/verify.py:79-155 (tensor_digest; blake2b of the scalars stays
+ * on the host). */
+int32_t mxb_digest(mxb_ctx *ctx, int32_t dev, const mxb_span *spans, uint64_t n, uint32_t modes,
+                   mxb_digest_out *out);
+/* Per-4-KiB-block hashes of one range, written to device memory `out_blocks`
+ * (ceil(nbytes/4096) uint64 values). */
+int32_t mxb_block_hashes(mxb_ctx *ctx, int32_t dev, uint64_t ptr, uint64_t nbytes,
+                         uint64_t out_blocks);
+
+/* ---- kernel 2: serving-peer fan-out -------------------------------------- */
+
+#define MXB_FANOUT_MAX_CHILDREN 7
+
+/* A fan-out node: this GPU's copy of the payload is the ranges
+ * `local[0..n)`, cut into chunks of `chunk_bytes`.  The node waits for each
+ * chunk to arrive from its parent (unless it is the root), stores it into
+ * every child's ranges over NVLink and raises the child's per-chunk counter.
+ * Replaces the name-matched whole-tensor pull of nixl_transfer.py:769-952 on
+ * one box. */
+int32_t mxb_fanout_create(mxb_ctx *ctx, int32_t dev, const mxb_span *local, uint64_t n,
+                          uint64_t chunk_bytes, mxb_fanout **out);
+/* Device address of this node's arrival counters (export it to the parent). */
+uint64_t mxb_fanout_counters(mxb_fanout *f);
+/* Ranges (same count and sizes as `local`) and counter address of child `k`,
+ * as addresses valid in this process. */
+int32_t mxb_fanout_set_child(mxb_fanout *f, int32_t k, const mxb_span *child, uint64_t n,
+                             uint64_t child_counters);
+/* Launch this node's kernel for one broadcast.  `is_root`: has no parent.
+ * `timeout_ms` bounds every device-side wait. */
+int32_t mxb_fanout_run(mxb_fanout *f, int32_t is_root, uint32_t timeout_ms);
+/* Wait for this node's kernel; MXB_ERR_TIMEOUT if a wait ran out. */
+int32_t mxb_fanout_wait(mxb_fanout *f, float *device_ms);
+int32_t mxb_fanout_destroy(mxb_fanout *f);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MXB200_H */

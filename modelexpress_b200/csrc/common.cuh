@@ -1,0 +1,118 @@
+// Shared declarations of the mxb200 library (host side).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/mxb200.h"
+
+namespace mxb {
+
+void set_error(const char *fmt, ...);
+
+#define MXB_CUDA(call)                                                                  \
+    do {                                                                                \
+        cudaError_t _e = (call);                                                        \
+        if (_e != cudaSuccess) {                                                        \
+            mxb::set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(_e),      \
+                           __FILE__, __LINE__);                                         \
+            return MXB_ERR_CUDA;                                                        \
+        }                                                                               \
+    } while (0)
+
+// Device-side status word values written by kernels whose waits ran out.
+enum : uint32_t { DEV_OK = 0, DEV_TIMEOUT = 1 };
+
+struct DeviceState {
+    int device = -1;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;       // compute stream of the context
+    cudaStream_t copy_stream = nullptr;  // copy-engine stream (H2D of ring slots)
+    uint32_t *status = nullptr;          // device status word (one per device)
+    uint32_t *status_host = nullptr;     // pinned mirror
+    // scratch for descriptor tables, grown on demand
+    void *table = nullptr;
+    size_t table_bytes = 0;
+    void *table_host = nullptr;  // pinned staging for the table upload
+    size_t table_host_bytes = 0;
+    // scratch for digest accumulators
+    void *digest = nullptr;
+    size_t digest_bytes = 0;
+    void *digest_host = nullptr;
+    size_t digest_host_bytes = 0;
+};
+
+struct Extent {
+    uint64_t base, end;
+};
+
+}  // namespace mxb
+
+struct mxb_ctx {
+    std::vector<mxb::DeviceState> devs;
+    std::vector<mxb::Extent> extents;
+    std::mutex mu;
+    std::atomic<uint64_t> launches{0};
+
+    mxb::DeviceState *find(int dev) {
+        for (auto &d : devs)
+            if (d.device == dev) return &d;
+        return nullptr;
+    }
+};
+
+namespace mxb {
+
+// RAII device switch.
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        if (prev != dev) ok = (cudaSetDevice(dev) == cudaSuccess);
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+int32_t ensure_table(DeviceState *d, size_t bytes);
+int32_t ensure_digest(DeviceState *d, size_t bytes);
+int32_t check_status(DeviceState *d);
+
+// Tiling of a descriptor table; shared by the scatter launcher and its tests.
+constexpr uint64_t kTileBytes = 64 * 1024;
+uint64_t tiles_of(const mxb_desc2d &d);
+
+// A descriptor table cut into tiles, resident on the device.
+struct ScatterTable {
+    const mxb_desc2d *descs = nullptr;  // device
+    const void *tiles = nullptr;        // device, Tile records
+    uint64_t total_tiles = 0;
+    size_t bytes = 0;
+    bool bulk_ok = false;  // every record meets the bulk engine's alignment rules
+};
+size_t scatter_table_bytes(const mxb_desc2d *descs, uint64_t n, uint64_t *live_out,
+                           uint64_t *tiles_out);
+// Fill host_buf with the table image whose device copy will live at dev_buf.
+// tile_begin_of_desc (n+1 entries, optional) receives each input record's first tile.
+int32_t build_scatter_table(const mxb_desc2d *descs, uint64_t n, void *host_buf, void *dev_buf,
+                            ScatterTable *out, uint64_t *tile_begin_of_desc);
+int32_t launch_scatter_tiles(mxb_ctx *ctx, DeviceState *dv, const ScatterTable &tb,
+                             uint64_t tile_begin, uint64_t tile_count, uint32_t flags,
+                             cudaStream_t stream);
+
+// Launchers implemented in the kernel files.
+int32_t launch_scatter(mxb_ctx *ctx, DeviceState *d, const mxb_desc2d *descs, uint64_t n,
+                       uint32_t flags, cudaStream_t stream);
+int32_t validate_descs(mxb_ctx *ctx, const mxb_desc2d *descs, uint64_t n);
+
+}  // namespace mxb

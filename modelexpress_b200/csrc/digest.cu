@@ -1,0 +1,303 @@
+// Kernel 4: integrity digests (sm_100a), one pass over the bytes.
+//
+// A persistent launch walks 64 KiB tiles of a batch of byte ranges.  One warp
+// owns one 4 KiB row: lane L loads the 16 bytes at row + step*512 + L*16 for
+// step 0..7 (eight independent 16-byte loads in flight per lane) and feeds up
+// to three reductions from the same registers:
+//   SAFE32  - sum of byte * ((index*2654435761 + 1) mod 2^32), mod 2^32, via
+//             two dp4a per word (byte sum and 0,1,2,3-weighted byte sum);
+//   ROWS    - signed int32 row sums widened to 64 bit, folded into
+//             sum(row) and sum(row * (k+1)) mod 2^64, plus the word tail and
+//             ragged-byte terms;
+//   BLOCK64 - a 64-bit hash per 4 KiB block: per-lane xxHash64 rounds over its
+//             16 words, lanes combined with rotate+xor, avalanche.
+// All three are sums in a wrap-around ring, so partial results are merged with
+// atomics in any order and the answer is exact.
+#include "common.cuh"
+
+namespace mxb {
+
+struct DigestAcc {  // device accumulator, one per span; same layout as mxb_digest_out
+    unsigned long long nbytes, row_sum, row_sum_w, tail_sum, tail_sum_w, ragged_sum, block_hash;
+    uint32_t safe_checksum, reserved;
+};
+static_assert(sizeof(DigestAcc) == sizeof(mxb_digest_out), "accumulator mirrors the ABI record");
+
+struct DTile {
+    uint32_t span;
+    uint32_t local;  // 64 KiB tile inside the span
+};
+
+constexpr uint64_t kP1 = 0x9E3779B185EBCA87ull;
+constexpr uint64_t kP2 = 0xC2B2AE3D27D4EB4Full;
+constexpr uint64_t kP3 = 0x165667B19E3779F9ull;
+constexpr uint64_t kP4 = 0x85EBCA77C2B2AE63ull;
+constexpr uint64_t kP5 = 0x27D4EB2F165667C5ull;
+constexpr uint32_t kKnuth = 2654435761u;
+
+__device__ __forceinline__ uint64_t rotl64(uint64_t x, int r) { return (x << r) | (x >> (64 - r)); }
+__device__ __forceinline__ uint64_t avalanche(uint64_t h) {
+    h ^= h >> 33;
+    h *= kP2;
+    h ^= h >> 29;
+    h *= kP3;
+    h ^= h >> 32;
+    return h;
+}
+
+// 16 bytes at p + off, zero beyond n; any alignment.
+__device__ __forceinline__ uint4 load16(const unsigned char *p, uint64_t off, uint64_t n,
+                                        bool aligned16) {
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (off >= n) return v;
+    const unsigned char *q = p + off;
+    if (off + 16 <= n) {
+        if (aligned16) return __ldcs(reinterpret_cast<const uint4 *>(q));
+        const uint64_t a = (uint64_t)(uintptr_t)q;
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(a & ~3ull);
+        const uint32_t sh = (uint32_t)(a & 3ull) * 8u;
+        uint32_t w0 = __ldcs(w), w1 = __ldcs(w + 1), w2 = __ldcs(w + 2), w3 = __ldcs(w + 3);
+        if (sh == 0) return make_uint4(w0, w1, w2, w3);
+        // the fifth word shares its aligned 4 bytes with byte off+15, which is valid
+        uint32_t w4 = __ldcs(w + 4);
+        v.x = __funnelshift_r(w0, w1, sh);
+        v.y = __funnelshift_r(w1, w2, sh);
+        v.z = __funnelshift_r(w2, w3, sh);
+        v.w = __funnelshift_r(w3, w4, sh);
+        return v;
+    }
+    uint32_t w[4] = {0, 0, 0, 0};
+    const uint32_t left = (uint32_t)(n - off);
+    for (uint32_t i = 0; i < left; ++i) w[i >> 2] |= (uint32_t)q[i] << (8 * (i & 3));
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+__device__ __forceinline__ int64_t warp_sum_i64(int64_t v) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ uint64_t warp_xor_u64(uint64_t v) {
+    for (int o = 16; o > 0; o >>= 1) v ^= __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ uint32_t warp_sum_u32(uint32_t v) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+constexpr int kDigestThreads = 512;
+constexpr uint64_t kRowBytes = 4096;
+constexpr uint64_t kDigestTile = 64 * 1024;
+
+struct WarpAcc {
+    uint64_t row_sum = 0, row_sum_w = 0, tail_sum = 0, tail_sum_w = 0, ragged = 0, block = 0;
+    uint32_t safe = 0;
+    uint32_t span = 0xffffffffu;
+};
+
+__device__ __forceinline__ void flush(WarpAcc &a, DigestAcc *acc, uint32_t lane) {
+    if (a.span != 0xffffffffu && lane == 0) {
+        DigestAcc *o = acc + a.span;
+        if (a.row_sum) atomicAdd(&o->row_sum, (unsigned long long)a.row_sum);
+        if (a.row_sum_w) atomicAdd(&o->row_sum_w, (unsigned long long)a.row_sum_w);
+        if (a.tail_sum) atomicAdd(&o->tail_sum, (unsigned long long)a.tail_sum);
+        if (a.tail_sum_w) atomicAdd(&o->tail_sum_w, (unsigned long long)a.tail_sum_w);
+        if (a.ragged) atomicAdd(&o->ragged_sum, (unsigned long long)a.ragged);
+        if (a.block) atomicAdd(&o->block_hash, (unsigned long long)a.block);
+        if (a.safe) atomicAdd(&o->safe_checksum, a.safe);
+    }
+    a.row_sum = a.row_sum_w = a.tail_sum = a.tail_sum_w = a.ragged = a.block = 0;
+    a.safe = 0;
+}
+
+__global__ void __launch_bounds__(kDigestThreads)
+digest_kernel(const mxb_span *__restrict__ spans, const DTile *__restrict__ tiles,
+              uint64_t total_tiles, uint32_t modes, DigestAcc *__restrict__ acc,
+              unsigned long long *__restrict__ block_out) {
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    WarpAcc a;
+    for (uint64_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        const DTile tile = tiles[t];
+        if (tile.span != a.span) {
+            flush(a, acc, lane);
+            a.span = tile.span;
+        }
+        const mxb_span sp = spans[tile.span];
+        const unsigned char *p = reinterpret_cast<const unsigned char *>(sp.ptr);
+        const uint64_t n = sp.nbytes;
+        const bool aligned16 = ((sp.ptr & 15ull) == 0);
+        const uint64_t row = (uint64_t)tile.local * (kDigestTile / kRowBytes) + warp;
+        const uint64_t row_off = row * kRowBytes;
+        if (row_off >= n) continue;  // warp-uniform
+        const uint64_t whole_rows = (n / 4) / 1024;  // rows made only of whole words
+        const uint64_t body = n - (n % 4);
+
+        uint4 v[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) v[s] = load16(p, row_off + s * 512 + lane * 16, n, aligned16);
+
+        if (modes & MXB_DIGEST_SAFE32) {
+            uint32_t sum = 0;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                // bytes past n were loaded as zero and add nothing
+                const uint32_t i0 = (uint32_t)(row_off + s * 512 + lane * 16);
+                const uint32_t w[4] = {v[s].x, v[s].y, v[s].z, v[s].w};
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    const uint32_t wm = (i0 + 4u * m) * kKnuth + 1u;
+                    sum += wm * __dp4a(w[m], 0x01010101u, 0u) +
+                           kKnuth * __dp4a(w[m], 0x03020100u, 0u);
+                }
+            }
+            a.safe += warp_sum_u32(sum);
+        }
+
+        if (modes & MXB_DIGEST_ROWS) {
+            if (row < whole_rows) {
+                int64_t s64 = 0;
+#pragma unroll
+                for (int s = 0; s < 8; ++s)
+                    s64 += (int64_t)(int32_t)v[s].x + (int64_t)(int32_t)v[s].y +
+                           (int64_t)(int32_t)v[s].z + (int64_t)(int32_t)v[s].w;
+                const uint64_t rs = (uint64_t)warp_sum_i64(s64);
+                a.row_sum += rs;
+                a.row_sum_w += rs * (row + 1);
+            } else {
+                // the partial last row: whole words are the "tail", the rest is ragged bytes
+                int64_t ts = 0;
+                uint64_t tw = 0, rg = 0;
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    const uint64_t off = row_off + s * 512 + lane * 16;
+                    const uint32_t w[4] = {v[s].x, v[s].y, v[s].z, v[s].w};
+#pragma unroll
+                    for (int m = 0; m < 4; ++m) {
+                        const uint64_t wo = off + 4 * m;
+                        if (wo + 4 <= body) {
+                            const int64_t val = (int64_t)(int32_t)w[m];
+                            ts += val;
+                            tw += (uint64_t)val * ((wo - row_off) / 4 + 1);
+                        } else if (wo < n) {
+                            // zero-filled above n, so the byte sum is exact
+                            rg += __dp4a(w[m], 0x01010101u, 0u);
+                        }
+                    }
+                }
+                a.tail_sum += (uint64_t)warp_sum_i64(ts);
+                a.tail_sum_w += (uint64_t)warp_sum_i64((int64_t)tw);
+                a.ragged += (uint64_t)warp_sum_i64((int64_t)rg);
+            }
+        }
+
+        if (modes & MXB_DIGEST_BLOCK64) {
+            uint64_t h = kP5 + (uint64_t)lane * kP4;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                const uint64_t x0 = (uint64_t)v[s].x | ((uint64_t)v[s].y << 32);
+                const uint64_t x1 = (uint64_t)v[s].z | ((uint64_t)v[s].w << 32);
+                h = rotl64(h + x0 * kP2, 31) * kP1;
+                h = rotl64(h + x1 * kP2, 31) * kP1;
+            }
+            h = warp_xor_u64(rotl64(h * kP3, 2 * (int)lane + 1));
+            h = avalanche(h);
+            if (block_out && lane == 0) block_out[row] = h;
+            a.block += avalanche(h + (row + 1) * kP1);
+        }
+    }
+    flush(a, acc, lane);
+}
+
+}  // namespace mxb
+
+using namespace mxb;
+
+extern "C" {
+
+static int32_t run_digest(mxb_ctx *ctx, int32_t dev, const mxb_span *spans, uint64_t n,
+                          uint32_t modes, mxb_digest_out *out, uint64_t block_out) {
+    if (!ctx || (!spans && n) || (!out && n) || (modes & ~7u) || modes == 0) {
+        set_error("mxb_digest: bad arguments");
+        return MXB_ERR_ARG;
+    }
+    DeviceState *d = ctx->find(dev);
+    if (!d) {
+        set_error("device %d is not part of this context", dev);
+        return MXB_ERR_ARG;
+    }
+    if (n == 0) return MXB_OK;
+    if (n > 0xffffffffull) return MXB_ERR_ARG;
+    uint64_t total = 0;
+    for (uint64_t i = 0; i < n; ++i) {
+        if (spans[i].nbytes && !spans[i].ptr) {
+            set_error("span %llu has a null address", (unsigned long long)i);
+            return MXB_ERR_ARG;
+        }
+        total += (spans[i].nbytes + kDigestTile - 1) / kDigestTile;
+    }
+    DeviceGuard g(dev);
+    const size_t span_bytes = (n * sizeof(mxb_span) + 255) & ~size_t(255);
+    const size_t tile_bytes = (total * sizeof(DTile) + 255) & ~size_t(255);
+    int32_t rc = ensure_table(d, span_bytes + tile_bytes);
+    if (rc != MXB_OK) return rc;
+    rc = ensure_digest(d, n * sizeof(DigestAcc));
+    if (rc != MXB_OK) return rc;
+    MXB_CUDA(cudaStreamSynchronize(d->stream));
+    mxb_span *hs = reinterpret_cast<mxb_span *>(d->table_host);
+    DTile *ht = reinterpret_cast<DTile *>(reinterpret_cast<char *>(d->table_host) + span_bytes);
+    uint64_t ti = 0;
+    for (uint64_t i = 0; i < n; ++i) {
+        hs[i] = spans[i];
+        uint64_t t = (spans[i].nbytes + kDigestTile - 1) / kDigestTile;
+        if (t > 0xffffffffull) return MXB_ERR_ARG;
+        for (uint64_t k = 0; k < t; ++k) ht[ti++] = DTile{(uint32_t)i, (uint32_t)k};
+    }
+    MXB_CUDA(cudaMemcpyAsync(d->table, d->table_host, span_bytes + tile_bytes,
+                             cudaMemcpyHostToDevice, d->stream));
+    MXB_CUDA(cudaMemsetAsync(d->digest, 0, n * sizeof(DigestAcc), d->stream));
+    if (total) {
+        uint64_t grid = (uint64_t)d->sm_count * 4;
+        if (grid > total) grid = total;
+        digest_kernel<<<(unsigned)grid, kDigestThreads, 0, d->stream>>>(
+            reinterpret_cast<const mxb_span *>(d->table),
+            reinterpret_cast<const DTile *>(reinterpret_cast<char *>(d->table) + span_bytes), total,
+            modes, reinterpret_cast<DigestAcc *>(d->digest),
+            reinterpret_cast<unsigned long long *>(block_out));
+        MXB_CUDA(cudaGetLastError());
+        ctx->launches.fetch_add(1);
+    }
+    MXB_CUDA(cudaMemcpyAsync(d->digest_host, d->digest, n * sizeof(DigestAcc),
+                             cudaMemcpyDeviceToHost, d->stream));
+    MXB_CUDA(cudaStreamSynchronize(d->stream));
+    const DigestAcc *res = reinterpret_cast<const DigestAcc *>(d->digest_host);
+    for (uint64_t i = 0; i < n; ++i) {
+        memcpy(&out[i], &res[i], sizeof(mxb_digest_out));
+        out[i].nbytes = spans[i].nbytes;
+        if (modes & MXB_DIGEST_BLOCK64) {
+            // the length term keeps zero padding from aliasing shorter inputs
+            uint64_t h = spans[i].nbytes * 0x27D4EB2F165667C5ull;
+            h ^= h >> 33;
+            h *= 0xC2B2AE3D27D4EB4Full;
+            h ^= h >> 29;
+            h *= 0x165667B19E3779F9ull;
+            h ^= h >> 32;
+            out[i].block_hash += h;
+        }
+    }
+    return MXB_OK;
+}
+
+int32_t mxb_digest(mxb_ctx *ctx, int32_t dev, const mxb_span *spans, uint64_t n, uint32_t modes,
+                   mxb_digest_out *out) {
+    return run_digest(ctx, dev, spans, n, modes, out, 0);
+}
+
+int32_t mxb_block_hashes(mxb_ctx *ctx, int32_t dev, uint64_t ptr, uint64_t nbytes,
+                         uint64_t out_blocks) {
+    if (!ptr || !out_blocks) return MXB_ERR_ARG;
+    mxb_span sp{ptr, nbytes};
+    mxb_digest_out o;
+    return run_digest(ctx, dev, &sp, 1, MXB_DIGEST_BLOCK64, &o, out_blocks);
+}
+
+}  // extern "C"

@@ -1,0 +1,312 @@
+// Kernel 2: serving-peer fan-out over NVLink (sm_100a).
+//
+// Every GPU of the broadcast runs one persistent launch of the same kernel on
+// its own device.  The payload (a list of byte ranges, identical in size on
+// every GPU) is cut into pieces of at most 64 KiB that never cross a chunk or a
+// range boundary.  CTA b owns pieces b, b+grid, ...  For each piece it
+//   1. waits (bounded) until this GPU's arrival counter of the piece's chunk
+//      shows that the parent delivered the whole chunk (the root skips this),
+//   2. stores the piece from local HBM into every child's range with 16-byte
+//      P2P stores,
+//   3. after a CTA barrier and a system-scope fence, raises the child's counter
+//      for that chunk by one (release, system scope).
+// A chunk is complete on a GPU when its counter reached run_index * (pieces in
+// the chunk); counters only grow, so repeated broadcasts need no reset.  Leaves
+// run the same kernel with no children: it returns once every chunk arrived.
+// No wait is unbounded: when the time budget runs out the kernel records
+// DEV_TIMEOUT in its status word and returns.
+#include "common.cuh"
+
+namespace mxb {
+
+struct FanPiece {
+    uint64_t local;   // address in this GPU's copy
+    uint32_t nbytes;  // <= 64 KiB
+    uint32_t chunk;
+};
+
+constexpr int kFanThreads = 512;
+constexpr uint32_t kFanPiece = 64 * 1024;
+
+struct FanArgs {
+    const FanPiece *pieces;
+    const uint64_t *child_ptr;        // [children][n_pieces] destination of each piece
+    const uint32_t *chunk_pieces;     // pieces per chunk
+    uint32_t *counters;               // this GPU's arrival counters, one per chunk
+    uint64_t child_counters[MXB_FANOUT_MAX_CHILDREN];
+    uint64_t n_pieces;
+    uint32_t n_children;
+    uint32_t is_root;
+    uint32_t run_index;  // 1-based
+    uint64_t timeout_ns;
+    uint32_t *status;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_sys_add(uint32_t *p, uint32_t v) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__global__ void __launch_bounds__(kFanThreads) fanout_kernel(FanArgs a) {
+    __shared__ uint32_t s_abort;
+    const uint32_t tid = threadIdx.x;
+    if (tid == 0) s_abort = 0;
+    __syncthreads();
+    for (uint64_t p = blockIdx.x; p < a.n_pieces; p += gridDim.x) {
+        const FanPiece pc = a.pieces[p];
+        if (!a.is_root) {
+            if (tid == 0) {
+                const uint32_t want = a.run_index * a.chunk_pieces[pc.chunk];
+                const uint32_t *ctr = a.counters + pc.chunk;
+                const uint64_t t0 = globaltimer_ns();
+                uint32_t spins = 0;
+                // counters grow monotonically and may wrap: compare as a signed distance
+                while ((int32_t)(ld_acquire_sys(ctr) - want) < 0) {
+                    if ((++spins & 63u) == 0) {
+                        if (globaltimer_ns() - t0 > a.timeout_ns) {
+                            s_abort = 1;
+                            atomicExch(a.status, DEV_TIMEOUT);
+                            break;
+                        }
+                        __nanosleep(200);
+                    }
+                }
+            }
+            __syncthreads();
+            if (s_abort) return;
+        }
+        const uint4 *src = reinterpret_cast<const uint4 *>(pc.local);
+        const uint32_t nvec = pc.nbytes >> 4;
+        for (uint32_t c = 0; c < a.n_children; ++c) {
+            uint4 *dst = reinterpret_cast<uint4 *>(a.child_ptr[(uint64_t)c * a.n_pieces + p]);
+            uint32_t i = tid;
+            for (; i + 3 * kFanThreads < nvec; i += 4 * kFanThreads) {
+                uint4 v0 = src[i], v1 = src[i + kFanThreads], v2 = src[i + 2 * kFanThreads],
+                      v3 = src[i + 3 * kFanThreads];
+                dst[i] = v0;
+                dst[i + kFanThreads] = v1;
+                dst[i + 2 * kFanThreads] = v2;
+                dst[i + 3 * kFanThreads] = v3;
+            }
+            for (; i < nvec; i += kFanThreads) dst[i] = src[i];
+            // ranges need not be multiples of 16 bytes
+            const unsigned char *sb = reinterpret_cast<const unsigned char *>(pc.local);
+            unsigned char *db = reinterpret_cast<unsigned char *>(dst);
+            for (uint32_t j = (nvec << 4) + tid; j < pc.nbytes; j += kFanThreads) db[j] = sb[j];
+        }
+        if (a.n_children) {
+            __syncthreads();
+            if (tid == 0) {
+                __threadfence_system();
+                for (uint32_t c = 0; c < a.n_children; ++c)
+                    red_release_sys_add(reinterpret_cast<uint32_t *>(a.child_counters[c]) + pc.chunk,
+                                        1u);
+            }
+        }
+    }
+}
+
+}  // namespace mxb
+
+using namespace mxb;
+
+struct mxb_fanout {
+    mxb_ctx *ctx = nullptr;
+    DeviceState *dv = nullptr;
+    std::vector<mxb_span> local;
+    uint64_t chunk_bytes = 0;
+    std::vector<FanPiece> pieces;
+    std::vector<uint64_t> piece_range, piece_off;  // provenance of each piece
+    std::vector<uint32_t> chunk_pieces;
+    std::vector<uint64_t> child_ptr[MXB_FANOUT_MAX_CHILDREN];
+    uint64_t child_counters[MXB_FANOUT_MAX_CHILDREN] = {};
+    uint32_t n_children = 0;
+    uint32_t *counters = nullptr;  // device
+    void *dev_tables = nullptr;
+    size_t dev_tables_bytes = 0;
+    bool dirty = true;
+    uint32_t run_index = 0;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+};
+
+extern "C" {
+
+int32_t mxb_fanout_create(mxb_ctx *ctx, int32_t dev, const mxb_span *local, uint64_t n,
+                          uint64_t chunk_bytes, mxb_fanout **out) {
+    if (!ctx || !local || !n || !out || chunk_bytes < 4096 || (chunk_bytes & 15u)) {
+        set_error("mxb_fanout_create: bad arguments (chunk must be a multiple of 16, >= 4096)");
+        return MXB_ERR_ARG;
+    }
+    DeviceState *dv = ctx->find(dev);
+    if (!dv) {
+        set_error("device %d is not part of this context", dev);
+        return MXB_ERR_ARG;
+    }
+    for (uint64_t i = 0; i < n; ++i)
+        if (local[i].nbytes && ((local[i].ptr & 15u) || !local[i].ptr)) {
+            set_error("range %llu: address must be non-null and 16-byte aligned",
+                      (unsigned long long)i);
+            return MXB_ERR_ALIGN;
+        }
+    mxb_fanout *f = new mxb_fanout();
+    f->ctx = ctx;
+    f->dv = dv;
+    f->local.assign(local, local + n);
+    f->chunk_bytes = chunk_bytes;
+    // pieces: walk the concatenated byte space; cut at range ends, chunk ends, 64 KiB
+    uint64_t vpos = 0;
+    for (uint64_t i = 0; i < n; ++i) {
+        uint64_t off = 0;
+        while (off < local[i].nbytes) {
+            uint64_t chunk = vpos / chunk_bytes;
+            uint64_t to_chunk_end = (chunk + 1) * chunk_bytes - vpos;
+            uint64_t len = local[i].nbytes - off;
+            if (len > to_chunk_end) len = to_chunk_end;
+            if (len > kFanPiece) len = kFanPiece;
+            // keep every piece start 16-byte aligned: only a range's last piece may be ragged
+            if (len < local[i].nbytes - off) len &= ~uint64_t(15);
+            if (len == 0) len = local[i].nbytes - off < 16 ? local[i].nbytes - off : 16;
+            f->pieces.push_back({local[i].ptr + off, (uint32_t)len, (uint32_t)chunk});
+            f->piece_range.push_back(i);
+            f->piece_off.push_back(off);
+            if (f->chunk_pieces.size() <= chunk) f->chunk_pieces.resize(chunk + 1, 0);
+            f->chunk_pieces[chunk] += 1;
+            off += len;
+            vpos += len;
+        }
+    }
+    DeviceGuard g(dev);
+    const size_t nchunks = f->chunk_pieces.size() ? f->chunk_pieces.size() : 1;
+    if (cudaMalloc((void **)&f->counters, nchunks * sizeof(uint32_t)) != cudaSuccess ||
+        cudaMemset(f->counters, 0, nchunks * sizeof(uint32_t)) != cudaSuccess ||
+        cudaEventCreate(&f->ev0) != cudaSuccess || cudaEventCreate(&f->ev1) != cudaSuccess ||
+        cudaDeviceSynchronize() != cudaSuccess) {
+        set_error("mxb_fanout_create: CUDA allocation failed: %s",
+                  cudaGetErrorString(cudaGetLastError()));
+        mxb_fanout_destroy(f);
+        return MXB_ERR_CUDA;
+    }
+    *out = f;
+    return MXB_OK;
+}
+
+uint64_t mxb_fanout_counters(mxb_fanout *f) { return f ? (uint64_t)(uintptr_t)f->counters : 0; }
+
+int32_t mxb_fanout_set_child(mxb_fanout *f, int32_t k, const mxb_span *child, uint64_t n,
+                             uint64_t child_counters) {
+    if (!f || k < 0 || k >= MXB_FANOUT_MAX_CHILDREN || !child || !child_counters ||
+        n != f->local.size()) {
+        set_error("mxb_fanout_set_child: bad arguments");
+        return MXB_ERR_ARG;
+    }
+    if ((uint32_t)k > f->n_children) {
+        set_error("mxb_fanout_set_child: children must be set in order");
+        return MXB_ERR_STATE;
+    }
+    for (uint64_t i = 0; i < n; ++i) {
+        if (child[i].nbytes != f->local[i].nbytes) {
+            set_error("child range %llu: size %llu differs from the local size %llu",
+                      (unsigned long long)i, (unsigned long long)child[i].nbytes,
+                      (unsigned long long)f->local[i].nbytes);
+            return MXB_ERR_ARG;
+        }
+        if (child[i].nbytes && (child[i].ptr & 15u)) return MXB_ERR_ALIGN;
+    }
+    std::vector<uint64_t> &cp = f->child_ptr[k];
+    cp.resize(f->pieces.size());
+    for (size_t p = 0; p < f->pieces.size(); ++p)
+        cp[p] = child[f->piece_range[p]].ptr + f->piece_off[p];
+    f->child_counters[k] = child_counters;
+    if ((uint32_t)k == f->n_children) f->n_children = k + 1;
+    f->dirty = true;
+    return MXB_OK;
+}
+
+int32_t mxb_fanout_run(mxb_fanout *f, int32_t is_root, uint32_t timeout_ms) {
+    if (!f) return MXB_ERR_ARG;
+    DeviceState *dv = f->dv;
+    DeviceGuard g(dv->device);
+    const size_t np = f->pieces.size();
+    const size_t b_pieces = (np * sizeof(FanPiece) + 255) & ~size_t(255);
+    const size_t b_child = (np * sizeof(uint64_t) * (f->n_children ? f->n_children : 1) + 255) &
+                           ~size_t(255);
+    const size_t b_chunk = (f->chunk_pieces.size() * sizeof(uint32_t) + 255) & ~size_t(255);
+    if (f->dirty) {
+        const size_t total = b_pieces + b_child + b_chunk;
+        if (total > f->dev_tables_bytes) {
+            if (f->dev_tables) cudaFree(f->dev_tables);
+            f->dev_tables = nullptr;
+            MXB_CUDA(cudaMalloc(&f->dev_tables, total));
+            f->dev_tables_bytes = total;
+        }
+        char *base = reinterpret_cast<char *>(f->dev_tables);
+        MXB_CUDA(cudaMemcpy(base, f->pieces.data(), np * sizeof(FanPiece), cudaMemcpyHostToDevice));
+        for (uint32_t c = 0; c < f->n_children; ++c)
+            MXB_CUDA(cudaMemcpy(base + b_pieces + (size_t)c * np * sizeof(uint64_t),
+                                f->child_ptr[c].data(), np * sizeof(uint64_t),
+                                cudaMemcpyHostToDevice));
+        MXB_CUDA(cudaMemcpy(base + b_pieces + b_child, f->chunk_pieces.data(),
+                            f->chunk_pieces.size() * sizeof(uint32_t), cudaMemcpyHostToDevice));
+        f->dirty = false;
+    }
+    char *base = reinterpret_cast<char *>(f->dev_tables);
+    FanArgs a;
+    memset(&a, 0, sizeof a);
+    a.pieces = reinterpret_cast<const FanPiece *>(base);
+    a.child_ptr = reinterpret_cast<const uint64_t *>(base + b_pieces);
+    a.chunk_pieces = reinterpret_cast<const uint32_t *>(base + b_pieces + b_child);
+    a.counters = f->counters;
+    for (uint32_t c = 0; c < f->n_children; ++c) a.child_counters[c] = f->child_counters[c];
+    a.n_pieces = np;
+    a.n_children = f->n_children;
+    a.is_root = is_root ? 1u : 0u;
+    a.run_index = ++f->run_index;
+    a.timeout_ns = (uint64_t)(timeout_ms ? timeout_ms : 1000u) * 1000000ull;
+    a.status = dv->status;
+    if (np == 0) return MXB_OK;
+    // all CTAs must be co-resident: they wait on data, never on each other, but a
+    // CTA that is not scheduled cannot forward its pieces
+    uint64_t grid = (uint64_t)dv->sm_count * 2;
+    if (grid > np) grid = np;
+    MXB_CUDA(cudaEventRecord(f->ev0, dv->stream));
+    fanout_kernel<<<(unsigned)grid, kFanThreads, 0, dv->stream>>>(a);
+    MXB_CUDA(cudaGetLastError());
+    MXB_CUDA(cudaEventRecord(f->ev1, dv->stream));
+    f->ctx->launches.fetch_add(1);
+    return MXB_OK;
+}
+
+int32_t mxb_fanout_wait(mxb_fanout *f, float *device_ms) {
+    if (!f) return MXB_ERR_ARG;
+    DeviceGuard g(f->dv->device);
+    int32_t rc = check_status(f->dv);
+    if (device_ms && f->run_index) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, f->ev0, f->ev1) == cudaSuccess) *device_ms = ms;
+        else cudaGetLastError();
+    }
+    return rc;
+}
+
+int32_t mxb_fanout_destroy(mxb_fanout *f) {
+    if (!f) return MXB_OK;
+    DeviceGuard g(f->dv->device);
+    cudaStreamSynchronize(f->dv->stream);
+    if (f->counters) cudaFree(f->counters);
+    if (f->dev_tables) cudaFree(f->dev_tables);
+    if (f->ev0) cudaEventDestroy(f->ev0);
+    if (f->ev1) cudaEventDestroy(f->ev1);
+    delete f;
+    return MXB_OK;
+}
+
+}  // extern "C"

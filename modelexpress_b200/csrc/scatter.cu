@@ -1,0 +1,438 @@
+// Kernel 1/3: descriptor-driven scatter (sm_100a).
+//
+// One persistent launch walks a device-resident table of 2-D byte slices
+// (mxb_desc2d) cut into tiles of at most 64 KiB.  Sources and destinations may
+// be local HBM, a peer GPU's HBM (NVLink P2P loads / stores) or pinned host
+// memory (PCIe reads), so the same kernel serves the staging-ring placement,
+// the warm install and the refit reshard.
+//
+// Two tile engines:
+//   * vector engine - 512 threads, 16-byte loads/stores unrolled 4 deep, with
+//     head/tail handling and narrower vectors when src and dst disagree mod 16;
+//   * bulk engine   - one warp per CTA drives cp.async.bulk (TMA, non-tensor)
+//     global->shared->global through a 3-stage 64 KiB ring, for tables whose
+//     addresses, pitches and row sizes are all multiples of 16.
+#include "common.cuh"
+
+namespace mxb {
+
+struct Tile {
+    uint32_t desc;   // index into the descriptor table
+    uint32_t local;  // tile number inside that descriptor
+};
+
+// ---------------------------------------------------------------------------
+// vector engine
+// ---------------------------------------------------------------------------
+
+template <typename V>
+__device__ __forceinline__ V ld_stream(const V *p) {
+    return __ldcs(p);
+}
+template <typename V>
+__device__ __forceinline__ void st_stream(V *p, V v) {
+    __stcs(p, v);
+}
+
+// Copy n elements of vector type V with T cooperating threads, 4 loads in flight.
+template <typename V>
+__device__ __forceinline__ void copy_vec(V *__restrict__ d, const V *__restrict__ s, uint64_t n,
+                                         uint32_t t, uint32_t T) {
+    uint64_t i = t;
+    for (; i + 3ull * T < n; i += 4ull * T) {
+        V a = ld_stream(s + i);
+        V b = ld_stream(s + i + T);
+        V c = ld_stream(s + i + 2ull * T);
+        V e = ld_stream(s + i + 3ull * T);
+        st_stream(d + i, a);
+        st_stream(d + i + T, b);
+        st_stream(d + i + 2ull * T, c);
+        st_stream(d + i + 3ull * T, e);
+    }
+    for (; i < n; i += T) st_stream(d + i, ld_stream(s + i));
+}
+
+template <typename V>
+__device__ __forceinline__ void copy_span_w(char *d, const char *s, uint64_t n, uint32_t t,
+                                            uint32_t T) {
+    constexpr uint64_t W = sizeof(V);
+    // bytes until the destination reaches a W boundary (src then agrees, since
+    // the caller chose W as the largest power of two dividing src^dst)
+    uint64_t head = (W - ((uint64_t)(uintptr_t)d & (W - 1))) & (W - 1);
+    if (head > n) head = n;
+    for (uint64_t i = t; i < head; i += T) d[i] = s[i];
+    d += head;
+    s += head;
+    n -= head;
+    uint64_t nv = n / W;
+    copy_vec<V>(reinterpret_cast<V *>(d), reinterpret_cast<const V *>(s), nv, t, T);
+    uint64_t done = nv * W;
+    for (uint64_t i = done + t; i < n; i += T) d[i] = s[i];
+}
+
+// Copy an arbitrary byte span with T threads (t = this thread's index).
+__device__ __forceinline__ void copy_span(char *d, const char *s, uint64_t n, uint32_t t,
+                                          uint32_t T) {
+    uint32_t mis = (uint32_t)(((uint64_t)(uintptr_t)d ^ (uint64_t)(uintptr_t)s) & 15u);
+    if (mis == 0)
+        copy_span_w<uint4>(d, s, n, t, T);
+    else if ((mis & 7u) == 0)
+        copy_span_w<uint2>(d, s, n, t, T);
+    else if ((mis & 3u) == 0)
+        copy_span_w<uint32_t>(d, s, n, t, T);
+    else if ((mis & 1u) == 0)
+        copy_span_w<uint16_t>(d, s, n, t, T);
+    else
+        for (uint64_t i = t; i < n; i += T) d[i] = s[i];
+}
+
+constexpr int kVecThreads = 512;
+constexpr uint64_t kWarpRowMax = 8192;  // rows up to this size are copied one warp per row
+
+__global__ void __launch_bounds__(kVecThreads)
+scatter_vec_kernel(const mxb_desc2d *__restrict__ descs, const Tile *__restrict__ tiles,
+                   uint64_t total_tiles) {
+    const uint32_t tid = threadIdx.x;
+    const uint32_t lane = tid & 31u, warp = tid >> 5, nwarps = kVecThreads / 32;
+    for (uint64_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        const Tile tile = tiles[t];
+        const mxb_desc2d d = descs[tile.desc];
+        char *dst = reinterpret_cast<char *>(d.dst);
+        const char *src = reinterpret_cast<const char *>(d.src);
+        if (d.row_bytes >= kTileBytes) {
+            // a piece of one long row
+            const uint64_t per_row = (d.row_bytes + kTileBytes - 1) / kTileBytes;
+            const uint64_t row = tile.local / per_row, piece = tile.local % per_row;
+            const uint64_t off = piece * kTileBytes;
+            const uint64_t len = d.row_bytes - off < kTileBytes ? d.row_bytes - off : kTileBytes;
+            copy_span(dst + row * d.dst_pitch + off, src + row * d.src_pitch + off, len, tid,
+                      kVecThreads);
+        } else {
+            const uint64_t rows_per_tile = kTileBytes / d.row_bytes;
+            const uint64_t r0 = (uint64_t)tile.local * rows_per_tile;
+            const uint64_t r1 = d.rows < r0 + rows_per_tile ? d.rows : r0 + rows_per_tile;
+            if (d.src_pitch == d.row_bytes && d.dst_pitch == d.row_bytes) {
+                // rows are back to back on both sides: one flat span
+                copy_span(dst + r0 * d.row_bytes, src + r0 * d.row_bytes, (r1 - r0) * d.row_bytes,
+                          tid, kVecThreads);
+            } else if (d.row_bytes <= kWarpRowMax) {
+                for (uint64_t r = r0 + warp; r < r1; r += nwarps)
+                    copy_span(dst + r * d.dst_pitch, src + r * d.src_pitch, d.row_bytes, lane, 32);
+            } else {
+                for (uint64_t r = r0; r < r1; ++r)
+                    copy_span(dst + r * d.dst_pitch, src + r * d.src_pitch, d.row_bytes, tid,
+                              kVecThreads);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// bulk engine (cp.async.bulk through shared memory)
+// ---------------------------------------------------------------------------
+
+constexpr int kBulkStages = 3;
+constexpr uint32_t kBulkSpin = 1u << 24;  // bounded mbarrier wait (iterations)
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void bulk_g2s(void *smem_dst, const void *gsrc, uint32_t bytes,
+                                         uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(smem_dst)),
+        "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void *gdst, const void *smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst),
+                 "r"(smem_u32(smem_src)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_all() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ uint64_t umin64(uint64_t a, uint64_t b) { return a < b ? a : b; }
+
+struct TileGeom {
+    const char *src;
+    char *dst;
+    uint64_t rows, row_bytes, src_pitch, dst_pitch;  // rows*row_bytes <= 64 KiB
+};
+
+__device__ __forceinline__ TileGeom tile_geom(const mxb_desc2d &d, uint32_t local) {
+    TileGeom g;
+    if (d.row_bytes >= kTileBytes) {
+        const uint64_t per_row = (d.row_bytes + kTileBytes - 1) / kTileBytes;
+        const uint64_t row = local / per_row, off = (local % per_row) * kTileBytes;
+        g.src = reinterpret_cast<const char *>(d.src) + row * d.src_pitch + off;
+        g.dst = reinterpret_cast<char *>(d.dst) + row * d.dst_pitch + off;
+        g.rows = 1;
+        g.row_bytes = umin64(kTileBytes, d.row_bytes - off);
+        g.src_pitch = g.dst_pitch = g.row_bytes;
+    } else {
+        const uint64_t rows_per_tile = kTileBytes / d.row_bytes;
+        const uint64_t r0 = (uint64_t)local * rows_per_tile;
+        g.rows = umin64(d.rows, r0 + rows_per_tile) - r0;
+        g.row_bytes = d.row_bytes;
+        g.src_pitch = d.src_pitch;
+        g.dst_pitch = d.dst_pitch;
+        g.src = reinterpret_cast<const char *>(d.src) + r0 * d.src_pitch;
+        g.dst = reinterpret_cast<char *>(d.dst) + r0 * d.dst_pitch;
+        if (g.src_pitch == g.row_bytes && g.dst_pitch == g.row_bytes) {
+            g.row_bytes *= g.rows;
+            g.rows = 1;
+            g.src_pitch = g.dst_pitch = g.row_bytes;
+        }
+    }
+    return g;
+}
+
+// One warp per CTA.  Lanes share the per-row copy issue; lane 0 owns the
+// barriers.  Every wait is bounded: when one runs out the kernel records
+// DEV_TIMEOUT, drains its own copies with a bounded wait and returns.
+__global__ void __launch_bounds__(32)
+scatter_bulk_kernel(const mxb_desc2d *__restrict__ descs, const Tile *__restrict__ tiles,
+                    uint64_t total_tiles, uint32_t *status) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ __align__(8) uint64_t bars[kBulkStages];
+    const uint32_t lane = threadIdx.x;
+    if (lane == 0) {
+        for (int s = 0; s < kBulkStages; ++s) mbar_init(&bars[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+
+    // my tiles: blockIdx.x, +gridDim.x, ...
+    const uint64_t first = blockIdx.x;
+    if (first >= total_tiles) return;
+    const uint64_t mine = (total_tiles - first + gridDim.x - 1) / gridDim.x;
+
+    auto issue_load = [&](uint64_t k) {
+        const Tile tile = tiles[first + k * gridDim.x];
+        const TileGeom g = tile_geom(descs[tile.desc], tile.local);
+        const int s = (int)(k % kBulkStages);
+        unsigned char *buf = smem + (size_t)s * kTileBytes;
+        if (lane == 0) mbar_expect_tx(&bars[s], (uint32_t)(g.rows * g.row_bytes));
+        __syncwarp();
+        for (uint64_t r = lane; r < g.rows; r += 32)
+            bulk_g2s(buf + r * g.row_bytes, g.src + r * g.src_pitch, (uint32_t)g.row_bytes,
+                     &bars[s]);
+    };
+
+    // Bounded, warp-uniform wait for the load of tile k to land.
+    auto wait_tile = [&](uint64_t k, uint32_t limit) -> bool {
+        const int s = (int)(k % kBulkStages);
+        const uint32_t parity = (uint32_t)((k / kBulkStages) & 1);
+        for (uint32_t spins = 0; spins < limit; ++spins)
+            if (__all_sync(0xffffffffu, mbar_try_wait(&bars[s], parity))) return true;
+        return false;
+    };
+
+    bool failed = false;
+    uint64_t k = 0, issued = 1;
+    issue_load(0);
+    for (; k < mine; ++k) {
+        const int s = (int)(k % kBulkStages);
+        if (k + 1 < mine) {
+            // stage (k+1)%3 last held tile k-2: its stores must have read smem
+            bulk_wait_read<1>();
+            __syncwarp();
+            issue_load(k + 1);
+            issued = k + 2;
+        }
+        if (!wait_tile(k, kBulkSpin)) {
+            failed = true;
+            break;
+        }
+        const Tile tile = tiles[first + k * gridDim.x];
+        const TileGeom g = tile_geom(descs[tile.desc], tile.local);
+        unsigned char *buf = smem + (size_t)s * kTileBytes;
+        for (uint64_t r = lane; r < g.rows; r += 32)
+            bulk_s2g(g.dst + r * g.dst_pitch, buf + r * g.row_bytes, (uint32_t)g.row_bytes);
+        bulk_commit();
+    }
+    bulk_wait_all<0>();
+    if (failed) {
+        if (lane == 0) atomicExch(status, DEV_TIMEOUT);
+        // give the loads still in flight a bounded time to land before the
+        // shared memory they target is released
+        for (uint64_t j = k; j < issued; ++j) wait_tile(j, 1u << 16);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// launcher
+// ---------------------------------------------------------------------------
+
+static bool all_bulk_ok(const mxb_desc2d *d, uint64_t n) {
+    for (uint64_t i = 0; i < n; ++i) {
+        if (d[i].rows == 0 || d[i].row_bytes == 0) continue;
+        if ((d[i].src | d[i].dst | d[i].row_bytes) & 15u) return false;
+        if (d[i].rows > 1 && ((d[i].src_pitch | d[i].dst_pitch) & 15u)) return false;
+        // the bulk engine issues one copy per row; short rows are better served
+        // by the vector engine
+        if (d[i].row_bytes < 1024) return false;
+    }
+    return true;
+}
+
+size_t scatter_table_bytes(const mxb_desc2d *descs, uint64_t n, uint64_t *live_out,
+                           uint64_t *tiles_out) {
+    uint64_t live = 0, total = 0;
+    for (uint64_t i = 0; i < n; ++i) {
+        uint64_t t = tiles_of(descs[i]);
+        if (t) {
+            ++live;
+            total += t;
+        }
+    }
+    if (live_out) *live_out = live;
+    if (tiles_out) *tiles_out = total;
+    return ((live * sizeof(mxb_desc2d) + 255) & ~size_t(255)) + total * sizeof(Tile);
+}
+
+int32_t build_scatter_table(const mxb_desc2d *descs, uint64_t n, void *host_buf, void *dev_buf,
+                            ScatterTable *out, uint64_t *tile_begin_of_desc) {
+    uint64_t live = 0, total = 0;
+    scatter_table_bytes(descs, n, &live, &total);
+    if (live > 0xffffffffull) {
+        set_error("too many descriptors (%llu)", (unsigned long long)live);
+        return MXB_ERR_ARG;
+    }
+    const size_t desc_bytes = (live * sizeof(mxb_desc2d) + 255) & ~size_t(255);
+    mxb_desc2d *hd = reinterpret_cast<mxb_desc2d *>(host_buf);
+    Tile *ht = reinterpret_cast<Tile *>(reinterpret_cast<char *>(host_buf) + desc_bytes);
+    uint64_t di = 0, ti = 0;
+    for (uint64_t i = 0; i < n; ++i) {
+        if (tile_begin_of_desc) tile_begin_of_desc[i] = ti;
+        uint64_t t = tiles_of(descs[i]);
+        if (!t) continue;
+        if (t > 0xffffffffull) {
+            set_error("descriptor %llu has too many tiles", (unsigned long long)i);
+            return MXB_ERR_ARG;
+        }
+        hd[di] = descs[i];
+        for (uint64_t k = 0; k < t; ++k) ht[ti++] = Tile{(uint32_t)di, (uint32_t)k};
+        ++di;
+    }
+    if (tile_begin_of_desc) tile_begin_of_desc[n] = ti;
+    out->descs = reinterpret_cast<const mxb_desc2d *>(dev_buf);
+    out->tiles = reinterpret_cast<const char *>(dev_buf) + desc_bytes;
+    out->total_tiles = total;
+    out->bytes = desc_bytes + total * sizeof(Tile);
+    out->bulk_ok = all_bulk_ok(hd, live);
+    return MXB_OK;
+}
+
+int32_t launch_scatter_tiles(mxb_ctx *ctx, DeviceState *dv, const ScatterTable &tb,
+                             uint64_t tile_begin, uint64_t tile_count, uint32_t flags,
+                             cudaStream_t stream) {
+    if (tile_count == 0) return MXB_OK;
+    const Tile *dt = reinterpret_cast<const Tile *>(tb.tiles) + tile_begin;
+    const bool bulk = (flags & MXB_SCATTER_BULK) && tb.bulk_ok;
+    if (bulk) {
+        static bool attr_set[64] = {};
+        const size_t smem = (size_t)kBulkStages * kTileBytes;
+        if (dv->device < 64 && !attr_set[dv->device]) {
+            MXB_CUDA(cudaFuncSetAttribute(scatter_bulk_kernel,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr_set[dv->device] = true;
+        }
+        uint64_t grid = (uint64_t)dv->sm_count;
+        if (grid > tile_count) grid = tile_count;
+        scatter_bulk_kernel<<<(unsigned)grid, 32, smem, stream>>>(tb.descs, dt, tile_count,
+                                                                   dv->status);
+    } else {
+        uint64_t grid = (uint64_t)dv->sm_count * 4;
+        if (grid > tile_count) grid = tile_count;
+        scatter_vec_kernel<<<(unsigned)grid, kVecThreads, 0, stream>>>(tb.descs, dt, tile_count);
+    }
+    MXB_CUDA(cudaGetLastError());
+    ctx->launches.fetch_add(1);
+    return MXB_OK;
+}
+
+int32_t launch_scatter(mxb_ctx *ctx, DeviceState *dv, const mxb_desc2d *descs, uint64_t n,
+                       uint32_t flags, cudaStream_t stream) {
+    uint64_t total = 0;
+    const size_t bytes = scatter_table_bytes(descs, n, nullptr, &total);
+    if (total == 0) return MXB_OK;
+    int32_t rc = ensure_table(dv, bytes);
+    if (rc != MXB_OK) return rc;
+    // the pinned staging copy is reused by every call: wait for the previous upload
+    MXB_CUDA(cudaStreamSynchronize(stream));
+    ScatterTable tb;
+    rc = build_scatter_table(descs, n, dv->table_host, dv->table, &tb, nullptr);
+    if (rc != MXB_OK) return rc;
+    MXB_CUDA(cudaMemcpyAsync(dv->table, dv->table_host, tb.bytes, cudaMemcpyHostToDevice, stream));
+    return launch_scatter_tiles(ctx, dv, tb, 0, tb.total_tiles, flags, stream);
+}
+
+}  // namespace mxb
+
+using namespace mxb;
+
+extern "C" {
+
+int32_t mxb_scatter(mxb_ctx *ctx, int32_t dev, const mxb_desc2d *descs, uint64_t n,
+                    uint32_t flags) {
+    if (!ctx || (!descs && n)) {
+        set_error("mxb_scatter: bad arguments");
+        return MXB_ERR_ARG;
+    }
+    DeviceState *d = ctx->find(dev);
+    if (!d) {
+        set_error("device %d is not part of this context", dev);
+        return MXB_ERR_ARG;
+    }
+    int32_t rc = validate_descs(ctx, descs, n);
+    if (rc != MXB_OK) return rc;
+    DeviceGuard g(dev);
+    rc = launch_scatter(ctx, d, descs, n, flags, d->stream);
+    if (rc != MXB_OK) return rc;
+    if (flags & MXB_SCATTER_NO_SYNC) return MXB_OK;
+    return check_status(d);
+}
+
+int32_t mxb_read_runs(mxb_ctx *ctx, int32_t dev, const mxb_run *runs, uint64_t n) {
+    if (!ctx || (!runs && n)) {
+        set_error("mxb_read_runs: bad arguments");
+        return MXB_ERR_ARG;
+    }
+    std::vector<mxb_desc2d> descs(n ? n : 1);
+    int64_t m = mxb_coalesce_runs(runs, n, descs.data(), descs.size());
+    if (m < 0) return MXB_ERR_ARG;
+    return mxb_scatter(ctx, dev, descs.data(), (uint64_t)m, MXB_SCATTER_DEFAULT);
+}
+
+}  // extern "C"

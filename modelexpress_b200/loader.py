@@ -1,0 +1,207 @@
+"""Checkpoint placement: safetensors files -> this rank's GPU parameters.
+
+``place_checkpoint`` is the B200 replacement for the host-staged load the
+reference reaches through engines/vllm/adapter.py:316-329: instead of one CPU
+``narrow`` and one pageable H2D ``copy_`` per tensor, the rank's slices are
+described once (``layout.plan_checkpoint``), gathered into a pinned ring by host
+threads, sent over PCIe on the copy-engine stream and written into the shards
+by one persistent scatter launch per ring chunk.
+
+``B200ScatterStrategy`` packages that as a load strategy with the reference's
+plugin contract (load_strategy/base.py:37-76): ``name``, ``requires``,
+``is_available(ctx)``, ``load(result, ctx) -> LoadResult``, ``rollback(ctx)``;
+an expected miss raises ``StrategyFailed(mutated=False)``, a failure after
+parameter bytes were touched raises ``StrategyFailed(mutated=True)``.
+"""
+
+from __future__ import annotations
+
+import mmap
+import os
+from dataclasses import dataclass, field
+from typing import Any
+
+import numpy as np
+
+from .layout import CheckpointPlan, plan_checkpoint
+from .runtime import PLACE_COPY_ENGINE, Context, PlaceResult, Ring, default_context
+from .safetensors_index import SAFETENSORS_DTYPES, checkpoint_index
+
+
+class StrategyFailed(Exception):
+    """adapter.py:24-34 of the reference: ``mutated`` tells the chain whether the
+    model must be re-initialised before the next strategy runs."""
+
+    def __init__(self, message: str, mutated: bool = False):
+        super().__init__(message)
+        self.mutated = mutated
+
+
+@dataclass
+class LoadResult:
+    """load_strategy/context.py:40-51."""
+
+    value: Any
+    model: Any = None
+    publishable: bool = True
+    metadata: dict = field(default_factory=dict)
+
+
+class FileImage:
+    """A checkpoint file mapped read-only; ``address`` is the host address of byte 0."""
+
+    def __init__(self, path: str):
+        self.path = path
+        self._f = open(path, "rb")
+        self.size = os.fstat(self._f.fileno()).st_size
+        self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)
+        self._np = np.frombuffer(self._mm, dtype=np.uint8)
+        self.address = self._np.ctypes.data
+
+    def close(self):
+        self._np = None
+        try:
+            self._mm.close()
+        finally:
+            self._f.close()
+
+
+def torch_dtype(tag: str):
+    import torch
+
+    return getattr(torch, SAFETENSORS_DTYPES[tag][1])
+
+
+def allocate_params(plan: CheckpointPlan, device) -> dict:
+    """Fresh device tensors for every parameter of the plan (zero-filled where
+    the checkpoint does not cover every byte, e.g. vocabulary padding)."""
+    import torch
+
+    out = {}
+    for name, spec in plan.params.items():
+        maker = torch.zeros if spec.zero_fill else torch.empty
+        out[name] = maker(tuple(spec.shape), dtype=torch_dtype(spec.dtype), device=device)
+    return out
+
+
+def placement_items(plan: CheckpointPlan, index: dict, file_address: dict, params: dict) -> np.ndarray:
+    """(n, 6) uint64 records: host source address -> device destination address."""
+    items = np.empty((len(plan.placements), 6), dtype=np.uint64)
+    for i, pl in enumerate(plan.placements):
+        info = index[pl.src_name]
+        dst = params[pl.dst_name]
+        spec = plan.params[pl.dst_name]
+        if tuple(dst.shape) != tuple(spec.shape) or not dst.is_contiguous():
+            raise ValueError(f"{pl.dst_name}: destination tensor must be contiguous with shape "
+                             f"{tuple(spec.shape)}, got {tuple(dst.shape)}")
+        if dst.element_size() != SAFETENSORS_DTYPES[pl.dtype][0]:
+            raise ValueError(f"{pl.dst_name}: element size differs from the checkpoint's {pl.dtype}")
+        items[i] = pl.record(file_address[info["file"]] + info["file_offset"], dst.data_ptr())
+    return items
+
+
+@dataclass
+class PlacedCheckpoint:
+    params: dict
+    plan: CheckpointPlan
+    stats: PlaceResult
+
+
+def place_checkpoint(model_path: str, tp_rank: int, tp_size: int, device=None, *,
+                     params: dict | None = None, ring: Ring | None = None,
+                     ctx: Context | None = None, host_threads: int | None = None,
+                     mode: int = PLACE_COPY_ENGINE, family: str = "auto",
+                     ring_bytes: int = 2 << 30, ring_slots: int = 16) -> PlacedCheckpoint:
+    """Load this rank's tensor-parallel shards of a safetensors checkpoint.
+
+    ``params`` may hold pre-allocated destination tensors (an engine's own
+    parameters, keyed by the engine's names); otherwise they are allocated.
+    """
+    import torch
+
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if dev.type != "cuda":
+        raise RuntimeError("place_checkpoint needs a CUDA device (no CPU fallback)")
+    dev_index = dev.index if dev.index is not None else torch.cuda.current_device()
+    index = checkpoint_index(model_path)
+    plan = plan_checkpoint({n: {"shape": i["shape"], "dtype": i["dtype"]} for n, i in index.items()},
+                           tp_rank, tp_size, family)
+    own_ring = ring is None
+    if ctx is None:
+        ctx = ring.ctx if ring is not None else default_context(dev_index)
+    if ring is None:
+        ring = ctx.ring(ring_bytes, ring_slots, dev_index)
+    if params is None:
+        params = allocate_params(plan, dev)
+        torch.cuda.synchronize(dev)
+    images = {}
+    try:
+        for path in sorted({i["file"] for i in index.values()}):
+            images[path] = FileImage(path)
+        items = placement_items(plan, index, {p: im.address for p, im in images.items()}, params)
+        threads = host_threads or min(32, os.cpu_count() or 8)
+        stats = ring.place(items, threads, mode)
+    finally:
+        for im in images.values():
+            im.close()
+        if own_ring:
+            ring.close()
+    return PlacedCheckpoint(params, plan, stats)
+
+
+class B200ScatterStrategy:
+    """Load strategy placing weights with the scatter kernel.
+
+    Plug it ahead of the engine-native fallback in the chain
+    (load_strategy/__init__.py:71-78).  ``ctx`` needs ``model_config.model``
+    (checkpoint directory), ``device_id`` and ``adapter``; the adapter must offer
+    ``tp_layout(result) -> (tp_rank, tp_size)`` and
+    ``named_destinations(result) -> {param_name: tensor}`` so that bytes land
+    in the engine's own parameters.
+    """
+
+    name = "b200_scatter"
+    requires: tuple = ()
+
+    def __init__(self, ring_bytes: int = 2 << 30, ring_slots: int = 16, host_threads: int | None = None):
+        self.ring_bytes, self.ring_slots, self.host_threads = ring_bytes, ring_slots, host_threads
+        self._touched = False
+
+    def is_available(self, ctx) -> bool:
+        try:
+            import torch
+
+            from . import _lib
+
+            _lib.load()
+            return bool(torch.cuda.is_available()) and getattr(ctx, "adapter", None) is not None
+        except Exception:
+            return False
+
+    def load(self, result: LoadResult, ctx) -> LoadResult:
+        model_dir = getattr(ctx.model_config, "model", None)
+        if not model_dir or not os.path.isdir(model_dir):
+            raise StrategyFailed(f"no local checkpoint directory at {model_dir!r}", mutated=False)
+        try:
+            tp_rank, tp_size = ctx.adapter.tp_layout(result)
+            params = ctx.adapter.named_destinations(result)
+        except AttributeError as e:
+            raise StrategyFailed(f"adapter lacks a hook this strategy needs: {e}", mutated=False) from e
+        self._touched = False
+        try:
+            self._touched = True
+            placed = place_checkpoint(model_dir, tp_rank, tp_size, f"cuda:{ctx.device_id}",
+                                      params=params, ring_bytes=self.ring_bytes,
+                                      ring_slots=self.ring_slots, host_threads=self.host_threads)
+        except (KeyError, ValueError) as e:
+            # layout could not be expressed: nothing was written yet
+            raise StrategyFailed(str(e), mutated=False) from e
+        except Exception as e:
+            raise StrategyFailed(str(e), mutated=True) from e
+        result.metadata["b200_scatter"] = {
+            "bytes_placed": placed.stats.bytes_placed, "seconds": placed.stats.seconds_total,
+            "chunks": placed.stats.chunks}
+        return result
+
+    def rollback(self, ctx) -> None:
+        self._touched = False

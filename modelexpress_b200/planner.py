@@ -1,0 +1,275 @@
+"""Descriptor compiler: captured copies + published shards -> 2-D scatter records.
+
+The reference plans a refit as a list of 1-D byte runs
+(refit/reshard/slice_plan.py:297-339 ``plan_pull``; one run per row of a strided
+slice, built by ``itertools.product`` in Python).  This module resolves the same
+geometry — the view chain a loader applied to a full source tensor, intersected
+with each published shard box — but emits the closed form the scatter kernel
+consumes: one ``(src, dst, rows, row_bytes, src_pitch, dst_pitch)`` record per
+innermost strided dimension.  Expanding a record row by row gives exactly the
+reference's run list, in the reference's order.
+
+Objects are duck-typed on the reference's field names, so its ``RecordedCopy``
+(types.py:57-70) and ``Shard`` (slice_plan.py:54-70) instances can be passed
+straight in; ``CopySpec`` / ``ShardSpec`` are equivalents for callers that do
+not have the reference package.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any
+
+import numpy as np
+
+
+class UnsupportedReshard(NotImplementedError):
+    """The loader's op-chain is not a pure permuted box view, or the copy needs
+    a dtype conversion; the caller must fail the update (types.py:21-24)."""
+
+
+@dataclass
+class CopySpec:
+    src_name: str
+    op_chain: tuple
+    param_name: str
+    dest_offset: int
+    dest_shape: tuple
+    dest_stride: tuple
+    dest_dtype: Any
+
+
+@dataclass
+class ShardSpec:
+    shard_offset: tuple
+    shape: tuple
+    session: str
+    addr: int
+    elsize: int
+    digest: str | None = None
+
+
+@dataclass
+class SourceSpec:
+    """Everything known about one full source tensor (transfer_plan.py:39-46)."""
+
+    global_shape: tuple
+    dtype: Any
+    elsize: int
+    shards: list
+
+
+def _strides_of(shape):
+    st, acc = [], 1
+    for extent in reversed(shape):
+        st.append(acc)
+        acc *= int(extent)
+    return st[::-1]
+
+
+class _View:
+    """A strided window into a row-major tensor, moved by view ops only."""
+
+    def __init__(self, shape):
+        self.shape = [int(x) for x in shape]
+        self.stride = _strides_of(self.shape)
+        self.offset = 0
+
+    def _dense(self):
+        expect = 1
+        for extent, st in zip(reversed(self.shape), reversed(self.stride)):
+            if extent != 1 and st != expect:
+                return False
+            expect *= extent
+        return True
+
+    def apply(self, op, args):
+        nd = len(self.shape)
+        if op == "narrow":
+            dim, start, size = (int(a) for a in args)
+            dim %= nd
+            if start < 0 or size < 0 or start + size > self.shape[dim]:
+                raise UnsupportedReshard(f"narrow({dim},{start},{size}) leaves the tensor")
+            self.offset += start * self.stride[dim]
+            self.shape[dim] = size
+        elif op == "__getitem__":
+            key = args[0] if args else slice(None)
+            for dim, k in enumerate(key if isinstance(key, tuple) else (key,)):
+                if not isinstance(k, slice) or k.step not in (None, 1):
+                    raise UnsupportedReshard(f"index {k!r} changes rank or stride")
+                lo, hi, _ = k.indices(self.shape[dim])
+                self.offset += lo * self.stride[dim]
+                self.shape[dim] = max(0, hi - lo)
+        elif op in ("transpose", "t"):
+            if op == "t":
+                if nd != 2:
+                    raise UnsupportedReshard("t() needs a matrix")
+                a, b = 0, 1
+            else:
+                a, b = int(args[0]) % nd, int(args[1]) % nd
+            for seq in (self.shape, self.stride):
+                seq[a], seq[b] = seq[b], seq[a]
+        elif op == "permute":
+            order = args[0] if len(args) == 1 and not isinstance(args[0], int) else args
+            order = [int(d) % nd for d in order]
+            if sorted(order) != list(range(nd)):
+                raise UnsupportedReshard("permute is not a permutation")
+            self.shape = [self.shape[d] for d in order]
+            self.stride = [self.stride[d] for d in order]
+        elif op == "contiguous":
+            if not self._dense():
+                raise UnsupportedReshard("contiguous() would materialise a copy")
+        else:
+            raise UnsupportedReshard(f"op {op!r} is not a pure view")
+
+
+def resolve_slice(copy, global_shape):
+    """(needed box in source coordinates, destination strides in source-dim
+    order) for one captured copy; slice_plan.py:227-245."""
+    gshape = [int(g) for g in global_shape]
+    view = _View(gshape)
+    for op, args, _kw in copy.op_chain:
+        view.apply(op, args)
+    nd = len(gshape)
+    if len(view.shape) != nd:
+        raise UnsupportedReshard("rank change")
+    gst = _strides_of(gshape)
+    dim_of_stride = {}
+    for s in range(nd):
+        dim_of_stride.setdefault(gst[s], s)
+    perm = [None] * nd
+    for d in range(nd):
+        if view.shape[d] == 1:
+            continue
+        s = dim_of_stride.get(view.stride[d])
+        if s is None:
+            raise UnsupportedReshard(f"stride {view.stride[d]} is not a source dim (merged dims)")
+        perm[d] = s
+    free = [s for s in range(nd) if s not in {p for p in perm if p is not None}]
+    for d in range(nd):
+        if perm[d] is None:
+            perm[d] = free.pop(0)
+    if sorted(perm) != list(range(nd)):
+        raise UnsupportedReshard("view is not a permutation of the source dims")
+    lo = [(view.offset // gst[s]) % gshape[s] if gshape[s] else 0 for s in range(nd)]
+    hi = list(lo)
+    for d in range(nd):
+        hi[perm[d]] = lo[perm[d]] + view.shape[d]
+    if any(hi[s] > gshape[s] for s in range(nd)):
+        raise UnsupportedReshard("box leaves the source")
+    if sum(lo[s] * gst[s] for s in range(nd)) != view.offset:
+        raise UnsupportedReshard("offset is not a box corner")
+    if tuple(copy.dest_shape) != tuple(view.shape):
+        raise UnsupportedReshard(
+            f"{copy.param_name}: destination {tuple(copy.dest_shape)} != view {tuple(view.shape)}")
+    dst_stride = [0] * nd
+    for d, s in enumerate(perm):
+        dst_stride[s] = int(copy.dest_stride[d])
+    return [(lo[s], hi[s]) for s in range(nd)], dst_stride
+
+
+def box_records(overlap, src_origin, src_strides, dst_origin, dst_strides, elsize,
+                src_base, dst_base):
+    """2-D records covering ``overlap`` (full-tensor coordinates).
+
+    Trailing dims are merged while both layouts are unit-packed (the same rule
+    as slice_plan.py:278-284); the next dim out becomes the row dimension with
+    its two pitches; dims further out are enumerated.  Returns an (m, 6) uint64
+    array in row-major order of the outer dims, i.e. the reference's run order."""
+    nd = len(overlap)
+    sizes = [hi - lo for lo, hi in overlap]
+    run, p = 1, nd
+    while p > 0 and src_strides[p - 1] == run and dst_strides[p - 1] == run:
+        run *= sizes[p - 1]
+        p -= 1
+    s0 = sum((lo - o) * st for (lo, _), o, st in zip(overlap, src_origin, src_strides))
+    d0 = sum((lo - o) * st for (lo, _), o, st in zip(overlap, dst_origin, dst_strides))
+    row_bytes = run * elsize
+    if p == 0:
+        return np.array([[src_base + s0 * elsize, dst_base + d0 * elsize, 1, row_bytes,
+                          row_bytes, row_bytes]], dtype=np.uint64)
+    rows = sizes[p - 1]
+    sp, dp = src_strides[p - 1] * elsize, dst_strides[p - 1] * elsize
+    if rows > 1 and (sp < row_bytes or dp < row_bytes):
+        # overlapping rows cannot be one record; fall back to one record per row
+        p_outer, rows, sp, dp = p, 1, row_bytes, row_bytes
+    else:
+        p_outer = p - 1
+    outer = [sizes[d] for d in range(p_outer)]
+    n_outer = int(np.prod(outer)) if outer else 1
+    out = np.empty((n_outer, 6), dtype=np.uint64)
+    if n_outer == 1:
+        so, do = np.zeros(1, dtype=np.int64), np.zeros(1, dtype=np.int64)
+    else:
+        grids = np.indices(outer, dtype=np.int64).reshape(len(outer), -1)
+        so = sum(grids[d] * src_strides[d] for d in range(p_outer))
+        do = sum(grids[d] * dst_strides[d] for d in range(p_outer))
+    out[:, 0] = src_base + (s0 + so) * elsize
+    out[:, 1] = dst_base + (d0 + do) * elsize
+    out[:, 2] = rows
+    out[:, 3] = row_bytes
+    out[:, 4] = sp if rows > 1 else row_bytes
+    out[:, 5] = dp if rows > 1 else row_bytes
+    return out
+
+
+def plan_pull_2d(copy, global_shape, src_dtype, elsize, shards, dst_base: int):
+    """Records that read exactly the slice ``copy`` needs out of ``shards`` and
+    write it at ``dst_base`` (the parameter's data pointer).  Returns a list of
+    ``(session, records)`` in shard order; raises ``UnsupportedReshard`` for a
+    dtype mismatch or a non-view op-chain, ``ValueError`` for rank-mismatched
+    shard geometry (as the reference does)."""
+    if src_dtype != copy.dest_dtype:
+        raise UnsupportedReshard(f"{copy.param_name}: dtype conversion required")
+    needed, dst_strides = resolve_slice(copy, global_shape)
+    origin = [lo for lo, _ in needed]
+    out = []
+    for sh in shards:
+        if not len(sh.shard_offset) == len(sh.shape) == len(needed):
+            raise ValueError("shard rank does not match the source rank")
+        overlap = []
+        for (a0, a1), o, s in zip(needed, sh.shard_offset, sh.shape):
+            lo, hi = max(a0, int(o)), min(a1, int(o) + int(s))
+            if lo >= hi:
+                overlap = None
+                break
+            overlap.append((lo, hi))
+        if overlap is None:
+            continue
+        recs = box_records(overlap, [int(o) for o in sh.shard_offset], _strides_of(sh.shape),
+                           origin, dst_strides, int(elsize), int(sh.addr),
+                           int(dst_base) + int(copy.dest_offset) * int(elsize))
+        out.append((sh.session, recs))
+    return out
+
+
+def expand_records(records) -> list:
+    """(src, dst, nbytes) runs of a record array, row by row (for checking)."""
+    runs = []
+    for src, dst, rows, rb, sp, dp in np.asarray(records, dtype=np.uint64).tolist():
+        for r in range(rows):
+            runs.append((src + r * sp, dst + r * dp, rb))
+    return runs
+
+
+def plan_transfer_2d(copies, sources: dict, resolve_param_ptr) -> tuple:
+    """All copies of a capture -> one record array.  Copies whose source is
+    missing, needs a conversion or is not box-shaped are returned by name in the
+    second element so the caller can fail closed (transfer_plan.py:192-299 keeps
+    the same three outcomes; there is no descriptor bound here because a strided
+    slice costs one record, not one per row)."""
+    recs, unsupported = [], []
+    for copy in copies:
+        src = sources.get(copy.src_name)
+        if src is None:
+            unsupported.append(copy.src_name)
+            continue
+        try:
+            parts = plan_pull_2d(copy, src.global_shape, src.dtype, src.elsize, src.shards,
+                                 resolve_param_ptr(copy.param_name))
+        except UnsupportedReshard:
+            unsupported.append(copy.src_name)
+            continue
+        recs.extend(r for _sess, r in parts)
+    table = np.concatenate(recs) if recs else np.zeros((0, 6), dtype=np.uint64)
+    return table, unsupported

@@ -1,0 +1,223 @@
+"""Object wrappers over the C ABI: context, staging ring, fan-out node.
+
+Plain integers are used for device addresses so that callers may pass
+``tensor.data_ptr()``, a peer pointer or a pinned host address alike.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _lib
+from ._lib import (DIGEST_BLOCK64, DIGEST_ROWS, DIGEST_SAFE32, PLACE_COPY_ENGINE,
+                   PLACE_ZERO_COPY, SCATTER_BULK, SCATTER_DEFAULT, SCATTER_NO_SYNC, check)
+
+__all__ = ["Context", "Ring", "Fanout", "PlaceResult", "default_context",
+           "DIGEST_SAFE32", "DIGEST_ROWS", "DIGEST_BLOCK64", "SCATTER_DEFAULT", "SCATTER_BULK",
+           "SCATTER_NO_SYNC", "PLACE_COPY_ENGINE", "PLACE_ZERO_COPY"]
+
+
+@dataclass
+class PlaceResult:
+    bytes_placed: int
+    chunks: int
+    launches: int
+    seconds_total: float
+    seconds_gather: float
+    seconds_device: float
+
+
+class Context:
+    """A set of CUDA devices of this process with peer access enabled."""
+
+    def __init__(self, devices=(0,)):
+        self._lib = _lib.load()
+        self.devices = [int(d) for d in devices]
+        ids = (ctypes.c_int32 * len(self.devices))(*self.devices)
+        h = ctypes.c_void_p()
+        check(self._lib.mxb_ctx_create(ids, len(self.devices), ctypes.byref(h)), "mxb_ctx_create")
+        self._h = h
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.mxb_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- memory ------------------------------------------------------------
+    def alloc(self, nbytes: int, dev: int | None = None) -> int:
+        out = ctypes.c_uint64()
+        check(self._lib.mxb_alloc(self._h, self._dev(dev), int(nbytes), ctypes.byref(out)), "mxb_alloc")
+        return out.value
+
+    def free(self, ptr: int, dev: int | None = None) -> None:
+        check(self._lib.mxb_free(self._h, self._dev(dev), int(ptr)), "mxb_free")
+
+    def register_extent(self, base: int, nbytes: int) -> None:
+        check(self._lib.mxb_register_extent(self._h, int(base), int(nbytes)), "mxb_register_extent")
+
+    def clear_extents(self) -> None:
+        check(self._lib.mxb_clear_extents(self._h), "mxb_clear_extents")
+
+    def sync(self, dev: int | None = None) -> None:
+        check(self._lib.mxb_sync(self._h, self._dev(dev)), "mxb_sync")
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.mxb_launch_count(self._h))
+
+    def _dev(self, dev):
+        return self.devices[0] if dev is None else int(dev)
+
+    # -- kernels -----------------------------------------------------------
+    def scatter(self, descs, dev: int | None = None, flags: int = SCATTER_DEFAULT) -> None:
+        """descs: iterable of (src, dst, rows, row_bytes, src_pitch, dst_pitch)."""
+        arr, n = _lib.desc_array(descs)
+        check(self._lib.mxb_scatter(self._h, self._dev(dev), arr, n, flags), "mxb_scatter")
+
+    def read_runs(self, runs, dev: int | None = None) -> None:
+        """runs: iterable of (src, dst, nbytes); returns when the bytes are visible."""
+        arr, n = _lib.run_array(runs)
+        check(self._lib.mxb_read_runs(self._h, self._dev(dev), arr, n), "mxb_read_runs")
+
+    def digest(self, spans, modes: int, dev: int | None = None) -> list:
+        """spans: iterable of (ptr, nbytes) -> list of DigestOut records."""
+        arr, n = _lib.span_array(spans)
+        out = (_lib.DigestOut * max(1, n))()
+        check(self._lib.mxb_digest(self._h, self._dev(dev), arr, n, modes, out), "mxb_digest")
+        return [out[i] for i in range(n)]
+
+    def block_hashes(self, ptr: int, nbytes: int, out_ptr: int, dev: int | None = None) -> None:
+        check(self._lib.mxb_block_hashes(self._h, self._dev(dev), int(ptr), int(nbytes), int(out_ptr)),
+              "mxb_block_hashes")
+
+    def ring(self, ring_bytes: int = 2 << 30, slots: int = 16, dev: int | None = None) -> "Ring":
+        return Ring(self, self._dev(dev), ring_bytes, slots)
+
+    def fanout(self, local_spans, chunk_bytes: int, dev: int | None = None) -> "Fanout":
+        return Fanout(self, self._dev(dev), local_spans, chunk_bytes)
+
+
+def coalesce_runs(runs) -> np.ndarray:
+    """Host-only: fold a run list into 2-D records; returns an (m, 6) uint64 array."""
+    lib = _lib.load()
+    arr, n = _lib.run_array(runs)
+    cap = max(1, n)
+    out = (_lib.Desc2D * cap)()
+    m = lib.mxb_coalesce_runs(arr, n, out, cap)
+    if m < 0:
+        raise _lib.MxbError(int(m), "mxb_coalesce_runs", "capacity")
+    res = np.zeros((m, 6), dtype=np.uint64)
+    if m:
+        ctypes.memmove(res.ctypes.data, out, m * ctypes.sizeof(_lib.Desc2D))
+    return res
+
+
+class Ring:
+    """Pinned staging ring bound to one device."""
+
+    def __init__(self, ctx: Context, dev: int, ring_bytes: int, slots: int):
+        self.ctx, self.dev = ctx, dev
+        h = ctypes.c_void_p()
+        check(ctx._lib.mxb_ring_create(ctx._h, dev, int(ring_bytes), int(slots), ctypes.byref(h)),
+              "mxb_ring_create")
+        self._h = h
+
+    def place(self, items, host_threads: int = 8, mode: int = PLACE_COPY_ENGINE) -> PlaceResult:
+        """items: (host_src, device_dst, rows, row_bytes, src_pitch, dst_pitch) records."""
+        arr, n = _lib.desc_array(items)
+        st = _lib.PlaceStats()
+        check(self.ctx._lib.mxb_place(self._h, arr, n, int(host_threads), int(mode), ctypes.byref(st)),
+              "mxb_place")
+        return PlaceResult(st.bytes_placed, st.chunks, st.launches, st.seconds_total,
+                           st.seconds_gather, st.seconds_device)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self.ctx._lib.mxb_ring_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Fanout:
+    """One node of a chunked, pipelined broadcast (see ``fanout.py`` for topologies)."""
+
+    def __init__(self, ctx: Context, dev: int, local_spans, chunk_bytes: int):
+        self.ctx, self.dev = ctx, dev
+        arr, n = _lib.span_array(local_spans)
+        self.n = n
+        h = ctypes.c_void_p()
+        check(ctx._lib.mxb_fanout_create(ctx._h, dev, arr, n, int(chunk_bytes), ctypes.byref(h)),
+              "mxb_fanout_create")
+        self._h = h
+        self.children = 0
+
+    @property
+    def counters(self) -> int:
+        return int(self.ctx._lib.mxb_fanout_counters(self._h))
+
+    def add_child(self, child_spans, child_counters: int) -> None:
+        arr, n = _lib.span_array(child_spans)
+        check(self.ctx._lib.mxb_fanout_set_child(self._h, self.children, arr, n, int(child_counters)),
+              "mxb_fanout_set_child")
+        self.children += 1
+
+    def run(self, is_root: bool, timeout_ms: int = 2000) -> None:
+        check(self.ctx._lib.mxb_fanout_run(self._h, 1 if is_root else 0, int(timeout_ms)),
+              "mxb_fanout_run")
+
+    def wait(self) -> float:
+        ms = ctypes.c_float(0.0)
+        check(self.ctx._lib.mxb_fanout_wait(self._h, ctypes.byref(ms)), "mxb_fanout_wait")
+        return float(ms.value)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self.ctx._lib.mxb_fanout_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def ipc_export(ptr: int) -> tuple:
+    lib = _lib.load()
+    h = (ctypes.c_uint8 * 64)()
+    off = ctypes.c_uint64()
+    check(lib.mxb_ipc_export(int(ptr), h, ctypes.byref(off)), "mxb_ipc_export")
+    return bytes(h), off.value
+
+
+def ipc_open(handle: bytes, offset: int) -> int:
+    lib = _lib.load()
+    h = (ctypes.c_uint8 * 64)(*handle)
+    out = ctypes.c_uint64()
+    check(lib.mxb_ipc_open(h, int(offset), ctypes.byref(out)), "mxb_ipc_open")
+    return out.value
+
+
+_default: dict = {}
+
+
+def default_context(device: int = 0) -> Context:
+    """Process-wide single-device context, created on first use."""
+    ctx = _default.get(device)
+    if ctx is None:
+        ctx = _default[device] = Context([device])
+    return ctx
