@@ -35,6 +35,7 @@ extern "C" {
 typedef struct mxb_ctx mxb_ctx;
 typedef struct mxb_ring mxb_ring;
 typedef struct mxb_fanout mxb_fanout;
+typedef struct mxb_table mxb_table;
 
 /* One contiguous byte run.  Mirrors ReadDescriptor(session, src_addr, dst_addr,
  * nbytes) of refit/reshard/transport/base.py:26-35 with the session resolved
@@ -144,6 +145,24 @@ int32_t mxb_scatter(mxb_ctx *ctx, int32_t dev, const mxb_desc2d *descs, uint64_t
 /* Same, from a 1-D run list: coalesces, launches and waits.  Direct
  * equivalent of InMemoryReferenceTransport.read (transport/base.py:46-62). */
 int32_t mxb_read_runs(mxb_ctx *ctx, int32_t dev, const mxb_run *runs, uint64_t n);
+
+/* A descriptor table kept resident on the device, for plans that are replayed
+ * (every refit cycle moves the same slices).  Stands in for the descriptor
+ * cache of refit/reshard/receiver.py:795-854 and the resolve-once / copy-many
+ * loop of engines/vllm/refit/installer.py:373-424. */
+int32_t mxb_table_create(mxb_ctx *ctx, int32_t dev, const mxb_desc2d *descs, uint64_t n,
+                         mxb_table **out);
+/* One persistent launch over the whole table on the context stream; returns
+ * without waiting (use mxb_sync). */
+int32_t mxb_table_launch(mxb_table *t, uint32_t flags);
+/* Bytes one launch moves. */
+uint64_t mxb_table_bytes(mxb_table *t);
+int32_t mxb_table_destroy(mxb_table *t);
+
+/* Timing on the context's compute stream of `dev`: record event `slot`
+ * (0..15); elapsed waits for event `b` and returns b - a in milliseconds. */
+int32_t mxb_event_record(mxb_ctx *ctx, int32_t dev, int32_t slot);
+int32_t mxb_event_elapsed(mxb_ctx *ctx, int32_t dev, int32_t a, int32_t b, float *ms);
 
 /* ---- staging ring: host bytes -> HBM shards ----------------------------- */
 

@@ -72,6 +72,12 @@ SIGNATURES = {
     "mxb_coalesce_runs": (i64, [_P(Run), u64, _P(Desc2D), u64]),
     "mxb_scatter": (i32, [_vp, i32, _P(Desc2D), u64, u32]),
     "mxb_read_runs": (i32, [_vp, i32, _P(Run), u64]),
+    "mxb_table_create": (i32, [_vp, i32, _P(Desc2D), u64, _P(_vp)]),
+    "mxb_table_launch": (i32, [_vp, u32]),
+    "mxb_table_bytes": (u64, [_vp]),
+    "mxb_table_destroy": (i32, [_vp]),
+    "mxb_event_record": (i32, [_vp, i32, i32]),
+    "mxb_event_elapsed": (i32, [_vp, i32, i32, i32, _P(ctypes.c_float)]),
     "mxb_ring_create": (i32, [_vp, i32, u64, u32, _P(_vp)]),
     "mxb_ring_destroy": (i32, [_vp]),
     "mxb_place": (i32, [_vp, _P(Desc2D), u64, i32, u32, _P(PlaceStats)]),

@@ -182,6 +182,8 @@ int32_t mxb_ctx_destroy(mxb_ctx *ctx) {
         if (d.digest_host) cudaFreeHost(d.digest_host);
         if (d.status) cudaFree(d.status);
         if (d.status_host) cudaFreeHost(d.status_host);
+        for (cudaEvent_t e : d.events)
+            if (e) cudaEventDestroy(e);
         if (d.stream) cudaStreamDestroy(d.stream);
         if (d.copy_stream) cudaStreamDestroy(d.copy_stream);
     }
@@ -200,6 +202,29 @@ int32_t mxb_sync(mxb_ctx *ctx, int32_t dev) {
     DeviceGuard g(dev);
     MXB_CUDA(cudaStreamSynchronize(d->copy_stream));
     return check_status(d);
+}
+
+int32_t mxb_event_record(mxb_ctx *ctx, int32_t dev, int32_t slot) {
+    if (!ctx || slot < 0 || slot >= 16) return MXB_ERR_ARG;
+    DeviceState *d = ctx->find(dev);
+    if (!d) return MXB_ERR_ARG;
+    DeviceGuard g(dev);
+    if (!d->events[slot]) MXB_CUDA(cudaEventCreate(&d->events[slot]));
+    MXB_CUDA(cudaEventRecord(d->events[slot], d->stream));
+    return MXB_OK;
+}
+
+int32_t mxb_event_elapsed(mxb_ctx *ctx, int32_t dev, int32_t a, int32_t b, float *ms) {
+    if (!ctx || !ms || a < 0 || a >= 16 || b < 0 || b >= 16) return MXB_ERR_ARG;
+    DeviceState *d = ctx->find(dev);
+    if (!d || !d->events[a] || !d->events[b]) {
+        set_error("mxb_event_elapsed: event not recorded");
+        return MXB_ERR_STATE;
+    }
+    DeviceGuard g(dev);
+    MXB_CUDA(cudaEventSynchronize(d->events[b]));
+    MXB_CUDA(cudaEventElapsedTime(ms, d->events[a], d->events[b]));
+    return MXB_OK;
 }
 
 uint64_t mxb_launch_count(mxb_ctx *ctx) { return ctx ? ctx->launches.load() : 0; }

@@ -48,6 +48,7 @@ struct DeviceState {
     size_t digest_bytes = 0;
     void *digest_host = nullptr;
     size_t digest_host_bytes = 0;
+    cudaEvent_t events[16] = {};  // user timing events on `stream`
 };
 
 struct Extent {

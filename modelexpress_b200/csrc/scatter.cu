@@ -402,7 +402,76 @@ int32_t launch_scatter(mxb_ctx *ctx, DeviceState *dv, const mxb_desc2d *descs, u
 
 using namespace mxb;
 
+struct mxb_table {
+    mxb_ctx *ctx = nullptr;
+    DeviceState *dv = nullptr;
+    void *dev_buf = nullptr;
+    ScatterTable tb;
+    uint64_t bytes_moved = 0;
+};
+
 extern "C" {
+
+int32_t mxb_table_create(mxb_ctx *ctx, int32_t dev, const mxb_desc2d *descs, uint64_t n,
+                         mxb_table **out) {
+    if (!ctx || (!descs && n) || !out) {
+        set_error("mxb_table_create: bad arguments");
+        return MXB_ERR_ARG;
+    }
+    DeviceState *d = ctx->find(dev);
+    if (!d) {
+        set_error("device %d is not part of this context", dev);
+        return MXB_ERR_ARG;
+    }
+    int32_t rc = validate_descs(ctx, descs, n);
+    if (rc != MXB_OK) return rc;
+    DeviceGuard g(dev);
+    mxb_table *t = new mxb_table();
+    t->ctx = ctx;
+    t->dv = d;
+    const size_t bytes = scatter_table_bytes(descs, n, nullptr, nullptr);
+    for (uint64_t i = 0; i < n; ++i) t->bytes_moved += descs[i].rows * descs[i].row_bytes;
+    if (bytes) {
+        std::vector<char> host(bytes);
+        if (cudaMalloc(&t->dev_buf, bytes) != cudaSuccess) {
+            set_error("cudaMalloc(table) failed");
+            cudaGetLastError();
+            delete t;
+            return MXB_ERR_NOMEM;
+        }
+        rc = build_scatter_table(descs, n, host.data(), t->dev_buf, &t->tb, nullptr);
+        if (rc == MXB_OK &&
+            cudaMemcpy(t->dev_buf, host.data(), t->tb.bytes, cudaMemcpyHostToDevice) != cudaSuccess) {
+            set_error("table upload failed");
+            cudaGetLastError();
+            rc = MXB_ERR_CUDA;
+        }
+        if (rc != MXB_OK) {
+            cudaFree(t->dev_buf);
+            delete t;
+            return rc;
+        }
+    }
+    *out = t;
+    return MXB_OK;
+}
+
+int32_t mxb_table_launch(mxb_table *t, uint32_t flags) {
+    if (!t) return MXB_ERR_ARG;
+    DeviceGuard g(t->dv->device);
+    return launch_scatter_tiles(t->ctx, t->dv, t->tb, 0, t->tb.total_tiles, flags, t->dv->stream);
+}
+
+uint64_t mxb_table_bytes(mxb_table *t) { return t ? t->bytes_moved : 0; }
+
+int32_t mxb_table_destroy(mxb_table *t) {
+    if (!t) return MXB_OK;
+    DeviceGuard g(t->dv->device);
+    cudaStreamSynchronize(t->dv->stream);
+    if (t->dev_buf) cudaFree(t->dev_buf);
+    delete t;
+    return MXB_OK;
+}
 
 int32_t mxb_scatter(mxb_ctx *ctx, int32_t dev, const mxb_desc2d *descs, uint64_t n,
                     uint32_t flags) {

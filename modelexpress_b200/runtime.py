@@ -15,7 +15,7 @@ from . import _lib
 from ._lib import (DIGEST_BLOCK64, DIGEST_ROWS, DIGEST_SAFE32, PLACE_COPY_ENGINE,
                    PLACE_ZERO_COPY, SCATTER_BULK, SCATTER_DEFAULT, SCATTER_NO_SYNC, check)
 
-__all__ = ["Context", "Ring", "Fanout", "PlaceResult", "default_context",
+__all__ = ["Context", "Ring", "Fanout", "Table", "PlaceResult", "default_context",
            "DIGEST_SAFE32", "DIGEST_ROWS", "DIGEST_BLOCK64", "SCATTER_DEFAULT", "SCATTER_BULK",
            "SCATTER_NO_SYNC", "PLACE_COPY_ENGINE", "PLACE_ZERO_COPY"]
 
@@ -99,6 +99,18 @@ class Context:
         check(self._lib.mxb_block_hashes(self._h, self._dev(dev), int(ptr), int(nbytes), int(out_ptr)),
               "mxb_block_hashes")
 
+    def table(self, descs, dev: int | None = None) -> "Table":
+        return Table(self, self._dev(dev), descs)
+
+    def event_record(self, slot: int, dev: int | None = None) -> None:
+        check(self._lib.mxb_event_record(self._h, self._dev(dev), int(slot)), "mxb_event_record")
+
+    def event_elapsed_ms(self, a: int, b: int, dev: int | None = None) -> float:
+        ms = ctypes.c_float(0.0)
+        check(self._lib.mxb_event_elapsed(self._h, self._dev(dev), int(a), int(b), ctypes.byref(ms)),
+              "mxb_event_elapsed")
+        return float(ms.value)
+
     def ring(self, ring_bytes: int = 2 << 30, slots: int = 16, dev: int | None = None) -> "Ring":
         return Ring(self, self._dev(dev), ring_bytes, slots)
 
@@ -119,6 +131,35 @@ def coalesce_runs(runs) -> np.ndarray:
     if m:
         ctypes.memmove(res.ctypes.data, out, m * ctypes.sizeof(_lib.Desc2D))
     return res
+
+
+class Table:
+    """A descriptor table resident on the device; ``launch`` replays it."""
+
+    def __init__(self, ctx: Context, dev: int, descs):
+        self.ctx, self.dev = ctx, dev
+        arr, n = _lib.desc_array(descs)
+        h = ctypes.c_void_p()
+        check(ctx._lib.mxb_table_create(ctx._h, dev, arr, n, ctypes.byref(h)), "mxb_table_create")
+        self._h = h
+
+    @property
+    def nbytes(self) -> int:
+        return int(self.ctx._lib.mxb_table_bytes(self._h))
+
+    def launch(self, flags: int = SCATTER_DEFAULT) -> None:
+        check(self.ctx._lib.mxb_table_launch(self._h, int(flags)), "mxb_table_launch")
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self.ctx._lib.mxb_table_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class Ring:

@@ -1,0 +1,184 @@
+"""Fan-out and reshard kernels.  On one GPU the ranks are emulated as buffers
+of the same device and the launches run one after another (kernels that wait
+on each other never share a GPU); with two or more GPUs the real peer path runs."""
+
+import numpy as np
+import pytest
+
+from helpers import read_full_tensors, tiny_dense_config
+from make_golden import golden_bytes
+from oracle import ref_port as R
+
+pytestmark = pytest.mark.gpu
+
+
+def _spans(torch, tensors):
+    return [(t.data_ptr(), t.numel() * t.element_size()) for t in tensors]
+
+
+def test_fanout_single_gpu_loopback():
+    """Root pushes to a 'child' on the same device; then the child's kernel runs
+    and finds every chunk counter already satisfied."""
+    import torch
+
+    from modelexpress_b200 import digest
+    from modelexpress_b200.runtime import Context
+
+    ctx = Context([0])
+    sizes = [1 << 20, 4096 + 16, 333 * 16, 100, 5 << 20, 48]
+    src = [torch.from_numpy(golden_bytes(20 + i, n)).cuda() for i, n in enumerate(sizes)]
+    dst = [torch.zeros(n, dtype=torch.uint8, device="cuda") for n in sizes]
+    torch.cuda.synchronize()
+    for chunk in (1 << 20, 64 << 10):
+        for d in dst:
+            d.zero_()
+        torch.cuda.synchronize()
+        root = ctx.fanout(_spans(torch, src), chunk, 0)
+        leaf = ctx.fanout(_spans(torch, dst), chunk, 0)
+        root.add_child(_spans(torch, dst), leaf.counters)
+        for _ in range(2):  # counters are cumulative: a second broadcast needs no reset
+            root.run(True, 2000)
+            assert root.wait() > 0
+            leaf.run(False, 2000)
+            leaf.wait()
+        for s, d in zip(src, dst):
+            assert torch.equal(s, d)
+        a = digest.digest_many(src)
+        b = digest.digest_many(dst)
+        assert a == b
+        root.close()
+        leaf.close()
+    ctx.close()
+
+
+def test_fanout_wait_runs_out_cleanly():
+    """A node whose parent never delivers: the bounded wait ends, the call
+    reports a timeout and the context keeps working."""
+    import torch
+
+    from modelexpress_b200._lib import MxbTimeout
+    from modelexpress_b200.runtime import Context
+
+    ctx = Context([0])
+    buf = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    node = ctx.fanout(_spans(torch, [buf]), 1 << 16, 0)
+    node.run(False, 50)
+    with pytest.raises(MxbTimeout):
+        node.wait()
+    with pytest.raises(TimeoutError):
+        node.run(False, 50)
+        node.wait()
+    # still usable
+    src = torch.from_numpy(golden_bytes(1, 1 << 16)).cuda()
+    torch.cuda.synchronize()
+    ctx.scatter([(src.data_ptr(), buf.data_ptr(), 1, 1 << 16, 1 << 16, 1 << 16)], 0)
+    assert torch.equal(src, buf)
+    node.close()
+    ctx.close()
+
+
+def test_manifest_matching_rules():
+    from modelexpress_b200.fanout import (ManifestMismatchError, TensorDescriptor, match_manifests,
+                                          topology)
+
+    s = [TensorDescriptor("a", 100, 64, 0, "bf16"), TensorDescriptor("b", 200, 32, 0, "bf16")]
+    t = [TensorDescriptor("b", 900, 32, 1, "bf16"), TensorDescriptor("a", 800, 64, 1, "bf16")]
+    assert match_manifests(s, t) == [("b", 200, 900, 32), ("a", 100, 800, 64)]
+    with pytest.raises(ManifestMismatchError):
+        match_manifests(s, [TensorDescriptor("a", 1, 65, 1, "bf16")])
+    with pytest.raises(ManifestMismatchError):
+        match_manifests(s, [TensorDescriptor("a", 1, 64, 1, "f16")])
+    with pytest.raises(ManifestMismatchError):
+        match_manifests(s, [TensorDescriptor("c", 1, 64, 1, "bf16")])
+    assert topology("chain", 4) == [[1], [2], [3], []]
+    assert topology("tree", 5) == [[1, 2], [3, 4], [], [], []]
+    assert topology("flat", 3, root=1) == [[], [0, 2], []]
+
+
+@pytest.mark.parametrize("kind", ["chain", "tree", "flat"])
+def test_fanout_across_gpus(kind):
+    import torch
+
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    from modelexpress_b200.fanout import Broadcast
+    from modelexpress_b200.runtime import Context
+
+    devs = list(range(min(n, 4)))
+    ctx = Context(devs)
+    sizes = [3 << 20, 4096 + 16, 7 << 20, 160]
+    bufs = []
+    for i, d in enumerate(devs):
+        if i == 0:
+            bufs.append([torch.from_numpy(golden_bytes(50 + j, s)).to(f"cuda:{d}") for j, s in enumerate(sizes)])
+        else:
+            bufs.append([torch.zeros(s, dtype=torch.uint8, device=f"cuda:{d}") for s in sizes])
+    for d in devs:
+        torch.cuda.synchronize(d)
+    bc = Broadcast(ctx, devs, [_spans(torch, b) for b in bufs], 1 << 20, kind)
+    bc.run(5000)
+    for b in bufs[1:]:
+        for s, t in zip(bufs[0], b):
+            assert torch.equal(s.cpu(), t.cpu())
+    bc.close()
+    ctx.close()
+
+
+def _reshard_case(torch, tmp_path, devices):
+    from modelexpress_b200 import layout, reshard, synth
+    from modelexpress_b200.runtime import Context
+    from modelexpress_b200.safetensors_index import checkpoint_index
+
+    cfg = tiny_dense_config()
+    d = str(tmp_path)
+    synth.write_checkpoint(d, synth.dense_tensors(cfg), cfg.seed, 1)
+    full = read_full_tensors(d)
+    idx = checkpoint_index(d)
+    index = {n: {"shape": i["shape"], "dtype": i["dtype"]} for n, i in idx.items()}
+    world = tp = 8
+    pieces = R.fsdp_shards(full, world)
+    sa = reshard.shard_arena(index, world)
+    pa = reshard.param_arena(layout.plan_checkpoint(index, 0, tp))
+    ctx = Context(sorted(set(devices)))
+    shard_t, param_t = [], []
+    for s in range(world):
+        host = np.zeros(sa.total, dtype=np.uint8)
+        for n, piece in pieces[s].items():
+            b = piece.view(np.uint8)
+            host[sa.offsets[n]: sa.offsets[n] + b.size] = b
+        shard_t.append(torch.from_numpy(host).to(f"cuda:{devices[s]}"))
+        param_t.append(torch.zeros(pa.total, dtype=torch.uint8, device=f"cuda:{devices[s]}"))
+    for dv in set(devices):
+        torch.cuda.synchronize(dv)
+    moved = 0
+    for s in range(world):  # every source rank pushes its pieces to every destination
+        recs = reshard.plan_reshard(index, world, tp, s, shard_t[s].data_ptr(),
+                                    [p.data_ptr() for p in param_t])
+        moved += reshard.reshard_bytes(recs)
+        ctx.scatter(recs, devices[s])
+    shapes = {n: a.shape for n, a in full.items()}
+    for t in range(tp):
+        want = R.regather_and_reslice(pieces, shapes, t, tp)
+        host = param_t[t].cpu().numpy()
+        for n, a in want.items():
+            got = host[pa.offsets[n]: pa.offsets[n] + a.nbytes].view(a.dtype).reshape(a.shape)
+            assert np.array_equal(got, a), (t, n)
+    assert moved == sum(a.nbytes for a in R.load_and_shard(full, 0, tp).values()) * tp
+    ctx.close()
+
+
+def test_reshard_emulated_ranks_one_gpu(tmp_path):
+    import torch
+
+    _reshard_case(torch, tmp_path, [0] * 8)
+
+
+def test_reshard_across_gpus(tmp_path):
+    import torch
+
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    _reshard_case(torch, tmp_path, [i % n for i in range(8)])

@@ -1,0 +1,152 @@
+"""Checkpoint placement through the staging ring against the oracle's load-and-shard."""
+
+import numpy as np
+import pytest
+
+from helpers import read_full_tensors, tiny_dense_config
+from oracle import ref_port as R
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ckpts(tmp_path_factory):
+    import torch
+
+    from modelexpress_b200 import synth
+
+    assert torch.cuda.is_available()
+    tiny = str(tmp_path_factory.mktemp("tiny"))
+    cfg = tiny_dense_config()
+    synth.write_checkpoint(tiny, synth.dense_tensors(cfg), cfg.seed, cfg.files)
+    # the CPU-runnable benchmark configuration, with fewer vocabulary rows to keep the test short
+    small = str(tmp_path_factory.mktemp("small"))
+    scfg = synth.scaled(synth.SMALL_LLAMA, layers=2, vocab=8000)
+    synth.write_checkpoint(small, synth.dense_tensors(scfg), scfg.seed, 1)
+    return tiny, small
+
+
+def _as_np(t):
+    import torch
+
+    t = t.detach().cpu().contiguous()
+    if t.element_size() == 2:
+        return t.view(torch.int16).numpy().view(np.uint16)
+    if t.element_size() == 1:
+        return t.view(torch.uint8).numpy()
+    return t.numpy()
+
+
+def _check(placed, want):
+    assert set(placed.params) == set(want)
+    for n, a in want.items():
+        got = _as_np(placed.params[n])
+        assert got.shape == a.shape, n
+        assert np.array_equal(got, a), n
+
+
+@pytest.mark.parametrize("mode", ["copy_engine", "zero_copy"])
+@pytest.mark.parametrize("tp", [1, 8])
+def test_tiny_checkpoint_every_rank(ckpts, tp, mode):
+    from modelexpress_b200.loader import place_checkpoint
+    from modelexpress_b200.runtime import PLACE_COPY_ENGINE, PLACE_ZERO_COPY, Context
+
+    tiny, _ = ckpts
+    full = read_full_tensors(tiny)
+    ctx = Context([0])
+    ring = ctx.ring(8 << 20, 4, 0)  # 2 MiB slots: tensors span several chunks
+    m = PLACE_COPY_ENGINE if mode == "copy_engine" else PLACE_ZERO_COPY
+    try:
+        for rank in range(tp):
+            placed = place_checkpoint(tiny, rank, tp, "cuda:0", ring=ring, host_threads=4, mode=m)
+            _check(placed, R.load_and_shard(full, rank, tp))
+            assert placed.stats.bytes_placed == placed.plan.bytes_placed
+            assert placed.stats.chunks >= 1 and placed.stats.launches == placed.stats.chunks
+    finally:
+        ring.close()
+        ctx.close()
+
+
+def test_small_llama_tp1_byte_exact(ckpts):
+    """The reference-runnable configuration: TP=1 load onto one GPU, checked
+    byte for byte and by both reference digests per tensor."""
+    from modelexpress_b200 import digest
+    from modelexpress_b200.loader import place_checkpoint
+
+    _, small = ckpts
+    full = read_full_tensors(small)
+    placed = place_checkpoint(small, 0, 1, "cuda:0", ring_bytes=64 << 20, ring_slots=4, host_threads=4)
+    want = R.load_and_shard(full, 0, 1)
+    _check(placed, want)
+    names = sorted(want)
+    res = digest.digest_many([placed.params[n] for n in names])
+    for n, r in zip(names, res):
+        assert r["safe_checksum"] == R.safe_checksum(want[n]), n
+        assert r["tensor_digest"] == R.tensor_digest(want[n]), n
+
+
+def test_vocab_padding_rows_are_zero(tmp_path):
+    import torch
+
+    from modelexpress_b200 import synth
+    from modelexpress_b200.loader import place_checkpoint
+
+    cfg = synth.DenseConfig("pad", 1, 128, 256, 4, 4, 32, 1000, False, 3, 1)  # 1000 pads to 1024
+    d = str(tmp_path)
+    synth.write_checkpoint(d, synth.dense_tensors(cfg), cfg.seed, 1)
+    full = read_full_tensors(d)
+    for rank in (0, 3):
+        placed = place_checkpoint(d, rank, 4, "cuda:0", ring_bytes=8 << 20, ring_slots=2, host_threads=2)
+        _check(placed, R.load_and_shard(full, rank, 4))
+    emb = placed.params["model.embed_tokens.weight"]
+    assert emb.shape == (256, 128) and bool((emb[232:] == 0).all())
+
+
+def test_strategy_contract(ckpts):
+    """load_strategy/base.py:37-76 contract: LoadResult on success, StrategyFailed
+    (mutated=False) on an expected miss."""
+    import torch
+
+    from modelexpress_b200.layout import plan_checkpoint
+    from modelexpress_b200.loader import (B200ScatterStrategy, LoadResult, StrategyFailed,
+                                          allocate_params)
+    from modelexpress_b200.safetensors_index import checkpoint_index
+
+    tiny, _ = ckpts
+
+    class Adapter:
+        def __init__(self, params):
+            self.params = params
+
+        def tp_layout(self, result):
+            return 1, 2
+
+        def named_destinations(self, result):
+            return self.params
+
+    class Cfg:
+        model = tiny
+
+    class Ctx:
+        model_config = Cfg()
+        device_id = 0
+        adapter = None
+
+    idx = checkpoint_index(tiny)
+    plan = plan_checkpoint({n: {"shape": i["shape"], "dtype": i["dtype"]} for n, i in idx.items()}, 1, 2)
+    params = allocate_params(plan, "cuda:0")
+    strat = B200ScatterStrategy(ring_bytes=8 << 20, ring_slots=2, host_threads=2)
+    ctx = Ctx()
+    assert strat.name == "b200_scatter" and not strat.is_available(ctx)
+    ctx.adapter = Adapter(params)
+    assert strat.is_available(ctx)
+    res = strat.load(LoadResult(value="model", model="model"), ctx)
+    assert res.metadata["b200_scatter"]["bytes_placed"] == plan.bytes_placed
+    want = R.load_and_shard(read_full_tensors(tiny), 1, 2)
+    for n, a in want.items():
+        assert np.array_equal(_as_np(params[n]), a), n
+    Cfg.model = "/nonexistent"
+    with pytest.raises(StrategyFailed) as ei:
+        strat.load(LoadResult(value="m"), ctx)
+    assert ei.value.mutated is False
+    strat.rollback(ctx)

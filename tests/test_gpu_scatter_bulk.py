@@ -1,0 +1,34 @@
+"""The cp.async.bulk tile engine of the scatter kernel against the oracle."""
+
+import numpy as np
+import pytest
+
+from make_golden import golden_bytes
+from test_gpu_scatter import _run_both, env  # noqa: F401  (fixture)
+
+pytestmark = pytest.mark.gpu
+
+
+def test_bulk_engine_matches_vector_engine(env):
+    ctx, torch = env
+    from modelexpress_b200.runtime import SCATTER_BULK
+
+    rng = np.random.default_rng(9)
+    src = golden_bytes(77, 24 << 20)
+    recs, dpos = [], 0
+    for _ in range(40):
+        if rng.integers(0, 2):
+            rows, rb = 1, 16 * int(rng.integers(64, 40_000))
+            sp = dp = rb
+        else:
+            rows, rb = int(rng.integers(1, 300)), 16 * int(rng.integers(64, 600))
+            sp, dp = rb + 16 * int(rng.integers(0, 40)), rb + 16 * int(rng.integers(0, 40))
+        span_s, span_d = (rows - 1) * sp + rb, (rows - 1) * dp + rb
+        s0 = 16 * int(rng.integers(0, (src.size - span_s) // 16))
+        recs.append((s0, dpos, rows, rb, sp, dp))
+        dpos += (span_d + 255) // 256 * 256
+    got, want = _run_both(ctx, torch, src, dpos, recs, SCATTER_BULK)
+    assert np.array_equal(got, want)
+    assert ctx.launch_count > 0
+
+
