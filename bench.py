@@ -30,6 +30,7 @@ import subprocess
 import sys
 import threading
 import time
+import warnings
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -251,7 +252,9 @@ def bench_place(args):
     file_dev, file_base = {}, {}
     for p, im in images.items():
         t = torch.empty(im.size, dtype=torch.uint8, device=dev)
-        t.copy_(torch.from_numpy(np.frombuffer(im._mm, dtype=np.uint8)))
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")  # read-only mmap view; it is only read
+            t.copy_(torch.from_numpy(np.frombuffer(im._mm, dtype=np.uint8)))
         file_dev[p], file_base[p] = t, t.data_ptr()
     torch.cuda.synchronize()
     dev_items = loader.placement_items(plan, idx, file_base, params)
@@ -324,7 +327,7 @@ def bench_place(args):
                      "kernel": kernel, "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": int(2 * bytes_placed)},
     }
-    if world == 1 and rank == 0:
+    if world == 1 and rank == 0 and os.environ.get("MXB_BENCH_SKIP_CPU") != "1":
         out["cpu_baseline"] = cpu_baseline(ckpt, tp_rank, threads_all=False)
     if rank == 0:
         print(json.dumps(out), flush=True)
