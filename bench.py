@@ -251,11 +251,15 @@ def bench_place(args):
     # ---- value: checkpoint image resident in HBM -> scatter ----------------------------
     file_dev, file_base = {}, {}
     for p, im in images.items():
-        t = torch.empty(im.size, dtype=torch.uint8, device=dev)
+        # place the image so that the safetensors data section (which starts 8 + header
+        # bytes into the file, only 8-byte aligned) begins on a 256-byte boundary
+        first = min(i["file_offset"] for i in idx.values() if i["file"] == p)
+        lead = (-first) % 256 + (8 if os.environ.get("MXB_BENCH_MISALIGN") == "1" else 0)
+        t = torch.empty(im.size + lead, dtype=torch.uint8, device=dev)
         with warnings.catch_warnings():
             warnings.simplefilter("ignore")  # read-only mmap view; it is only read
-            t.copy_(torch.from_numpy(np.frombuffer(im._mm, dtype=np.uint8)))
-        file_dev[p], file_base[p] = t, t.data_ptr()
+            t[lead:].copy_(torch.from_numpy(np.frombuffer(im._mm, dtype=np.uint8)))
+        file_dev[p], file_base[p] = t, t.data_ptr() + lead
     torch.cuda.synchronize()
     dev_items = loader.placement_items(plan, idx, file_base, params)
     for v in params.values():
@@ -297,7 +301,7 @@ def bench_place(args):
     ms_per_step = ms / args.steps
     peak, peak_src = measured_peak()
     achieved = 2.0 * bytes_placed / (ms_per_step * 1e-3) / 1e9  # read + write per GPU
-    kernel = "scatter_bulk_kernel" if flags == SCATTER_BULK else "scatter_vec_kernel"
+    kernel = "scatter_bulk_kernel" if table.engine(flags) == "bulk" else "scatter_vec_kernel"
     out = {
         "metric": "GB/s placed into HBM (Llama-3-8B bf16, TP=8 shards)",
         "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,

@@ -157,6 +157,9 @@ int32_t mxb_table_create(mxb_ctx *ctx, int32_t dev, const mxb_desc2d *descs, uin
 int32_t mxb_table_launch(mxb_table *t, uint32_t flags);
 /* Bytes one launch moves. */
 uint64_t mxb_table_bytes(mxb_table *t);
+/* Tile engine a launch with `flags` uses: 0 = vector loads/stores, 1 = bulk
+ * copies (only when MXB_SCATTER_BULK is set and every record qualifies). */
+int32_t mxb_table_engine(mxb_table *t, uint32_t flags);
 int32_t mxb_table_destroy(mxb_table *t);
 
 /* Timing on the context's compute stream of `dev`: record event `slot`

@@ -75,6 +75,7 @@ SIGNATURES = {
     "mxb_table_create": (i32, [_vp, i32, _P(Desc2D), u64, _P(_vp)]),
     "mxb_table_launch": (i32, [_vp, u32]),
     "mxb_table_bytes": (u64, [_vp]),
+    "mxb_table_engine": (i32, [_vp, u32]),
     "mxb_table_destroy": (i32, [_vp]),
     "mxb_event_record": (i32, [_vp, i32, i32]),
     "mxb_event_elapsed": (i32, [_vp, i32, i32, i32, _P(ctypes.c_float)]),

@@ -110,7 +110,7 @@ __device__ __forceinline__ void flush(WarpAcc &a, DigestAcc *acc, uint32_t lane)
     a.safe = 0;
 }
 
-__global__ void __launch_bounds__(kDigestThreads)
+__global__ void __launch_bounds__(kDigestThreads, 2)
 digest_kernel(const mxb_span *__restrict__ spans, const DTile *__restrict__ tiles,
               uint64_t total_tiles, uint32_t modes, DigestAcc *__restrict__ acc,
               unsigned long long *__restrict__ block_out) {

@@ -186,8 +186,12 @@ int32_t mxb_fanout_create(mxb_ctx *ctx, int32_t dev, const mxb_span *local, uint
     }
     DeviceGuard g(dev);
     const size_t nchunks = f->chunk_pieces.size() ? f->chunk_pieces.size() : 1;
-    if (cudaMalloc((void **)&f->counters, nchunks * sizeof(uint32_t)) != cudaSuccess ||
-        cudaMemset(f->counters, 0, nchunks * sizeof(uint32_t)) != cudaSuccess ||
+    // a whole 2 MiB allocation of its own, so that an IPC handle of the counters
+    // exposes nothing else of this process
+    size_t ctr_bytes = nchunks * sizeof(uint32_t);
+    if (ctr_bytes < (2u << 20)) ctr_bytes = 2u << 20;
+    if (cudaMalloc((void **)&f->counters, ctr_bytes) != cudaSuccess ||
+        cudaMemset(f->counters, 0, ctr_bytes) != cudaSuccess ||
         cudaEventCreate(&f->ev0) != cudaSuccess || cudaEventCreate(&f->ev1) != cudaSuccess ||
         cudaDeviceSynchronize() != cudaSuccess) {
         set_error("mxb_fanout_create: CUDA allocation failed: %s",

@@ -131,7 +131,7 @@ struct mxb_ring {
 namespace {
 
 constexpr uint64_t kPackAlign = 256;
-constexpr uint64_t kGatherPiece = 4ull << 20;  // bytes of host memcpy per work item
+constexpr uint64_t kGatherPiece = 1ull << 20;  // bytes of host memcpy per work item
 
 inline uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
 

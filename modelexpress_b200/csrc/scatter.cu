@@ -70,6 +70,50 @@ __device__ __forceinline__ void copy_span_w(char *d, const char *s, uint64_t n, 
     for (uint64_t i = done + t; i < n; i += T) d[i] = s[i];
 }
 
+// Destination 16-byte aligned, source only A-byte aligned (A = 8 or 4): every
+// 16-byte store is assembled from 16/A narrower loads, so a checkpoint whose
+// data section starts 8 bytes off a 16-byte boundary still moves at full width
+// on the store side.
+template <typename S>
+__device__ __forceinline__ uint4 gather16(const S *p);
+template <>
+__device__ __forceinline__ uint4 gather16<uint2>(const uint2 *p) {
+    uint2 a = __ldcs(p), b = __ldcs(p + 1);
+    return make_uint4(a.x, a.y, b.x, b.y);
+}
+template <>
+__device__ __forceinline__ uint4 gather16<uint32_t>(const uint32_t *p) {
+    return make_uint4(__ldcs(p), __ldcs(p + 1), __ldcs(p + 2), __ldcs(p + 3));
+}
+
+template <typename S>
+__device__ __forceinline__ void copy_span_shift(char *d, const char *s, uint64_t n, uint32_t t,
+                                                uint32_t T) {
+    constexpr uint64_t PER = 16 / sizeof(S);
+    uint64_t head = (16 - ((uint64_t)(uintptr_t)d & 15)) & 15;
+    if (head > n) head = n;
+    for (uint64_t i = t; i < head; i += T) d[i] = s[i];
+    d += head;
+    s += head;
+    n -= head;
+    const uint64_t nv = n >> 4;
+    uint4 *dv = reinterpret_cast<uint4 *>(d);
+    const S *sv = reinterpret_cast<const S *>(s);
+    uint64_t i = t;
+    for (; i + 3ull * T < nv; i += 4ull * T) {
+        uint4 a = gather16<S>(sv + i * PER);
+        uint4 b = gather16<S>(sv + (i + T) * PER);
+        uint4 c = gather16<S>(sv + (i + 2ull * T) * PER);
+        uint4 e = gather16<S>(sv + (i + 3ull * T) * PER);
+        __stcs(dv + i, a);
+        __stcs(dv + i + T, b);
+        __stcs(dv + i + 2ull * T, c);
+        __stcs(dv + i + 3ull * T, e);
+    }
+    for (; i < nv; i += T) __stcs(dv + i, gather16<S>(sv + i * PER));
+    for (uint64_t j = (nv << 4) + t; j < n; j += T) d[j] = s[j];
+}
+
 // Copy an arbitrary byte span with T threads (t = this thread's index).
 __device__ __forceinline__ void copy_span(char *d, const char *s, uint64_t n, uint32_t t,
                                           uint32_t T) {
@@ -77,9 +121,9 @@ __device__ __forceinline__ void copy_span(char *d, const char *s, uint64_t n, ui
     if (mis == 0)
         copy_span_w<uint4>(d, s, n, t, T);
     else if ((mis & 7u) == 0)
-        copy_span_w<uint2>(d, s, n, t, T);
+        copy_span_shift<uint2>(d, s, n, t, T);
     else if ((mis & 3u) == 0)
-        copy_span_w<uint32_t>(d, s, n, t, T);
+        copy_span_shift<uint32_t>(d, s, n, t, T);
     else if ((mis & 1u) == 0)
         copy_span_w<uint16_t>(d, s, n, t, T);
     else
@@ -463,6 +507,11 @@ int32_t mxb_table_launch(mxb_table *t, uint32_t flags) {
 }
 
 uint64_t mxb_table_bytes(mxb_table *t) { return t ? t->bytes_moved : 0; }
+
+int32_t mxb_table_engine(mxb_table *t, uint32_t flags) {
+    if (!t) return MXB_ERR_ARG;
+    return ((flags & MXB_SCATTER_BULK) && t->tb.bulk_ok) ? 1 : 0;
+}
 
 int32_t mxb_table_destroy(mxb_table *t) {
     if (!t) return MXB_OK;

@@ -147,6 +147,10 @@ class Table:
     def nbytes(self) -> int:
         return int(self.ctx._lib.mxb_table_bytes(self._h))
 
+    def engine(self, flags: int = SCATTER_DEFAULT) -> str:
+        """Which tile engine a launch with ``flags`` runs: "vector" or "bulk"."""
+        return "bulk" if self.ctx._lib.mxb_table_engine(self._h, int(flags)) == 1 else "vector"
+
     def launch(self, flags: int = SCATTER_DEFAULT) -> None:
         check(self.ctx._lib.mxb_table_launch(self._h, int(flags)), "mxb_table_launch")
 
