@@ -201,7 +201,7 @@ def bench_place(args):
     import torch
 
     from modelexpress_b200 import layout, loader
-    from modelexpress_b200.runtime import (PLACE_COPY_ENGINE, PLACE_ZERO_COPY, SCATTER_BULK,
+    from modelexpress_b200.runtime import (PLACE_COPY_ENGINE, PLACE_ZERO_COPY, SCATTER_VECTOR,
                                            SCATTER_DEFAULT, Context)
     from modelexpress_b200.safetensors_index import checkpoint_index
 
@@ -266,7 +266,7 @@ def bench_place(args):
         v.zero_()
     torch.cuda.synchronize()
     table = ctx.table(dev_items, local)
-    flags = SCATTER_BULK if os.environ.get("MXB_SCATTER", "vec") == "bulk" else SCATTER_DEFAULT
+    flags = SCATTER_VECTOR if os.environ.get("MXB_SCATTER", "auto") == "vec" else SCATTER_DEFAULT
     for _ in range(max(3, args.warmup)):
         table.launch(flags)
     ctx.sync(local)
@@ -301,7 +301,7 @@ def bench_place(args):
     ms_per_step = ms / args.steps
     peak, peak_src = measured_peak()
     achieved = 2.0 * bytes_placed / (ms_per_step * 1e-3) / 1e9  # read + write per GPU
-    kernel = "scatter_bulk_kernel" if table.engine(flags) == "bulk" else "scatter_vec_kernel"
+    kernel = "scatter_vec_kernel" if table.engine(flags) == "vector" else "scatter_bulk_kernel"
     out = {
         "metric": "GB/s placed into HBM (Llama-3-8B bf16, TP=8 shards)",
         "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,

@@ -130,8 +130,10 @@ int64_t mxb_coalesce_runs(const mxb_run *runs, uint64_t n, mxb_desc2d *out, uint
 
 /* ---- kernel 1/3: descriptor-driven scatter ----------------------------- */
 
-#define MXB_SCATTER_DEFAULT 0u
-#define MXB_SCATTER_BULK 1u    /* move large 16-byte-aligned rows with cp.async.bulk */
+#define MXB_SCATTER_DEFAULT 0u /* bulk engine (cp.async.bulk) for records whose addresses,
+                                  pitches and row sizes are multiples of 16 bytes with rows
+                                  of at least 1 KiB; vector engine for the rest */
+#define MXB_SCATTER_VECTOR 1u  /* vector engine (16-byte loads/stores) for everything */
 #define MXB_SCATTER_NO_SYNC 2u /* return after enqueueing on the context stream */
 
 /* One persistent launch on `dev` moves every record of the host table
@@ -157,8 +159,8 @@ int32_t mxb_table_create(mxb_ctx *ctx, int32_t dev, const mxb_desc2d *descs, uin
 int32_t mxb_table_launch(mxb_table *t, uint32_t flags);
 /* Bytes one launch moves. */
 uint64_t mxb_table_bytes(mxb_table *t);
-/* Tile engine a launch with `flags` uses: 0 = vector loads/stores, 1 = bulk
- * copies (only when MXB_SCATTER_BULK is set and every record qualifies). */
+/* Tile engines a launch with `flags` uses: 0 = vector only, 1 = bulk only,
+ * 2 = bulk for the qualifying records and vector for the rest (two kernels). */
 int32_t mxb_table_engine(mxb_table *t, uint32_t flags);
 int32_t mxb_table_destroy(mxb_table *t);
 

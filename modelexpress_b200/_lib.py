@@ -18,7 +18,7 @@ ERR_NAMES = {-1: "MXB_ERR_ARG", -2: "MXB_ERR_BOUNDS", -3: "MXB_ERR_ALIGN", -4: "
              -5: "MXB_ERR_TIMEOUT", -6: "MXB_ERR_PEER", -7: "MXB_ERR_NOMEM", -8: "MXB_ERR_STATE"}
 
 DIGEST_SAFE32, DIGEST_ROWS, DIGEST_BLOCK64 = 1, 2, 4
-SCATTER_DEFAULT, SCATTER_BULK, SCATTER_NO_SYNC = 0, 1, 2
+SCATTER_DEFAULT, SCATTER_VECTOR, SCATTER_NO_SYNC = 0, 1, 2
 PLACE_COPY_ENGINE, PLACE_ZERO_COPY = 0, 1
 FANOUT_MAX_CHILDREN = 7
 

@@ -93,23 +93,26 @@ int32_t check_status(DeviceState *d);
 constexpr uint64_t kTileBytes = 64 * 1024;
 uint64_t tiles_of(const mxb_desc2d &d);
 
-// A descriptor table cut into tiles, resident on the device.
+// A descriptor table cut into tiles, resident on the device.  The tiles of
+// records that meet the bulk engine's rules come first, the rest after them.
 struct ScatterTable {
     const mxb_desc2d *descs = nullptr;  // device
-    const void *tiles = nullptr;        // device, Tile records
-    uint64_t total_tiles = 0;
+    const void *tiles = nullptr;        // device, Tile records: [bulk tiles | vector tiles]
+    uint64_t n_bulk = 0, n_vec = 0;
     size_t bytes = 0;
-    bool bulk_ok = false;  // every record meets the bulk engine's alignment rules
 };
 size_t scatter_table_bytes(const mxb_desc2d *descs, uint64_t n, uint64_t *live_out,
                            uint64_t *tiles_out);
 // Fill host_buf with the table image whose device copy will live at dev_buf.
-// tile_begin_of_desc (n+1 entries, optional) receives each input record's first tile.
+// bulk_begin / vec_begin (n+1 entries each, optional) receive, per input record,
+// its first tile in the bulk list and in the vector list.
 int32_t build_scatter_table(const mxb_desc2d *descs, uint64_t n, void *host_buf, void *dev_buf,
-                            ScatterTable *out, uint64_t *tile_begin_of_desc);
+                            ScatterTable *out, uint64_t *bulk_begin, uint64_t *vec_begin);
+// Launch the bulk engine over a range of the bulk list and the vector engine
+// over a range of the vector list (MXB_SCATTER_VECTOR: vector engine for both).
 int32_t launch_scatter_tiles(mxb_ctx *ctx, DeviceState *dv, const ScatterTable &tb,
-                             uint64_t tile_begin, uint64_t tile_count, uint32_t flags,
-                             cudaStream_t stream);
+                             uint64_t bulk_begin, uint64_t bulk_count, uint64_t vec_begin,
+                             uint64_t vec_count, uint32_t flags, cudaStream_t stream);
 
 // Launchers implemented in the kernel files.
 int32_t launch_scatter(mxb_ctx *ctx, DeviceState *d, const mxb_desc2d *descs, uint64_t n,

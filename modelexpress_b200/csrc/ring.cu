@@ -324,11 +324,11 @@ int32_t mxb_place(mxb_ring *r, const mxb_desc2d *items, uint64_t n, int32_t host
         r->table_bytes = want;
     }
     ScatterTable tb;
-    std::vector<uint64_t> tile_begin(descs.size() + 1, 0);
+    std::vector<uint64_t> bulk_begin(descs.size() + 1, 0), vec_begin(descs.size() + 1, 0);
     if (!descs.empty()) {
         MXB_CUDA(cudaStreamSynchronize(dv->stream));
         rc = build_scatter_table(descs.data(), descs.size(), r->table_host, r->table_dev, &tb,
-                                 tile_begin.data());
+                                 bulk_begin.data(), vec_begin.data());
         if (rc != MXB_OK) return rc;
         MXB_CUDA(cudaMemcpyAsync(r->table_dev, r->table_host, tb.bytes, cudaMemcpyHostToDevice,
                                  dv->stream));
@@ -371,10 +371,12 @@ int32_t mxb_place(mxb_ring *r, const mxb_desc2d *items, uint64_t n, int32_t host
         r->pool->run(pieces);
         gather_s += std::chrono::duration<double>(clk::now() - g0).count();
 
-        const uint64_t tb0 = tile_begin[ch.desc_begin], tb1 = tile_begin[ch.desc_end];
+        const uint64_t b0 = bulk_begin[ch.desc_begin], b1 = bulk_begin[ch.desc_end];
+        const uint64_t v0 = vec_begin[ch.desc_begin], v1 = vec_begin[ch.desc_end];
+        // the zero-copy source is pinned host memory: plain loads, not bulk copies
+        const uint32_t eng = zero_copy ? MXB_SCATTER_VECTOR : MXB_SCATTER_DEFAULT;
         if (zero_copy) {
-            rc = launch_scatter_tiles(r->ctx, dv, tb, tb0, tb1 - tb0, MXB_SCATTER_DEFAULT,
-                                      dv->stream);
+            rc = launch_scatter_tiles(r->ctx, dv, tb, b0, b1 - b0, v0, v1 - v0, eng, dv->stream);
             if (rc != MXB_OK) return rc;
             MXB_CUDA(cudaEventRecord(r->slot_free[slot], dv->stream));
         } else {
@@ -385,8 +387,7 @@ int32_t mxb_place(mxb_ring *r, const mxb_desc2d *items, uint64_t n, int32_t host
                                      dv->copy_stream));
             MXB_CUDA(cudaEventRecord(r->slot_free[slot], dv->copy_stream));
             MXB_CUDA(cudaStreamWaitEvent(dv->stream, r->slot_free[slot], 0));
-            rc = launch_scatter_tiles(r->ctx, dv, tb, tb0, tb1 - tb0,
-                                      MXB_SCATTER_DEFAULT, dv->stream);
+            rc = launch_scatter_tiles(r->ctx, dv, tb, b0, b1 - b0, v0, v1 - v0, eng, dv->stream);
             if (rc != MXB_OK) return rc;
             MXB_CUDA(cudaEventRecord(r->stage_free[st], dv->stream));
             stage_used[st] = true;

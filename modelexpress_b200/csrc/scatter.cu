@@ -338,16 +338,13 @@ scatter_bulk_kernel(const mxb_desc2d *__restrict__ descs, const Tile *__restrict
 // launcher
 // ---------------------------------------------------------------------------
 
-static bool all_bulk_ok(const mxb_desc2d *d, uint64_t n) {
-    for (uint64_t i = 0; i < n; ++i) {
-        if (d[i].rows == 0 || d[i].row_bytes == 0) continue;
-        if ((d[i].src | d[i].dst | d[i].row_bytes) & 15u) return false;
-        if (d[i].rows > 1 && ((d[i].src_pitch | d[i].dst_pitch) & 15u)) return false;
-        // the bulk engine issues one copy per row; short rows are better served
-        // by the vector engine
-        if (d[i].row_bytes < 1024) return false;
-    }
-    return true;
+// A record goes to the bulk engine when every address, pitch and row size is a
+// multiple of 16 bytes (cp.async.bulk's rule) and rows are long enough for one
+// bulk copy per row to pay; everything else goes to the vector engine.
+static bool bulk_ok(const mxb_desc2d &d) {
+    if ((d.src | d.dst | d.row_bytes) & 15u) return false;
+    if (d.rows > 1 && ((d.src_pitch | d.dst_pitch) & 15u)) return false;
+    return d.row_bytes >= 1024;
 }
 
 size_t scatter_table_bytes(const mxb_desc2d *descs, uint64_t n, uint64_t *live_out,
@@ -366,7 +363,7 @@ size_t scatter_table_bytes(const mxb_desc2d *descs, uint64_t n, uint64_t *live_o
 }
 
 int32_t build_scatter_table(const mxb_desc2d *descs, uint64_t n, void *host_buf, void *dev_buf,
-                            ScatterTable *out, uint64_t *tile_begin_of_desc) {
+                            ScatterTable *out, uint64_t *bulk_begin, uint64_t *vec_begin) {
     uint64_t live = 0, total = 0;
     scatter_table_bytes(descs, n, &live, &total);
     if (live > 0xffffffffull) {
@@ -376,54 +373,81 @@ int32_t build_scatter_table(const mxb_desc2d *descs, uint64_t n, void *host_buf,
     const size_t desc_bytes = (live * sizeof(mxb_desc2d) + 255) & ~size_t(255);
     mxb_desc2d *hd = reinterpret_cast<mxb_desc2d *>(host_buf);
     Tile *ht = reinterpret_cast<Tile *>(reinterpret_cast<char *>(host_buf) + desc_bytes);
-    uint64_t di = 0, ti = 0;
+    // pass 1: count the bulk tiles so the two lists can be laid out back to back
+    uint64_t n_bulk = 0;
     for (uint64_t i = 0; i < n; ++i) {
-        if (tile_begin_of_desc) tile_begin_of_desc[i] = ti;
         uint64_t t = tiles_of(descs[i]);
-        if (!t) continue;
         if (t > 0xffffffffull) {
             set_error("descriptor %llu has too many tiles", (unsigned long long)i);
             return MXB_ERR_ARG;
         }
+        if (t && bulk_ok(descs[i])) n_bulk += t;
+    }
+    uint64_t di = 0, bi = 0, vi = 0;
+    Tile *hb = ht, *hv = ht + n_bulk;
+    for (uint64_t i = 0; i < n; ++i) {
+        if (bulk_begin) bulk_begin[i] = bi;
+        if (vec_begin) vec_begin[i] = vi;
+        uint64_t t = tiles_of(descs[i]);
+        if (!t) continue;
         hd[di] = descs[i];
-        for (uint64_t k = 0; k < t; ++k) ht[ti++] = Tile{(uint32_t)di, (uint32_t)k};
+        if (bulk_ok(descs[i]))
+            for (uint64_t k = 0; k < t; ++k) hb[bi++] = Tile{(uint32_t)di, (uint32_t)k};
+        else
+            for (uint64_t k = 0; k < t; ++k) hv[vi++] = Tile{(uint32_t)di, (uint32_t)k};
         ++di;
     }
-    if (tile_begin_of_desc) tile_begin_of_desc[n] = ti;
+    if (bulk_begin) bulk_begin[n] = bi;
+    if (vec_begin) vec_begin[n] = vi;
     out->descs = reinterpret_cast<const mxb_desc2d *>(dev_buf);
     out->tiles = reinterpret_cast<const char *>(dev_buf) + desc_bytes;
-    out->total_tiles = total;
+    out->n_bulk = n_bulk;
+    out->n_vec = total - n_bulk;
     out->bytes = desc_bytes + total * sizeof(Tile);
-    out->bulk_ok = all_bulk_ok(hd, live);
+    return MXB_OK;
+}
+
+static int32_t launch_vec(mxb_ctx *ctx, DeviceState *dv, const mxb_desc2d *dd, const Tile *dt,
+                          uint64_t count, cudaStream_t stream) {
+    if (!count) return MXB_OK;
+    uint64_t grid = (uint64_t)dv->sm_count * 4;
+    if (grid > count) grid = count;
+    scatter_vec_kernel<<<(unsigned)grid, kVecThreads, 0, stream>>>(dd, dt, count);
+    MXB_CUDA(cudaGetLastError());
+    ctx->launches.fetch_add(1);
+    return MXB_OK;
+}
+
+static int32_t launch_bulk(mxb_ctx *ctx, DeviceState *dv, const mxb_desc2d *dd, const Tile *dt,
+                           uint64_t count, cudaStream_t stream) {
+    if (!count) return MXB_OK;
+    static bool attr_set[64] = {};
+    const size_t smem = (size_t)kBulkStages * kTileBytes;
+    if (dv->device < 64 && !attr_set[dv->device]) {
+        MXB_CUDA(cudaFuncSetAttribute(scatter_bulk_kernel,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set[dv->device] = true;
+    }
+    uint64_t grid = (uint64_t)dv->sm_count;
+    if (grid > count) grid = count;
+    scatter_bulk_kernel<<<(unsigned)grid, 32, smem, stream>>>(dd, dt, count, dv->status);
+    MXB_CUDA(cudaGetLastError());
+    ctx->launches.fetch_add(1);
     return MXB_OK;
 }
 
 int32_t launch_scatter_tiles(mxb_ctx *ctx, DeviceState *dv, const ScatterTable &tb,
-                             uint64_t tile_begin, uint64_t tile_count, uint32_t flags,
-                             cudaStream_t stream) {
-    if (tile_count == 0) return MXB_OK;
-    const Tile *dt = reinterpret_cast<const Tile *>(tb.tiles) + tile_begin;
-    const bool bulk = (flags & MXB_SCATTER_BULK) && tb.bulk_ok;
-    if (bulk) {
-        static bool attr_set[64] = {};
-        const size_t smem = (size_t)kBulkStages * kTileBytes;
-        if (dv->device < 64 && !attr_set[dv->device]) {
-            MXB_CUDA(cudaFuncSetAttribute(scatter_bulk_kernel,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr_set[dv->device] = true;
-        }
-        uint64_t grid = (uint64_t)dv->sm_count;
-        if (grid > tile_count) grid = tile_count;
-        scatter_bulk_kernel<<<(unsigned)grid, 32, smem, stream>>>(tb.descs, dt, tile_count,
-                                                                   dv->status);
-    } else {
-        uint64_t grid = (uint64_t)dv->sm_count * 4;
-        if (grid > tile_count) grid = tile_count;
-        scatter_vec_kernel<<<(unsigned)grid, kVecThreads, 0, stream>>>(tb.descs, dt, tile_count);
-    }
-    MXB_CUDA(cudaGetLastError());
-    ctx->launches.fetch_add(1);
-    return MXB_OK;
+                             uint64_t bulk_begin, uint64_t bulk_count, uint64_t vec_begin,
+                             uint64_t vec_count, uint32_t flags, cudaStream_t stream) {
+    const Tile *bulk_tiles = reinterpret_cast<const Tile *>(tb.tiles) + bulk_begin;
+    const Tile *vec_tiles = reinterpret_cast<const Tile *>(tb.tiles) + tb.n_bulk + vec_begin;
+    int32_t rc;
+    if (flags & MXB_SCATTER_VECTOR)
+        rc = launch_vec(ctx, dv, tb.descs, bulk_tiles, bulk_count, stream);
+    else
+        rc = launch_bulk(ctx, dv, tb.descs, bulk_tiles, bulk_count, stream);
+    if (rc != MXB_OK) return rc;
+    return launch_vec(ctx, dv, tb.descs, vec_tiles, vec_count, stream);
 }
 
 int32_t launch_scatter(mxb_ctx *ctx, DeviceState *dv, const mxb_desc2d *descs, uint64_t n,
@@ -436,10 +460,10 @@ int32_t launch_scatter(mxb_ctx *ctx, DeviceState *dv, const mxb_desc2d *descs, u
     // the pinned staging copy is reused by every call: wait for the previous upload
     MXB_CUDA(cudaStreamSynchronize(stream));
     ScatterTable tb;
-    rc = build_scatter_table(descs, n, dv->table_host, dv->table, &tb, nullptr);
+    rc = build_scatter_table(descs, n, dv->table_host, dv->table, &tb, nullptr, nullptr);
     if (rc != MXB_OK) return rc;
     MXB_CUDA(cudaMemcpyAsync(dv->table, dv->table_host, tb.bytes, cudaMemcpyHostToDevice, stream));
-    return launch_scatter_tiles(ctx, dv, tb, 0, tb.total_tiles, flags, stream);
+    return launch_scatter_tiles(ctx, dv, tb, 0, tb.n_bulk, 0, tb.n_vec, flags, stream);
 }
 
 }  // namespace mxb
@@ -483,7 +507,7 @@ int32_t mxb_table_create(mxb_ctx *ctx, int32_t dev, const mxb_desc2d *descs, uin
             delete t;
             return MXB_ERR_NOMEM;
         }
-        rc = build_scatter_table(descs, n, host.data(), t->dev_buf, &t->tb, nullptr);
+        rc = build_scatter_table(descs, n, host.data(), t->dev_buf, &t->tb, nullptr, nullptr);
         if (rc == MXB_OK &&
             cudaMemcpy(t->dev_buf, host.data(), t->tb.bytes, cudaMemcpyHostToDevice) != cudaSuccess) {
             set_error("table upload failed");
@@ -503,14 +527,16 @@ int32_t mxb_table_create(mxb_ctx *ctx, int32_t dev, const mxb_desc2d *descs, uin
 int32_t mxb_table_launch(mxb_table *t, uint32_t flags) {
     if (!t) return MXB_ERR_ARG;
     DeviceGuard g(t->dv->device);
-    return launch_scatter_tiles(t->ctx, t->dv, t->tb, 0, t->tb.total_tiles, flags, t->dv->stream);
+    return launch_scatter_tiles(t->ctx, t->dv, t->tb, 0, t->tb.n_bulk, 0, t->tb.n_vec, flags,
+                                t->dv->stream);
 }
 
 uint64_t mxb_table_bytes(mxb_table *t) { return t ? t->bytes_moved : 0; }
 
 int32_t mxb_table_engine(mxb_table *t, uint32_t flags) {
     if (!t) return MXB_ERR_ARG;
-    return ((flags & MXB_SCATTER_BULK) && t->tb.bulk_ok) ? 1 : 0;
+    if ((flags & MXB_SCATTER_VECTOR) || t->tb.n_bulk == 0) return 0;
+    return t->tb.n_vec == 0 ? 1 : 2;
 }
 
 int32_t mxb_table_destroy(mxb_table *t) {

@@ -13,10 +13,10 @@ import numpy as np
 
 from . import _lib
 from ._lib import (DIGEST_BLOCK64, DIGEST_ROWS, DIGEST_SAFE32, PLACE_COPY_ENGINE,
-                   PLACE_ZERO_COPY, SCATTER_BULK, SCATTER_DEFAULT, SCATTER_NO_SYNC, check)
+                   PLACE_ZERO_COPY, SCATTER_VECTOR, SCATTER_DEFAULT, SCATTER_NO_SYNC, check)
 
 __all__ = ["Context", "Ring", "Fanout", "Table", "PlaceResult", "default_context",
-           "DIGEST_SAFE32", "DIGEST_ROWS", "DIGEST_BLOCK64", "SCATTER_DEFAULT", "SCATTER_BULK",
+           "DIGEST_SAFE32", "DIGEST_ROWS", "DIGEST_BLOCK64", "SCATTER_DEFAULT", "SCATTER_VECTOR",
            "SCATTER_NO_SYNC", "PLACE_COPY_ENGINE", "PLACE_ZERO_COPY"]
 
 
@@ -148,8 +148,8 @@ class Table:
         return int(self.ctx._lib.mxb_table_bytes(self._h))
 
     def engine(self, flags: int = SCATTER_DEFAULT) -> str:
-        """Which tile engine a launch with ``flags`` runs: "vector" or "bulk"."""
-        return "bulk" if self.ctx._lib.mxb_table_engine(self._h, int(flags)) == 1 else "vector"
+        """Which tile engines a launch with ``flags`` runs: "vector", "bulk" or "bulk+vector"."""
+        return ("vector", "bulk", "bulk+vector")[self.ctx._lib.mxb_table_engine(self._h, int(flags))]
 
     def launch(self, flags: int = SCATTER_DEFAULT) -> None:
         check(self.ctx._lib.mxb_table_launch(self._h, int(flags)), "mxb_table_launch")

@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 
 def test_bulk_engine_matches_vector_engine(env):
     ctx, torch = env
-    from modelexpress_b200.runtime import SCATTER_BULK
+    from modelexpress_b200.runtime import SCATTER_DEFAULT, SCATTER_VECTOR
 
     rng = np.random.default_rng(9)
     src = golden_bytes(77, 24 << 20)
@@ -27,8 +27,24 @@ def test_bulk_engine_matches_vector_engine(env):
         s0 = 16 * int(rng.integers(0, (src.size - span_s) // 16))
         recs.append((s0, dpos, rows, rb, sp, dp))
         dpos += (span_d + 255) // 256 * 256
-    got, want = _run_both(ctx, torch, src, dpos, recs, SCATTER_BULK)
+    got, want = _run_both(ctx, torch, src, dpos, recs, SCATTER_DEFAULT)
     assert np.array_equal(got, want)
+    got2, _ = _run_both(ctx, torch, src, dpos, recs, SCATTER_VECTOR)
+    assert np.array_equal(got2, want)
+    tb = ctx.table([(1 << 20, 2 << 20, 4, 2048, 4096, 2048)])  # addresses only classified, never launched
+    assert tb.engine(SCATTER_DEFAULT) == "bulk" and tb.engine(SCATTER_VECTOR) == "vector"
+    tb.close()
+    # a mixed table: most records qualify for bulk copies, some do not (odd offsets, short rows)
+    mixed, pos = list(recs), dpos
+    for k in range(12):
+        rows, rb = int(rng.integers(1, 50)), int(rng.integers(1, 900))
+        mixed.append((int(rng.integers(0, 1 << 20)) | 1, pos + 3, rows, rb, rb + 5, rb + 7))
+        pos += 3 + rows * (rb + 7) + 64
+    got3, want3 = _run_both(ctx, torch, src, pos, mixed, SCATTER_DEFAULT)
+    assert np.array_equal(got3, want3)
+    tb = ctx.table([(1 << 20, 2 << 20, 4, 2048, 4096, 2048), ((1 << 20) + 1, 3 << 20, 1, 64, 64, 64)])
+    assert tb.engine(SCATTER_DEFAULT) == "bulk+vector"
+    tb.close()
     assert ctx.launch_count > 0
 
 
