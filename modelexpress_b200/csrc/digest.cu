@@ -72,8 +72,8 @@ __device__ __forceinline__ uint4 load16(const unsigned char *p, uint64_t off, ui
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-__device__ __forceinline__ int64_t warp_sum_i64(int64_t v) {
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+__device__ __forceinline__ uint64_t warp_sum_u64(uint64_t v) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, (unsigned long long)v, o);
     return v;
 }
 __device__ __forceinline__ uint64_t warp_xor_u64(uint64_t v) {
@@ -110,102 +110,152 @@ __device__ __forceinline__ void flush(WarpAcc &a, DigestAcc *acc, uint32_t lane)
     a.safe = 0;
 }
 
-__global__ void __launch_bounds__(kDigestThreads, 2)
+// What one warp needs to know about the row it is digesting.
+struct RowMeta {
+    uint64_t n = 0;        // span length
+    uint64_t row = 0;      // 4 KiB row index inside the span
+    uint32_t span = 0xffffffffu;
+    bool valid = false;    // the row holds at least one byte
+};
+
+// Read the tile record, its span, and issue this lane's eight 16-byte loads.
+__device__ __forceinline__ void fetch_row(const mxb_span *__restrict__ spans,
+                                          const DTile *__restrict__ tiles, uint64_t t,
+                                          uint32_t warp, uint32_t lane, RowMeta &m, uint4 (&v)[8]) {
+    const DTile tile = tiles[t];
+    const mxb_span sp = spans[tile.span];
+    m.span = tile.span;
+    m.n = sp.nbytes;
+    m.row = (uint64_t)tile.local * (kDigestTile / kRowBytes) + warp;
+    const uint64_t row_off = m.row * kRowBytes;
+    m.valid = row_off < m.n;
+    if (!m.valid) return;
+    const unsigned char *p = reinterpret_cast<const unsigned char *>(sp.ptr);
+    const bool aligned16 = ((sp.ptr & 15ull) == 0);
+#pragma unroll
+    for (int s = 0; s < 8; ++s) v[s] = load16(p, row_off + s * 512 + lane * 16, m.n, aligned16);
+}
+
+template <uint32_t MODES>
+__device__ __forceinline__ void digest_row(const RowMeta &m, const uint4 (&v)[8], uint32_t lane,
+                                           WarpAcc &a, unsigned long long *__restrict__ block_out) {
+    const uint64_t row_off = m.row * kRowBytes;
+    if (MODES & MXB_DIGEST_SAFE32) {
+        // weight of byte k of word m of step s of this lane:
+        //   ((row_off + lane*16) * K + 1)  +  (512*s) * K  +  (4*m + k) * K      (mod 2^32)
+        // so three dp4a chains over the 32 words are enough: A = sum of bytes,
+        // B = sum of bytes * s, X = sum of bytes * (4*m + k).  Bytes past the end
+        // of the span were loaded as zero and add nothing.
+        uint32_t A = 0, B = 0, X = 0;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            const uint32_t w[4] = {v[s].x, v[s].y, v[s].z, v[s].w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                A = __dp4a(w[q], 0x01010101u, A);
+                if (s) B = __dp4a(w[q], 0x01010101u * (uint32_t)s, B);
+                X = __dp4a(w[q], 0x03020100u + 0x04040404u * (uint32_t)q, X);
+            }
+        }
+        const uint32_t base = (uint32_t)(row_off + lane * 16) * kKnuth + 1u;
+        a.safe += warp_sum_u32(base * A + (512u * kKnuth) * B + kKnuth * X);
+    }
+    if (MODES & MXB_DIGEST_ROWS) {
+        const uint64_t whole_rows = (m.n / 4) / 1024;  // rows made only of whole words
+        if (m.row < whole_rows) {
+            int64_t s64 = 0;
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+                s64 += (int64_t)(int32_t)v[s].x + (int64_t)(int32_t)v[s].y +
+                       (int64_t)(int32_t)v[s].z + (int64_t)(int32_t)v[s].w;
+            const uint64_t rs = warp_sum_u64((uint64_t)s64);
+            a.row_sum += rs;
+            a.row_sum_w += rs * (m.row + 1);
+        } else {
+            // the partial last row: whole words are the "tail", the rest is ragged bytes
+            const uint64_t body = m.n - (m.n % 4);
+            uint64_t ts = 0, tw = 0, rg = 0;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                const uint64_t off = row_off + s * 512 + lane * 16;
+                const uint32_t w[4] = {v[s].x, v[s].y, v[s].z, v[s].w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const uint64_t wo = off + 4 * q;
+                    if (wo + 4 <= body) {
+                        const uint64_t val = (uint64_t)(int64_t)(int32_t)w[q];
+                        ts += val;
+                        tw += val * ((wo - row_off) / 4 + 1);
+                    } else if (wo < m.n) {
+                        rg += __dp4a(w[q], 0x01010101u, 0u);  // zero-filled above n
+                    }
+                }
+            }
+            a.tail_sum += warp_sum_u64(ts);
+            a.tail_sum_w += warp_sum_u64(tw);
+            a.ragged += warp_sum_u64(rg);
+        }
+    }
+    if (MODES & MXB_DIGEST_BLOCK64) {
+        uint64_t h = kP5 + (uint64_t)lane * kP4;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            const uint64_t x0 = (uint64_t)v[s].x | ((uint64_t)v[s].y << 32);
+            const uint64_t x1 = (uint64_t)v[s].z | ((uint64_t)v[s].w << 32);
+            h = rotl64(h + x0 * kP2, 31) * kP1;
+            h = rotl64(h + x1 * kP2, 31) * kP1;
+        }
+        h = warp_xor_u64(rotl64(h * kP3, 2 * (int)lane + 1));
+        h = avalanche(h);
+        if (block_out && lane == 0) block_out[m.row] = h;
+        a.block += avalanche(h + (m.row + 1) * kP1);
+    }
+}
+
+// Software-pipelined: the loads of the warp's next row are in flight while the
+// current row is reduced, so the memory system never waits for the arithmetic.
+template <uint32_t MODES>
+__global__ void __launch_bounds__(kDigestThreads, 1)
 digest_kernel(const mxb_span *__restrict__ spans, const DTile *__restrict__ tiles,
-              uint64_t total_tiles, uint32_t modes, DigestAcc *__restrict__ acc,
+              uint64_t total_tiles, DigestAcc *__restrict__ acc,
               unsigned long long *__restrict__ block_out) {
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     WarpAcc a;
-    for (uint64_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-        const DTile tile = tiles[t];
-        if (tile.span != a.span) {
+    RowMeta cur, nxt;
+    uint4 vc[8], vn[8];
+    uint64_t t = blockIdx.x;
+    if (t >= total_tiles) return;
+    fetch_row(spans, tiles, t, warp, lane, cur, vc);
+    for (;;) {
+        const uint64_t tn = t + gridDim.x;
+        const bool more = tn < total_tiles;
+        if (more) fetch_row(spans, tiles, tn, warp, lane, nxt, vn);
+        if (cur.span != a.span) {
             flush(a, acc, lane);
-            a.span = tile.span;
+            a.span = cur.span;
         }
-        const mxb_span sp = spans[tile.span];
-        const unsigned char *p = reinterpret_cast<const unsigned char *>(sp.ptr);
-        const uint64_t n = sp.nbytes;
-        const bool aligned16 = ((sp.ptr & 15ull) == 0);
-        const uint64_t row = (uint64_t)tile.local * (kDigestTile / kRowBytes) + warp;
-        const uint64_t row_off = row * kRowBytes;
-        if (row_off >= n) continue;  // warp-uniform
-        const uint64_t whole_rows = (n / 4) / 1024;  // rows made only of whole words
-        const uint64_t body = n - (n % 4);
-
-        uint4 v[8];
+        if (cur.valid) digest_row<MODES>(cur, vc, lane, a, block_out);
+        if (!more) break;
+        cur = nxt;
 #pragma unroll
-        for (int s = 0; s < 8; ++s) v[s] = load16(p, row_off + s * 512 + lane * 16, n, aligned16);
-
-        if (modes & MXB_DIGEST_SAFE32) {
-            uint32_t sum = 0;
-#pragma unroll
-            for (int s = 0; s < 8; ++s) {
-                // bytes past n were loaded as zero and add nothing
-                const uint32_t i0 = (uint32_t)(row_off + s * 512 + lane * 16);
-                const uint32_t w[4] = {v[s].x, v[s].y, v[s].z, v[s].w};
-#pragma unroll
-                for (int m = 0; m < 4; ++m) {
-                    const uint32_t wm = (i0 + 4u * m) * kKnuth + 1u;
-                    sum += wm * __dp4a(w[m], 0x01010101u, 0u) +
-                           kKnuth * __dp4a(w[m], 0x03020100u, 0u);
-                }
-            }
-            a.safe += warp_sum_u32(sum);
-        }
-
-        if (modes & MXB_DIGEST_ROWS) {
-            if (row < whole_rows) {
-                int64_t s64 = 0;
-#pragma unroll
-                for (int s = 0; s < 8; ++s)
-                    s64 += (int64_t)(int32_t)v[s].x + (int64_t)(int32_t)v[s].y +
-                           (int64_t)(int32_t)v[s].z + (int64_t)(int32_t)v[s].w;
-                const uint64_t rs = (uint64_t)warp_sum_i64(s64);
-                a.row_sum += rs;
-                a.row_sum_w += rs * (row + 1);
-            } else {
-                // the partial last row: whole words are the "tail", the rest is ragged bytes
-                int64_t ts = 0;
-                uint64_t tw = 0, rg = 0;
-#pragma unroll
-                for (int s = 0; s < 8; ++s) {
-                    const uint64_t off = row_off + s * 512 + lane * 16;
-                    const uint32_t w[4] = {v[s].x, v[s].y, v[s].z, v[s].w};
-#pragma unroll
-                    for (int m = 0; m < 4; ++m) {
-                        const uint64_t wo = off + 4 * m;
-                        if (wo + 4 <= body) {
-                            const int64_t val = (int64_t)(int32_t)w[m];
-                            ts += val;
-                            tw += (uint64_t)val * ((wo - row_off) / 4 + 1);
-                        } else if (wo < n) {
-                            // zero-filled above n, so the byte sum is exact
-                            rg += __dp4a(w[m], 0x01010101u, 0u);
-                        }
-                    }
-                }
-                a.tail_sum += (uint64_t)warp_sum_i64(ts);
-                a.tail_sum_w += (uint64_t)warp_sum_i64((int64_t)tw);
-                a.ragged += (uint64_t)warp_sum_i64((int64_t)rg);
-            }
-        }
-
-        if (modes & MXB_DIGEST_BLOCK64) {
-            uint64_t h = kP5 + (uint64_t)lane * kP4;
-#pragma unroll
-            for (int s = 0; s < 8; ++s) {
-                const uint64_t x0 = (uint64_t)v[s].x | ((uint64_t)v[s].y << 32);
-                const uint64_t x1 = (uint64_t)v[s].z | ((uint64_t)v[s].w << 32);
-                h = rotl64(h + x0 * kP2, 31) * kP1;
-                h = rotl64(h + x1 * kP2, 31) * kP1;
-            }
-            h = warp_xor_u64(rotl64(h * kP3, 2 * (int)lane + 1));
-            h = avalanche(h);
-            if (block_out && lane == 0) block_out[row] = h;
-            a.block += avalanche(h + (row + 1) * kP1);
-        }
+        for (int s = 0; s < 8; ++s) vc[s] = vn[s];
+        t = tn;
     }
     flush(a, acc, lane);
+}
+
+typedef void (*digest_fn)(const mxb_span *, const DTile *, uint64_t, DigestAcc *,
+                          unsigned long long *);
+static digest_fn digest_variant(uint32_t modes) {
+    switch (modes) {
+        case 1: return digest_kernel<1>;
+        case 2: return digest_kernel<2>;
+        case 3: return digest_kernel<3>;
+        case 4: return digest_kernel<4>;
+        case 5: return digest_kernel<5>;
+        case 6: return digest_kernel<6>;
+        default: return digest_kernel<7>;
+    }
 }
 
 }  // namespace mxb
@@ -256,12 +306,13 @@ static int32_t run_digest(mxb_ctx *ctx, int32_t dev, const mxb_span *spans, uint
                              cudaMemcpyHostToDevice, d->stream));
     MXB_CUDA(cudaMemsetAsync(d->digest, 0, n * sizeof(DigestAcc), d->stream));
     if (total) {
-        uint64_t grid = (uint64_t)d->sm_count * 4;
+        // one 512-thread CTA per SM (the pipelined kernel holds two rows per lane in registers)
+        uint64_t grid = (uint64_t)d->sm_count;
         if (grid > total) grid = total;
-        digest_kernel<<<(unsigned)grid, kDigestThreads, 0, d->stream>>>(
+        digest_variant(modes)<<<(unsigned)grid, kDigestThreads, 0, d->stream>>>(
             reinterpret_cast<const mxb_span *>(d->table),
             reinterpret_cast<const DTile *>(reinterpret_cast<char *>(d->table) + span_bytes), total,
-            modes, reinterpret_cast<DigestAcc *>(d->digest),
+            reinterpret_cast<DigestAcc *>(d->digest),
             reinterpret_cast<unsigned long long *>(block_out));
         MXB_CUDA(cudaGetLastError());
         ctx->launches.fetch_add(1);

@@ -16,6 +16,9 @@
 
 namespace mxb {
 
+void stream_copy(void *dst, const void *src, size_t n);  // hostcopy.cpp
+void stream_fence();
+
 struct GatherOp {  // host memcpy work: rows of row_bytes from src (pitch) to slot offset
     const char *src;
     uint64_t slot_off;
@@ -74,12 +77,13 @@ class GatherPool {
             if (i >= ps.size()) break;
             const GatherPiece &p = ps[i];
             if (p.src_pitch == p.row_bytes && p.dst_pitch == p.row_bytes) {
-                memcpy(p.dst, p.src, p.rows * p.row_bytes);
+                stream_copy(p.dst, p.src, p.rows * p.row_bytes);
             } else {
                 for (uint64_t r = 0; r < p.rows; ++r)
-                    memcpy(p.dst + r * p.dst_pitch, p.src + r * p.src_pitch, p.row_bytes);
+                    stream_copy(p.dst + r * p.dst_pitch, p.src + r * p.src_pitch, p.row_bytes);
             }
         }
+        stream_fence();  // before the slot is handed to the copy engine / the kernel
     }
     void loop() {
         uint64_t seen = 0;
