@@ -13,6 +13,9 @@
 //             16 words, lanes combined with rotate+xor, avalanche.
 // All three are sums in a wrap-around ring, so partial results are merged with
 // atomics in any order and the answer is exact.
+#include <cstdlib>
+
+#include "bulk.cuh"
 #include "common.cuh"
 
 namespace mxb {
@@ -212,40 +215,124 @@ __device__ __forceinline__ void digest_row(const RowMeta &m, const uint4 (&v)[8]
     }
 }
 
-// Software-pipelined: the loads of the warp's next row are in flight while the
-// current row is reduced, so the memory system never waits for the arithmetic.
+// Generic engine: any alignment, ragged tails.  One row per warp per tile.
 template <uint32_t MODES>
-__global__ void __launch_bounds__(kDigestThreads, 1)
+__global__ void __launch_bounds__(kDigestThreads, 2)
 digest_kernel(const mxb_span *__restrict__ spans, const DTile *__restrict__ tiles,
               uint64_t total_tiles, DigestAcc *__restrict__ acc,
               unsigned long long *__restrict__ block_out) {
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     WarpAcc a;
-    RowMeta cur, nxt;
-    uint4 vc[8], vn[8];
-    uint64_t t = blockIdx.x;
-    if (t >= total_tiles) return;
-    fetch_row(spans, tiles, t, warp, lane, cur, vc);
-    for (;;) {
-        const uint64_t tn = t + gridDim.x;
-        const bool more = tn < total_tiles;
-        if (more) fetch_row(spans, tiles, tn, warp, lane, nxt, vn);
+    RowMeta cur;
+    uint4 vc[8];
+    for (uint64_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        fetch_row(spans, tiles, t, warp, lane, cur, vc);
         if (cur.span != a.span) {
             flush(a, acc, lane);
             a.span = cur.span;
         }
         if (cur.valid) digest_row<MODES>(cur, vc, lane, a, block_out);
-        if (!more) break;
-        cur = nxt;
-#pragma unroll
-        for (int s = 0; s < 8; ++s) vc[s] = vn[s];
-        t = tn;
     }
     flush(a, acc, lane);
 }
 
+// Bulk engine: whole 64 KiB tiles of 16-byte-aligned spans.  One elected thread
+// streams tiles into a 3-stage shared-memory ring with cp.async.bulk (192 KiB
+// in flight per SM at no register cost); the 16 warps each reduce one 4 KiB row
+// of the landed tile out of shared memory.  Waits are bounded.
+constexpr int kDigestStages = 3;
+constexpr uint32_t kDigestSpin = 1u << 22;
+
+template <uint32_t MODES>
+__global__ void __launch_bounds__(kDigestThreads, 1)
+digest_bulk_kernel(const mxb_span *__restrict__ spans, const DTile *__restrict__ tiles,
+                   uint64_t total_tiles, DigestAcc *__restrict__ acc,
+                   unsigned long long *__restrict__ block_out, uint32_t *status) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ __align__(8) uint64_t full[kDigestStages];
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    if (tid == 0) {
+        for (int s = 0; s < kDigestStages; ++s) mbar_init(&full[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const uint64_t first = blockIdx.x;
+    if (first >= total_tiles) return;
+    const uint64_t mine = (total_tiles - first + gridDim.x - 1) / gridDim.x;
+    auto issue = [&](uint64_t k) {  // thread 0 only
+        const DTile tile = tiles[first + k * gridDim.x];
+        const unsigned char *src = reinterpret_cast<const unsigned char *>(spans[tile.span].ptr) +
+                                   (uint64_t)tile.local * kDigestTile;
+        const int s = (int)(k % kDigestStages);
+        mbar_expect_tx(&full[s], (uint32_t)kDigestTile);
+        bulk_g2s(smem + (size_t)s * kDigestTile, src, (uint32_t)kDigestTile, &full[s]);
+    };
+    if (tid == 0) {
+        issue(0);
+        if (mine > 1) issue(1);
+    }
+    WarpAcc a;
+    uint64_t issued = mine > 1 ? 2 : 1;
+    uint64_t k = 0;
+    bool failed = false;
+    for (; k < mine; ++k) {
+        const int s = (int)(k % kDigestStages);
+        // stage (k+2)%3 held tile k-1, which every warp finished before the barrier below
+        if (tid == 0 && k + 2 < mine) issue(k + 2);
+        if (k + 2 < mine) issued = k + 3;
+        const DTile tile = tiles[first + k * gridDim.x];
+        RowMeta m;
+        m.span = tile.span;
+        m.n = spans[tile.span].nbytes;
+        m.row = (uint64_t)tile.local * (kDigestTile / kRowBytes) + warp;
+        m.valid = true;
+        const uint32_t parity = (uint32_t)((k / kDigestStages) & 1);
+        bool ok = false;
+        for (uint32_t spin = 0; spin < kDigestSpin && !ok; ++spin) ok = mbar_try_wait(&full[s], parity);
+        if (__syncthreads_or(!ok)) {
+            failed = true;
+            break;
+        }
+        const uint4 *row = reinterpret_cast<const uint4 *>(smem + (size_t)s * kDigestTile +
+                                                           (size_t)warp * kRowBytes);
+        uint4 v[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) v[q] = row[q * 32 + lane];
+        if (m.span != a.span) {
+            flush(a, acc, lane);
+            a.span = m.span;
+        }
+        digest_row<MODES>(m, v, lane, a, block_out);
+        __syncthreads();  // the stage may be refilled
+    }
+    flush(a, acc, lane);
+    if (failed) {
+        if (tid == 0) atomicExch(status, DEV_TIMEOUT);
+        // bounded wait for the copies still in flight before shared memory is released
+        for (uint64_t j = k; j < issued; ++j) {
+            const int s = (int)(j % kDigestStages);
+            const uint32_t parity = (uint32_t)((j / kDigestStages) & 1);
+            for (uint32_t spin = 0; spin < (1u << 16); ++spin)
+                if (mbar_try_wait(&full[s], parity)) break;
+        }
+    }
+}
+
 typedef void (*digest_fn)(const mxb_span *, const DTile *, uint64_t, DigestAcc *,
                           unsigned long long *);
+typedef void (*digest_bulk_fn)(const mxb_span *, const DTile *, uint64_t, DigestAcc *,
+                               unsigned long long *, uint32_t *);
+static digest_bulk_fn digest_bulk_variant(uint32_t modes) {
+    switch (modes) {
+        case 1: return digest_bulk_kernel<1>;
+        case 2: return digest_bulk_kernel<2>;
+        case 3: return digest_bulk_kernel<3>;
+        case 4: return digest_bulk_kernel<4>;
+        case 5: return digest_bulk_kernel<5>;
+        case 6: return digest_bulk_kernel<6>;
+        default: return digest_bulk_kernel<7>;
+    }
+}
 static digest_fn digest_variant(uint32_t modes) {
     switch (modes) {
         case 1: return digest_kernel<1>;
@@ -295,31 +382,57 @@ static int32_t run_digest(mxb_ctx *ctx, int32_t dev, const mxb_span *spans, uint
     MXB_CUDA(cudaStreamSynchronize(d->stream));
     mxb_span *hs = reinterpret_cast<mxb_span *>(d->table_host);
     DTile *ht = reinterpret_cast<DTile *>(reinterpret_cast<char *>(d->table_host) + span_bytes);
-    uint64_t ti = 0;
+    // full 64 KiB tiles of 16-byte-aligned spans go to the bulk engine (listed
+    // first), everything else (ragged last tiles, unaligned spans) to the generic one
+    const bool allow_bulk = getenv("MXB_DIGEST_GENERIC") == nullptr;
+    uint64_t n_bulk = 0;
+    for (uint64_t i = 0; i < n; ++i)
+        if (allow_bulk && (spans[i].ptr & 15ull) == 0) n_bulk += spans[i].nbytes / kDigestTile;
+    uint64_t bi = 0, gi = n_bulk;
     for (uint64_t i = 0; i < n; ++i) {
         hs[i] = spans[i];
         uint64_t t = (spans[i].nbytes + kDigestTile - 1) / kDigestTile;
         if (t > 0xffffffffull) return MXB_ERR_ARG;
-        for (uint64_t k = 0; k < t; ++k) ht[ti++] = DTile{(uint32_t)i, (uint32_t)k};
+        const uint64_t fullt = (allow_bulk && (spans[i].ptr & 15ull) == 0) ? spans[i].nbytes / kDigestTile : 0;
+        for (uint64_t k = 0; k < t; ++k) {
+            if (k < fullt) ht[bi++] = DTile{(uint32_t)i, (uint32_t)k};
+            else ht[gi++] = DTile{(uint32_t)i, (uint32_t)k};
+        }
     }
     MXB_CUDA(cudaMemcpyAsync(d->table, d->table_host, span_bytes + tile_bytes,
                              cudaMemcpyHostToDevice, d->stream));
     MXB_CUDA(cudaMemsetAsync(d->digest, 0, n * sizeof(DigestAcc), d->stream));
-    if (total) {
-        // one 512-thread CTA per SM (the pipelined kernel holds two rows per lane in registers)
+    const mxb_span *dspans = reinterpret_cast<const mxb_span *>(d->table);
+    const DTile *dtiles = reinterpret_cast<const DTile *>(reinterpret_cast<char *>(d->table) + span_bytes);
+    if (n_bulk) {
+        static bool attr_set[64][8] = {};
+        const size_t smem = (size_t)kDigestStages * kDigestTile;
+        digest_bulk_fn fn = digest_bulk_variant(modes);
+        if (d->device < 64 && !attr_set[d->device][modes & 7]) {
+            MXB_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr_set[d->device][modes & 7] = true;
+        }
         uint64_t grid = (uint64_t)d->sm_count;
-        if (grid > total) grid = total;
+        if (grid > n_bulk) grid = n_bulk;
+        fn<<<(unsigned)grid, kDigestThreads, smem, d->stream>>>(
+            dspans, dtiles, n_bulk, reinterpret_cast<DigestAcc *>(d->digest),
+            reinterpret_cast<unsigned long long *>(block_out), d->status);
+        MXB_CUDA(cudaGetLastError());
+        ctx->launches.fetch_add(1);
+    }
+    if (total > n_bulk) {
+        uint64_t grid = (uint64_t)d->sm_count * 2;
+        if (grid > total - n_bulk) grid = total - n_bulk;
         digest_variant(modes)<<<(unsigned)grid, kDigestThreads, 0, d->stream>>>(
-            reinterpret_cast<const mxb_span *>(d->table),
-            reinterpret_cast<const DTile *>(reinterpret_cast<char *>(d->table) + span_bytes), total,
-            reinterpret_cast<DigestAcc *>(d->digest),
+            dspans, dtiles + n_bulk, total - n_bulk, reinterpret_cast<DigestAcc *>(d->digest),
             reinterpret_cast<unsigned long long *>(block_out));
         MXB_CUDA(cudaGetLastError());
         ctx->launches.fetch_add(1);
     }
     MXB_CUDA(cudaMemcpyAsync(d->digest_host, d->digest, n * sizeof(DigestAcc),
                              cudaMemcpyDeviceToHost, d->stream));
-    MXB_CUDA(cudaStreamSynchronize(d->stream));
+    rc = check_status(d);
+    if (rc != MXB_OK) return rc;
     const DigestAcc *res = reinterpret_cast<const DigestAcc *>(d->digest_host);
     for (uint64_t i = 0; i < n; ++i) {
         memcpy(&out[i], &res[i], sizeof(mxb_digest_out));
