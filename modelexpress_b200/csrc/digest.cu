@@ -139,7 +139,34 @@ __device__ __forceinline__ void fetch_row(const mxb_span *__restrict__ spans,
     for (int s = 0; s < 8; ++s) v[s] = load16(p, row_off + s * 512 + lane * 16, m.n, aligned16);
 }
 
-template <uint32_t MODES>
+// The partial last row of a span: whole words are the "tail" terms, the bytes
+// after the last whole word the "ragged" term.  Only the kernels instantiated
+// with TAIL = true carry this code; full tiles never need it.
+__device__ __forceinline__ void digest_tail_row(const RowMeta &m, const uint4 (&v)[8], uint32_t lane,
+                                             WarpAcc &a) {
+    const uint64_t row_off = m.row * kRowBytes;
+    const uint64_t body = m.n - (m.n % 4);
+    uint64_t ts = 0, tw = 0, rg = 0;
+    for (int s = 0; s < 8; ++s) {
+        const uint64_t off = row_off + s * 512 + lane * 16;
+        const uint32_t w[4] = {v[s].x, v[s].y, v[s].z, v[s].w};
+        for (int q = 0; q < 4; ++q) {
+            const uint64_t wo = off + 4 * q;
+            if (wo + 4 <= body) {
+                const uint64_t val = (uint64_t)(int64_t)(int32_t)w[q];
+                ts += val;
+                tw += val * ((wo - row_off) / 4 + 1);
+            } else if (wo < m.n) {
+                rg += __dp4a(w[q], 0x01010101u, 0u);  // zero-filled above n
+            }
+        }
+    }
+    a.tail_sum += warp_sum_u64(ts);
+    a.tail_sum_w += warp_sum_u64(tw);
+    a.ragged += warp_sum_u64(rg);
+}
+
+template <uint32_t MODES, bool TAIL>
 __device__ __forceinline__ void digest_row(const RowMeta &m, const uint4 (&v)[8], uint32_t lane,
                                            WarpAcc &a, unsigned long long *__restrict__ block_out) {
     const uint64_t row_off = m.row * kRowBytes;
@@ -174,29 +201,8 @@ __device__ __forceinline__ void digest_row(const RowMeta &m, const uint4 (&v)[8]
             const uint64_t rs = warp_sum_u64((uint64_t)s64);
             a.row_sum += rs;
             a.row_sum_w += rs * (m.row + 1);
-        } else {
-            // the partial last row: whole words are the "tail", the rest is ragged bytes
-            const uint64_t body = m.n - (m.n % 4);
-            uint64_t ts = 0, tw = 0, rg = 0;
-#pragma unroll
-            for (int s = 0; s < 8; ++s) {
-                const uint64_t off = row_off + s * 512 + lane * 16;
-                const uint32_t w[4] = {v[s].x, v[s].y, v[s].z, v[s].w};
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const uint64_t wo = off + 4 * q;
-                    if (wo + 4 <= body) {
-                        const uint64_t val = (uint64_t)(int64_t)(int32_t)w[q];
-                        ts += val;
-                        tw += val * ((wo - row_off) / 4 + 1);
-                    } else if (wo < m.n) {
-                        rg += __dp4a(w[q], 0x01010101u, 0u);  // zero-filled above n
-                    }
-                }
-            }
-            a.tail_sum += warp_sum_u64(ts);
-            a.tail_sum_w += warp_sum_u64(tw);
-            a.ragged += warp_sum_u64(rg);
+        } else if (TAIL) {
+            digest_tail_row(m, v, lane, a);
         }
     }
     if (MODES & MXB_DIGEST_BLOCK64) {
@@ -216,7 +222,7 @@ __device__ __forceinline__ void digest_row(const RowMeta &m, const uint4 (&v)[8]
 }
 
 // Generic engine: any alignment, ragged tails.  One row per warp per tile.
-template <uint32_t MODES>
+template <uint32_t MODES, bool TAIL>
 __global__ void __launch_bounds__(kDigestThreads, 2)
 digest_kernel(const mxb_span *__restrict__ spans, const DTile *__restrict__ tiles,
               uint64_t total_tiles, DigestAcc *__restrict__ acc,
@@ -231,7 +237,7 @@ digest_kernel(const mxb_span *__restrict__ spans, const DTile *__restrict__ tile
             flush(a, acc, lane);
             a.span = cur.span;
         }
-        if (cur.valid) digest_row<MODES>(cur, vc, lane, a, block_out);
+        if (cur.valid) digest_row<MODES, TAIL>(cur, vc, lane, a, block_out);
     }
     flush(a, acc, lane);
 }
@@ -302,7 +308,7 @@ digest_bulk_kernel(const mxb_span *__restrict__ spans, const DTile *__restrict__
             flush(a, acc, lane);
             a.span = m.span;
         }
-        digest_row<MODES>(m, v, lane, a, block_out);
+        digest_row<MODES, false>(m, v, lane, a, block_out);
         __syncthreads();  // the stage may be refilled
     }
     flush(a, acc, lane);
@@ -333,15 +339,16 @@ static digest_bulk_fn digest_bulk_variant(uint32_t modes) {
         default: return digest_bulk_kernel<7>;
     }
 }
+template <bool TAIL>
 static digest_fn digest_variant(uint32_t modes) {
     switch (modes) {
-        case 1: return digest_kernel<1>;
-        case 2: return digest_kernel<2>;
-        case 3: return digest_kernel<3>;
-        case 4: return digest_kernel<4>;
-        case 5: return digest_kernel<5>;
-        case 6: return digest_kernel<6>;
-        default: return digest_kernel<7>;
+        case 1: return digest_kernel<1, TAIL>;
+        case 2: return digest_kernel<2, TAIL>;
+        case 3: return digest_kernel<3, TAIL>;
+        case 4: return digest_kernel<4, TAIL>;
+        case 5: return digest_kernel<5, TAIL>;
+        case 6: return digest_kernel<6, TAIL>;
+        default: return digest_kernel<7, TAIL>;
     }
 }
 
@@ -382,20 +389,28 @@ static int32_t run_digest(mxb_ctx *ctx, int32_t dev, const mxb_span *spans, uint
     MXB_CUDA(cudaStreamSynchronize(d->stream));
     mxb_span *hs = reinterpret_cast<mxb_span *>(d->table_host);
     DTile *ht = reinterpret_cast<DTile *>(reinterpret_cast<char *>(d->table_host) + span_bytes);
-    // full 64 KiB tiles of 16-byte-aligned spans go to the bulk engine (listed
-    // first), everything else (ragged last tiles, unaligned spans) to the generic one
-    const bool allow_bulk = getenv("MXB_DIGEST_GENERIC") == nullptr;
-    uint64_t n_bulk = 0;
-    for (uint64_t i = 0; i < n; ++i)
-        if (allow_bulk && (spans[i].ptr & 15ull) == 0) n_bulk += spans[i].nbytes / kDigestTile;
-    uint64_t bi = 0, gi = n_bulk;
+    // Full 64 KiB tiles are listed first, ragged last tiles after them.  Full tiles
+    // of 16-byte-aligned spans may use the bulk engine (shared-memory staging); the
+    // ragged ones always use the vector engine with tail handling.
+    const char *eng = getenv("MXB_DIGEST_ENGINE");  // "bulk" | "vector" | unset = per-mode choice
+    bool want_bulk = (modes == MXB_DIGEST_ROWS);
+    if (eng && !strcmp(eng, "bulk")) want_bulk = true;
+    if (eng && !strcmp(eng, "vector")) want_bulk = false;
+    bool all_aligned = true;
+    uint64_t n_full = 0;
+    for (uint64_t i = 0; i < n; ++i) {
+        n_full += spans[i].nbytes / kDigestTile;
+        if (spans[i].nbytes >= kDigestTile && (spans[i].ptr & 15ull)) all_aligned = false;
+    }
+    const bool use_bulk = want_bulk && all_aligned;
+    uint64_t fi = 0, gi = n_full;
     for (uint64_t i = 0; i < n; ++i) {
         hs[i] = spans[i];
         uint64_t t = (spans[i].nbytes + kDigestTile - 1) / kDigestTile;
         if (t > 0xffffffffull) return MXB_ERR_ARG;
-        const uint64_t fullt = (allow_bulk && (spans[i].ptr & 15ull) == 0) ? spans[i].nbytes / kDigestTile : 0;
+        const uint64_t fullt = spans[i].nbytes / kDigestTile;
         for (uint64_t k = 0; k < t; ++k) {
-            if (k < fullt) ht[bi++] = DTile{(uint32_t)i, (uint32_t)k};
+            if (k < fullt) ht[fi++] = DTile{(uint32_t)i, (uint32_t)k};
             else ht[gi++] = DTile{(uint32_t)i, (uint32_t)k};
         }
     }
@@ -404,7 +419,9 @@ static int32_t run_digest(mxb_ctx *ctx, int32_t dev, const mxb_span *spans, uint
     MXB_CUDA(cudaMemsetAsync(d->digest, 0, n * sizeof(DigestAcc), d->stream));
     const mxb_span *dspans = reinterpret_cast<const mxb_span *>(d->table);
     const DTile *dtiles = reinterpret_cast<const DTile *>(reinterpret_cast<char *>(d->table) + span_bytes);
-    if (n_bulk) {
+    DigestAcc *dacc = reinterpret_cast<DigestAcc *>(d->digest);
+    unsigned long long *dblk = reinterpret_cast<unsigned long long *>(block_out);
+    if (n_full && use_bulk) {
         static bool attr_set[64][8] = {};
         const size_t smem = (size_t)kDigestStages * kDigestTile;
         digest_bulk_fn fn = digest_bulk_variant(modes);
@@ -413,19 +430,24 @@ static int32_t run_digest(mxb_ctx *ctx, int32_t dev, const mxb_span *spans, uint
             attr_set[d->device][modes & 7] = true;
         }
         uint64_t grid = (uint64_t)d->sm_count;
-        if (grid > n_bulk) grid = n_bulk;
-        fn<<<(unsigned)grid, kDigestThreads, smem, d->stream>>>(
-            dspans, dtiles, n_bulk, reinterpret_cast<DigestAcc *>(d->digest),
-            reinterpret_cast<unsigned long long *>(block_out), d->status);
+        if (grid > n_full) grid = n_full;
+        fn<<<(unsigned)grid, kDigestThreads, smem, d->stream>>>(dspans, dtiles, n_full, dacc, dblk,
+                                                                 d->status);
+        MXB_CUDA(cudaGetLastError());
+        ctx->launches.fetch_add(1);
+    } else if (n_full) {
+        uint64_t grid = (uint64_t)d->sm_count * 2;
+        if (grid > n_full) grid = n_full;
+        digest_variant<false>(modes)<<<(unsigned)grid, kDigestThreads, 0, d->stream>>>(
+            dspans, dtiles, n_full, dacc, dblk);
         MXB_CUDA(cudaGetLastError());
         ctx->launches.fetch_add(1);
     }
-    if (total > n_bulk) {
+    if (total > n_full) {
         uint64_t grid = (uint64_t)d->sm_count * 2;
-        if (grid > total - n_bulk) grid = total - n_bulk;
-        digest_variant(modes)<<<(unsigned)grid, kDigestThreads, 0, d->stream>>>(
-            dspans, dtiles + n_bulk, total - n_bulk, reinterpret_cast<DigestAcc *>(d->digest),
-            reinterpret_cast<unsigned long long *>(block_out));
+        if (grid > total - n_full) grid = total - n_full;
+        digest_variant<true>(modes)<<<(unsigned)grid, kDigestThreads, 0, d->stream>>>(
+            dspans, dtiles + n_full, total - n_full, dacc, dblk);
         MXB_CUDA(cudaGetLastError());
         ctx->launches.fetch_add(1);
     }

@@ -111,7 +111,7 @@ def place_checkpoint(model_path: str, tp_rank: int, tp_size: int, device=None, *
                      params: dict | None = None, ring: Ring | None = None,
                      ctx: Context | None = None, host_threads: int | None = None,
                      mode: int = PLACE_COPY_ENGINE, family: str = "auto",
-                     ring_bytes: int = 2 << 30, ring_slots: int = 16) -> PlacedCheckpoint:
+                     ring_bytes: int = 2 << 30, ring_slots: int = 32) -> PlacedCheckpoint:
     """Load this rank's tensor-parallel shards of a safetensors checkpoint.
 
     ``params`` may hold pre-allocated destination tensors (an engine's own
@@ -139,7 +139,8 @@ def place_checkpoint(model_path: str, tp_rank: int, tp_size: int, device=None, *
         for path in sorted({i["file"] for i in index.values()}):
             images[path] = FileImage(path)
         items = placement_items(plan, index, {p: im.address for p, im in images.items()}, params)
-        threads = host_threads or min(32, os.cpu_count() or 8)
+        # three quarters of the cores: the gather threads share DRAM bandwidth with the PCIe DMA
+        threads = host_threads or max(2, min(32, (os.cpu_count() or 8) * 3 // 4))
         stats = ring.place(items, threads, mode)
     finally:
         for im in images.values():
@@ -163,7 +164,7 @@ class B200ScatterStrategy:
     name = "b200_scatter"
     requires: tuple = ()
 
-    def __init__(self, ring_bytes: int = 2 << 30, ring_slots: int = 16, host_threads: int | None = None):
+    def __init__(self, ring_bytes: int = 2 << 30, ring_slots: int = 32, host_threads: int | None = None):
         self.ring_bytes, self.ring_slots, self.host_threads = ring_bytes, ring_slots, host_threads
         self._touched = False
 

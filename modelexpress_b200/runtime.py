@@ -111,7 +111,7 @@ class Context:
               "mxb_event_elapsed")
         return float(ms.value)
 
-    def ring(self, ring_bytes: int = 2 << 30, slots: int = 16, dev: int | None = None) -> "Ring":
+    def ring(self, ring_bytes: int = 2 << 30, slots: int = 32, dev: int | None = None) -> "Ring":
         return Ring(self, self._dev(dev), ring_bytes, slots)
 
     def fanout(self, local_spans, chunk_bytes: int, dev: int | None = None) -> "Fanout":
