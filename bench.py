@@ -225,7 +225,8 @@ def bench_place(args):
     slots = env_int("MXB_RING_SLOTS", 32)
     mode = PLACE_ZERO_COPY if os.environ.get("MXB_PLACE_MODE", "ce") == "zc" else PLACE_COPY_ENGINE
     ring = ctx.ring(2 << 30, slots, local)
-    for _ in range(args.warmup):
+    skip_e2e = os.environ.get("MXB_BENCH_SKIP_E2E") == "1"  # profiling runs that only want the table launches
+    for _ in range(0 if skip_e2e else args.warmup):
         ring.place(items, threads, mode)
     sampler = ClockSampler(local)
     launches0 = ctx.launch_count
@@ -233,9 +234,11 @@ def bench_place(args):
     torch.cuda.synchronize()
     sampler.start()
     t0 = time.perf_counter()
-    e2e_stats = [ring.place(items, threads, mode) for _ in range(args.steps)]
+    e2e_stats = [ring.place(items, threads, mode) for _ in range(1 if skip_e2e else args.steps)]
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
+    if skip_e2e:
+        e2e_s *= args.steps
     barrier(world)
     e2e_s = max_over_ranks(e2e_s, world)
     e2e_launches = ctx.launch_count - launches0
@@ -331,6 +334,8 @@ def bench_place(args):
                      "kernel": kernel, "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": int(2 * bytes_placed)},
     }
+    if skip_e2e:
+        out["profiling_only"] = "e2e region skipped (MXB_BENCH_SKIP_E2E=1); its numbers are not measurements"
     if world == 1 and rank == 0 and os.environ.get("MXB_BENCH_SKIP_CPU") != "1":
         out["cpu_baseline"] = cpu_baseline(ckpt, tp_rank, threads_all=False)
     if rank == 0:

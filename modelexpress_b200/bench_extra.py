@@ -80,7 +80,7 @@ NVLINK_PEER_GBS = 770.0  # measured peer copy on this pool, per direction per GP
 
 
 def _base(metric, value, unit, world, args, ms_per_step, config, dtype="u8", scaling="weak"):
-    return {"metric": metric, "value": round(value, 2), "unit": unit, "n_gpus": world,
+    return {"metric": metric, "value": round(value, 6 if unit == "s" else 2), "unit": unit, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
             "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": dtype,
             "data": "synthetic", "config": config}
@@ -420,7 +420,8 @@ def run_reshard(args):
     out["roofline"] = {"bound": "nvlink" if link_time > hbm_time else "hbm",
                        "achieved": round(ms * 1e-3, 6), "peak": round(bound, 6), "unit": "s",
                        "frac": round(bound / (ms * 1e-3), 4), "traffic": None,
-                       "kernel": "scatter_vec_kernel",
+                       "kernel": "scatter_bulk_kernel (+ scatter_vec_kernel for unaligned records)"
+                       if tables and tables[0].engine(flags) != "vector" else "scatter_vec_kernel",
                        "peak_source": f"max(local copy bytes x2 / {peak} GB/s {src}, NVLink bytes / "
                                       f"{NVLINK_PEER_GBS} GB/s measured peer copy)"}
     if rank == 0:
