@@ -211,6 +211,31 @@ int32_t mxb_digest(mxb_ctx *ctx, int32_t dev, const mxb_span *spans, uint64_t n,
 int32_t mxb_block_hashes(mxb_ctx *ctx, int32_t dev, uint64_t ptr, uint64_t nbytes,
                          uint64_t out_blocks);
 
+/* Digest without allocating anything (no counterpart in the reference).
+ *
+ * For callers that are not allowed to grow the process's device memory: a
+ * serving engine that has already handed every free byte of HBM to its KV
+ * cache (a cudaMalloc there fails, or succeeds by taking memory the engine
+ * counted on), or a verification hook that runs where the framework's caching
+ * allocator must not be disturbed.  Such a caller still wants to check the
+ * weights it just received, so this variant of mxb_digest keeps its whole
+ * scratch (range table, tile table, accumulators; about 148 KiB) in a fixed
+ * array inside the library's device image.  It needs no context, creates no
+ * stream and calls no cudaMalloc/cudaFree: work is queued on `stream` (a
+ * cudaStream_t, NULL for the default stream) of device `dev` and the call
+ * returns after that stream has drained, with out[i] filled for spans[i].
+ *
+ * Limits, checked before anything is queued (MXB_ERR_ARG with a message): at
+ * most 256 ranges and at most 16384 tiles of 64 KiB (1 GiB) per call; larger
+ * jobs are split by the caller.  The first call on a device looks up the
+ * array's device address; make that call outside any stream capture.  All
+ * calls on a device share the one array (it keeps the previous call's
+ * contents; the accumulators a call uses are cleared by that call), so the
+ * library serialises callers on the host; work that a caller queues on other
+ * streams to run at the same time against this array would race. */
+int32_t mxb_digest_noalloc(int32_t dev, const mxb_span *spans, uint64_t n, uint32_t modes,
+                           mxb_digest_out *out, void *stream);
+
 /* ---- kernel 2: serving-peer fan-out -------------------------------------- */
 
 #define MXB_FANOUT_MAX_CHILDREN 7

@@ -84,6 +84,7 @@ SIGNATURES = {
     "mxb_place": (i32, [_vp, _P(Desc2D), u64, i32, u32, _P(PlaceStats)]),
     "mxb_digest": (i32, [_vp, i32, _P(Span), u64, u32, _P(DigestOut)]),
     "mxb_block_hashes": (i32, [_vp, i32, u64, u64, u64]),
+    "mxb_digest_noalloc": (i32, [i32, _P(Span), u64, u32, _P(DigestOut), _vp]),
     "mxb_fanout_create": (i32, [_vp, i32, _P(Span), u64, u64, _P(_vp)]),
     "mxb_fanout_counters": (u64, [_vp]),
     "mxb_fanout_set_child": (i32, [_vp, i32, _P(Span), u64, u64]),

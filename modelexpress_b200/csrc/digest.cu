@@ -490,3 +490,125 @@ int32_t mxb_block_hashes(mxb_ctx *ctx, int32_t dev, uint64_t ptr, uint64_t nbyte
 }
 
 }  // extern "C"
+
+/* ---- digests for callers that must not allocate device memory ---------------------------- */
+
+namespace {
+
+constexpr uint64_t kNoAllocMaxSpans = 256;
+constexpr uint64_t kNoAllocMaxTiles = 16384;  // 1 GiB of 64 KiB tiles
+
+struct NoAllocScratch {
+    mxb_span spans[kNoAllocMaxSpans];
+    DTile tiles[kNoAllocMaxTiles];
+    DigestAcc acc[kNoAllocMaxSpans];
+};
+
+// The whole scratch of the allocation-free entry point: 4 KiB of spans, 128 KiB
+// of tiles and 16 KiB of accumulators, resident on every GPU that loads the
+// library until the process exits.  In host code this name is only a handle for
+// cudaGetSymbolAddress; it is never passed to a kernel as if it were an address.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[sizeof(NoAllocScratch)];
+
+std::mutex g_noalloc_mu;
+NoAllocScratch *g_noalloc_ptr[64] = {};  // device address of the scratch, per device
+
+}  // namespace
+
+extern "C" int32_t mxb_digest_noalloc(int32_t dev, const mxb_span *spans, uint64_t n,
+                                      uint32_t modes, mxb_digest_out *out, void *stream) {
+    if ((!spans && n) || (!out && n) || (modes & ~7u) || modes == 0 || dev < 0 || dev >= 64) {
+        set_error("mxb_digest_noalloc: bad arguments");
+        return MXB_ERR_ARG;
+    }
+    if (n > kNoAllocMaxSpans) {
+        set_error("mxb_digest_noalloc: %llu ranges exceed the fixed scratch (at most %llu per call)",
+                  (unsigned long long)n, (unsigned long long)kNoAllocMaxSpans);
+        return MXB_ERR_ARG;
+    }
+    uint64_t total = 0;
+    for (uint64_t i = 0; i < n; ++i) {
+        if (spans[i].nbytes && !spans[i].ptr) {
+            set_error("span %llu has a null address", (unsigned long long)i);
+            return MXB_ERR_ARG;
+        }
+        total += (spans[i].nbytes + kDigestTile - 1) / kDigestTile;
+    }
+    if (total > kNoAllocMaxTiles) {
+        set_error("mxb_digest_noalloc: %llu tiles of 64 KiB exceed the fixed scratch (at most %llu "
+                  "per call, i.e. 1 GiB); split the ranges over several calls",
+                  (unsigned long long)total, (unsigned long long)kNoAllocMaxTiles);
+        return MXB_ERR_ARG;
+    }
+    if (n == 0) return MXB_OK;
+    DeviceGuard g(dev);
+    if (!g.ok) {
+        set_error("cudaSetDevice(%d) failed", dev);
+        cudaGetLastError();
+        return MXB_ERR_CUDA;
+    }
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    // The scratch is shared by every call on this device; calls are serialised on the
+    // host here, and each call finishes (stream synchronised) before it returns.
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    NoAllocScratch *sc = g_noalloc_ptr[dev];
+    if (!sc) {
+        // set-up, once per device, with that device current
+        void *p = nullptr;
+        MXB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        sc = g_noalloc_ptr[dev] = reinterpret_cast<NoAllocScratch *>(p);
+    }
+    // host image of the table: spans, then tiles (full tiles first, ragged last tiles after)
+    static thread_local mxb_span h_spans[kNoAllocMaxSpans];
+    static thread_local DTile h_tiles[kNoAllocMaxTiles];
+    uint64_t n_full = 0;
+    for (uint64_t i = 0; i < n; ++i) n_full += spans[i].nbytes / kDigestTile;
+    uint64_t fi = 0, gi = n_full;
+    for (uint64_t i = 0; i < n; ++i) {
+        h_spans[i] = spans[i];
+        const uint64_t t = (spans[i].nbytes + kDigestTile - 1) / kDigestTile;
+        const uint64_t fullt = spans[i].nbytes / kDigestTile;
+        for (uint64_t k = 0; k < t; ++k) {
+            if (k < fullt) h_tiles[fi++] = DTile{(uint32_t)i, (uint32_t)k};
+            else h_tiles[gi++] = DTile{(uint32_t)i, (uint32_t)k};
+        }
+    }
+    MXB_CUDA(cudaMemcpyAsync(sc->spans, h_spans, n * sizeof(mxb_span), cudaMemcpyHostToDevice, st));
+    if (total)
+        MXB_CUDA(cudaMemcpyAsync(sc->tiles, h_tiles, total * sizeof(DTile), cudaMemcpyHostToDevice, st));
+    // the accumulators keep the previous call's sums: clear the ones this call uses
+    MXB_CUDA(cudaMemsetAsync(sc->acc, 0, n * sizeof(DigestAcc), st));
+    int sms = 0;
+    MXB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (n_full) {
+        uint64_t grid = (uint64_t)sms * 2;
+        if (grid > n_full) grid = n_full;
+        digest_variant<false>(modes)<<<(unsigned)grid, kDigestThreads, 0, st>>>(
+            sc->spans, sc->tiles, n_full, sc->acc, nullptr);
+        MXB_CUDA(cudaGetLastError());
+    }
+    if (total > n_full) {
+        uint64_t grid = (uint64_t)sms * 2;
+        if (grid > total - n_full) grid = total - n_full;
+        digest_variant<true>(modes)<<<(unsigned)grid, kDigestThreads, 0, st>>>(
+            sc->spans, sc->tiles + n_full, total - n_full, sc->acc, nullptr);
+        MXB_CUDA(cudaGetLastError());
+    }
+    static thread_local DigestAcc h_acc[kNoAllocMaxSpans];
+    MXB_CUDA(cudaMemcpyAsync(h_acc, sc->acc, n * sizeof(DigestAcc), cudaMemcpyDeviceToHost, st));
+    MXB_CUDA(cudaStreamSynchronize(st));
+    for (uint64_t i = 0; i < n; ++i) {
+        memcpy(&out[i], &h_acc[i], sizeof(mxb_digest_out));
+        out[i].nbytes = spans[i].nbytes;
+        if (modes & MXB_DIGEST_BLOCK64) {
+            uint64_t h = spans[i].nbytes * 0x27D4EB2F165667C5ull;
+            h ^= h >> 33;
+            h *= 0xC2B2AE3D27D4EB4Full;
+            h ^= h >> 29;
+            h *= 0x165667B19E3779F9ull;
+            h ^= h >> 32;
+            out[i].block_hash += h;
+        }
+    }
+    return MXB_OK;
+}
