@@ -15,6 +15,9 @@
 // run the same kernel with no children: it returns once every chunk arrived.
 // No wait is unbounded: when the time budget runs out the kernel records
 // DEV_TIMEOUT in its status word and returns.
+#include <cstdlib>
+
+#include "bulk.cuh"
 #include "common.cuh"
 
 namespace mxb {
@@ -111,6 +114,135 @@ __global__ void __launch_bounds__(kFanThreads) fanout_kernel(FanArgs a) {
                     red_release_sys_add(reinterpret_cast<uint32_t *>(a.child_counters[c]) + pc.chunk,
                                         1u);
             }
+        }
+    }
+}
+
+// Bulk engine: one warp per CTA, one CTA per SM, pieces staged through a 3-stage
+// 64 KiB shared-memory ring with cp.async.bulk (local HBM -> shared -> every
+// child's HBM over NVLink).  The child's counter for piece k is raised only after
+// the bulk stores of piece k have completed (wait_group, not wait_group.read).
+constexpr int kFanStages = 3;
+
+__device__ __forceinline__ bool fan_wait_chunk(const FanArgs &a, uint32_t chunk) {
+    const uint32_t want = a.run_index * a.chunk_pieces[chunk];
+    const uint32_t *ctr = a.counters + chunk;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while ((int32_t)(ld_acquire_sys(ctr) - want) < 0) {
+        if ((++spins & 63u) == 0) {
+            if (globaltimer_ns() - t0 > a.timeout_ns) return false;
+            __nanosleep(200);
+        }
+    }
+    // what the parent wrote is read next by the async proxy (bulk load)
+    asm volatile("fence.proxy.async;" ::: "memory");
+    return true;
+}
+
+__device__ __forceinline__ void fan_signal(const FanArgs &a, uint32_t chunk) {
+    __threadfence_system();
+    for (uint32_t c = 0; c < a.n_children; ++c)
+        red_release_sys_add(reinterpret_cast<uint32_t *>(a.child_counters[c]) + chunk, 1u);
+}
+
+__global__ void __launch_bounds__(32) fanout_bulk_kernel(FanArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ __align__(8) uint64_t full[kFanStages];
+    const uint32_t lane = threadIdx.x;
+    if (lane == 0) {
+        for (int s = 0; s < kFanStages; ++s) mbar_init(&full[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    const uint64_t first = blockIdx.x;
+    if (first >= a.n_pieces) return;
+    const uint64_t mine = (a.n_pieces - first + gridDim.x - 1) / gridDim.x;
+    bool failed = false;
+
+    // wait for the piece's chunk (unless root) and start its load; warp-uniform result
+    auto start_piece = [&](uint64_t k) -> bool {
+        const FanPiece pc = a.pieces[first + k * gridDim.x];
+        bool ok = true;
+        if (!a.is_root) {
+            if (lane == 0) ok = fan_wait_chunk(a, pc.chunk);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        }
+        if (!ok) return false;
+        if ((pc.nbytes & 15u) == 0 && a.n_children) {  // bulk-eligible (addresses are 16-byte aligned)
+            const int s = (int)(k % kFanStages);
+            if (lane == 0) {
+                mbar_expect_tx(&full[s], pc.nbytes);
+                bulk_g2s(smem + (size_t)s * kFanPiece, reinterpret_cast<const void *>(pc.local),
+                         pc.nbytes, &full[s]);
+            }
+        }
+        return true;
+    };
+
+    uint64_t signalled = 0;  // pieces [0, signalled) have raised the children's counters
+    if (!start_piece(0)) failed = true;
+    uint64_t k = 0;
+    for (; k < mine && !failed; ++k) {
+        const FanPiece pc = a.pieces[first + k * gridDim.x];
+        const int s = (int)(k % kFanStages);
+        if (k + 1 < mine) {
+            // stage (k+1)%3 held piece k-2, whose stores completed before piece k-2 was signalled
+            if (!start_piece(k + 1)) {
+                failed = true;
+                break;
+            }
+        }
+        if (a.n_children) {
+            if ((pc.nbytes & 15u) == 0) {
+                const uint32_t parity = (uint32_t)((k / kFanStages) & 1);
+                bool ok = false;
+                for (uint32_t spin = 0; spin < (1u << 24); ++spin) {
+                    ok = __all_sync(0xffffffffu, mbar_try_wait(&full[s], parity));
+                    if (ok) break;
+                }
+                if (!ok) {
+                    failed = true;
+                    break;
+                }
+                if (lane == 0) {
+                    for (uint32_t c = 0; c < a.n_children; ++c)
+                        bulk_s2g(reinterpret_cast<void *>(a.child_ptr[(uint64_t)c * a.n_pieces + first +
+                                                                       k * gridDim.x]),
+                                 smem + (size_t)s * kFanPiece, pc.nbytes);
+                }
+            } else {
+                // ragged last piece of a range: plain loads and stores by the warp
+                const unsigned char *sb = reinterpret_cast<const unsigned char *>(pc.local);
+                for (uint32_t c = 0; c < a.n_children; ++c) {
+                    unsigned char *db = reinterpret_cast<unsigned char *>(
+                        a.child_ptr[(uint64_t)c * a.n_pieces + first + k * gridDim.x]);
+                    for (uint32_t j = lane; j < pc.nbytes; j += 32) db[j] = sb[j];
+                }
+                __syncwarp();
+            }
+            bulk_commit();  // every piece closes one group (possibly empty), so groups count pieces
+            // all groups but the newest are complete: pieces up to k-1 may be announced
+            bulk_wait_all<1>();
+            __syncwarp();
+            if (lane == 0)
+                for (; signalled < k; ++signalled)
+                    fan_signal(a, a.pieces[first + signalled * gridDim.x].chunk);
+            signalled = k;
+        }
+    }
+    bulk_wait_all<0>();
+    __syncwarp();
+    if (!failed && a.n_children && lane == 0)
+        for (; signalled < mine; ++signalled)
+            fan_signal(a, a.pieces[first + signalled * gridDim.x].chunk);
+    if (failed) {
+        if (lane == 0) atomicExch(a.status, DEV_TIMEOUT);
+        // bounded wait for a load that may still be in flight before shared memory is released
+        for (uint64_t j = k; j < k + 2 && j < mine; ++j) {
+            const uint32_t parity = (uint32_t)((j / kFanStages) & 1);
+            for (uint32_t spin = 0; spin < (1u << 14); ++spin)
+                if (mbar_try_wait(&full[j % kFanStages], parity)) break;
         }
     }
 }
@@ -279,10 +411,28 @@ int32_t mxb_fanout_run(mxb_fanout *f, int32_t is_root, uint32_t timeout_ms) {
     if (np == 0) return MXB_OK;
     // all CTAs must be co-resident: they wait on data, never on each other, but a
     // CTA that is not scheduled cannot forward its pieces
-    uint64_t grid = (uint64_t)dv->sm_count * 2;
-    if (grid > np) grid = np;
+    const char *eng = getenv("MXB_FANOUT_ENGINE");  // "bulk": shared-memory staged bulk copies
+    const bool bulk = eng && !strcmp(eng, "bulk");
     MXB_CUDA(cudaEventRecord(f->ev0, dv->stream));
-    fanout_kernel<<<(unsigned)grid, kFanThreads, 0, dv->stream>>>(a);
+    if (bulk) {
+        static bool attr_set[64] = {};
+        const size_t smem = (size_t)kFanStages * kFanPiece;
+        if (dv->device < 64 && !attr_set[dv->device]) {
+            MXB_CUDA(cudaFuncSetAttribute(fanout_bulk_kernel,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr_set[dv->device] = true;
+        }
+        uint64_t grid = (uint64_t)dv->sm_count;
+        if (grid > np) grid = np;
+        fanout_bulk_kernel<<<(unsigned)grid, 32, smem, dv->stream>>>(a);
+    } else {
+        int per_sm = 2;
+        if (const char *g = getenv("MXB_FANOUT_CTAS_PER_SM")) per_sm = atoi(g) > 0 ? atoi(g) : 2;
+        if (per_sm > 4) per_sm = 4;
+        uint64_t grid = (uint64_t)dv->sm_count * per_sm;
+        if (grid > np) grid = np;
+        fanout_kernel<<<(unsigned)grid, kFanThreads, 0, dv->stream>>>(a);
+    }
     MXB_CUDA(cudaGetLastError());
     MXB_CUDA(cudaEventRecord(f->ev1, dv->stream));
     f->ctx->launches.fetch_add(1);
