@@ -351,6 +351,7 @@ def run_reshard(args):
     param_bases = [peer_params[t % world] + (t // world) * pa.total for t in range(R)]
     t0 = time.perf_counter()
     tables, nbytes, remote, nrecs = [], 0, 0, 0
+    all_recs = []
     for j, r in enumerate(mine):
         recs = reshard.plan_reshard(index, R, R, r, shard_base + j * sa.total, param_bases, "dense",
                                     shards=sa, params=pa)
@@ -359,9 +360,13 @@ def run_reshard(args):
         lo, hi = param_base, param_base + pa.total * per
         far = (recs[:, 1] < lo) | (recs[:, 1] >= hi)
         remote += int((recs[far, 2] * recs[far, 3]).sum())
-        tables.append(ctx.table(recs, local))
+        all_recs.append(recs)
+    # one resident table (one launch) per GPU for all the logical ranks it hosts
+    tables.append(ctx.table(np.concatenate(all_recs), local))
     plan_s = time.perf_counter() - t0
-    flags = 0
+    from .runtime import SCATTER_VECTOR
+
+    flags = SCATTER_VECTOR if os.environ.get("MXB_SCATTER", "auto") == "vec" else 0
     times = []
     for it in range(args.warmup + args.steps):
         _barrier(world)
