@@ -221,7 +221,9 @@ def bench_place(args):
     # ---- e2e: host file image -> ring -> PCIe -> scatter -------------------------------
     images = {p: loader.FileImage(p) for p in sorted({i["file"] for i in idx.values()})}
     items = loader.placement_items(plan, idx, {p: im.address for p, im in images.items()}, params)
-    threads = env_int("MXB_HOST_THREADS", max(2, min(32, (os.cpu_count() or 8) * 3 // 4)))
+    # three quarters of the cores, shared between the ranks of this box
+    local_world = max(1, env_int("LOCAL_WORLD_SIZE", world))
+    threads = env_int("MXB_HOST_THREADS", max(2, min(32, (os.cpu_count() or 8) * 3 // 4 // local_world)))
     slots = env_int("MXB_RING_SLOTS", 32)
     mode = PLACE_ZERO_COPY if os.environ.get("MXB_PLACE_MODE", "ce") == "zc" else PLACE_COPY_ENGINE
     ring = ctx.ring(2 << 30, slots, local)

@@ -271,6 +271,41 @@ def run_fanout(args):
                     raise SystemExit(f"fan-out: rank {r} digests differ from the source (chunk {mib} MiB)")
         _barrier(world)
         node.close()
+    # rank-matched pair copy: the first half of the GPUs each hold two TP=8 shards and
+    # replicate them to the matching GPU of the second half (independent 1-hop copies)
+    pairs = None
+    if world % 2 == 0:
+        half = world // 2
+        shard = 2008031232
+        pay = 2 * shard if total >= 2 * shard else (total // 512) * 256
+        pspans = [(base, pay)]
+        node = ctx.fanout(pspans, 16 << 20, local)
+        ctrs = _open_peers(ctx, node.counters, world)
+        if rank < half:
+            node.add_child([(peers[rank + half], pay)], ctrs[rank + half])
+        _barrier(world)
+        times = []
+        for it in range(args.warmup + args.steps):
+            if rank >= half:
+                arena[:pay].zero_()
+                torch.cuda.synchronize()
+            _barrier(world)
+            node.run(rank < half, 20000)
+            ms = _max(node.wait(), world)
+            if it >= args.warmup:
+                times.append(ms)
+        recs = ctx.digest(pspans, DIGEST_SAFE32 | DIGEST_BLOCK64, local)
+        alld = _gather_objects((int(recs[0].safe_checksum), int(recs[0].block_hash)), world)
+        if rank == 0:
+            for r in range(half):
+                if alld[r] != alld[r + half]:
+                    raise SystemExit(f"pair copy: GPU {r + half} differs from GPU {r}")
+        pms = sum(times) / len(times)
+        pairs = {"pairs": half, "bytes_per_pair": pay, "device_ms": round(pms, 3),
+                 "gbs_per_pair": round(pay / (pms * 1e-3) / 1e9, 1),
+                 "gbs_aggregate": round(pay * half / (pms * 1e-3) / 1e9, 1)}
+        _barrier(world)
+        node.close()
     best = max(sweep, key=lambda k: sweep[k]["gbs_per_target"])
     dev_ms = sweep[best]["device_ms"]
     per_target = sweep[best]["gbs_per_target"]
@@ -278,7 +313,7 @@ def run_fanout(args):
                 per_target, "GB/s", world, args, dev_ms,
                 {"workload": "configs[2]: 16.06 GB TP=1 copy on GPU 0 broadcast over NVLink P2P stores",
                  "topology": kind, "payload_bytes": payload, "ranges": len(sizes),
-                 "chunk_sweep_mib": sweep, "best_chunk_mib": int(best),
+                 "chunk_sweep_mib": sweep, "best_chunk_mib": int(best), "rank_matched_pairs": pairs,
                  "check": "safe_checksum and 64-bit block hash of every destination range equal the source"},
                 scaling="strong")
     out["gpu_launches"] = (args.warmup + args.steps) * len(chunks_mib)
