@@ -108,10 +108,11 @@ def plan_reshard(index: dict, world: int, tp_size: int, src_rank: int, shard_bas
     ``shard_base``, destinations inside rank t's parameter arena at
     ``param_bases[t]`` (addresses valid in this process).  (n, 6) uint64."""
     shards = shards or shard_arena(index, world)
-    recs = []
+    per_dst = []
     for t in range(tp_size):
         plan = plan_checkpoint(index, t, tp_size, family)
         pa = params or param_arena(plan)
+        recs = []
         for pl in plan.placements:
             so, do, rows, rb, sp, dp = pl.geometry()
             per = shards.sizes[pl.src_name]
@@ -119,7 +120,21 @@ def plan_reshard(index: dict, world: int, tp_size: int, src_rank: int, shard_bas
             recs += clip_records(so, do, rows, rb, sp, dp, lo, hi,
                                  shard_base + shards.offsets[pl.src_name],
                                  param_bases[t] + pa.offsets[pl.dst_name])
-    return np.array(recs, dtype=np.uint64).reshape(-1, 6)
+        per_dst.append(recs)
+    # All-to-all schedule: rank s starts with destination s+1 and the records of
+    # the destinations are interleaved, so that at any moment the sources spread
+    # their stores over all peers instead of all hitting destination 0's ingress
+    # first.  The kernel walks the table in order, so table order is link order.
+    order = [(src_rank + 1 + i) % tp_size for i in range(tp_size)]
+    out, cursor = [], [0] * tp_size
+    remaining = sum(len(r) for r in per_dst)
+    while remaining:
+        for t in order:
+            if cursor[t] < len(per_dst[t]):
+                out.append(per_dst[t][cursor[t]])
+                cursor[t] += 1
+                remaining -= 1
+    return np.array(out, dtype=np.uint64).reshape(-1, 6)
 
 
 def reshard_bytes(records: np.ndarray) -> int:
