@@ -106,8 +106,11 @@ size_t scatter_table_bytes(const mxb_desc2d *descs, uint64_t n, uint64_t *live_o
 // Fill host_buf with the table image whose device copy will live at dev_buf.
 // bulk_begin / vec_begin (n+1 entries each, optional) receive, per input record,
 // its first tile in the bulk list and in the vector list.
+// Records that touch another GPU's memory (as seen from `device`; -1 skips the check)
+// always go to the vector list.
 int32_t build_scatter_table(const mxb_desc2d *descs, uint64_t n, void *host_buf, void *dev_buf,
-                            ScatterTable *out, uint64_t *bulk_begin, uint64_t *vec_begin);
+                            ScatterTable *out, uint64_t *bulk_begin, uint64_t *vec_begin,
+                            int device);
 // Launch the bulk engine over a range of the bulk list and the vector engine
 // over a range of the vector list (MXB_SCATTER_VECTOR: vector engine for both).
 int32_t launch_scatter_tiles(mxb_ctx *ctx, DeviceState *dv, const ScatterTable &tb,

@@ -332,7 +332,7 @@ int32_t mxb_place(mxb_ring *r, const mxb_desc2d *items, uint64_t n, int32_t host
     if (!descs.empty()) {
         MXB_CUDA(cudaStreamSynchronize(dv->stream));
         rc = build_scatter_table(descs.data(), descs.size(), r->table_host, r->table_dev, &tb,
-                                 bulk_begin.data(), vec_begin.data());
+                                 bulk_begin.data(), vec_begin.data(), -1);
         if (rc != MXB_OK) return rc;
         MXB_CUDA(cudaMemcpyAsync(r->table_dev, r->table_host, tb.bytes, cudaMemcpyHostToDevice,
                                  dv->stream));

@@ -150,3 +150,28 @@ def test_strategy_contract(ckpts):
         strat.load(LoadResult(value="m"), ctx)
     assert ei.value.mutated is False
     strat.rollback(ctx)
+
+
+def test_fp8_moe_slice_expert_parallel_placement(tmp_path):
+    """DeepSeek-V3-style block-FP8 slice: experts expert-parallel into w13/w2 slots with
+    their scale blocks, MLA and shared expert tensor-parallel; thousands of small
+    records in a handful of launches."""
+    import torch
+
+    from modelexpress_b200 import synth
+    from modelexpress_b200.loader import place_checkpoint
+
+    cfg = synth.MoEConfig(layers=2, hidden=512, experts=16, moe_intermediate=512, q_lora=256,
+                          kv_lora=128, qk_rope=64, qk_nope=64, v_head=64, heads=16, files=2)
+    d = str(tmp_path)
+    synth.write_checkpoint(d, synth.moe_tensors(cfg), cfg.seed, cfg.files)
+    full = read_full_tensors(d)
+    for rank in (0, 5):
+        placed = place_checkpoint(d, rank, 8, "cuda:0", ring_bytes=32 << 20, ring_slots=4, host_threads=4)
+        want = R.load_and_shard_moe(full, rank, 8)
+        assert set(placed.params) == set(want)
+        for n, a in want.items():
+            got = placed.params[n].detach().cpu().contiguous().view(torch.uint8).numpy()
+            assert got.size == a.nbytes, n
+            assert np.array_equal(got.reshape(-1), a.view(np.uint8).reshape(-1)), (rank, n)
+        assert placed.stats.launches <= 2 * placed.stats.chunks

@@ -186,6 +186,27 @@ def test_moe_layout_places_experts_and_scales():
         assert np.array_equal(ob, full[a + "o_proj.weight"][:, rank * 128:(rank + 1) * 128])
 
 
+def test_moe_layout_matches_oracle_on_a_written_checkpoint(tmp_path):
+    cfg = synth.MoEConfig(layers=1, hidden=512, experts=8, moe_intermediate=512, q_lora=128,
+                          kv_lora=128, qk_rope=64, qk_nope=64, v_head=64, heads=8, files=2)
+    d = str(tmp_path)
+    synth.write_checkpoint(d, synth.moe_tensors(cfg), cfg.seed, cfg.files)
+    full = read_full_tensors(d)
+    idx = checkpoint_index(d)
+    index = {n: {"shape": i["shape"], "dtype": i["dtype"]} for n, i in idx.items()}
+    for rank in (0, 3):
+        want = R.load_and_shard_moe(full, rank, 4)
+        plan = layout.plan_checkpoint(index, rank, 4)
+        assert set(plan.params) == set(want)
+        bufs = {n: np.zeros(s.shape, dtype=NP_OF_TAG[s.dtype]) for n, s in plan.params.items()}
+        srcs = {n: np.ascontiguousarray(a) for n, a in full.items()}
+        run_records_on_host([pl.record(srcs[pl.src_name].ctypes.data, bufs[pl.dst_name].ctypes.data)
+                             for pl in plan.placements])
+        for n, a in want.items():
+            assert bufs[n].shape == a.shape, n
+            assert np.array_equal(bufs[n].view(np.uint8), a.view(np.uint8)), (rank, n)
+
+
 @pytest.mark.parametrize("world,tp", [(8, 8), (4, 2), (2, 4)])
 def test_reshard_plan_matches_oracle_regather(tiny_ckpt, world, tp):
     full = read_full_tensors(tiny_ckpt)
