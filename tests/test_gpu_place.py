@@ -161,7 +161,7 @@ def test_fp8_moe_slice_expert_parallel_placement(tmp_path):
     from modelexpress_b200 import synth
     from modelexpress_b200.loader import place_checkpoint
 
-    cfg = synth.MoEConfig(layers=2, hidden=512, experts=16, moe_intermediate=512, q_lora=256,
+    cfg = synth.MoEConfig(layers=2, hidden=512, experts=16, moe_intermediate=1024, q_lora=256,
                           kv_lora=128, qk_rope=64, qk_nope=64, v_head=64, heads=16, files=2)
     d = str(tmp_path)
     synth.write_checkpoint(d, synth.moe_tensors(cfg), cfg.seed, cfg.files)
