@@ -104,3 +104,33 @@ class Broadcast:
     def close(self):
         for n in self.nodes:
             n.close()
+
+
+def manifest_from_module(model, device_id: int | None = None) -> list:
+    """Manifest rows for every CUDA tensor of a module tree, with the reference's
+    rules (tensor_utils.py:299-360): parameters then buffers; contiguous tensors
+    as they are, non-contiguous ones as the flat bytes of their whole storage
+    under ``name.__storage``; tensors sharing a ``data_ptr`` listed once (tied
+    weights); zero-element tensors keep their name and skip the de-duplication."""
+    import torch
+
+    rows, seen = [], set()
+    named = list(model.named_parameters()) + list(model.named_buffers())
+    for name, tensor in named:
+        t = tensor.data if hasattr(tensor, "data") else tensor
+        if not t.is_cuda:
+            continue
+        dev = t.device.index if device_id is None else device_id
+        if t.numel() == 0:
+            rows.append(TensorDescriptor(name, 0, 0, dev, str(t.dtype)))
+            continue
+        if t.is_contiguous():
+            ptr, size, nm, dt = t.data_ptr(), t.numel() * t.element_size(), name, str(t.dtype)
+        else:
+            sv = torch.empty(0, dtype=torch.uint8, device=t.device).set_(t.untyped_storage())
+            ptr, size, nm, dt = sv.data_ptr(), sv.numel(), f"{name}.__storage", "torch.uint8"
+        if ptr in seen:
+            continue
+        seen.add(ptr)
+        rows.append(TensorDescriptor(nm, ptr, size, dev, dt))
+    return rows

@@ -119,6 +119,21 @@ def plan_dense(index: dict, tp_rank: int, tp_size: int) -> CheckpointPlan:
             fused = "qkv_proj" if m.group(2) in _QKV else "gate_up_proj"
             groups.setdefault((m.group(1), fused, m.group(3)), {})[m.group(2)] = (name, shape, dtype)
             continue
+        if re.search(r"\.gate_up_proj\.(weight|weight_scale_inv)$", name) and len(shape) >= 1:
+            # a checkpoint that ships [gate; up] already merged (GLM-4 style): the two
+            # partitions are column-parallel independently, so rank r takes rows
+            # [r*L, (r+1)*L) of each half and stacks them (installer.py:670-693)
+            parts = 2
+            if shape[0] % (parts * tp_size):
+                raise ValueError(f"{name}: {shape[0]} rows do not split into {parts} x tp={tp_size}")
+            part_src = shape[0] // parts
+            loc = part_src // tp_size
+            dshape = (parts * loc,) + tuple(shape[1:])
+            plan.params[name] = ParamSpec(name, dshape, dtype)
+            for p in range(parts):
+                plan.placements.append(Placement(name, shape, dtype, 0, p * part_src + tp_rank * loc,
+                                                 loc, name, dshape, p * loc))
+            continue
         if re.search(r"\.(o_proj|down_proj)\.(weight|weight_scale_inv)$", name) and len(shape) == 2:
             loc = _split(shape[1], tp_size, name)
             plan.params[name] = ParamSpec(name, (shape[0], loc), dtype)

@@ -252,24 +252,85 @@ def expand_records(records) -> list:
     return runs
 
 
-def plan_transfer_2d(copies, sources: dict, resolve_param_ptr) -> tuple:
-    """All copies of a capture -> one record array.  Copies whose source is
-    missing, needs a conversion or is not box-shaped are returned by name in the
-    second element so the caller can fail closed (transfer_plan.py:192-299 keeps
-    the same three outcomes; there is no descriptor bound here because a strided
-    slice costs one record, not one per row)."""
-    recs, unsupported = [], []
+@dataclass
+class ConvertSpec:
+    """A copy whose served dtype differs from the destination's: its bytes are
+    pulled into ``staging`` (served dtype, contiguous, ``dest_shape``) and cast
+    into the live parameter afterwards (transfer_plan.py:49-60, 226-256)."""
+
+    param_name: str
+    dest_shape: tuple
+    dest_stride: tuple
+    dest_offset: int
+    src_dtype: Any
+    staging_offset: int  # byte offset in the convert staging buffer
+    nbytes: int
+
+
+def plan_transfer_2d(copies, sources: dict, resolve_param_ptr, convert_base: int | None = None) -> tuple:
+    """All copies of a capture -> one record array.
+
+    Returns ``(records, unsupported, converts)``.  Same-dtype copies write
+    straight into the live parameters.  A copy whose source dtype differs from
+    the destination's is planned into a contiguous staging buffer at
+    ``convert_base`` (served dtype, row-major) and listed in ``converts`` for
+    the caller to cast, as the reference does; without ``convert_base`` such
+    copies are reported unsupported.  Sources that are missing or not
+    box-shaped are returned by name so the caller can fail closed
+    (transfer_plan.py:192-299 keeps the same outcomes; there is no descriptor
+    bound here because a strided slice costs one record, not one per row)."""
+    recs, unsupported, converts = [], [], []
+    staged = 0
     for copy in copies:
         src = sources.get(copy.src_name)
         if src is None:
             unsupported.append(copy.src_name)
             continue
         try:
-            parts = plan_pull_2d(copy, src.global_shape, src.dtype, src.elsize, src.shards,
-                                 resolve_param_ptr(copy.param_name))
+            if src.dtype != copy.dest_dtype:
+                if convert_base is None:
+                    raise UnsupportedReshard("dtype conversion required and no staging given")
+                n = int(np.prod(copy.dest_shape)) if len(copy.dest_shape) else 1
+                staging_copy = CopySpec(copy.src_name, copy.op_chain, copy.param_name, 0,
+                                        tuple(copy.dest_shape), tuple(_strides_of(copy.dest_shape)),
+                                        src.dtype)
+                off = (staged + 255) // 256 * 256
+                parts = plan_pull_2d(staging_copy, src.global_shape, src.dtype, src.elsize,
+                                     src.shards, int(convert_base) + off)
+                converts.append(ConvertSpec(copy.param_name, tuple(copy.dest_shape),
+                                            tuple(copy.dest_stride), int(copy.dest_offset), src.dtype,
+                                            off, n * int(src.elsize)))
+                staged = off + n * int(src.elsize)
+            else:
+                parts = plan_pull_2d(copy, src.global_shape, src.dtype, src.elsize, src.shards,
+                                     resolve_param_ptr(copy.param_name))
         except UnsupportedReshard:
             unsupported.append(copy.src_name)
             continue
         recs.extend(r for _sess, r in parts)
     table = np.concatenate(recs) if recs else np.zeros((0, 6), dtype=np.uint64)
-    return table, unsupported
+    return table, unsupported, converts
+
+
+def convert_staging_bytes(copies, sources: dict) -> int:
+    """Size of the staging buffer ``plan_transfer_2d`` needs for dtype converts."""
+    total = 0
+    for copy in copies:
+        src = sources.get(copy.src_name)
+        if src is not None and src.dtype != copy.dest_dtype:
+            n = int(np.prod(copy.dest_shape)) if len(copy.dest_shape) else 1
+            total = (total + 255) // 256 * 256 + n * int(src.elsize)
+    return total
+
+
+def apply_converts(converts, staging, params: dict) -> None:
+    """Cast the staged sources into their parameters (receiver.py:964-971): the
+    one step left to torch, for the few tensors (a bf16-served router feeding an
+    fp32 parameter) that need it."""
+    import torch
+
+    for c in converts:
+        src = staging[c.staging_offset: c.staging_offset + c.nbytes].view(c.src_dtype).reshape(c.dest_shape)
+        p = params[c.param_name]
+        dst = torch.as_strided(p, c.dest_shape, c.dest_stride, p.storage_offset() + c.dest_offset)
+        dst.copy_(src)

@@ -182,3 +182,50 @@ def test_reshard_across_gpus(tmp_path):
     if n < 2:
         pytest.skip("needs at least two GPUs")
     _reshard_case(torch, tmp_path, [i % n for i in range(8)])
+
+
+def test_module_manifest_follows_reference_rules():
+    import torch
+
+    from modelexpress_b200.fanout import manifest_from_module
+
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = torch.nn.Parameter(torch.zeros(4, 8, device="cuda"))
+            self.tied = self.a                                  # same data_ptr: listed once
+            base = torch.zeros(8, 8, device="cuda")
+            self.register_buffer("strided", base[:, ::2])       # non-contiguous -> storage bytes
+            self.register_buffer("empty", torch.zeros(0, device="cuda"))
+            self.register_buffer("cpu_buf", torch.zeros(3))     # not on the accelerator
+
+    rows = manifest_from_module(M())
+    names = [r.name for r in rows]
+    assert names == ["a", "strided.__storage", "empty"]
+    assert rows[0].size == 4 * 8 * 4 and rows[1].size == 8 * 8 * 4 and rows[2].size == 0
+
+
+def test_strict_verify_catches_a_misplaced_shard():
+    """nixl_staged_transfer.py:529-549: digests of every published box are recomputed
+    from the assembled tensor; one launch for all of them."""
+    import torch
+
+    from modelexpress_b200 import planner, verify
+
+    full = torch.arange(64 * 1024, dtype=torch.int32, device="cuda").reshape(64, 1024)
+    boxes = {s: full[s * 16:(s + 1) * 16].contiguous() for s in range(4)}
+    dig = verify.published_digests(boxes)
+    shards = [planner.ShardSpec((s * 16, 0), (16, 1024), f"t{s}", 0, 4, dig[s]) for s in range(4)]
+    sources = {"w": planner.SourceSpec((64, 1024), "i32", 4, shards)}
+    assert verify.verify_sources({"w": full.reshape(-1)}, sources) == 4
+    bad = full.clone()
+    bad[16:32], bad[32:48] = full[32:48].clone(), full[16:32].clone()   # right bytes, wrong place
+    with pytest.raises(RuntimeError, match="digest mismatch for source 'w' at offset \\(16, 0\\)"):
+        verify.verify_sources({"w": bad}, sources)
+    shards[2].digest = None
+    with pytest.raises(RuntimeError, match="did not publish"):
+        verify.verify_sources({"w": full}, sources)
+    with pytest.raises(ValueError, match="rank mismatch"):
+        verify.shard_region(full, (64, 1024), (1,), (2, 3))
+    region = verify.shard_region(full.reshape(-1), (64, 1024), (1, 2), (2, 3))
+    assert torch.equal(region, full[1:3, 2:5])

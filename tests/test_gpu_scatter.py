@@ -167,7 +167,8 @@ def test_toy_model_reshard_through_the_transport(env):
             sources[name] = planner.SourceSpec(tuple(t.shape), "f32", 4, shards)
         copies = [planner.CopySpec(c["src_name"], _chain(c["op_chain"]), c["param_name"], c["dest_offset"],
                                    tuple(c["dest_shape"]), tuple(c["dest_stride"]), "f32") for c in g["copies"]]
-        table, unsupported = planner.plan_transfer_2d(copies, sources, lambda n: params[n].data_ptr())
+        table, unsupported, converts = planner.plan_transfer_2d(copies, sources, lambda n: params[n].data_ptr())
+        assert converts == []
         assert unsupported == []
         torch.cuda.synchronize()
         ctx.scatter(table, 0)
@@ -211,3 +212,28 @@ def test_resident_table_replays(env):
     want = src.cpu().numpy().reshape(256, 4096)[:, :2048].reshape(-1)
     assert np.array_equal(dst.cpu().numpy()[: want.size], want)
     tb.close()
+
+
+def test_convert_sources_are_staged_then_cast(env):
+    """A bf16-served source feeding an fp32 parameter (the router case of
+    refit/reshard/receiver.py:964-971): bytes move as bf16 into staging through the
+    kernel, the cast is the only step left to torch; result equals a direct cast."""
+    ctx, torch = env
+    from modelexpress_b200 import planner
+
+    src = torch.randn(8, 16, dtype=torch.float32, device="cuda").to(torch.bfloat16)
+    halves = [src[:4].contiguous(), src[4:].contiguous()]
+    shards = [planner.ShardSpec((i * 4, 0), (4, 16), f"t{i}", h.data_ptr(), 2) for i, h in enumerate(halves)]
+    sources = {"gate.weight": planner.SourceSpec((8, 16), torch.bfloat16, 2, shards)}
+    param = torch.zeros(6, 16, dtype=torch.float32, device="cuda")
+    copy = planner.CopySpec("gate.weight", (("narrow", (0, 1, 6), ()),), "gate", 0, (6, 16), (16, 1),
+                            torch.float32)
+    nbytes = planner.convert_staging_bytes([copy], sources)
+    staging = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    table, unsupported, converts = planner.plan_transfer_2d(
+        [copy], sources, lambda n: param.data_ptr(), convert_base=staging.data_ptr())
+    assert unsupported == [] and len(converts) == 1
+    ctx.scatter(table, 0)
+    planner.apply_converts(converts, staging, {"gate": param})
+    assert torch.equal(param, src[1:7].to(torch.float32))  # a widening cast is exact

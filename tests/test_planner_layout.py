@@ -251,3 +251,38 @@ def test_clip_records_ragged_split():
             if 7 <= r * 6 + c < 23:
                 want[r, c - 2] = m[r, c]
     assert np.array_equal(dst.reshape(5, 3), want)
+
+
+@pytest.mark.parametrize("rank", [0, 1])
+def test_premerged_gate_up_is_sharded_per_member(rank):
+    """tests/test_mdl_tp.py:50-81 of the reference: a checkpoint that ships one
+    [gate; up] tensor must shard gate and up independently."""
+    src = np.arange(16, dtype=np.float32).reshape(8, 2)
+    name = "mlp.gate_up_proj.weight"
+    plan = layout.plan_dense({name: {"shape": [8, 2], "dtype": "F32"}}, rank, 2)
+    dst = np.zeros(plan.params[name].shape, dtype=np.float32)
+    run_records_on_host([pl.record(src.ctypes.data, dst.ctypes.data) for pl in plan.placements])
+    gate = src[rank * 2:(rank + 1) * 2]
+    up = src[4 + rank * 2: 4 + (rank + 1) * 2]
+    assert np.array_equal(dst, np.concatenate((gate, up)))
+    # and the same arithmetic as the installer's own helper (fixture)
+    writes = R.premerged_writes(4, 2, 8, 2, rank)
+    assert [(pl.dst_start, pl.start, pl.size) for pl in plan.placements] == [tuple(w) for w in writes]
+    with pytest.raises(ValueError):
+        layout.plan_dense({name: {"shape": [10, 2], "dtype": "F32"}}, 0, 2)
+
+
+def test_dtype_mismatch_is_planned_through_staging():
+    """transfer_plan.py:226-256: a served dtype that differs from the destination's is
+    pulled into staging of the served dtype and listed for a cast."""
+    shard = planner.ShardSpec((0, 0), (4, 8), "s", 1000, 2)
+    sources = {"router": planner.SourceSpec((4, 8), "bf16", 2, [shard])}
+    copy = planner.CopySpec("router", (("narrow", (0, 1, 2), ()),), "gate", 0, (2, 8), (8, 1), "f32")
+    table, unsupported, converts = planner.plan_transfer_2d([copy], sources, lambda n: 0)
+    assert unsupported == ["router"] and converts == [] and len(table) == 0
+    table, unsupported, converts = planner.plan_transfer_2d([copy], sources, lambda n: 0, convert_base=1 << 20)
+    assert unsupported == [] and len(converts) == 1
+    assert planner.expand_records(table) == [(1000 + 16, 1 << 20, 32)]
+    c = converts[0]
+    assert (c.param_name, c.dest_shape, c.src_dtype, c.staging_offset, c.nbytes) == ("gate", (2, 8), "bf16", 0, 32)
+    assert planner.convert_staging_bytes([copy], sources) == 32
