@@ -3,9 +3,10 @@ INFRASTRUCTURE ONLY (the benchmark's ``cpu_baseline`` leg and reference arm).
 
 What the reference runs for this path (engines/vllm/adapter.py:316-329) is
 vLLM's DefaultModelLoader: for every checkpoint tensor, ``safe_open(...)
-.get_tensor(name)`` materialises the FULL tensor on the host, the layer's
-``weight_loader`` narrows it to the rank's slice and ``param.copy_`` writes the
-slice into the parameter, one tensor at a time.  This port does exactly those
+.get_tensor(name)`` hands out the full tensor (a view of the memory-mapped
+file, paged in on first touch), the layer's ``weight_loader`` narrows it to the
+rank's slice and ``param.copy_`` writes the slice into the parameter, one
+tensor at a time.  This port does exactly those
 three steps with torch CPU tensors; the slice rules are the oracle's
 (``ref_port._classify`` / ``load_and_shard``), which the CPU tests pin against
 real vLLM layers.  Destinations are host tensors, so no PCIe copy is included:
@@ -53,7 +54,7 @@ def load_and_shard_torch(model_dir: str, tp_rank: int, tp_size: int, params: dic
     for path in files:
         with safe_open(path, framework="pt", device="cpu") as f:
             for name in f.keys():
-                loaded = f.get_tensor(name)  # full tensor on the host, as the reference does
+                loaded = f.get_tensor(name)  # the full tensor, mapped from the file, as the reference does
                 dest, kind, member = ref_port._classify(name)
                 p = params[dest]
                 if kind in ("qkv", "gate_up"):
