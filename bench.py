@@ -121,10 +121,14 @@ def measured_peak():
         return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
-def ncu_traffic(kernel: str):
+def ncu_traffic(kernel: str, bytes_placed: int):
+    """DRAM bytes per launch from the committed ncu capture of a smaller case,
+    scaled by the bytes this launch places."""
     try:
         with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
-            return json.load(f).get(kernel)
+            rec = json.load(f).get(kernel)
+        return {"bytes_per_launch": int(rec["dram_bytes_per_byte_placed"] * bytes_placed),
+                "how": rec["how"]}
     except Exception:
         return None
 
@@ -345,7 +349,7 @@ def bench_place(args):
         "gpu_launches": int(kern_launches),
         "gpu_launches_e2e": int(e2e_launches),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 4), "traffic": ncu_traffic(kernel),
+                     "frac": round(achieved / peak, 4), "traffic": ncu_traffic(kernel, bytes_placed),
                      "kernel": kernel, "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": int(2 * bytes_placed)},
     }
