@@ -8,6 +8,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <memory>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -49,6 +50,8 @@ struct DeviceState {
     void *digest_host = nullptr;
     size_t digest_host_bytes = 0;
     cudaEvent_t events[16] = {};  // user timing events on `stream`
+    // serialises the entry points that share this device's scratch (tables, accumulators)
+    std::unique_ptr<std::mutex> mu{new std::mutex()};
 };
 
 struct Extent {

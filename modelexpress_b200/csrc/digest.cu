@@ -380,6 +380,7 @@ static int32_t run_digest(mxb_ctx *ctx, int32_t dev, const mxb_span *spans, uint
         total += (spans[i].nbytes + kDigestTile - 1) / kDigestTile;
     }
     DeviceGuard g(dev);
+    std::lock_guard<std::mutex> lk(*d->mu);
     const size_t span_bytes = (n * sizeof(mxb_span) + 255) & ~size_t(255);
     const size_t tile_bytes = (total * sizeof(DTile) + 255) & ~size_t(255);
     int32_t rc = ensure_table(d, span_bytes + tile_bytes);

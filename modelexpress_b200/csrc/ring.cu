@@ -293,6 +293,7 @@ int32_t mxb_place(mxb_ring *r, const mxb_desc2d *items, uint64_t n, int32_t host
     }
     DeviceState *dv = r->dv;
     DeviceGuard g(dv->device);
+    std::lock_guard<std::mutex> lk(*dv->mu);
     if (host_threads < 1) host_threads = 1;
     if (!r->pool || r->pool_threads != host_threads) {
         delete r->pool;

@@ -571,6 +571,7 @@ int32_t mxb_scatter(mxb_ctx *ctx, int32_t dev, const mxb_desc2d *descs, uint64_t
     int32_t rc = validate_descs(ctx, descs, n);
     if (rc != MXB_OK) return rc;
     DeviceGuard g(dev);
+    std::lock_guard<std::mutex> lk(*d->mu);
     rc = launch_scatter(ctx, d, descs, n, flags, d->stream);
     if (rc != MXB_OK) return rc;
     if (flags & MXB_SCATTER_NO_SYNC) return MXB_OK;
