@@ -101,6 +101,26 @@ def clip_records(so: int, do: int, rows: int, rb: int, sp: int, dp: int, lo: int
     return out
 
 
+def split_record(rec, max_bytes: int = 8 << 20) -> list:
+    """Cut a record into pieces of at most ``max_bytes`` (whole rows, or 256-byte
+    multiples of one long row) so that the merge below can interleave finely."""
+    src, dst, rows, rb, sp, dp = (int(x) for x in rec)
+    if rows * rb <= max_bytes:
+        return [rec]
+    out = []
+    if rows == 1:
+        step = max(256, max_bytes // 256 * 256)
+        for off in range(0, rb, step):
+            n = min(step, rb - off)
+            out.append((src + off, dst + off, 1, n, n, n))
+    else:
+        per = max(1, max_bytes // rb)
+        for r0 in range(0, rows, per):
+            n = min(per, rows - r0)
+            out.append((src + r0 * sp, dst + r0 * dp, n, rb, sp if n > 1 else rb, dp if n > 1 else rb))
+    return out
+
+
 def plan_reshard(index: dict, world: int, tp_size: int, src_rank: int, shard_base: int,
                  param_bases: list, family: str = "auto", shards: ArenaLayout | None = None,
                  params: ArenaLayout | None = None) -> np.ndarray:
@@ -117,23 +137,36 @@ def plan_reshard(index: dict, world: int, tp_size: int, src_rank: int, shard_bas
             so, do, rows, rb, sp, dp = pl.geometry()
             per = shards.sizes[pl.src_name]
             lo, hi = src_rank * per, (src_rank + 1) * per
-            recs += clip_records(so, do, rows, rb, sp, dp, lo, hi,
-                                 shard_base + shards.offsets[pl.src_name],
-                                 param_bases[t] + pa.offsets[pl.dst_name])
+            for rec in clip_records(so, do, rows, rb, sp, dp, lo, hi,
+                                    shard_base + shards.offsets[pl.src_name],
+                                    param_bases[t] + pa.offsets[pl.dst_name]):
+                recs += split_record(rec)
         per_dst.append(recs)
-    # All-to-all schedule: rank s starts with destination s+1 and the records of
-    # the destinations are interleaved, so that at any moment the sources spread
-    # their stores over all peers instead of all hitting destination 0's ingress
-    # first.  The kernel walks the table in order, so table order is link order.
+    # All-to-all schedule.  The kernel walks the table in order, so table order is
+    # link order: the destinations' record lists are merged by progress (the list
+    # that is furthest behind, in bytes, goes next; ties start at destination s+1),
+    # so every peer link and the local copies are busy from the first tile to the
+    # last instead of all sources hitting destination 0's ingress first.
     order = [(src_rank + 1 + i) % tp_size for i in range(tp_size)]
-    out, cursor = [], [0] * tp_size
+    totals = [sum(r[2] * r[3] for r in per_dst[t]) or 1 for t in range(tp_size)]
+    done = [0] * tp_size
+    cursor = [0] * tp_size
+    out = []
     remaining = sum(len(r) for r in per_dst)
     while remaining:
+        best = None
         for t in order:
-            if cursor[t] < len(per_dst[t]):
-                out.append(per_dst[t][cursor[t]])
-                cursor[t] += 1
-                remaining -= 1
+            if cursor[t] >= len(per_dst[t]):
+                continue
+            frac = done[t] / totals[t]
+            if best is None or frac < best[0]:
+                best = (frac, t)
+        t = best[1]
+        rec = per_dst[t][cursor[t]]
+        out.append(rec)
+        cursor[t] += 1
+        done[t] += rec[2] * rec[3]
+        remaining -= 1
     return np.array(out, dtype=np.uint64).reshape(-1, 6)
 
 
