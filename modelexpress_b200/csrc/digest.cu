@@ -121,12 +121,9 @@ struct RowMeta {
     bool valid = false;    // the row holds at least one byte
 };
 
-// Read the tile record, its span, and issue this lane's eight 16-byte loads.
-__device__ __forceinline__ void fetch_row(const mxb_span *__restrict__ spans,
-                                          const DTile *__restrict__ tiles, uint64_t t,
-                                          uint32_t warp, uint32_t lane, RowMeta &m, uint4 (&v)[8]) {
-    const DTile tile = tiles[t];
-    const mxb_span sp = spans[tile.span];
+// Issue this lane's eight 16-byte loads of the row that `tile` assigns to `warp`.
+__device__ __forceinline__ void load_row(const DTile tile, const mxb_span sp, uint32_t warp,
+                                         uint32_t lane, RowMeta &m, uint4 (&v)[8]) {
     m.span = tile.span;
     m.n = sp.nbytes;
     m.row = (uint64_t)tile.local * (kDigestTile / kRowBytes) + warp;
@@ -221,7 +218,10 @@ __device__ __forceinline__ void digest_row(const RowMeta &m, const uint4 (&v)[8]
     }
 }
 
-// Generic engine: any alignment, ragged tails.  One row per warp per tile.
+// Vector engine: any alignment; one row per warp per tile.  The tile record and
+// span of the NEXT tile are fetched while the current row's loads are in flight,
+// so a warp never sits through two dependent table reads before it can issue
+// data loads.
 template <uint32_t MODES, bool TAIL>
 __global__ void __launch_bounds__(kDigestThreads, 2)
 digest_kernel(const mxb_span *__restrict__ spans, const DTile *__restrict__ tiles,
@@ -231,13 +231,29 @@ digest_kernel(const mxb_span *__restrict__ spans, const DTile *__restrict__ tile
     WarpAcc a;
     RowMeta cur;
     uint4 vc[8];
-    for (uint64_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-        fetch_row(spans, tiles, t, warp, lane, cur, vc);
+    uint64_t t = blockIdx.x;
+    if (t >= total_tiles) return;
+    DTile tile = tiles[t];
+    mxb_span sp = spans[tile.span];
+    for (;;) {
+        load_row(tile, sp, warp, lane, cur, vc);
+        const uint64_t tn = t + gridDim.x;
+        const bool more = tn < total_tiles;
+        DTile ntile = tile;
+        mxb_span nsp = sp;
+        if (more) {
+            ntile = tiles[tn];
+            nsp = spans[ntile.span];
+        }
         if (cur.span != a.span) {
             flush(a, acc, lane);
             a.span = cur.span;
         }
         if (cur.valid) digest_row<MODES, TAIL>(cur, vc, lane, a, block_out);
+        if (!more) break;
+        tile = ntile;
+        sp = nsp;
+        t = tn;
     }
     flush(a, acc, lane);
 }
