@@ -257,9 +257,8 @@ def bench_place(args):
     e2e_s = max_over_ranks(e2e_s, world)
     e2e_launches = ctx.launch_count - launches0
 
-    # parity spot check of what the e2e path placed (full check lives in tests/)
-    from oracle import c_port  # checker only
-
+    # consistency check of what the e2e path placed against the resident path below
+    # (parity against the oracle lives in tests/ and in the cpu_baseline leg)
     some = [n for n in list(plan.params)[:6]]
     from modelexpress_b200 import digest as dg
 
@@ -303,14 +302,8 @@ def bench_place(args):
 
     # parity of the resident path against the e2e path's result (same bytes expected)
     dev_sums2 = [r["safe_checksum"] for r in dg.digest_many([params[n] for n in some], 1, ctx)]
-    host_ok = dev_sums == dev_sums2
-    if rank == 0:
-        # and against the oracle for one tensor
-        n0 = some[0]
-        a = params[n0].detach().cpu().contiguous().view(torch.uint8).numpy()
-        host_ok = host_ok and (c_port.safe_checksum(a, mt=True) == dev_sums2[0])
-    if not host_ok:
-        raise SystemExit("bench: placed bytes do not match between paths / oracle")
+    if dev_sums != dev_sums2:
+        raise SystemExit("bench: the ring path and the resident path placed different bytes")
 
     total_bytes = bytes_placed * world  # every rank places one shard of equal size
     value = total_bytes * args.steps / (ms * 1e-3) / 1e9
@@ -356,7 +349,8 @@ def bench_place(args):
     if skip_e2e:
         out["profiling_only"] = "e2e region skipped (MXB_BENCH_SKIP_E2E=1); its numbers are not measurements"
     if world == 1 and rank == 0 and os.environ.get("MXB_BENCH_SKIP_CPU") != "1" and not moe:
-        out["cpu_baseline"] = cpu_baseline(ckpt, tp_rank, threads_all=False)
+        out["cpu_baseline"] = cpu_baseline(ckpt, tp_rank, threads_all=False,
+                                           check={n: (params[n], dev_sums2[i]) for i, n in enumerate(some[:2])})
     if rank == 0:
         print(json.dumps(out), flush=True)
     table.close()
@@ -370,15 +364,24 @@ def bench_place(args):
         dist.destroy_process_group()
 
 
-def cpu_baseline(ckpt: str, tp_rank: int, threads_all: bool, passes: int | None = None) -> dict:
-    """The oracle's port of the reference's host-staged loop, timed on host cores."""
+def cpu_baseline(ckpt: str, tp_rank: int, threads_all: bool, passes: int | None = None,
+                 check: dict | None = None) -> dict:
+    """The oracle's port of the reference's host-staged loop, timed on host cores.
+    ``check`` ({param: (device tensor, kernel safe_checksum)}) is verified against
+    the oracle's own result for the same rank before anything is timed."""
     import torch
 
-    from oracle import cpu_loader  # the one place bench.py may run oracle/ as the thing timed
+    from oracle import c_port, cpu_loader  # the one place bench.py may run oracle/
+
 
     cores = (os.cpu_count() or 1) if threads_all else 1
     torch.set_num_threads(cores)
     params, placed, sec = cpu_loader.load_and_shard_torch(ckpt, tp_rank, TP)  # warm page cache
+    for name, (dev_tensor, dev_sum) in (check or {}).items():
+        want = params[name].contiguous().view(torch.uint8).numpy()
+        if c_port.safe_checksum(want, mt=True) != dev_sum or not torch.equal(
+                dev_tensor.detach().cpu().view(torch.uint8).reshape(-1), torch.from_numpy(want).reshape(-1)):
+            raise SystemExit(f"bench: {name} placed on the GPU differs from the CPU reference loop")
     n, tot_b, tot_s = 0, 0, 0.0
     budget = 12.0
     while tot_s < budget and n < (passes or 6):
@@ -451,9 +454,9 @@ def main():
         return bench_reference(args)
     if args.workload in ("place", "moe"):
         return bench_place(args)
-    from modelexpress_b200 import bench_extra
+    import bench_workloads
 
-    return bench_extra.run(args)
+    return bench_workloads.run(args)
 
 
 if __name__ == "__main__":
