@@ -175,3 +175,56 @@ def test_fp8_moe_slice_expert_parallel_placement(tmp_path):
             assert got.size == a.nbytes, n
             assert np.array_equal(got.reshape(-1), a.view(np.uint8).reshape(-1)), (rank, n)
         assert placed.stats.launches <= 2 * placed.stats.chunks
+
+
+@pytest.mark.parametrize("mode", ["copy_engine", "zero_copy"])
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_ring_random_items_any_alignment(seed, mode):
+    """Host -> device items with odd sizes, odd destination phases, pitches that are not
+    multiples of 16 and rows larger than a ring slot (split by bytes across chunks),
+    against the oracle's memmove loop."""
+    import torch
+
+    from make_golden import golden_bytes
+    from modelexpress_b200.runtime import PLACE_COPY_ENGINE, PLACE_ZERO_COPY, Context
+    from oracle import c_port as C
+
+    rng = np.random.default_rng(seed)
+    src = golden_bytes(500 + seed, 24 << 20)
+    items_rel, dpos = [], 0
+    for _ in range(50):
+        kind = int(rng.integers(0, 5))
+        if kind == 0:    # a row larger than the 1 MiB slot
+            rows, rb = 1, int(rng.integers(1 << 20, 3 << 20))
+            sp = dp = rb
+        elif kind == 1:  # row-parallel style
+            rows, rb = int(rng.integers(2, 600)), 16 * int(rng.integers(1, 200))
+            sp, dp = rb * int(rng.integers(2, 6)), rb + 16 * int(rng.integers(0, 3))
+        elif kind == 2:  # ragged everything
+            rows, rb = int(rng.integers(1, 300)), int(rng.integers(1, 3000))
+            sp, dp = rb + int(rng.integers(0, 40)), rb + int(rng.integers(0, 40))
+        elif kind == 3:  # multi-row item taller than a slot
+            rows, rb = int(rng.integers(700, 1500)), 2048
+            sp, dp = 4096, 2048 + 16 * int(rng.integers(0, 2))
+        else:            # tiny
+            rows, rb = 1, int(rng.integers(1, 64))
+            sp = dp = rb
+        span_s = (rows - 1) * sp + rb
+        span_d = (rows - 1) * dp + rb
+        s0 = int(rng.integers(0, src.size - span_s))
+        d0 = dpos + int(rng.integers(0, 33))
+        items_rel.append((s0, d0, rows, rb, sp, dp))
+        dpos = d0 + span_d
+    ctx = Context([0])
+    ring = ctx.ring(4 << 20, 4, 0)  # 1 MiB slots
+    dst_d = torch.full((dpos + 64,), 0x5A, dtype=torch.uint8, device="cuda")
+    dst_h = np.full(dpos + 64, 0x5A, dtype=np.uint8)
+    torch.cuda.synchronize()
+    items = [(src.ctypes.data + s, dst_d.data_ptr() + d, r, rb, sp, dp) for s, d, r, rb, sp, dp in items_rel]
+    st = ring.place(items, 3, PLACE_COPY_ENGINE if mode == "copy_engine" else PLACE_ZERO_COPY)
+    C.scatter2d([(src.ctypes.data + s, dst_h.ctypes.data + d, r, rb, sp, dp) for s, d, r, rb, sp, dp in items_rel])
+    assert np.array_equal(dst_d.cpu().numpy(), dst_h)
+    assert st.bytes_placed == sum(r * rb for _s, _d, r, rb, _sp, _dp in items_rel)
+    assert st.chunks > 10
+    ring.close()
+    ctx.close()
