@@ -156,7 +156,10 @@ class Table:
 
     def close(self):
         if getattr(self, "_h", None):
-            self.ctx._lib.mxb_table_destroy(self._h)
+            # the object lives inside its context: if that was closed first there is
+            # nothing left to release
+            if getattr(self.ctx, "_h", None):
+                self.ctx._lib.mxb_table_destroy(self._h)
             self._h = None
 
     def __del__(self):
@@ -187,7 +190,10 @@ class Ring:
 
     def close(self):
         if getattr(self, "_h", None):
-            self.ctx._lib.mxb_ring_destroy(self._h)
+            # the object lives inside its context: if that was closed first there is
+            # nothing left to release
+            if getattr(self.ctx, "_h", None):
+                self.ctx._lib.mxb_ring_destroy(self._h)
             self._h = None
 
     def __del__(self):
@@ -231,7 +237,10 @@ class Fanout:
 
     def close(self):
         if getattr(self, "_h", None):
-            self.ctx._lib.mxb_fanout_destroy(self._h)
+            # the object lives inside its context: if that was closed first there is
+            # nothing left to release
+            if getattr(self.ctx, "_h", None):
+                self.ctx._lib.mxb_fanout_destroy(self._h)
             self._h = None
 
     def __del__(self):
