@@ -10,7 +10,7 @@
 //             sum(row) and sum(row * (k+1)) mod 2^64, plus the word tail and
 //             ragged-byte terms;
 //   BLOCK64 - a 64-bit hash per 4 KiB block: per-lane xxHash64 rounds over its
-//             16 words, lanes combined with rotate+xor, avalanche.
+//             16 words, avalanched with the block index, lanes summed.
 // All three are sums in a wrap-around ring, so partial results are merged with
 // atomics in any order and the answer is exact.
 #include <cstdlib>
@@ -92,6 +92,9 @@ constexpr int kDigestThreads = 512;
 constexpr uint64_t kRowBytes = 4096;
 constexpr uint64_t kDigestTile = 64 * 1024;
 
+// Per-LANE partial sums.  Every digest term is a sum that separates over lanes
+// (sum_k (k+1) * sum_lanes p = sum_lanes sum_k (k+1) * p), so lanes accumulate on
+// their own and the warp reduces once per span, not once per row.
 struct WarpAcc {
     uint64_t row_sum = 0, row_sum_w = 0, tail_sum = 0, tail_sum_w = 0, ragged = 0, block = 0;
     uint32_t safe = 0;
@@ -99,6 +102,15 @@ struct WarpAcc {
 };
 
 __device__ __forceinline__ void flush(WarpAcc &a, DigestAcc *acc, uint32_t lane) {
+    if (a.span != 0xffffffffu) {
+        a.row_sum = warp_sum_u64(a.row_sum);
+        a.row_sum_w = warp_sum_u64(a.row_sum_w);
+        a.tail_sum = warp_sum_u64(a.tail_sum);
+        a.tail_sum_w = warp_sum_u64(a.tail_sum_w);
+        a.ragged = warp_sum_u64(a.ragged);
+        a.block = warp_sum_u64(a.block);
+        a.safe = warp_sum_u32(a.safe);
+    }
     if (a.span != 0xffffffffu && lane == 0) {
         DigestAcc *o = acc + a.span;
         if (a.row_sum) atomicAdd(&o->row_sum, (unsigned long long)a.row_sum);
@@ -158,9 +170,9 @@ __device__ __forceinline__ void digest_tail_row(const RowMeta &m, const uint4 (&
             }
         }
     }
-    a.tail_sum += warp_sum_u64(ts);
-    a.tail_sum_w += warp_sum_u64(tw);
-    a.ragged += warp_sum_u64(rg);
+    a.tail_sum += ts;
+    a.tail_sum_w += tw;
+    a.ragged += rg;
 }
 
 template <uint32_t MODES, bool TAIL>
@@ -185,7 +197,7 @@ __device__ __forceinline__ void digest_row(const RowMeta &m, const uint4 (&v)[8]
             }
         }
         const uint32_t base = (uint32_t)(row_off + lane * 16) * kKnuth + 1u;
-        a.safe += warp_sum_u32(base * A + (512u * kKnuth) * B + kKnuth * X);
+        a.safe += base * A + (512u * kKnuth) * B + kKnuth * X;
     }
     if (MODES & MXB_DIGEST_ROWS) {
         const uint64_t whole_rows = (m.n / 4) / 1024;  // rows made only of whole words
@@ -195,9 +207,8 @@ __device__ __forceinline__ void digest_row(const RowMeta &m, const uint4 (&v)[8]
             for (int s = 0; s < 8; ++s)
                 s64 += (int64_t)(int32_t)v[s].x + (int64_t)(int32_t)v[s].y +
                        (int64_t)(int32_t)v[s].z + (int64_t)(int32_t)v[s].w;
-            const uint64_t rs = warp_sum_u64((uint64_t)s64);
-            a.row_sum += rs;
-            a.row_sum_w += rs * (m.row + 1);
+            a.row_sum += (uint64_t)s64;
+            a.row_sum_w += (uint64_t)s64 * (m.row + 1);
         } else if (TAIL) {
             digest_tail_row(m, v, lane, a);
         }
@@ -211,10 +222,13 @@ __device__ __forceinline__ void digest_row(const RowMeta &m, const uint4 (&v)[8]
             h = rotl64(h + x0 * kP2, 31) * kP1;
             h = rotl64(h + x1 * kP2, 31) * kP1;
         }
-        h = warp_xor_u64(rotl64(h * kP3, 2 * (int)lane + 1));
-        h = avalanche(h);
-        if (block_out && lane == 0) block_out[m.row] = h;
-        a.block += avalanche(h + (m.row + 1) * kP1);
+        // the lane's share of block `row`; the block hash is the sum of its 32 lane shares
+        const uint64_t share = avalanche(h + (m.row + 1) * kP1);
+        if (block_out) {
+            const uint64_t hb = warp_sum_u64(share);
+            if (lane == 0) block_out[m.row] = hb;
+        }
+        a.block += share;
     }
 }
 

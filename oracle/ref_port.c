@@ -149,7 +149,7 @@ static inline uint64_t avalanche(uint64_t h) {
     return h;
 }
 
-static uint64_t one_block(const uint8_t *p, uint64_t avail) {
+static uint64_t one_block(const uint8_t *p, uint64_t avail, uint64_t b) {
     uint8_t buf[4096];
     if (avail < 4096) {
         memset(buf, 0, sizeof buf);
@@ -165,9 +165,9 @@ static uint64_t one_block(const uint8_t *p, uint64_t avail) {
                 memcpy(&x, p + step * 512 + lane * 16 + k * 8, 8);
                 acc = rotl64(acc + x * P2, 31) * P1;
             }
-        h ^= rotl64(acc * P3, 2 * lane + 1);
+        h += avalanche(acc + (b + 1) * P1); /* the lane's share of block b */
     }
-    return avalanche(h);
+    return h;
 }
 
 void orc_block_hashes64(const uint8_t *p, uint64_t n, uint64_t *out) {
@@ -175,7 +175,7 @@ void orc_block_hashes64(const uint8_t *p, uint64_t n, uint64_t *out) {
 #pragma omp parallel for schedule(static)
     for (uint64_t b = 0; b < nblk; ++b) {
         uint64_t off = b * 4096;
-        out[b] = one_block(p + off, n - off);
+        out[b] = one_block(p + off, n - off, b);
     }
 }
 
@@ -184,7 +184,7 @@ uint64_t orc_block_hash64(const uint8_t *p, uint64_t n) {
 #pragma omp parallel for reduction(+ : total) schedule(static)
     for (uint64_t b = 0; b < nblk; ++b) {
         uint64_t off = b * 4096;
-        total += avalanche(one_block(p + off, n - off) + (b + 1) * P1);
+        total += one_block(p + off, n - off, b);
     }
     return total + avalanche(n * P5);
 }
