@@ -48,6 +48,16 @@ __device__ __forceinline__ uint64_t avalanche(uint64_t h) {
     return h;
 }
 
+// Streaming 16-byte load: read-only path, no L1 allocation, 256-byte L2 sectors
+// fetched together (every byte of the span is read exactly once, in order).
+__device__ __forceinline__ uint4 ld_stream16(const uint4 *p) {
+    uint4 v;
+    asm("ld.global.nc.L1::no_allocate.L2::256B.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
 // 16 bytes at p + off, zero beyond n; any alignment.
 __device__ __forceinline__ uint4 load16(const unsigned char *p, uint64_t off, uint64_t n,
                                         bool aligned16) {
@@ -55,7 +65,7 @@ __device__ __forceinline__ uint4 load16(const unsigned char *p, uint64_t off, ui
     if (off >= n) return v;
     const unsigned char *q = p + off;
     if (off + 16 <= n) {
-        if (aligned16) return __ldcs(reinterpret_cast<const uint4 *>(q));
+        if (aligned16) return ld_stream16(reinterpret_cast<const uint4 *>(q));
         const uint64_t a = (uint64_t)(uintptr_t)q;
         const uint32_t *w = reinterpret_cast<const uint32_t *>(a & ~3ull);
         const uint32_t sh = (uint32_t)(a & 3ull) * 8u;
