@@ -6,7 +6,11 @@
  * pointer, a peer pointer opened with mxb_ipc_open, or pinned host memory).
  * All functions return an int32 status (MXB_OK or a negative MXB_ERR_*) unless
  * stated otherwise; mxb_last_error() gives the text of the last failure on the
- * calling thread.  Nothing here falls back to the CPU: without a usable CUDA
+ * calling thread.  Kernels and copies run on streams the context owns; work
+ * the caller queued on its own streams for the same buffers must have
+ * completed before a call, and a call that waits (everything except the
+ * NO_SYNC / launch forms) returns with its results visible to any stream.
+ * Nothing here falls back to the CPU: without a usable CUDA
  * device the compute entry points return MXB_ERR_CUDA.
  *
  * Each entry point cites the reference interface it stands in for, by path

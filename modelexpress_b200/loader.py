@@ -133,7 +133,9 @@ def place_checkpoint(model_path: str, tp_rank: int, tp_size: int, device=None, *
         ring = ctx.ring(ring_bytes, ring_slots, dev_index)
     if params is None:
         params = allocate_params(plan, dev)
-        torch.cuda.synchronize(dev)
+    # the library works on its own streams: whatever the caller queued on torch's
+    # stream for these tensors (allocation fills, earlier writes) must be done first
+    torch.cuda.current_stream(dev).synchronize()
     images = {}
     try:
         for path in sorted({i["file"] for i in index.values()}):

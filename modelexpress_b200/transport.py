@@ -40,6 +40,9 @@ class MxbTransport:
 
     The run list is folded into 2-D records on the host (a row-parallel slice of
     4096 one-KiB runs becomes one record) and moved by the sm_100a kernel.
+    The launch runs on the library's own stream and ``read`` returns after it has
+    finished; work the caller queued earlier on another stream for the same
+    buffers must have completed (synchronise that stream first).
     Raises ``MxbError`` (``RuntimeError``) on a CUDA failure and ``MxbTimeout``
     (``TimeoutError``) when a device-side wait ran out; unknown sessions raise
     ``KeyError`` when a session table was given, as the NIXL transport does.

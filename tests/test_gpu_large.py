@@ -41,6 +41,7 @@ def test_digest_and_scatter_beyond_4_gib():
     got = ctx.digest([(dst.data_ptr(), BIG)], 4, 0)[0]
     assert int(got.block_hash) == int(rec.block_hash)
     dst.zero_()
+    torch.cuda.synchronize()  # the library runs on its own stream: order the fill before it
     rows, rb, sp = 70_000, 32_768, 65_536           # 2.3 GB moved, source span 4.6 GB > BIG? keep inside
     rows = min(rows, (BIG - rb) // sp)
     ctx.scatter([(src.data_ptr(), dst.data_ptr(), rows, rb, sp, rb)], 0)
