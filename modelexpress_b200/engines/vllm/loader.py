@@ -1,0 +1,131 @@
+"""``MxModelLoader`` for vLLM, weights placed by the B200 scatter path.
+
+vLLM's ``--load-format modelexpress`` imports
+``modelexpress.engines.vllm.loader:MxModelLoader`` and calls three methods on it
+(vllm/model_executor/model_loader/modelexpress_loader.py:15-68).  The
+reference's class (engines/vllm/loader.py:62-183) initialises the model, runs
+its strategy chain and returns ``model.eval()``.  This class keeps that surface
+— ``__init__(load_config)``, ``load_model(vllm_config, model_config, prefix)``,
+``download_model(model_config)``, ``load_weights(model, model_config)``, the
+``nixl_manager`` / ``tensors`` properties — and runs a two-entry chain:
+``B200ScatterStrategy`` (safetensors -> pinned ring -> PCIe -> scatter kernel,
+straight into the engine's parameters), then vLLM's own ``DefaultModelLoader``
+when the checkpoint is not a local safetensors directory or its layout is not
+one the placement rules know.  The ``shim/`` directory next to this package
+exposes the class at the dotted path vLLM imports.
+"""
+
+from __future__ import annotations
+
+import copy
+import logging
+import os
+
+from ...loader import B200ScatterStrategy, LoadResult, StrategyFailed
+
+logger = logging.getLogger("modelexpress_b200.engines.vllm")
+
+try:  # vLLM is the host engine; without it the class still imports for inspection
+    from vllm.model_executor.model_loader.base_loader import BaseModelLoader
+except Exception:  # pragma: no cover - exercised only where vLLM is absent
+    class BaseModelLoader:  # type: ignore[no-redef]
+        def __init__(self, load_config):
+            self.load_config = load_config
+
+
+class VllmScatterAdapter:
+    """The two hooks ``B200ScatterStrategy`` needs from an engine adapter, for vLLM
+    (the reference's adapter contract is adapter.py:54-196)."""
+
+    def tp_layout(self, result) -> tuple:
+        from vllm.distributed import (get_tensor_model_parallel_rank,
+                                      get_tensor_model_parallel_world_size)
+
+        return int(get_tensor_model_parallel_rank()), int(get_tensor_model_parallel_world_size())
+
+    def named_destinations(self, result) -> dict:
+        return {name: p.data for name, p in result.model.named_parameters()}
+
+
+class _Ctx:
+    def __init__(self, model_config, device_id: int):
+        self.model_config = model_config
+        self.device_id = device_id
+        self.adapter = VllmScatterAdapter()
+
+
+class MxModelLoader(BaseModelLoader):
+    """Drop-in for the reference's vLLM loader class."""
+
+    def __init__(self, load_config):
+        super().__init__(load_config)
+        self._tensors: dict = {}
+        self.last_strategy: str | None = None
+
+    # -- BaseModelLoader surface ------------------------------------------------
+    def download_model(self, model_config) -> None:
+        """A local checkpoint directory needs nothing; anything else goes through
+        vLLM's own downloader, as the reference does (loader.py:138-158)."""
+        if os.path.isdir(str(model_config.model)):
+            return
+        self._native().download_model(model_config)
+
+    def load_weights(self, model, model_config) -> None:
+        """Load weights into an already-initialised model (standalone API)."""
+        import torch
+
+        device_id = torch.cuda.current_device()
+        result = LoadResult(value=model, model=model)
+        strategy = B200ScatterStrategy()
+        ctx = _Ctx(model_config, device_id)
+        try:
+            if not strategy.is_available(ctx):
+                raise StrategyFailed("CUDA library or device unavailable", mutated=False)
+            strategy.load(result, ctx)
+            self.last_strategy = strategy.name
+            logger.info("weights placed by %s: %s", strategy.name, result.metadata.get(strategy.name))
+        except StrategyFailed as e:
+            strategy.rollback(ctx)
+            if e.mutated:
+                # bytes may be half-written: the engine loader below rewrites every parameter
+                logger.warning("b200_scatter failed after touching weights (%s); reloading natively", e)
+            else:
+                logger.info("b200_scatter not applicable (%s); using the engine's loader", e)
+            self._native().load_weights(model, model_config)
+            self.last_strategy = "default"
+        self._tensors = {n: p.data for n, p in model.named_parameters()}
+
+    def load_model(self, vllm_config, model_config, prefix: str = ""):
+        import torch
+        from vllm.model_executor.model_loader.utils import (initialize_model,
+                                                            process_weights_after_loading)
+        from vllm.utils.torch_utils import set_default_torch_dtype
+
+        device_config = vllm_config.device_config
+        target_device = torch.device(device_config.device)
+        with set_default_torch_dtype(model_config.dtype):
+            with target_device:
+                model = initialize_model(vllm_config=vllm_config, model_config=model_config, prefix=prefix)
+            self.load_weights(model, model_config)
+            process_weights_after_loading(model, model_config, target_device)
+        return model.eval()
+
+    # -- reference-compatible extras ---------------------------------------------
+    @property
+    def nixl_manager(self):
+        """There is no NIXL agent on this path (peers are reached over NVLink)."""
+        return None
+
+    @property
+    def tensors(self) -> dict:
+        return self._tensors
+
+    def _native(self):
+        from vllm.model_executor.model_loader.default_loader import DefaultModelLoader
+
+        disk_config = copy.copy(self.load_config)
+        try:
+            disk_config.load_format = "auto"
+        except AttributeError:
+            object.__setattr__(disk_config, "load_format", "auto")
+        return DefaultModelLoader(disk_config)

@@ -38,7 +38,7 @@ def _build_vllm_model(model_dir):
         ps.initialize_model_parallel(1, 1)
     with set_default_torch_dtype(torch.bfloat16), torch.device("cuda"):
         model = initialize_model(vllm_config=vc)
-    return model, ctx
+    return model, ctx, vc, mc
 
 
 def test_place_checkpoint_equals_vllm_load_weights(tmp_path):
@@ -56,7 +56,7 @@ def test_place_checkpoint_equals_vllm_load_weights(tmp_path):
                             head_dim=32, vocab=1024, qkv_bias=False, seed=21, files=1)
     synth.write_checkpoint(d, synth.dense_tensors(cfg), cfg.seed, 1)
     try:
-        model, ctx = _build_vllm_model(d)
+        model, ctx, vc, mc = _build_vllm_model(d)
     except Exception as e:  # vLLM internals differ between versions / environments
         pytest.skip(f"vLLM could not build a model here: {type(e).__name__}: {e}")
     try:
@@ -78,5 +78,36 @@ def test_place_checkpoint_equals_vllm_load_weights(tmp_path):
         for n, t in truth.items():
             assert torch.equal(params[n].detach().view(torch.int16), t.view(torch.int16)), n
         assert placed.stats.bytes_placed == sum(t.numel() * t.element_size() for t in truth.values())
+
+        # the outermost seam: vLLM's own `--load-format modelexpress` wrapper importing
+        # modelexpress.engines.vllm.loader:MxModelLoader (here: the shim directory)
+        import sys
+
+        from vllm.config import LoadConfig
+
+        shim = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                            "modelexpress_b200", "shim")
+        sys.path.insert(0, shim)
+        try:
+            from vllm.model_executor.model_loader.modelexpress_loader import ModelExpressModelLoader
+
+            wrapper = ModelExpressModelLoader(LoadConfig(load_format="auto"))
+            model2 = wrapper.load_model(vllm_config=vc, model_config=mc)
+            inner = wrapper._loader
+            assert type(inner).__name__ == "MxModelLoader" and inner.last_strategy == "b200_scatter"
+            assert inner.nixl_manager is None and set(inner.tensors) == set(truth)
+            assert not model2.training
+            for n, p in model2.named_parameters():
+                assert torch.equal(p.detach().view(torch.int16), truth[n].view(torch.int16)), n
+            # standalone API on the already-initialised first model
+            for p in params.values():
+                p.data.zero_()
+            inner.load_weights(model, mc)
+            for n, t in truth.items():
+                assert torch.equal(params[n].detach().view(torch.int16), t.view(torch.int16)), n
+        finally:
+            sys.path.remove(shim)
+            for k in [k for k in sys.modules if k == "modelexpress" or k.startswith("modelexpress.")]:
+                del sys.modules[k]
     finally:
         ctx.__exit__(None, None, None)
