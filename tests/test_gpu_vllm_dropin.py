@@ -91,8 +91,14 @@ def test_place_checkpoint_equals_vllm_load_weights(tmp_path):
         try:
             from vllm.model_executor.model_loader.modelexpress_loader import ModelExpressModelLoader
 
+            from vllm.config import DeviceConfig, VllmConfig, set_current_vllm_config
+
             wrapper = ModelExpressModelLoader(LoadConfig(load_format="auto"))
-            model2 = wrapper.load_model(vllm_config=vc, model_config=mc)
+            # a second model needs its own config object (layer names are registered per config)
+            vc2 = VllmConfig(model_config=mc, device_config=DeviceConfig(device="cuda"),
+                             load_config=LoadConfig(load_format="auto"))
+            with set_current_vllm_config(vc2):
+                model2 = wrapper.load_model(vllm_config=vc2, model_config=mc)
             inner = wrapper._loader
             assert type(inner).__name__ == "MxModelLoader" and inner.last_strategy == "b200_scatter"
             assert inner.nixl_manager is None and set(inner.tensors) == set(truth)
