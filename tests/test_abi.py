@@ -90,3 +90,23 @@ def test_coalesce_folds_strided_runs_and_round_trips():
         for src, dst, rows, rb, sp, dp in recs.tolist():
             exp += [(src + r * sp, dst + r * dp, rb) for r in range(rows)]
         assert sorted(exp) == sorted(x for x in rr if x[2])
+
+
+def test_vllm_import_path_shim_exposes_the_loader_class():
+    """vLLM imports modelexpress.engines.vllm.loader:MxModelLoader; the shim directory
+    must expose our class there with the reference's entry points."""
+    import importlib
+    import sys
+
+    shim = os.path.join(ROOT, "modelexpress_b200", "shim")
+    sys.path.insert(0, shim)
+    try:
+        mod = importlib.import_module("modelexpress.engines.vllm.loader")
+        cls = mod.MxModelLoader
+        for name in ("load_model", "download_model", "load_weights", "nixl_manager", "tensors"):
+            assert hasattr(cls, name), name
+        assert cls.__module__ == "modelexpress_b200.engines.vllm.loader"
+    finally:
+        sys.path.remove(shim)
+        for k in [k for k in sys.modules if k == "modelexpress" or k.startswith("modelexpress.")]:
+            del sys.modules[k]
