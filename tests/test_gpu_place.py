@@ -228,3 +228,52 @@ def test_ring_random_items_any_alignment(seed, mode):
     assert st.chunks > 10
     ring.close()
     ctx.close()
+
+
+def test_sglang_loader_signature_with_stand_ins(ckpts):
+    """engines/sglang/loader.py:61-86: keyword-only load_model(model=, model_config=,
+    device_config=) on an already initialised model."""
+    import torch
+
+    from modelexpress_b200.engines.sglang.loader import MxModelLoader
+    from modelexpress_b200.layout import plan_checkpoint
+    from modelexpress_b200.loader import torch_dtype
+    from modelexpress_b200.safetensors_index import checkpoint_index
+
+    tiny, _ = ckpts
+    idx = checkpoint_index(tiny)
+    plan = plan_checkpoint({n: {"shape": i["shape"], "dtype": i["dtype"]} for n, i in idx.items()}, 2, 4)
+
+    class Model(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.names = {}
+            for i, (n, s) in enumerate(plan.params.items()):
+                p = torch.nn.Parameter(torch.zeros(tuple(s.shape), dtype=torch_dtype(s.dtype), device="cuda"),
+                                       requires_grad=False)
+                self.register_parameter(f"p{i}", p)
+                self.names[f"p{i}"] = n
+
+        def named_parameters(self, *a, **k):
+            for n, p in super().named_parameters(*a, **k):
+                yield self.names[n], p
+
+    class ModelConfig:
+        model_path = tiny
+
+    class DeviceConfig:
+        gpu_id = 0
+
+    model = Model()
+    torch.cuda.synchronize()
+    out = MxModelLoader(object(), tp_rank=2, tp_size=4).load_model(
+        model=model, model_config=ModelConfig(), device_config=DeviceConfig())
+    assert out is model and not model.training
+    want = R.load_and_shard(read_full_tensors(tiny), 2, 4)
+    got = dict(model.named_parameters())
+    for n, a in want.items():
+        assert np.array_equal(_as_np(got[n]), a), n
+    ModelConfig.model_path = "/nonexistent"
+    with pytest.raises(RuntimeError, match="No loading strategy succeeded"):
+        MxModelLoader(object(), tp_rank=0, tp_size=1).load_model(
+            model=model, model_config=ModelConfig(), device_config=DeviceConfig())
