@@ -95,7 +95,7 @@ def test_unaligned_views_digest_like_their_copies(torch_mod, half):
     assert r_view == r_copy
     want = R.tensor_digest(view.cpu().view(torch.int16).numpy())
     assert r_view["tensor_digest"] == want
-    # every byte offset, with the oracle as the judge
+    # every byte offset, checked against the oracle
     raw = torch.from_numpy(golden_bytes(8, 70_000)).cuda()
     host = raw.cpu().numpy()
     views = [raw[o:o + 65_000 + o] for o in range(0, 8)]

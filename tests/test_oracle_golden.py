@@ -53,7 +53,7 @@ def test_digests_match_reference(case):
 
 
 def test_known_reference_values():
-    # values computed from the reference code and quoted in the survey notes
+    # values computed from the reference code when the fixtures were first generated
     assert R.tensor_digest(np.arange(4096, dtype=np.int32)) == "b80e42d0aa211223be9669385be8976b"
     import torch
 
