@@ -238,7 +238,8 @@ def bench_place(args):
     threads = env_int("MXB_HOST_THREADS", max(2, min(32, (os.cpu_count() or 8) * 3 // 4 // local_world)))
     slots = env_int("MXB_RING_SLOTS", 32)
     mode = PLACE_ZERO_COPY if os.environ.get("MXB_PLACE_MODE", "ce") == "zc" else PLACE_COPY_ENGINE
-    ring = ctx.ring(2 << 30, slots, local)
+    ring_bytes = env_int("MXB_RING_BYTES", 2 << 30)
+    ring = ctx.ring(ring_bytes, slots, local)
     skip_e2e = os.environ.get("MXB_BENCH_SKIP_E2E") == "1"  # profiling runs that only want the table launches
     for _ in range(0 if skip_e2e else args.warmup):
         ring.place(items, threads, mode)
@@ -329,7 +330,7 @@ def bench_place(args):
             "tensors": len(idx), "records_per_step": len(plan.placements),
             "source_for_value": "checkpoint file image resident in HBM",
             "l2": "inputs larger than L2 (every step reads and writes bytes_placed, far above 126 MB)",
-            "ring": {"bytes": 2 << 30, "slots": slots, "host_threads": threads,
+            "ring": {"bytes": ring_bytes, "slots": slots, "host_threads": threads,
                      "mode": "zero_copy" if mode == PLACE_ZERO_COPY else "copy_engine"},
             "seconds_to_loaded_e2e": round(e2e_s / args.steps, 4),
         },
