@@ -258,6 +258,21 @@ def bench_place(args):
     e2e_s = max_over_ranks(e2e_s, world)
     e2e_launches = ctx.launch_count - launches0
 
+    # the binding roofline of the e2e path: pinned -> device copies, all ranks at once
+    pin = torch.empty(1 << 30, dtype=torch.uint8).pin_memory()
+    dev_buf = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+    dev_buf.copy_(pin, non_blocking=True)
+    torch.cuda.synchronize()
+    barrier(world)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(3):
+        dev_buf.copy_(pin, non_blocking=True)
+    ev1.record()
+    torch.cuda.synchronize()
+    pcie_gbs = sum_over_ranks(3 * (1 << 30) / (ev0.elapsed_time(ev1) * 1e-3) / 1e9, world)
+    del pin, dev_buf
+
     # consistency check of what the e2e path placed against the resident path below
     # (parity against the oracle lives in tests/ and in the cpu_baseline leg)
     some = [n for n in list(plan.params)[:6]]
@@ -339,7 +354,11 @@ def bench_place(args):
                 "h2d_bytes_per_step": int(bytes_placed), "d2h_bytes_per_step": 4,
                 "host_gather_s_per_step": round(sum(s.seconds_gather for s in e2e_stats) / args.steps, 4),
                 "device_s_per_step": round(sum(s.seconds_device for s in e2e_stats) / args.steps, 4),
-                "chunks_per_step": int(e2e_stats[0].chunks)},
+                "chunks_per_step": int(e2e_stats[0].chunks),
+                "binding_roofline": {"bound": "pcie_h2d", "peak": round(pcie_gbs, 1), "unit": "GB/s",
+                                     "frac": round(e2e_value / pcie_gbs, 4),
+                                     "how": "pinned->device cudaMemcpyAsync of 1 GiB x3 on every rank at "
+                                            "once, summed over ranks, measured in this run"}},
         "gpu_launches": int(kern_launches),
         "gpu_launches_e2e": int(e2e_launches),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
