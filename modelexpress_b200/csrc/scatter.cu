@@ -132,6 +132,33 @@ __device__ __forceinline__ void copy_span(char *d, const char *s, uint64_t n, ui
 }
 
 constexpr int kVecThreads = 512;
+
+// rows x nvec 16-byte vectors, both sides 16-byte aligned; at most 64 KiB in total
+__device__ __forceinline__ void copy_rows16(char *d, const char *s, uint32_t rows, uint32_t nvec,
+                                            uint64_t sp, uint64_t dp, uint32_t t) {
+    const uint32_t total = rows * nvec;
+    uint32_t i = t;
+    for (; i + 3 * kVecThreads < total; i += 4 * kVecThreads) {
+        uint32_t r[4], v[4];
+        uint4 x[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t j = i + k * kVecThreads;
+            r[k] = j / nvec;
+            v[k] = j - r[k] * nvec;
+            x[k] = __ldcs(reinterpret_cast<const uint4 *>(s + (uint64_t)r[k] * sp) + v[k]);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            __stcs(reinterpret_cast<uint4 *>(d + (uint64_t)r[k] * dp) + v[k], x[k]);
+    }
+    for (; i < total; i += kVecThreads) {
+        const uint32_t r = i / nvec, v = i - r * nvec;
+        __stcs(reinterpret_cast<uint4 *>(d + (uint64_t)r * dp) + v,
+               __ldcs(reinterpret_cast<const uint4 *>(s + (uint64_t)r * sp) + v));
+    }
+}
+
 constexpr uint64_t kWarpRowMax = 8192;  // rows up to this size are copied one warp per row
 
 __global__ void __launch_bounds__(kVecThreads)
@@ -160,6 +187,12 @@ scatter_vec_kernel(const mxb_desc2d *__restrict__ descs, const Tile *__restrict_
                 // rows are back to back on both sides: one flat span
                 copy_span(dst + r0 * d.row_bytes, src + r0 * d.row_bytes, (r1 - r0) * d.row_bytes,
                           tid, kVecThreads);
+            } else if (((d.src | d.dst | d.src_pitch | d.dst_pitch | d.row_bytes) & 15u) == 0) {
+                // aligned strided rows (a row-parallel slice): the tile is a rows x vectors
+                // grid walked by the whole CTA, four independent 16-byte loads per thread
+                // in flight whatever the row length
+                copy_rows16(dst + r0 * d.dst_pitch, src + r0 * d.src_pitch, (uint32_t)(r1 - r0),
+                            (uint32_t)(d.row_bytes >> 4), d.src_pitch, d.dst_pitch, tid);
             } else if (d.row_bytes <= kWarpRowMax) {
                 for (uint64_t r = r0 + warp; r < r1; r += nwarps)
                     copy_span(dst + r * d.dst_pitch, src + r * d.src_pitch, d.row_bytes, lane, 32);
