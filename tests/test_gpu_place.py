@@ -277,3 +277,62 @@ def test_sglang_loader_signature_with_stand_ins(ckpts):
     with pytest.raises(RuntimeError, match="No loading strategy succeeded"):
         MxModelLoader(object(), tp_rank=0, tp_size=1).load_model(
             model=model, model_config=ModelConfig(), device_config=DeviceConfig())
+
+
+@pytest.mark.parametrize("rank", [0, 1])
+def test_mdl_loader_warm_install(rank):
+    """tests/test_mdl_tp.py:50-81 and test_mdl_fp8-style fused members on the GPU:
+    global HF tensors -> this rank's fused / pre-merged / row-parallel parameters in one
+    launch; the second cycle with the same buffers is 'warm' (no re-planning)."""
+    import torch
+
+    from modelexpress_b200.installer import MdlLoader
+
+    class Model(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            z = lambda *s: torch.nn.Parameter(torch.zeros(*s, dtype=torch.bfloat16, device="cuda"),
+                                              requires_grad=False)
+            self.qkv = z(12, 8)          # (8 + 2*8) / 2 rows... q 16 rows, k 4, v 4 global, tp=2
+            self.gate_up = z(8, 8)       # pre-merged [gate; up], 16 rows global
+            self.o = z(8, 8)             # row-parallel: [8, 16] global
+            self.norm = z(8)
+
+        def named_parameters(self, *a, **k):
+            yield "l.self_attn.qkv_proj.weight", self.qkv
+            yield "l.mlp.gate_up_proj.weight", self.gate_up
+            yield "l.self_attn.o_proj.weight", self.o
+            yield "l.input_layernorm.weight", self.norm
+
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    mk = lambda *s: torch.randn(*s, device="cuda", generator=g).to(torch.bfloat16)
+    w = {"l.self_attn.q_proj.weight": mk(16, 8), "l.self_attn.k_proj.weight": mk(4, 8),
+         "l.self_attn.v_proj.weight": mk(4, 8), "l.mlp.gate_up_proj.weight": mk(16, 8),
+         "l.self_attn.o_proj.weight": mk(8, 16), "l.input_layernorm.weight": mk(8)}
+    model = Model()
+    torch.cuda.synchronize()
+    mdl = MdlLoader(model, tp_rank=rank, tp_size=2)
+
+    def check():
+        q, k, v = (w[f"l.self_attn.{m}_proj.weight"] for m in "qkv")
+        want_qkv = torch.cat((q[rank * 8:(rank + 1) * 8], k[rank * 2:(rank + 1) * 2], v[rank * 2:(rank + 1) * 2]))
+        gu = w["l.mlp.gate_up_proj.weight"]
+        want_gu = torch.cat((gu[rank * 4:(rank + 1) * 4], gu[8 + rank * 4: 8 + (rank + 1) * 4]))
+        assert torch.equal(model.qkv, want_qkv)
+        assert torch.equal(model.gate_up, want_gu)
+        assert torch.equal(model.o, w["l.self_attn.o_proj.weight"][:, rank * 8:(rank + 1) * 8])
+        assert torch.equal(model.norm, w["l.input_layernorm.weight"])
+
+    mdl.load_weights(list(w.items()))
+    assert mdl.last_cycle == "cold" and mdl.cycles == 1
+    check()
+    for t in w.values():                      # a new version of the weights in the same buffers
+        t.copy_(mk(*t.shape))
+    mdl.load_weights(list(w.items()))
+    assert mdl.last_cycle == "warm" and mdl.cycles == 2
+    check()
+    assert mdl.covered_params == {n for n, _ in model.named_parameters()}
+    with pytest.raises(KeyError):
+        MdlLoader(model, 0, 2).load_weights([("l.unknown.weight", mk(4, 4))])
+    mdl.close()
