@@ -456,6 +456,8 @@ def run_reshard(args):
                        if tables and tables[0].engine(flags) != "vector" else "scatter_vec_kernel",
                        "peak_source": f"max(local copy bytes x2 / {peak} GB/s {src}, NVLink bytes / "
                                       f"{NVLINK_PEER_GBS} GB/s measured peer copy)"}
+    if rank == 0 and world == 1 and os.environ.get("MXB_BENCH_SKIP_CPU") != "1":
+        out["cpu_baseline"] = _reshard_cpu_baseline(cfg, R)
     if rank == 0:
         print(json.dumps(out), flush=True)
     for tb in tables:
@@ -465,6 +467,33 @@ def run_reshard(args):
         import torch.distributed as dist
 
         dist.destroy_process_group()
+
+
+def _reshard_cpu_baseline(cfg, R):
+    """The reference's CPU regather-and-reslice (its memmove transport loop,
+    refit/reshard/transport/base.py:56-62, here the oracle's C port on all host
+    threads) over a 2-layer model of the same shapes: the same plan, host buffers."""
+    from modelexpress_b200 import layout, reshard, synth
+    from oracle import c_port  # cpu_baseline leg: the timed CPU port
+
+    small = synth.scaled(cfg, layers=2)
+    tensors = synth.dense_tensors(small)
+    index = {n: {"shape": list(s), "dtype": d} for n, s, d, _k in tensors}
+    sa = reshard.shard_arena(index, R)
+    pa = reshard.param_arena(layout.plan_checkpoint(index, 0, R, "dense"))
+    shards = [np.full(sa.total, 7, dtype=np.uint8) for _ in range(R)]  # memmove speed is data-independent
+    params = [np.full(pa.total, 1, dtype=np.uint8) for _ in range(R)]  # touched, so no page faults are timed
+    recs = [reshard.plan_reshard(index, R, R, s, shards[s].ctypes.data, [p.ctypes.data for p in params],
+                                 "dense", shards=sa, params=pa) for s in range(R)]
+    moved = sum(reshard.reshard_bytes(r) for r in recs)
+    c_port.scatter2d(recs[0].tolist(), mt=True)  # warm
+    t0 = time.perf_counter()
+    for r in recs:
+        c_port.scatter2d(r.tolist(), mt=True)
+    dt = time.perf_counter() - t0
+    return {"value": round(moved / dt / 1e9, 3), "unit": "GB/s written", "cores": os.cpu_count(),
+            "kind": "port", "sample": f"2 of {cfg.layers} layers plus embed/lm_head ({moved} B), "
+                                      "all 8 source ranks, OpenMP memmove loop over the same records"}
 
 
 def run(args):
