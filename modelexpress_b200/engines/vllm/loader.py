@@ -7,11 +7,14 @@ reference's class (engines/vllm/loader.py:62-183) initialises the model, runs
 its strategy chain and returns ``model.eval()``.  This class keeps that surface
 — ``__init__(load_config)``, ``load_model(vllm_config, model_config, prefix)``,
 ``download_model(model_config)``, ``load_weights(model, model_config)``, the
-``nixl_manager`` / ``tensors`` properties — and runs a two-entry chain:
-``B200ScatterStrategy`` (safetensors -> pinned ring -> PCIe -> scatter kernel,
-straight into the engine's parameters), then vLLM's own ``DefaultModelLoader``
-when the checkpoint is not a local safetensors directory or its layout is not
-one the placement rules know.  The ``shim/`` directory next to this package
+``nixl_manager`` / ``tensors`` properties — and runs a three-entry chain:
+``B200CapturedStrategy`` (the model's own ``load_weights`` dry-run over
+byte-less placeholders tells which window of which checkpoint tensor lands
+where, for any architecture vLLM can load; safetensors -> pinned ring -> PCIe
+-> scatter kernel, straight into the engine's parameters), then
+``B200ScatterStrategy`` (the same data path planned from built-in layout
+rules), then vLLM's own ``DefaultModelLoader`` when the checkpoint is not a
+local safetensors directory.  The ``shim/`` directory next to this package
 exposes the class at the dotted path vLLM imports.
 """
 
@@ -21,7 +24,7 @@ import copy
 import logging
 import os
 
-from ...loader import B200ScatterStrategy, LoadResult, StrategyFailed
+from ...loader import B200CapturedStrategy, B200ScatterStrategy, LoadResult, StrategyFailed
 
 logger = logging.getLogger("modelexpress_b200.engines.vllm")
 
@@ -76,21 +79,22 @@ class MxModelLoader(BaseModelLoader):
 
         device_id = torch.cuda.current_device()
         result = LoadResult(value=model, model=model)
-        strategy = B200ScatterStrategy()
         ctx = _Ctx(model_config, device_id)
-        try:
-            if not strategy.is_available(ctx):
-                raise StrategyFailed("CUDA library or device unavailable", mutated=False)
-            strategy.load(result, ctx)
-            self.last_strategy = strategy.name
-            logger.info("weights placed by %s: %s", strategy.name, result.metadata.get(strategy.name))
-        except StrategyFailed as e:
-            strategy.rollback(ctx)
-            if e.mutated:
-                # bytes may be half-written: the engine loader below rewrites every parameter
-                logger.warning("b200_scatter failed after touching weights (%s); reloading natively", e)
-            else:
-                logger.info("b200_scatter not applicable (%s); using the engine's loader", e)
+        self.last_strategy = None
+        for strategy in (B200CapturedStrategy(), B200ScatterStrategy()):
+            try:
+                if not strategy.is_available(ctx):
+                    raise StrategyFailed("CUDA library or device unavailable", mutated=False)
+                strategy.load(result, ctx)
+                self.last_strategy = strategy.name
+                logger.info("weights placed by %s: %s", strategy.name, result.metadata.get(strategy.name))
+                break
+            except StrategyFailed as e:
+                strategy.rollback(ctx)
+                # after a failure that touched weights every later strategy rewrites all of them
+                level = logger.warning if e.mutated else logger.info
+                level("%s did not load the model (%s); trying the next strategy", strategy.name, e)
+        if self.last_strategy is None:
             self._native().load_weights(model, model_config)
             self.last_strategy = "default"
         self._tensors = {n: p.data for n, p in model.named_parameters()}

@@ -152,6 +152,156 @@ def place_checkpoint(model_path: str, tp_rank: int, tp_size: int, device=None, *
     return PlacedCheckpoint(params, plan, stats)
 
 
+@dataclass
+class CapturedPlacement:
+    """Outcome of ``place_captured``."""
+
+    stats: PlaceResult
+    copies: int                 # recorded copies that became scatter records
+    records: int
+    converted: list             # parameters filled through a dtype cast
+    engine_loaded: list         # sources left to the engine's own loader
+    reasons: dict               # source -> why capture or planning gave it up
+    written_params: set         # parameters and buffers that received records
+
+
+def _engine_tensor(image: FileImage, info: dict):
+    """A real (host) tensor over the checkpoint bytes, for the engine's loader."""
+    import torch
+
+    raw = torch.frombuffer(image._mm, dtype=torch.uint8, count=int(info["size"]),
+                           offset=int(info["file_offset"]))
+    return raw.view(torch_dtype(info["dtype"])).reshape(tuple(info["shape"]))
+
+
+@dataclass
+class CapturedTable:
+    """What one capture of an engine's loader compiles to."""
+
+    records: np.ndarray         # (n, 6) uint64 scatter records
+    converts: list              # planner.ConvertSpec for copies that change dtype
+    staging_bytes: int          # device staging those converts need
+    reasons: dict               # source -> why it is left to the engine's loader
+    copies: int                 # recorded copies that became records
+    written_params: set         # parameters and buffers at least one record writes into
+
+
+def model_destinations(model) -> dict:
+    """{name: tensor} over parameters and buffers, shared ones under every name."""
+    import torch
+
+    return {n: (t.data if isinstance(t, torch.nn.Parameter) else t)
+            for n, t in list(model.named_parameters(remove_duplicate=False))
+            + list(model.named_buffers(remove_duplicate=False))}
+
+
+def captured_table(model, index: dict, file_address: dict, *, load_weights=None, device=None,
+                   alloc_staging=None, dests: dict | None = None) -> CapturedTable:
+    """Dry-run ``load_weights`` over the checkpoint's header and compile what it
+    copies into scatter records from ``file_address[file] + file_offset`` to the
+    model's own tensors.  ``alloc_staging(nbytes) -> address`` provides the
+    buffer dtype-changing copies are staged in; without it such copies are left
+    to the engine's loader."""
+    from .geometry import capture_geometry
+    from .planner import ShardSpec, SourceSpec, convert_staging_bytes, plan_transfer_2d
+
+    loader = load_weights if load_weights is not None else model.load_weights
+    manifest = [(n, torch_dtype(i["dtype"]), tuple(i["shape"])) for n, i in index.items()]
+    cap = capture_geometry(model, manifest, loader, device=device)
+    if dests is None:
+        dests = model_destinations(model)
+    sources = {}
+    for name, info in index.items():
+        elsize = SAFETENSORS_DTYPES[info["dtype"]][0]
+        shape = tuple(int(x) for x in info["shape"])
+        sources[name] = SourceSpec(shape, torch_dtype(info["dtype"]), elsize, [
+            ShardSpec(tuple(0 for _ in shape), shape, info["file"],
+                      int(file_address[info["file"]]) + int(info["file_offset"]), elsize)])
+    staging_bytes = convert_staging_bytes(cap.copies, sources) if alloc_staging is not None else 0
+    convert_base = int(alloc_staging(staging_bytes)) if staging_bytes else None
+    table, not_planned, converts = plan_transfer_2d(
+        cap.copies, sources, lambda n: dests[n].data_ptr(), convert_base)
+    reasons = dict(cap.unsupported_reasons)
+    for n in not_planned:
+        reasons.setdefault(n, "the copied window is not a box of the source tensor, or changes dtype")
+    dropped = set(not_planned)
+    planned = [c for c in cap.copies if c.src_name not in dropped]
+    return CapturedTable(table, converts, staging_bytes, reasons, len(planned),
+                         {c.param_name for c in planned})
+
+
+def place_captured(model, model_path: str, device=None, *, load_weights=None,
+                   ring: Ring | None = None, ctx: Context | None = None,
+                   host_threads: int | None = None, mode: int = PLACE_COPY_ENGINE,
+                   ring_bytes: int = 2 << 30, ring_slots: int = 32,
+                   on_unsupported: str = "engine") -> CapturedPlacement:
+    """Load a safetensors checkpoint into ``model`` for ANY architecture whose
+    engine-side ``load_weights`` only slices and copies.
+
+    The engine's own loader is dry-run once over byte-less placeholders
+    (``geometry.capture_geometry``), which yields, for this rank, the exact window
+    of every checkpoint tensor and where it lands — fused projections, expert
+    stacks, tensor-parallel shards, vocabulary padding, renamed or skipped
+    tensors, all as the engine itself decides them.  Those copies become 2-D
+    records (``planner.plan_transfer_2d``; the file is the single published shard
+    of each tensor) and go through the pinned ring and the scatter kernel.  A
+    copy whose checkpoint dtype differs from the parameter's is staged on the
+    device and cast there.  Sources the loader has to compute on (a scalar read
+    with ``.item()``, a transposing ``contiguous()``) are few and small: with
+    ``on_unsupported="engine"`` they are handed to the same ``load_weights`` as
+    real host tensors afterwards, with ``"raise"`` the call fails before any
+    byte is written."""
+    import torch
+
+    from .planner import apply_converts
+
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if dev.type != "cuda":
+        raise RuntimeError("place_captured needs a CUDA device (no CPU fallback)")
+    dev_index = dev.index if dev.index is not None else torch.cuda.current_device()
+    loader = load_weights if load_weights is not None else model.load_weights
+    index = checkpoint_index(model_path)
+    dests = model_destinations(model)
+    own_ring = ring is None
+    if ctx is None:
+        ctx = ring.ctx if ring is not None else default_context(dev_index)
+    images: dict = {}
+    try:
+        for path in sorted({i["file"] for i in index.values()}):
+            images[path] = FileImage(path)
+        staging = []
+
+        def alloc_staging(nbytes: int) -> int:
+            staging.append(torch.empty(nbytes, dtype=torch.uint8, device=dev))
+            return staging[0].data_ptr()
+
+        cap = captured_table(model, index, {p: im.address for p, im in images.items()},
+                             load_weights=loader, device=dev, alloc_staging=alloc_staging, dests=dests)
+        leftover = [n for n in index if n in cap.reasons]
+        if leftover and on_unsupported != "engine":
+            raise StrategyFailed(
+                f"{len(leftover)} source tensor(s) need the engine's loader, e.g. "
+                f"{leftover[0]}: {cap.reasons[leftover[0]]}", mutated=False)
+        table = cap.records
+        if ring is None:
+            ring = ctx.ring(ring_bytes, ring_slots, dev_index)
+        torch.cuda.current_stream(dev).synchronize()
+        threads = host_threads or max(2, min(32, (os.cpu_count() or 8) * 3 // 4))
+        stats = ring.place(table, threads, mode)
+        if cap.converts:
+            apply_converts(cap.converts, staging[0], dests)
+        if leftover:
+            loader((n, _engine_tensor(images[index[n]["file"]], index[n])) for n in leftover)
+        torch.cuda.current_stream(dev).synchronize()
+    finally:
+        for im in images.values():
+            im.close()
+        if own_ring and ring is not None:
+            ring.close()
+    return CapturedPlacement(stats, cap.copies, int(len(table)), [c.param_name for c in cap.converts],
+                             leftover, cap.reasons, cap.written_params)
+
+
 class B200ScatterStrategy:
     """Load strategy placing weights with the scatter kernel.
 
@@ -208,3 +358,38 @@ class B200ScatterStrategy:
 
     def rollback(self, ctx) -> None:
         self._touched = False
+
+
+class B200CapturedStrategy(B200ScatterStrategy):
+    """The same placement, planned from the engine's own ``load_weights`` instead of
+    layout rules (``place_captured``): it covers whatever architecture the engine
+    can load.  The adapter needs one hook, ``model_of(result) -> torch.nn.Module``
+    (default: ``result.model``); ranks and shard shapes are whatever the engine's
+    loader makes of its parallel state."""
+
+    name = "b200_captured"
+
+    def load(self, result: LoadResult, ctx) -> LoadResult:
+        model_dir = getattr(ctx.model_config, "model", None)
+        if not model_dir or not os.path.isdir(model_dir):
+            raise StrategyFailed(f"no local checkpoint directory at {model_dir!r}", mutated=False)
+        hook = getattr(ctx.adapter, "model_of", None)
+        model = hook(result) if hook is not None else result.model
+        if model is None or not hasattr(model, "load_weights"):
+            raise StrategyFailed("the engine model has no load_weights to capture", mutated=False)
+        self._touched = True
+        try:
+            placed = place_captured(model, model_dir, f"cuda:{ctx.device_id}",
+                                    ring_bytes=self.ring_bytes, ring_slots=self.ring_slots,
+                                    host_threads=self.host_threads)
+        except StrategyFailed:
+            raise
+        except (KeyError, ValueError, FileNotFoundError) as e:
+            raise StrategyFailed(str(e), mutated=False) from e
+        except Exception as e:
+            raise StrategyFailed(str(e), mutated=True) from e
+        result.metadata[self.name] = {
+            "bytes_placed": placed.stats.bytes_placed, "seconds": placed.stats.seconds_total,
+            "chunks": placed.stats.chunks, "records": placed.records,
+            "engine_loaded": len(placed.engine_loaded), "converted": len(placed.converted)}
+        return result

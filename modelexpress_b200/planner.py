@@ -17,6 +17,7 @@ not have the reference package.
 
 from __future__ import annotations
 
+import copy as _copy
 from dataclasses import dataclass
 from typing import Any
 
@@ -123,49 +124,69 @@ class _View:
             raise UnsupportedReshard(f"op {op!r} is not a pure view")
 
 
-def resolve_slice(copy, global_shape):
-    """(needed box in source coordinates, destination strides in source-dim
-    order) for one captured copy; slice_plan.py:227-245."""
+def window_box(offset, shape, stride, global_shape, dest_stride, keep_rank: bool = True):
+    """A strided window of a row-major tensor -> (box in source coordinates,
+    destination strides in source-dim order); slice_plan.py:170-225.
+
+    Every window dim of extent > 1 must walk exactly one source dim (its stride
+    equals that dim's row-major stride) and the offset must be a corner of the
+    box.  With ``keep_rank`` the window must have the source's rank, as the
+    reference requires; without it, size-1 window dims are ignored and source
+    dims the window does not walk have extent 1 (an integer index, ``select``,
+    ``unbind`` or ``squeeze`` of the source)."""
     gshape = [int(g) for g in global_shape]
-    view = _View(gshape)
-    for op, args, _kw in copy.op_chain:
-        view.apply(op, args)
     nd = len(gshape)
-    if len(view.shape) != nd:
+    if keep_rank and len(shape) != nd:
         raise UnsupportedReshard("rank change")
     gst = _strides_of(gshape)
     dim_of_stride = {}
     for s in range(nd):
         dim_of_stride.setdefault(gst[s], s)
-    perm = [None] * nd
-    for d in range(nd):
-        if view.shape[d] == 1:
+    perm = [None] * len(shape)
+    for d in range(len(shape)):
+        if shape[d] == 1:
             continue
-        s = dim_of_stride.get(view.stride[d])
+        s = dim_of_stride.get(int(stride[d]))
         if s is None:
-            raise UnsupportedReshard(f"stride {view.stride[d]} is not a source dim (merged dims)")
+            raise UnsupportedReshard(f"stride {stride[d]} is not a source dim (merged dims)")
         perm[d] = s
-    free = [s for s in range(nd) if s not in {p for p in perm if p is not None}]
-    for d in range(nd):
-        if perm[d] is None:
-            perm[d] = free.pop(0)
-    if sorted(perm) != list(range(nd)):
+    used = [p for p in perm if p is not None]
+    if len(set(used)) != len(used):
         raise UnsupportedReshard("view is not a permutation of the source dims")
-    lo = [(view.offset // gst[s]) % gshape[s] if gshape[s] else 0 for s in range(nd)]
-    hi = list(lo)
-    for d in range(nd):
-        hi[perm[d]] = lo[perm[d]] + view.shape[d]
+    lo = [(int(offset) // gst[s]) % gshape[s] if gshape[s] else 0 for s in range(nd)]
+    hi = [x + 1 if gshape[s] else x for s, x in enumerate(lo)]
+    for d, s in enumerate(perm):
+        if s is not None:
+            hi[s] = lo[s] + int(shape[d])
     if any(hi[s] > gshape[s] for s in range(nd)):
         raise UnsupportedReshard("box leaves the source")
-    if sum(lo[s] * gst[s] for s in range(nd)) != view.offset:
+    if sum(lo[s] * gst[s] for s in range(nd)) != int(offset):
         raise UnsupportedReshard("offset is not a box corner")
-    if tuple(copy.dest_shape) != tuple(view.shape):
-        raise UnsupportedReshard(
-            f"{copy.param_name}: destination {tuple(copy.dest_shape)} != view {tuple(view.shape)}")
     dst_stride = [0] * nd
     for d, s in enumerate(perm):
-        dst_stride[s] = int(copy.dest_stride[d])
+        if s is not None:
+            dst_stride[s] = int(dest_stride[d])
     return [(lo[s], hi[s]) for s in range(nd)], dst_stride
+
+
+def resolve_slice(copy, global_shape):
+    """(needed box in source coordinates, destination strides in source-dim
+    order) for one captured copy; slice_plan.py:227-245.  ``copy`` carries
+    either the reference's op-chain, which is replayed here, or the resolved
+    window of a ``geometry.ViewCopy``."""
+    if hasattr(copy, "src_stride"):
+        offset, shape, stride, keep_rank = copy.src_offset, copy.src_shape, copy.src_stride, False
+    else:
+        view = _View(global_shape)
+        for op, args, _kw in copy.op_chain:
+            view.apply(op, args)
+        offset, shape, stride, keep_rank = view.offset, view.shape, view.stride, True
+    if len(shape) == len(copy.dest_shape) and tuple(copy.dest_shape) != tuple(shape):
+        raise UnsupportedReshard(
+            f"{copy.param_name}: destination {tuple(copy.dest_shape)} != view {tuple(shape)}")
+    if len(shape) != len(copy.dest_shape):
+        raise UnsupportedReshard("rank change")
+    return window_box(offset, shape, stride, global_shape, copy.dest_stride, keep_rank)
 
 
 def box_records(overlap, src_origin, src_strides, dst_origin, dst_strides, elsize,
@@ -291,9 +312,11 @@ def plan_transfer_2d(copies, sources: dict, resolve_param_ptr, convert_base: int
                 if convert_base is None:
                     raise UnsupportedReshard("dtype conversion required and no staging given")
                 n = int(np.prod(copy.dest_shape)) if len(copy.dest_shape) else 1
-                staging_copy = CopySpec(copy.src_name, copy.op_chain, copy.param_name, 0,
-                                        tuple(copy.dest_shape), tuple(_strides_of(copy.dest_shape)),
-                                        src.dtype)
+                # the same window, landing contiguously in staging at the served dtype
+                staging_copy = _copy.copy(copy)
+                staging_copy.dest_offset = 0
+                staging_copy.dest_stride = tuple(_strides_of(copy.dest_shape))
+                staging_copy.dest_dtype = src.dtype
                 off = (staged + 255) // 256 * 256
                 parts = plan_pull_2d(staging_copy, src.global_shape, src.dtype, src.elsize,
                                      src.shards, int(convert_base) + off)

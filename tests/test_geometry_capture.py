@@ -1,0 +1,298 @@
+"""Geometry capture on the CPU: what a loader's dry run records, what it refuses,
+and — the parity part — that the compiled records move exactly the bytes the
+loader itself moves when it is run for real (reference tests of the same
+behaviour: tests/test_reshard_refit_geometry.py:88-240 for capture,
+tests/test_reshard_refit_slice_plan.py for the resolved boxes)."""
+
+import importlib
+import os
+from unittest import mock
+
+import numpy as np
+import pytest
+import torch
+
+from modelexpress_b200.geometry import (TracedSource, capture_geometry,
+                                        summarize_unsupported)
+from modelexpress_b200.loader import captured_table
+from modelexpress_b200.planner import apply_converts
+from oracle import c_port
+
+G = os.path.join(os.path.dirname(__file__), "golden")
+TAG = {torch.float32: "F32", torch.bfloat16: "BF16", torch.float16: "F16", torch.int32: "I32",
+       torch.uint8: "U8"}
+
+
+class Toy(torch.nn.Module):
+    """Loader patterns met in engines: fused rows, a column slice, a transposed
+    expert stack, a slice assignment, a device move, a padded table, a buffer."""
+
+    def __init__(self, rank=1, tp=2):
+        super().__init__()
+        self.rank, self.tp = rank, tp
+        self.qkv = torch.nn.Parameter(torch.zeros(8 + 4 + 4, 16))
+        self.down = torch.nn.Parameter(torch.zeros(16, 12))
+        self.experts = torch.nn.Parameter(torch.zeros(3, 6, 16))
+        self.norm = torch.nn.Parameter(torch.zeros(16))
+        self.embed = torch.nn.Parameter(torch.ones(24, 16))
+        self.router = torch.nn.Parameter(torch.zeros(3, 16, dtype=torch.float32))
+        self.scale = torch.nn.Parameter(torch.zeros(1))
+        self.doubled = torch.nn.Parameter(torch.zeros(16))
+        self.register_buffer("table", torch.zeros(4, 4))
+
+    def load_weights(self, weights):
+        done = set()
+        for name, w in weights:
+            done.add(name)
+            if name in ("q", "k", "v"):
+                rows = {"q": 8, "k": 4, "v": 4}[name]
+                at = {"q": 0, "k": 8, "v": 12}[name]
+                self.qkv.data.narrow(0, at, rows).copy_(w.narrow(0, self.rank * rows, rows))
+            elif name == "down":
+                self.down.data.copy_(w[:, self.rank * 12:(self.rank + 1) * 12])
+            elif name == "experts_t":      # stored (E, hidden, inter): transposed per expert
+                for e, we in enumerate(w.unbind(0)):
+                    self.experts.data[e].copy_(we.t().narrow(0, self.rank * 6, 6))
+            elif name == "norm":
+                self.norm.data[:] = w.to(self.norm.device)
+            elif name == "embed":          # 20 real rows, 24 padded
+                self.embed.data[: w.shape[0]].copy_(w)
+                self.embed.data[w.shape[0]:].fill_(0)
+            elif name == "router":         # served bf16, kept fp32
+                self.router.data.copy_(w)
+            elif name == "scale":
+                self.scale.data.fill_(w.item())
+            elif name == "table":
+                self.table.copy_(w.squeeze(0))
+            elif name == "cast":
+                self.doubled.data.copy_(w.float() * 2)
+            elif name == "temp":
+                tmp = torch.empty(16)
+                tmp.copy_(w)
+                self.norm.data.copy_(tmp + 1)
+            elif name == "skipme":
+                done.discard(name)
+        return done
+
+
+MANIFEST = [("q", torch.float32, (16, 16)), ("k", torch.float32, (8, 16)), ("scale", torch.float32, (1,)),
+            ("v", torch.float32, (8, 16)), ("down", torch.float32, (16, 24)),
+            ("experts_t", torch.float32, (3, 16, 12)), ("cast", torch.bfloat16, (16,)),
+            ("norm", torch.float32, (16,)), ("embed", torch.float32, (20, 16)),
+            ("router", torch.bfloat16, (3, 16)), ("table", torch.float32, (1, 4, 4)),
+            ("temp", torch.float32, (16,)), ("skipme", torch.float32, (5,))]
+
+
+def test_capture_records_windows_and_destinations():
+    cap = capture_geometry(Toy(), MANIFEST)
+    by = {}
+    for c in cap.copies:
+        by.setdefault(c.src_name, []).append(c)
+    q, = by["q"]
+    assert (q.src_offset, q.src_shape, q.src_stride) == (8 * 16, (8, 16), (16, 1))
+    assert (q.param_name, q.dest_offset, q.dest_shape, q.dest_stride) == ("qkv", 0, (8, 16), (16, 1))
+    assert by["k"][0].dest_offset == 8 * 16 and by["v"][0].dest_offset == 12 * 16
+    d, = by["down"]
+    assert (d.src_offset, d.src_stride, d.dest_stride) == (12, (24, 1), (12, 1))
+    ex = by["experts_t"]
+    assert [c.src_offset for c in ex] == [e * 16 * 12 + 6 for e in range(3)]
+    assert all(c.src_shape == (6, 16) and c.src_stride == (1, 12) for c in ex)
+    assert [c.dest_offset for c in ex] == [0, 96, 192]
+    assert by["norm"][0].param_name == "norm" and by["embed"][0].dest_shape == (20, 16)
+    assert by["router"][0].src_dtype == torch.bfloat16 and by["router"][0].dest_dtype == torch.float32
+    assert by["table"][0].param_name == "table" and by["table"][0].src_shape == (4, 4)
+    assert "skipme" not in by and "skipme" not in cap.unsupported
+
+
+def test_unsupported_sources_are_isolated_with_their_cause():
+    cap = capture_geometry(Toy(), MANIFEST)
+    assert cap.unsupported == ["scale", "cast", "temp"]
+    assert "item" in cap.unsupported_reasons["scale"]
+    assert "float" in cap.unsupported_reasons["cast"]
+    assert "not a parameter" in cap.unsupported_reasons["temp"] and cap.unattributed == 1
+    assert not [c for c in cap.copies if c.src_name in cap.unsupported]
+    # sources before, between and after the failing ones were all captured, once each
+    names = [c.src_name for c in cap.copies]
+    assert names.count("q") == names.count("v") == names.count("norm") == names.count("table") == 1
+    assert names.count("experts_t") == 3
+
+
+def test_one_call_and_one_call_per_source_agree():
+    a = capture_geometry(Toy(), MANIFEST)
+    b = capture_geometry(Toy(), MANIFEST, isolate=True)
+    assert a.copies == b.copies and a.unsupported == b.unsupported
+
+
+def test_summarize_unsupported_groups_causes():
+    got = summarize_unsupported({"a": "x", "b": "y", "c": "x"})
+    assert got == [("x", 2), ("y", 1)] and summarize_unsupported(None) == []
+
+
+def test_traced_source_answers_metadata_and_refuses_data():
+    t = TracedSource.source("w", (4, 6), torch.bfloat16, "cpu")
+    assert t.shape == (4, 6) and t.dtype == torch.bfloat16 and t.dim() == 2 and t.numel() == 24
+    assert t.device.type == "cpu" and t.is_contiguous() and t.size(1) == 6
+    v = t.t()
+    assert isinstance(v, TracedSource) and v.shape == (6, 4) and not v.is_contiguous()
+    assert t.to("cpu") is t and t.to(torch.bfloat16) is t
+    a, b = t.chunk(2, dim=1)
+    assert a.shape == (4, 3) and b._window.storage_offset() == 3
+    for bad in (lambda: t + 1, lambda: t.float(), lambda: v.contiguous(), lambda: t.sum().item(),
+                lambda: torch.cat([t, t]), lambda: t.view(torch.int16), lambda: t.clone()):
+        with pytest.raises(NotImplementedError):
+            bad()
+    assert v.t().contiguous().shape == (4, 6)   # contiguous() of a dense window is still a view
+
+
+def _image(manifest, seed=0):
+    """An in-memory 'file': tensors back to back at odd offsets, plus an index in
+    the shape checkpoint_index returns."""
+    rng = np.random.default_rng(seed)
+    index, chunks, at = {}, [], 0
+    for name, dtype, shape in manifest:
+        n = int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
+        pad = int(rng.integers(0, 3)) * 2
+        chunks.append(np.zeros(pad, dtype=np.uint8))
+        at += pad
+        if dtype in (torch.float32,):
+            raw = rng.standard_normal(int(np.prod(shape))).astype(np.float32).view(np.uint8)
+        else:                          # bf16: any bit pattern without NaN/Inf exponents
+            u = rng.integers(0, 0x7F00, size=int(np.prod(shape)), dtype=np.uint16)
+            raw = u.view(np.uint8)
+        chunks.append(raw)
+        index[name] = {"file": "mem", "file_offset": at, "size": n, "dtype": TAG[dtype], "shape": list(shape)}
+        at += n
+    return np.concatenate(chunks), index
+
+
+def _real_tensor(image, info, dtype):
+    raw = torch.from_numpy(image[info["file_offset"]: info["file_offset"] + info["size"]].copy())
+    return raw.view(dtype).reshape(info["shape"])
+
+
+def _run_records(model, image, index, manifest):
+    """Compile the capture and move the bytes with the CPU scatter (the checker)."""
+    staging = []
+
+    def alloc(nbytes):
+        staging.append(torch.zeros(nbytes, dtype=torch.uint8))
+        return staging[0].data_ptr()
+
+    cap = captured_table(model, index, {"mem": image.ctypes.data}, device=torch.device("cpu"),
+                         alloc_staging=alloc)
+    c_port.scatter2d(cap.records)
+    if cap.converts:
+        dests = {n: p.data for n, p in model.named_parameters()}
+        apply_converts(cap.converts, staging[0], dests)
+    left = [(n, _real_tensor(image, index[n], dt)) for n, dt, _s in manifest if n in cap.reasons]
+    model.load_weights(iter(left))
+    return cap
+
+
+@pytest.mark.parametrize("rank", [0, 1])
+def test_records_move_what_the_loader_moves(rank):
+    manifest = [m for m in MANIFEST if m[0] != "temp"]
+    image, index = _image(manifest, seed=rank)
+    truth = Toy(rank)
+    truth.load_weights((n, _real_tensor(image, index[n], dt)) for n, dt, _s in manifest)
+    model = Toy(rank)
+    cap = _run_records(model, image, index, manifest)
+    assert sorted(cap.reasons) == ["cast", "scale"]
+    assert [c.param_name for c in cap.converts] == ["router"]
+    assert cap.written_params == {"qkv", "down", "experts", "norm", "embed", "router", "table"}
+    for (n, a), (_n, b) in zip(model.state_dict().items(), truth.state_dict().items()):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), n
+
+
+def test_without_staging_a_dtype_change_goes_to_the_engine():
+    image, index = _image(MANIFEST[:1] + [m for m in MANIFEST if m[0] == "router"])
+    cap = captured_table(Toy(), index, {"mem": image.ctypes.data}, device=torch.device("cpu"))
+    assert list(cap.reasons) == ["router"] and not cap.converts and cap.copies == 1
+
+
+# ---- real vLLM parallel layers, checked against outputs recorded from vLLM itself --------------
+
+def _vllm_mini(rank, tp, dims):
+    """A module made of vLLM's own QKV / merged-column / row-parallel /
+    vocab-parallel layers with the usual stacked-parameter ``load_weights``."""
+    from vllm.config import DeviceConfig, VllmConfig, set_current_vllm_config
+    from vllm.model_executor.layers import linear as L
+    from vllm.model_executor.layers import vocab_parallel_embedding as V
+    from vllm.model_executor.model_loader.weight_utils import default_weight_loader
+
+    h, qh, kvh, hd, inter, voc = dims
+    patches = []
+    for m in ("vllm.model_executor.layers.linear", "vllm.model_executor.layers.vocab_parallel_embedding",
+              "vllm.model_executor.parameter", "vllm.model_executor.utils",
+              "vllm.distributed.parallel_state"):
+        mod = importlib.import_module(m)
+        for fn, val in (("get_tensor_model_parallel_rank", rank),
+                        ("get_tensor_model_parallel_world_size", tp)):
+            if hasattr(mod, fn):
+                patches.append(mock.patch.object(mod, fn, lambda v=val: v))
+
+    class Mini(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.qkv_proj = L.QKVParallelLinear(h, hd, qh, kvh, bias=True)
+            self.gate_up_proj = L.MergedColumnParallelLinear(h, [inter, inter], bias=False)
+            self.o_proj = L.RowParallelLinear(qh * hd, h, bias=False)
+            self.down_proj = L.RowParallelLinear(inter, h, bias=False)
+            self.embed_tokens = V.VocabParallelEmbedding(voc, h)
+
+        def load_weights(self, weights):
+            stacked = [("qkv_proj", "q_proj", "q"), ("qkv_proj", "k_proj", "k"), ("qkv_proj", "v_proj", "v"),
+                       ("gate_up_proj", "gate_proj", 0), ("gate_up_proj", "up_proj", 1)]
+            params = dict(self.named_parameters())
+            for name, w in weights:
+                for fused, part, shard_id in stacked:
+                    if part in name:
+                        p = params[name.replace(part, fused)]
+                        p.weight_loader(p, w, shard_id)
+                        break
+                else:
+                    p = params[name]
+                    getattr(p, "weight_loader", default_weight_loader)(p, w)
+
+    cfg = VllmConfig(device_config=DeviceConfig(device="cpu"))
+    return Mini, patches, cfg, set_current_vllm_config
+
+
+def test_capture_of_real_vllm_layers_matches_recorded_vllm_outputs():
+    pytest.importorskip("vllm")
+    z = np.load(os.path.join(G, "vllm_layers.npz"))
+    tp, h, qh, kvh, hd, inter, voc = (int(x) for x in z["meta"])
+    src = {"q_proj.weight": "q_proj", "k_proj.weight": "k_proj", "v_proj.weight": "v_proj",
+           "q_proj.bias": "q_bias", "k_proj.bias": "k_bias", "v_proj.bias": "v_bias",
+           "gate_proj.weight": "gate_proj", "up_proj.weight": "up_proj", "o_proj.weight": "o_proj",
+           "down_proj.weight": "down_proj", "embed_tokens.weight": "embed"}
+    chunks, index, at = [], {}, 0
+    for name, key in src.items():
+        a = np.ascontiguousarray(z[f"src/{key}"].astype(np.uint16))
+        chunks.append(a.reshape(-1).view(np.uint8))
+        index[name] = {"file": "mem", "file_offset": at, "size": a.nbytes, "dtype": "BF16",
+                       "shape": list(a.shape)}
+        at += a.nbytes
+    image = np.concatenate(chunks)
+    want = {"qkv_proj.weight": "qkv_w", "qkv_proj.bias": "qkv_b", "gate_up_proj.weight": "gate_up",
+            "o_proj.weight": "o", "down_proj.weight": "down", "embed_tokens.weight": "embed"}
+    for rank in range(tp):
+        Mini, patches, cfg, use = _vllm_mini(rank, tp, (h, qh, kvh, hd, inter, voc))
+        for p in patches:
+            p.start()
+        try:
+            with use(cfg):
+                torch.set_default_dtype(torch.bfloat16)
+                try:
+                    model = Mini()
+                finally:
+                    torch.set_default_dtype(torch.float32)
+                cap = captured_table(model, index, {"mem": image.ctypes.data}, device=torch.device("cpu"))
+        finally:
+            for p in patches:
+                p.stop()
+        assert not cap.reasons and cap.copies == len(src)
+        c_port.scatter2d(cap.records)
+        for pname, key in want.items():
+            got = dict(model.named_parameters())[pname].data.contiguous().view(torch.int16).numpy().view(np.uint16)
+            assert np.array_equal(got, z[f"rank{rank}/{key}"]), (rank, pname)

@@ -79,6 +79,18 @@ def test_place_checkpoint_equals_vllm_load_weights(tmp_path):
             assert torch.equal(params[n].detach().view(torch.int16), t.view(torch.int16)), n
         assert placed.stats.bytes_placed == sum(t.numel() * t.element_size() for t in truth.values())
 
+        # the same load planned from vLLM's own load_weights instead of layout rules
+        from modelexpress_b200.loader import place_captured
+
+        for p in params.values():
+            p.data.zero_()
+        got = place_captured(model, d, "cuda:0", ring_bytes=16 << 20, ring_slots=4, host_threads=2)
+        assert got.engine_loaded == [] and not got.converted, got.reasons
+        assert got.stats.bytes_placed == placed.stats.bytes_placed
+        assert got.written_params == set(truth)
+        for n, t in truth.items():
+            assert torch.equal(params[n].detach().view(torch.int16), t.view(torch.int16)), n
+
         # the outermost seam: vLLM's own `--load-format modelexpress` wrapper importing
         # modelexpress.engines.vllm.loader:MxModelLoader (here: the shim directory)
         import sys
@@ -100,7 +112,7 @@ def test_place_checkpoint_equals_vllm_load_weights(tmp_path):
             with set_current_vllm_config(vc2):
                 model2 = wrapper.load_model(vllm_config=vc2, model_config=mc)
             inner = wrapper._loader
-            assert type(inner).__name__ == "MxModelLoader" and inner.last_strategy == "b200_scatter"
+            assert type(inner).__name__ == "MxModelLoader" and inner.last_strategy == "b200_captured"
             assert inner.nixl_manager is None and set(inner.tensors) == set(truth)
             assert not model2.training
             for n, p in model2.named_parameters():
@@ -115,5 +127,88 @@ def test_place_checkpoint_equals_vllm_load_weights(tmp_path):
             sys.path.remove(shim)
             for k in [k for k in sys.modules if k == "modelexpress" or k.startswith("modelexpress.")]:
                 del sys.modules[k]
+    finally:
+        ctx.__exit__(None, None, None)
+
+
+MOE_CFG = {"architectures": ["Qwen3MoeForCausalLM"], "model_type": "qwen3_moe", "hidden_size": 256,
+           "intermediate_size": 512, "moe_intermediate_size": 128, "num_hidden_layers": 2,
+           "num_attention_heads": 8, "num_key_value_heads": 4, "head_dim": 32, "vocab_size": 1024,
+           "num_experts": 8, "num_experts_per_tok": 2, "decoder_sparse_step": 1, "norm_topk_prob": True,
+           "mlp_only_layers": [], "max_position_embeddings": 512, "rms_norm_eps": 1e-6,
+           "rope_theta": 10000.0, "tie_word_embeddings": False, "torch_dtype": "bfloat16",
+           "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2}
+
+
+def _qwen3_moe_tensors(c):
+    h, hd = c["hidden_size"], c["head_dim"]
+    out = [("model.embed_tokens.weight", (c["vocab_size"], h), "BF16", "matrix")]
+    for i in range(c["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        out += [(p + "input_layernorm.weight", (h,), "BF16", "matrix"),
+                (p + "self_attn.q_proj.weight", (c["num_attention_heads"] * hd, h), "BF16", "matrix"),
+                (p + "self_attn.k_proj.weight", (c["num_key_value_heads"] * hd, h), "BF16", "matrix"),
+                (p + "self_attn.v_proj.weight", (c["num_key_value_heads"] * hd, h), "BF16", "matrix"),
+                (p + "self_attn.q_norm.weight", (hd,), "BF16", "matrix"),
+                (p + "self_attn.k_norm.weight", (hd,), "BF16", "matrix"),
+                (p + "self_attn.o_proj.weight", (h, c["num_attention_heads"] * hd), "BF16", "matrix"),
+                (p + "post_attention_layernorm.weight", (h,), "BF16", "matrix"),
+                (p + "mlp.gate.weight", (c["num_experts"], h), "BF16", "matrix")]
+        for e in range(c["num_experts"]):
+            q = f"{p}mlp.experts.{e}."
+            out += [(q + "gate_proj.weight", (c["moe_intermediate_size"], h), "BF16", "matrix"),
+                    (q + "up_proj.weight", (c["moe_intermediate_size"], h), "BF16", "matrix"),
+                    (q + "down_proj.weight", (h, c["moe_intermediate_size"]), "BF16", "matrix")]
+    out += [("model.norm.weight", (h,), "BF16", "matrix"),
+            ("lm_head.weight", (c["vocab_size"], h), "BF16", "matrix")]
+    return out
+
+
+def test_place_captured_loads_a_vllm_moe_model_with_no_layout_rules(tmp_path):
+    """An architecture the built-in placement rules do not describe (per-expert
+    checkpoint tensors stacked into vLLM's fused expert parameters): the capture
+    of vLLM's own ``load_weights`` plans it, and every parameter ends up
+    bit-identical to what ``load_weights`` itself produces."""
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from modelexpress_b200 import synth
+    from modelexpress_b200.loader import place_captured
+
+    d = str(tmp_path)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(MOE_CFG, f)
+    synth.write_checkpoint(d, _qwen3_moe_tensors(MOE_CFG), 33, 2)
+    try:
+        model, ctx, vc, mc = _build_vllm_model(d)
+    except Exception as e:
+        pytest.skip(f"vLLM could not build a MoE model here: {type(e).__name__}: {e}")
+    try:
+        from safetensors import safe_open
+
+        weights = []
+        for fn in sorted(os.listdir(d)):
+            if fn.endswith(".safetensors"):
+                with safe_open(os.path.join(d, fn), framework="pt", device="cpu") as f:
+                    weights += [(k, f.get_tensor(k)) for k in f.keys()]
+        model.load_weights(iter(weights))
+        torch.cuda.synchronize()
+        params = dict(model.named_parameters())
+        truth = {n: p.detach().clone() for n, p in params.items()}
+        for p in params.values():
+            p.data.zero_()
+        torch.cuda.synchronize()
+        got = place_captured(model, d, "cuda:0", ring_bytes=16 << 20, ring_slots=4, host_threads=2)
+        ckpt_bytes = sum(t.numel() * t.element_size() for _n, t in weights)
+        engine_bytes = sum(t.numel() * t.element_size() for n, t in weights if n in got.engine_loaded)
+        # everything but at most a handful of small tensors goes through the scatter kernel
+        assert engine_bytes <= ckpt_bytes // 100, got.reasons
+        assert got.stats.bytes_placed >= ckpt_bytes - engine_bytes - sum(
+            t.numel() * t.element_size() for n, t in weights if "rotary" in n)
+        experts = [n for n in truth if "experts" in n]
+        assert experts and set(experts) <= got.written_params
+        for n, t in truth.items():
+            assert torch.equal(params[n].detach().view(torch.uint8), t.view(torch.uint8)), n
     finally:
         ctx.__exit__(None, None, None)
