@@ -36,6 +36,11 @@ def _build_vllm_model(model_dir):
         ps.init_distributed_environment(world_size=1, rank=0, local_rank=0, backend="nccl",
                                         distributed_init_method=f"tcp://127.0.0.1:{port}")
         ps.initialize_model_parallel(1, 1)
+    elif getattr(mc, "is_moe", False) and getattr(ps, "_EP", None) is None:
+        # the groups were made for a dense model earlier in this process: an expert-parallel
+        # group only exists when they are made under a MoE config
+        ps.destroy_model_parallel()
+        ps.initialize_model_parallel(1, 1)
     with set_default_torch_dtype(torch.bfloat16), torch.device("cuda"):
         model = initialize_model(vllm_config=vc)
     return model, ctx, vc, mc
