@@ -210,6 +210,40 @@ def test_without_staging_a_dtype_change_goes_to_the_engine():
     assert list(cap.reasons) == ["router"] and not cap.converts and cap.copies == 1
 
 
+def test_captured_copies_plan_against_row_sharded_sources():
+    """The refit case: the same captured copies, but every source tensor is
+    published as three row shards living in separate buffers (the trainer's
+    layout, slice_plan.py:54-70); the records must still assemble what the
+    loader assembles from the full tensors."""
+    from modelexpress_b200.planner import ShardSpec, SourceSpec, plan_transfer_2d
+
+    manifest = [m for m in MANIFEST if m[0] in ("q", "k", "v", "down", "experts_t", "norm", "embed", "table")]
+    image, index = _image(manifest, seed=7)
+    full = {n: _real_tensor(image, index[n], dt) for n, dt, _s in manifest}
+    truth = Toy(1)
+    truth.load_weights(iter(full.items()))
+    model = Toy(1)
+    cap = capture_geometry(model, manifest)
+    keep, sources = [], {}
+    for name, t in full.items():
+        rows = t.shape[0]
+        cuts = sorted({0, rows // 3, (2 * rows) // 3, rows})
+        shards = []
+        for lo, hi in zip(cuts[:-1], cuts[1:]):
+            part = t[lo:hi].contiguous()
+            keep.append(part)
+            shards.append(ShardSpec((lo,) + (0,) * (t.dim() - 1), tuple(part.shape), f"{name}@{lo}",
+                                    part.data_ptr(), t.element_size()))
+        sources[name] = SourceSpec(tuple(t.shape), t.dtype, t.element_size(), shards)
+    dests = dict(model.named_parameters())
+    dests.update(dict(model.named_buffers()))
+    table, unsupported, converts = plan_transfer_2d(cap.copies, sources, lambda n: dests[n].data_ptr())
+    assert not unsupported and not converts
+    c_port.scatter2d(table)
+    for (n, a), (_n, b) in zip(model.state_dict().items(), truth.state_dict().items()):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), n
+
+
 # ---- real vLLM parallel layers, checked against outputs recorded from vLLM itself --------------
 
 def _vllm_mini(rank, tp, dims):
