@@ -2,7 +2,7 @@
 """Benchmark of the weight-placement hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload place|fanout|reshard|digest]
+                    [--workload place|moe|fanout|reshard|digest|vllm]
 
 Default workload (the headline): a Llama-3-8B-shaped bf16 synthetic checkpoint
 (4 safetensors files, ~16 GB, seed 1) placed into tensor-parallel TP=8 shards.
@@ -244,9 +244,9 @@ def bench_place(args):
     # three quarters of the cores, shared between the ranks of this box
     local_world = max(1, env_int("LOCAL_WORLD_SIZE", world))
     threads = env_int("MXB_HOST_THREADS", max(2, min(32, (os.cpu_count() or 8) * 3 // 4 // local_world)))
-    slots = env_int("MXB_RING_SLOTS", 32)
+    slots = env_int("MXB_RING_SLOTS", 4)
     mode = PLACE_ZERO_COPY if os.environ.get("MXB_PLACE_MODE", "ce") == "zc" else PLACE_COPY_ENGINE
-    ring_bytes = env_int("MXB_RING_BYTES", 2 << 30)
+    ring_bytes = env_int("MXB_RING_BYTES", 128 << 20)
     ring = ctx.ring(ring_bytes, slots, local)
     skip_e2e = os.environ.get("MXB_BENCH_SKIP_E2E") == "1"  # profiling runs that only want the table launches
     for _ in range(0 if skip_e2e else args.warmup):
@@ -476,7 +476,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="place", choices=["place", "moe", "fanout", "reshard", "digest"])
+    ap.add_argument("--workload", default="place", choices=["place", "moe", "fanout", "reshard", "digest", "vllm"])
     args = ap.parse_args()
     if args.impl == "reference":
         return bench_reference(args)

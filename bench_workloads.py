@@ -3,6 +3,8 @@
 digest   integrity digests of a Llama-3-8B-sized byte image resident in HBM
 fanout   serving-peer fan-out of the 8B weights from GPU 0 to the other GPUs
 reshard  FSDP-8 -> TP-8 refit reshard of a Qwen2.5-32B-shaped model
+vllm     a whole Llama-3-8B-shaped model loaded through vLLM's model-loader seam
+         (needs vLLM; one GPU), next to vLLM's own default loader on the same files
 
 Each prints one JSON line on rank 0 in the same shape as the headline bench.
 Multi-GPU workloads run one process per GPU (torchrun); peers' memory is mapped
@@ -496,8 +498,113 @@ def _reshard_cpu_baseline(cfg, R):
                                       "all 8 source ranks, OpenMP memmove loop over the same records"}
 
 
+# ---------------------------------------------------------------------------
+# vLLM seam
+# ---------------------------------------------------------------------------
+
+
+def run_vllm(args):
+    """Time to loaded weights at the seam the reference plugs into: vLLM's
+    model-loader interface (engines/vllm/loader.py:62-183 in the reference).
+    One real ``LlamaForCausalLM`` is built on the GPU; each step loads every
+    parameter from safetensors files in the page cache, once per arm:
+    ``MxModelLoader.load_weights`` (capture of vLLM's own load_weights -> pinned
+    ring -> PCIe -> scatter kernel) and vLLM's ``DefaultModelLoader.load_weights``
+    (what the reference's chain ends in).  Both must leave identical parameters."""
+    import torch
+
+    from modelexpress_b200 import synth
+    from modelexpress_b200.digest import digest_many
+    from modelexpress_b200.engines.vllm.loader import MxModelLoader
+
+    rank, world, local = _dist()
+    if world != 1:
+        raise SystemExit("the vllm workload runs on one GPU")
+    try:
+        from vllm.config import (DeviceConfig, LoadConfig, ModelConfig, VllmConfig,
+                                 set_current_vllm_config)
+        from vllm.distributed import parallel_state as ps
+        from vllm.model_executor.model_loader.default_loader import DefaultModelLoader
+        from vllm.model_executor.model_loader.utils import initialize_model
+        from vllm.utils.torch_utils import set_default_torch_dtype
+    except Exception as e:
+        raise SystemExit(f"the vllm workload needs vLLM: {type(e).__name__}: {e}")
+
+    cfg = synth.scaled(synth.LLAMA3_8B, layers=_env_int("MXB_BENCH_LAYERS", 32))
+    tensors = synth.dense_tensors(cfg)
+    total = sum(synth.tensor_nbytes(s, d) for _n, s, d, _k in tensors)
+    root = os.environ.get("MXB_BENCH_DIR", "/tmp/mxb_bench")
+    d = synth.ensure_checkpoint(os.path.join(root, f"vllm_{cfg.name}_{cfg.layers}"), tensors, 1, 4,
+                                device="cuda")
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump({"architectures": ["LlamaForCausalLM"], "model_type": "llama",
+                   "hidden_size": cfg.hidden, "intermediate_size": cfg.intermediate,
+                   "num_hidden_layers": cfg.layers, "num_attention_heads": cfg.q_heads,
+                   "num_key_value_heads": cfg.kv_heads, "head_dim": cfg.head_dim,
+                   "vocab_size": cfg.vocab, "max_position_embeddings": 8192, "rms_norm_eps": 1e-5,
+                   "rope_theta": 500000.0, "tie_word_embeddings": False, "torch_dtype": "bfloat16",
+                   "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2}, f)
+    mc = ModelConfig(model=d, skip_tokenizer_init=True, dtype="bfloat16", enforce_eager=True)
+    vc = VllmConfig(model_config=mc, device_config=DeviceConfig(device="cuda"),
+                    load_config=LoadConfig(load_format="dummy"))
+    with set_current_vllm_config(vc):
+        ps.init_distributed_environment(world_size=1, rank=0, local_rank=0, backend="nccl",
+                                        distributed_init_method=f"tcp://127.0.0.1:{29600 + os.getpid() % 300}")
+        ps.initialize_model_parallel(1, 1)
+        with set_default_torch_dtype(torch.bfloat16), torch.device("cuda"):
+            model = initialize_model(vllm_config=vc)
+        params = [p.data for _n, p in model.named_parameters()]
+        loaded_bytes = sum(p.numel() * p.element_size() for p in params)
+
+        def digests():
+            return [(r["safe_checksum"], r["block_hash64"]) for r in digest_many(params)]
+
+        def timed(fn, steps, warmup):
+            for _ in range(warmup):
+                fn()
+            times = []
+            for _ in range(steps):
+                for p in params:
+                    p.zero_()
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                fn()
+                torch.cuda.synchronize()
+                times.append(time.perf_counter() - t0)
+            return times
+
+        ours = MxModelLoader(LoadConfig(load_format="auto"))
+        t_ours = timed(lambda: ours.load_weights(model, mc), args.steps, max(1, args.warmup))
+        if ours.last_strategy != "b200_captured":
+            raise SystemExit(f"vllm bench: weights were placed by {ours.last_strategy!r}")
+        mine = digests()
+        native = DefaultModelLoader(LoadConfig(load_format="auto"))
+        native_steps = max(1, min(args.steps, _env_int("MXB_BENCH_NATIVE_STEPS", 3)))
+        t_native = timed(lambda: native.load_weights(model, mc), native_steps, 1)
+        if digests() != mine:
+            raise SystemExit("vllm bench: parameters differ between the two loaders")
+    s_ours, s_native = sum(t_ours) / len(t_ours), sum(t_native) / len(t_native)
+    out = _base("GB/s of parameters loaded through vLLM's model-loader seam (files in page cache -> HBM)",
+                loaded_bytes / s_ours / 1e9, "GB/s", 1, args, s_ours * 1e3,
+                {"workload": f"vLLM LlamaForCausalLM, Llama-3-8B shapes, {cfg.layers} layers, TP=1, bf16, "
+                             f"4 safetensors files ({total} B), every parameter loaded per step",
+                 "parameter_bytes": loaded_bytes, "l2": "input larger than L2",
+                 "seconds_per_load": round(s_ours, 4), "best_seconds": round(min(t_ours), 4),
+                 "seconds_each": [round(t, 4) for t in t_ours], "last_load": ours.last_metadata})
+    out["e2e"] = {"value": out["value"], "unit": "GB/s", "h2d_bytes_per_step": loaded_bytes,
+                  "d2h_bytes_per_step": 0}
+    out["engine_default_loader"] = {
+        "value": round(loaded_bytes / s_native / 1e9, 2), "unit": "GB/s", "steps": native_steps,
+        "seconds_per_load": round(s_native, 4), "best_seconds": round(min(t_native), 4),
+        "what": "vllm DefaultModelLoader.load_weights on the same model and files",
+        "parameters_identical": True}
+    out["gpu_launches"] = None
+    print(json.dumps(out), flush=True)
+
+
 def run(args):
-    fn = {"digest": run_digest, "fanout": run_fanout, "reshard": run_reshard}.get(args.workload)
+    fn = {"digest": run_digest, "fanout": run_fanout, "reshard": run_reshard,
+          "vllm": run_vllm}.get(args.workload)
     if fn is None:
         raise SystemExit(f"unknown workload {args.workload!r}")
     return fn(args)

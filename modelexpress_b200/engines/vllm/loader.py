@@ -64,6 +64,7 @@ class MxModelLoader(BaseModelLoader):
         super().__init__(load_config)
         self._tensors: dict = {}
         self.last_strategy: str | None = None
+        self.last_metadata: dict | None = None
 
     # -- BaseModelLoader surface ------------------------------------------------
     def download_model(self, model_config) -> None:
@@ -87,6 +88,7 @@ class MxModelLoader(BaseModelLoader):
                     raise StrategyFailed("CUDA library or device unavailable", mutated=False)
                 strategy.load(result, ctx)
                 self.last_strategy = strategy.name
+                self.last_metadata = result.metadata.get(strategy.name)
                 logger.info("weights placed by %s: %s", strategy.name, result.metadata.get(strategy.name))
                 break
             except StrategyFailed as e:

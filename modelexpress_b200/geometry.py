@@ -119,7 +119,18 @@ def _extent(t: torch.Tensor) -> int:
 
 
 def _leaves(tree):
-    return torch.utils._pytree.tree_leaves(tree)
+    """Tensors among call arguments: the arguments themselves and what lists,
+    tuples and dicts of them hold (``torch.cat([a, b])``)."""
+    out, stack = [], [tree]
+    while stack:
+        x = stack.pop()
+        if isinstance(x, torch.Tensor):
+            out.append(x)
+        elif isinstance(x, (list, tuple)):
+            stack.extend(x)
+        elif isinstance(x, dict):
+            stack.extend(x.values())
+    return out
 
 
 def _is_identity_move(func, args, kwargs) -> bool:

@@ -18,6 +18,8 @@ from __future__ import annotations
 
 import mmap
 import os
+import time
+from concurrent.futures import ThreadPoolExecutor
 from dataclasses import dataclass, field
 from typing import Any
 
@@ -26,6 +28,12 @@ import numpy as np
 from .layout import CheckpointPlan, plan_checkpoint
 from .runtime import PLACE_COPY_ENGINE, Context, PlaceResult, Ring, default_context
 from .safetensors_index import SAFETENSORS_DTYPES, checkpoint_index
+
+
+# The ring a load creates for itself.  Pinning host memory costs about 0.4 ms per MiB, inside
+# the time to loaded weights, and the pipeline is as fast with four 32 MiB slots as with 2 GiB.
+RING_BYTES = 128 << 20
+RING_SLOTS = 4
 
 
 class StrategyFailed(Exception):
@@ -111,7 +119,7 @@ def place_checkpoint(model_path: str, tp_rank: int, tp_size: int, device=None, *
                      params: dict | None = None, ring: Ring | None = None,
                      ctx: Context | None = None, host_threads: int | None = None,
                      mode: int = PLACE_COPY_ENGINE, family: str = "auto",
-                     ring_bytes: int = 2 << 30, ring_slots: int = 32) -> PlacedCheckpoint:
+                     ring_bytes: int = RING_BYTES, ring_slots: int = RING_SLOTS) -> PlacedCheckpoint:
     """Load this rank's tensor-parallel shards of a safetensors checkpoint.
 
     ``params`` may hold pre-allocated destination tensors (an engine's own
@@ -148,7 +156,7 @@ def place_checkpoint(model_path: str, tp_rank: int, tp_size: int, device=None, *
         for im in images.values():
             im.close()
         if own_ring:
-            ring.close()
+            _release(ring)
     return PlacedCheckpoint(params, plan, stats)
 
 
@@ -163,6 +171,14 @@ class CapturedPlacement:
     engine_loaded: list         # sources left to the engine's own loader
     reasons: dict               # source -> why capture or planning gave it up
     written_params: set         # parameters and buffers that received records
+    timings: dict = field(default_factory=dict)   # seconds: capture, ring_create, place_wait, engine
+
+
+def _release(ring: Ring) -> None:
+    """Free a one-shot ring off the caller's path: unpinning host memory takes
+    tens of milliseconds and now and then most of a second, none of which the
+    loaded weights have to wait for."""
+    ring.ctx.release_later(ring)
 
 
 def _engine_tensor(image: FileImage, info: dict):
@@ -233,8 +249,9 @@ def captured_table(model, index: dict, file_address: dict, *, load_weights=None,
 def place_captured(model, model_path: str, device=None, *, load_weights=None,
                    ring: Ring | None = None, ctx: Context | None = None,
                    host_threads: int | None = None, mode: int = PLACE_COPY_ENGINE,
-                   ring_bytes: int = 2 << 30, ring_slots: int = 32,
-                   on_unsupported: str = "engine") -> CapturedPlacement:
+                   ring_bytes: int = RING_BYTES, ring_slots: int = RING_SLOTS,
+                   on_unsupported: str = "engine", pipeline: bool = True,
+                   first_batch: int = 32) -> CapturedPlacement:
     """Load a safetensors checkpoint into ``model`` for ANY architecture whose
     engine-side ``load_weights`` only slices and copies.
 
@@ -249,8 +266,10 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
     device and cast there.  Sources the loader has to compute on (a scalar read
     with ``.item()``, a transposing ``contiguous()``) are few and small: with
     ``on_unsupported="engine"`` they are handed to the same ``load_weights`` as
-    real host tensors afterwards, with ``"raise"`` the call fails before any
-    byte is written."""
+    real host tensors afterwards (so where two sources write the same bytes,
+    the engine-loaded one wins), with ``"raise"`` the call fails before any
+    byte is written.  ``stats.seconds_total`` spans the dry run and the
+    placement, which overlap (``pipeline``)."""
     import torch
 
     from .planner import apply_converts
@@ -266,40 +285,85 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
     if ctx is None:
         ctx = ring.ctx if ring is not None else default_context(dev_index)
     images: dict = {}
+    pool = ThreadPoolExecutor(1)          # the ring is one pipeline: its calls run in order
     try:
         for path in sorted({i["file"] for i in index.values()}):
             images[path] = FileImage(path)
-        staging = []
-
-        def alloc_staging(nbytes: int) -> int:
-            staging.append(torch.empty(nbytes, dtype=torch.uint8, device=dev))
-            return staging[0].data_ptr()
-
-        cap = captured_table(model, index, {p: im.address for p, im in images.items()},
-                             load_weights=loader, device=dev, alloc_staging=alloc_staging, dests=dests)
-        leftover = [n for n in index if n in cap.reasons]
-        if leftover and on_unsupported != "engine":
-            raise StrategyFailed(
-                f"{len(leftover)} source tensor(s) need the engine's loader, e.g. "
-                f"{leftover[0]}: {cap.reasons[leftover[0]]}", mutated=False)
-        table = cap.records
-        if ring is None:
-            ring = ctx.ring(ring_bytes, ring_slots, dev_index)
-        torch.cuda.current_stream(dev).synchronize()
+        addresses = {p: im.address for p, im in images.items()}
         threads = host_threads or max(2, min(32, (os.cpu_count() or 8) * 3 // 4))
-        stats = ring.place(table, threads, mode)
-        if cap.converts:
-            apply_converts(cap.converts, staging[0], dests)
+        names = list(index)
+        # the dry run costs tens of microseconds of Python per tensor: it is done in batches
+        # (small first, then doubling) so that the ring is already moving batch k while
+        # batch k+1 is being captured
+        cuts, step = [0], max(1, int(first_batch))
+        while cuts[-1] < len(names):
+            cuts.append(min(len(names), cuts[-1] + step))
+            step *= 2
+        if not pipeline or on_unsupported != "engine":
+            cuts = [0, len(names)]       # one batch: nothing is written before all is planned
+        parts, pending, stagings = [], [], []
+        timings = {"capture": 0.0, "ring_create": 0.0, "place_wait": 0.0, "engine": 0.0}
+        t0 = time.perf_counter()
+        for lo, hi in zip(cuts[:-1], cuts[1:]):
+            held = []
+
+            def alloc_staging(nbytes: int, held=held) -> int:
+                held.append(torch.empty(nbytes, dtype=torch.uint8, device=dev))
+                return held[0].data_ptr()
+
+            tc = time.perf_counter()
+            cap = captured_table(model, {n: index[n] for n in names[lo:hi]}, addresses,
+                                 load_weights=loader, device=dev, alloc_staging=alloc_staging,
+                                 dests=dests)
+            timings["capture"] += time.perf_counter() - tc
+            parts.append(cap)
+            if cap.reasons and on_unsupported != "engine":
+                first = next(iter(cap.reasons))
+                raise StrategyFailed(
+                    f"{len(cap.reasons)} source tensor(s) need the engine's loader, e.g. "
+                    f"{first}: {cap.reasons[first]}", mutated=False)
+            if cap.converts:
+                stagings.append((cap.converts, held[0]))
+            if len(cap.records):
+                if ring is None:
+                    tc = time.perf_counter()
+                    ring = ctx.ring(ring_bytes, ring_slots, dev_index)
+                    timings["ring_create"] = time.perf_counter() - tc
+                # the library works on its own streams: what the caller (or the dry run's
+                # real side effects, e.g. zeroed vocabulary padding) queued on torch's
+                # stream must be done before these destinations are written
+                torch.cuda.current_stream(dev).synchronize()
+                pending.append(pool.submit(ring.place, cap.records, threads, mode))
+        tc = time.perf_counter()
+        results = [f.result() for f in pending]
+        timings["place_wait"] = time.perf_counter() - tc
+        seconds = time.perf_counter() - t0
+        for converts, buf in stagings:
+            apply_converts(converts, buf, dests)
+        reasons = {}
+        for cap in parts:
+            reasons.update(cap.reasons)
+        leftover = [n for n in names if n in reasons]
         if leftover:
+            tc = time.perf_counter()
             loader((n, _engine_tensor(images[index[n]["file"]], index[n])) for n in leftover)
+            timings["engine"] = time.perf_counter() - tc
         torch.cuda.current_stream(dev).synchronize()
     finally:
+        pool.shutdown(wait=True)
         for im in images.values():
             im.close()
         if own_ring and ring is not None:
-            ring.close()
-    return CapturedPlacement(stats, cap.copies, int(len(table)), [c.param_name for c in cap.converts],
-                             leftover, cap.reasons, cap.written_params)
+            _release(ring)
+    stats = PlaceResult(sum(r.bytes_placed for r in results), sum(r.chunks for r in results),
+                        sum(r.launches for r in results), seconds,
+                        sum(r.seconds_gather for r in results), sum(r.seconds_device for r in results))
+    written = set()
+    for cap in parts:
+        written |= cap.written_params
+    return CapturedPlacement(stats, sum(c.copies for c in parts), sum(len(c.records) for c in parts),
+                             [c.param_name for cv, _b in stagings for c in cv], leftover, reasons,
+                             written, {k: round(v, 4) for k, v in timings.items()})
 
 
 class B200ScatterStrategy:
@@ -316,7 +380,7 @@ class B200ScatterStrategy:
     name = "b200_scatter"
     requires: tuple = ()
 
-    def __init__(self, ring_bytes: int = 2 << 30, ring_slots: int = 32, host_threads: int | None = None):
+    def __init__(self, ring_bytes: int = RING_BYTES, ring_slots: int = RING_SLOTS, host_threads: int | None = None):
         self.ring_bytes, self.ring_slots, self.host_threads = ring_bytes, ring_slots, host_threads
         self._touched = False
 
@@ -391,5 +455,6 @@ class B200CapturedStrategy(B200ScatterStrategy):
         result.metadata[self.name] = {
             "bytes_placed": placed.stats.bytes_placed, "seconds": placed.stats.seconds_total,
             "chunks": placed.stats.chunks, "records": placed.records,
-            "engine_loaded": len(placed.engine_loaded), "converted": len(placed.converted)}
+            "engine_loaded": len(placed.engine_loaded), "converted": len(placed.converted),
+            "timings": placed.timings}
         return result

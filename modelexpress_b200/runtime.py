@@ -7,6 +7,7 @@ Plain integers are used for device addresses so that callers may pass
 from __future__ import annotations
 
 import ctypes
+import threading
 from dataclasses import dataclass
 
 import numpy as np
@@ -18,6 +19,9 @@ from ._lib import (DIGEST_BLOCK64, DIGEST_ROWS, DIGEST_SAFE32, PLACE_COPY_ENGINE
 __all__ = ["Context", "Ring", "Fanout", "Table", "PlaceResult", "default_context",
            "DIGEST_SAFE32", "DIGEST_ROWS", "DIGEST_BLOCK64", "SCATTER_DEFAULT", "SCATTER_VECTOR",
            "SCATTER_NO_SYNC", "PLACE_COPY_ENGINE", "PLACE_ZERO_COPY"]
+
+
+_close_lock = threading.Lock()
 
 
 @dataclass
@@ -40,11 +44,24 @@ class Context:
         h = ctypes.c_void_p()
         check(self._lib.mxb_ctx_create(ids, len(self.devices), ctypes.byref(h)), "mxb_ctx_create")
         self._h = h
+        self._background: list = []   # threads still releasing objects of this context
 
     def close(self):
         if getattr(self, "_h", None):
+            for t in self._background:
+                t.join()
+            self._background = []
             self._lib.mxb_ctx_destroy(self._h)
             self._h = None
+
+    def release_later(self, obj) -> None:
+        """Close ``obj`` (a ring) on a background thread; ``close()`` waits for it."""
+        import threading
+
+        self._background = [t for t in self._background if t.is_alive()]
+        t = threading.Thread(target=obj.close, name="mxb-release", daemon=True)
+        self._background.append(t)
+        t.start()
 
     def __del__(self):
         try:
@@ -189,12 +206,13 @@ class Ring:
                            st.seconds_gather, st.seconds_device)
 
     def close(self):
-        if getattr(self, "_h", None):
+        with _close_lock:            # a background release and __del__ may both get here
+            h, self._h = getattr(self, "_h", None), None
+        if h:
             # the object lives inside its context: if that was closed first there is
             # nothing left to release
             if getattr(self.ctx, "_h", None):
-                self.ctx._lib.mxb_ring_destroy(self._h)
-            self._h = None
+                self.ctx._lib.mxb_ring_destroy(h)
 
     def __del__(self):
         try:
