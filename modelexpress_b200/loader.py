@@ -304,6 +304,18 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
         parts, pending, stagings = [], [], []
         timings = {"capture": 0.0, "ring_create": 0.0, "place_wait": 0.0, "engine": 0.0}
         t0 = time.perf_counter()
+        made = []
+
+        def make_ring():
+            # first job of the placing thread: pinning the ring overlaps the first dry-run batch
+            tc = time.perf_counter()
+            made.append(ctx.ring(ring_bytes, ring_slots, dev_index))
+            timings["ring_create"] = time.perf_counter() - tc
+
+        def place_batch(records):
+            return (ring if ring is not None else made[0]).place(records, threads, mode)
+
+        ring_job = pool.submit(make_ring) if ring is None else None
         for lo, hi in zip(cuts[:-1], cuts[1:]):
             held = []
 
@@ -325,16 +337,14 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
             if cap.converts:
                 stagings.append((cap.converts, held[0]))
             if len(cap.records):
-                if ring is None:
-                    tc = time.perf_counter()
-                    ring = ctx.ring(ring_bytes, ring_slots, dev_index)
-                    timings["ring_create"] = time.perf_counter() - tc
                 # the library works on its own streams: what the caller (or the dry run's
                 # real side effects, e.g. zeroed vocabulary padding) queued on torch's
                 # stream must be done before these destinations are written
                 torch.cuda.current_stream(dev).synchronize()
-                pending.append(pool.submit(ring.place, cap.records, threads, mode))
+                pending.append(pool.submit(place_batch, cap.records))
         tc = time.perf_counter()
+        if ring_job is not None:
+            ring_job.result()
         results = [f.result() for f in pending]
         timings["place_wait"] = time.perf_counter() - tc
         seconds = time.perf_counter() - t0
@@ -353,8 +363,8 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
         pool.shutdown(wait=True)
         for im in images.values():
             im.close()
-        if own_ring and ring is not None:
-            _release(ring)
+        if own_ring and made:
+            _release(made[0])
     stats = PlaceResult(sum(r.bytes_placed for r in results), sum(r.chunks for r in results),
                         sum(r.launches for r in results), seconds,
                         sum(r.seconds_gather for r in results), sum(r.seconds_device for r in results))
