@@ -330,3 +330,31 @@ def test_capture_of_real_vllm_layers_matches_recorded_vllm_outputs():
         for pname, key in want.items():
             got = dict(model.named_parameters())[pname].data.contiguous().view(torch.int16).numpy().view(np.uint16)
             assert np.array_equal(got, z[f"rank{rank}/{key}"]), (rank, pname)
+
+
+def test_whole_vllm_models_on_cpu_every_tp_rank():
+    """Real vLLM ``LlamaForCausalLM`` and ``Qwen2ForCausalLM`` (q/k/v biases) built on
+    the CPU, tensor-parallel size 4, every rank: records compiled from the dry run
+    of the model's own ``load_weights`` reproduce what ``load_weights`` produces,
+    bit for bit, with nothing left to the engine.  Runs in a child process (vLLM's
+    parallel state is global)."""
+    pytest.importorskip("vllm")
+    import json
+    import subprocess
+    import sys
+
+    helper = os.path.join(os.path.dirname(__file__), "vllm_cpu_model.py")
+    run = subprocess.run([sys.executable, helper], capture_output=True, text=True, timeout=900)
+    lines = [ln for ln in run.stdout.splitlines() if ln.startswith("RESULT ")]
+    if run.returncode != 0 or not lines:
+        pytest.skip("vLLM could not build a model on the CPU here: " + run.stderr.strip()[-400:])
+    res = json.loads(lines[-1][len("RESULT "):])
+    assert sorted(res) == [f"{a}/rank{r}" for a in ("llama", "qwen2") for r in range(4)]
+    for key, r in res.items():
+        assert r["mismatch"] == [] and r["engine"] == [], (key, r)
+        assert r["copies"] == r["records"] == (27 if key.startswith("qwen2") else 21), (key, r)
+    # vocabulary 1000 pads to 1024: the last rank's embed and lm_head shards hold 24 real rows
+    # fewer (x 256 columns x 2 bytes x 2 tensors) than the other ranks'
+    for arch in ("llama", "qwen2"):
+        b = [res[f"{arch}/rank{r}"]["bytes"] for r in range(4)]
+        assert b[0] == b[1] == b[2] and b[0] - b[3] == 2 * 24 * 256 * 2
