@@ -244,6 +244,45 @@ def test_captured_copies_plan_against_row_sharded_sources():
         assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), n
 
 
+def test_fused_gqa_trainer_storage_as_many_shards_per_source():
+    """Sources published the way a Megatron trainer holds them: ONE fused QKV
+    tensor interleaved per KV group ([q_g; k_g; v_g] for each group g), exposed
+    as per-group alias shards of the HF q / k / v tensors
+    (modelexpress_rl/train/engines/megatron/aliases.py; the reference pins these
+    boxes in tests/test_reshard_megatron_gqa.py:195-342).  The captured copies of
+    a fused-qkv loader must pull the right group rows straight out of the
+    interleaved storage."""
+    from modelexpress_b200.planner import ShardSpec, SourceSpec, plan_transfer_2d
+
+    groups, q_rows, kv_rows, cols = 4, 4, 2, 16         # per group: 4 q rows, 2 k rows, 2 v rows
+    per_group = q_rows + 2 * kv_rows
+    fused = torch.randn(groups * per_group, cols)
+    rows = fused.view(groups, per_group, cols)
+    full = {"q": rows[:, :q_rows].reshape(-1, cols).contiguous(),
+            "k": rows[:, q_rows:q_rows + kv_rows].reshape(-1, cols).contiguous(),
+            "v": rows[:, q_rows + kv_rows:].reshape(-1, cols).contiguous()}
+    el = fused.element_size()
+    sources = {}
+    for name, first, n in (("q", 0, q_rows), ("k", q_rows, kv_rows), ("v", q_rows + kv_rows, kv_rows)):
+        shards = [ShardSpec((g * n, 0), (n, cols), f"trainer/{name}/{g}",
+                            fused.data_ptr() + (g * per_group + first) * cols * el, el)
+                  for g in range(groups)]
+        sources[name] = SourceSpec((groups * n, cols), torch.float32, el, shards)
+    manifest = [(n, torch.float32, tuple(t.shape)) for n, t in full.items()]
+    for rank in (0, 1):
+        truth = Toy(rank)
+        truth.load_weights(iter(full.items()))
+        model = Toy(rank)
+        cap = capture_geometry(model, manifest)
+        table, unsupported, converts = plan_transfer_2d(
+            cap.copies, sources, lambda n: dict(model.named_parameters())[n].data_ptr())
+        assert not unsupported and not converts
+        # rank r keeps q rows [8r, 8r+8) = groups 2r, 2r+1 and k/v rows [4r, 4r+4): two shards each
+        assert len(table) == 6 and int(table[:, 2].astype(np.int64).sum()) == 6
+        c_port.scatter2d(table)
+        assert torch.equal(model.qkv.data, truth.qkv.data), rank
+
+
 # ---- real vLLM parallel layers, checked against outputs recorded from vLLM itself --------------
 
 def _vllm_mini(rank, tp, dims):
