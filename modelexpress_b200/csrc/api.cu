@@ -21,6 +21,7 @@ int32_t ensure_table(DeviceState *d, size_t bytes) {
     d->table = nullptr;
     d->table_host = nullptr;
     d->table_bytes = d->table_host_bytes = 0;
+    d->table_tag = 0;
     MXB_CUDA(cudaMalloc(&d->table, want));
     MXB_CUDA(cudaHostAlloc(&d->table_host, want, cudaHostAllocDefault));
     d->table_bytes = d->table_host_bytes = want;

@@ -44,6 +44,7 @@ struct DeviceState {
     size_t table_bytes = 0;
     void *table_host = nullptr;  // pinned staging for the table upload
     size_t table_host_bytes = 0;
+    uint64_t table_tag = 0;      // what the table holds: 0 = nothing reusable, else a digest span-list hash
     // scratch for digest accumulators
     void *digest = nullptr;
     size_t digest_bytes = 0;

@@ -502,6 +502,7 @@ int32_t launch_scatter(mxb_ctx *ctx, DeviceState *dv, const mxb_desc2d *descs, u
     // the pinned staging copy is reused by every call: wait for the previous upload
     MXB_CUDA(cudaStreamSynchronize(stream));
     ScatterTable tb;
+    dv->table_tag = 0;  // the shared table no longer holds a digest tile list
     rc = build_scatter_table(descs, n, dv->table_host, dv->table, &tb, nullptr, nullptr, dv->device);
     if (rc != MXB_OK) return rc;
     MXB_CUDA(cudaMemcpyAsync(dv->table, dv->table_host, tb.bytes, cudaMemcpyHostToDevice, stream));
