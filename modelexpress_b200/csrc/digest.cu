@@ -236,8 +236,8 @@ __device__ __forceinline__ void digest_row(const RowMeta &m, const uint4 (&v)[8]
         a.safe += base * A + (512u * kKnuth) * B + kKnuth * X;
     }
     if (MODES & MXB_DIGEST_ROWS) {
-        const uint64_t whole_rows = (m.n / 4) / 1024;  // rows made only of whole words
-        if (m.row < whole_rows) {
+        // rows made only of whole words; every row of a full tile is one
+        if (!TAIL || m.row < (m.n / 4) / 1024) {
             // (a widening multiply-add per word, 16-bit halves through dp2a and unsigned sums
             // with a count of negatives all measured the same as this plain form)
             int64_t s64 = 0;
@@ -274,39 +274,82 @@ __device__ __forceinline__ void digest_row(const RowMeta &m, const uint4 (&v)[8]
 // span of the NEXT tile are fetched while the current row's loads are in flight,
 // so a warp never sits through two dependent table reads before it can issue
 // data loads.
+//
+// Registers: 512 threads x 2 CTAs per SM leave 64 per thread, 32 of which hold the
+// row in flight.  The full-tile kernels therefore keep their per-lane partial sums
+// in shared memory (each thread owns one slot, no synchronisation), where the
+// compiler would otherwise spill them to local memory inside the loop.
+struct LaneSums {
+    unsigned long long row_sum[kDigestThreads], row_sum_w[kDigestThreads], block[kDigestThreads];
+    uint32_t safe[kDigestThreads];
+};
+
 template <uint32_t MODES, bool TAIL>
 __global__ void __launch_bounds__(kDigestThreads, 2)
 digest_kernel(const mxb_span *__restrict__ spans, const DTile *__restrict__ tiles,
               uint64_t total_tiles, DigestAcc *__restrict__ acc,
               unsigned long long *__restrict__ block_out) {
-    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    __shared__ LaneSums sums;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     WarpAcc a;
     RowMeta cur;
     uint4 vc[8];
-    uint64_t t = blockIdx.x;
-    if (t >= total_tiles) return;
+    const uint32_t ntiles = (uint32_t)total_tiles;  // the host refuses more than 2^32 tiles
+    uint32_t t = blockIdx.x;
+    if (t >= ntiles) return;
+    if (!TAIL) {
+        sums.row_sum[tid] = sums.row_sum_w[tid] = sums.block[tid] = 0;
+        sums.safe[tid] = 0;
+    }
+    // the sums of the span this warp is in, out of shared memory and into `a`
+    auto collect = [&]() {
+        if (!TAIL) {
+            a.row_sum = sums.row_sum[tid];
+            a.row_sum_w = sums.row_sum_w[tid];
+            a.block = sums.block[tid];
+            a.safe = sums.safe[tid];
+            sums.row_sum[tid] = sums.row_sum_w[tid] = sums.block[tid] = 0;
+            sums.safe[tid] = 0;
+        }
+    };
     DTile tile = tiles[t];
-    mxb_span sp = spans[tile.span];
+    mxb_span sp;
+    sp.ptr = spans[tile.span].ptr;
+    sp.nbytes = TAIL ? spans[tile.span].nbytes : 0;  // full tiles never look at the length
     for (;;) {
         load_row<!TAIL>(tile, sp, warp, lane, cur, vc);
-        const uint64_t tn = t + gridDim.x;
-        const bool more = tn < total_tiles;
+        const uint32_t tn = t + gridDim.x;
+        const bool more = tn < ntiles;
         DTile ntile = tile;
         mxb_span nsp = sp;
         if (more) {
             ntile = tiles[tn];
-            nsp = spans[ntile.span];
+            nsp.ptr = spans[ntile.span].ptr;
+            if (TAIL) nsp.nbytes = spans[ntile.span].nbytes;
         }
         if (cur.span != a.span) {
+            collect();
             flush(a, acc, lane);
             a.span = cur.span;
         }
-        if (cur.valid) digest_row<MODES, TAIL>(cur, vc, lane, a, block_out);
+        if (TAIL) {
+            if (cur.valid) digest_row<MODES, TAIL>(cur, vc, lane, a, block_out);
+        } else {
+            WarpAcc r;  // this row's terms only: short-lived registers
+            digest_row<MODES, TAIL>(cur, vc, lane, r, block_out);
+            if (MODES & MXB_DIGEST_ROWS) {
+                sums.row_sum[tid] += r.row_sum;
+                sums.row_sum_w[tid] += r.row_sum_w;
+            }
+            if (MODES & MXB_DIGEST_BLOCK64) sums.block[tid] += r.block;
+            if (MODES & MXB_DIGEST_SAFE32) sums.safe[tid] += r.safe;
+        }
         if (!more) break;
         tile = ntile;
         sp = nsp;
         t = tn;
     }
+    collect();
     flush(a, acc, lane);
 }
 
@@ -446,6 +489,10 @@ static int32_t run_digest(mxb_ctx *ctx, int32_t dev, const mxb_span *spans, uint
             return MXB_ERR_ARG;
         }
         total += (spans[i].nbytes + kDigestTile - 1) / kDigestTile;
+    }
+    if (total > 0xffffffffull) {
+        set_error("mxb_digest: more than 2^32 tiles (256 TiB) in one call");
+        return MXB_ERR_ARG;
     }
     DeviceGuard g(dev);
     std::lock_guard<std::mutex> lk(*d->mu);
