@@ -185,8 +185,13 @@ def _engine_tensor(image: FileImage, info: dict):
     """A real (host) tensor over the checkpoint bytes, for the engine's loader."""
     import torch
 
-    raw = torch.frombuffer(image._mm, dtype=torch.uint8, count=int(info["size"]),
-                           offset=int(info["file_offset"]))
+    import warnings
+
+    with warnings.catch_warnings():
+        # the mapping is read-only and so is every use the engine's loader makes of a source
+        warnings.filterwarnings("ignore", message="The given buffer is not writable")
+        raw = torch.frombuffer(image._mm, dtype=torch.uint8, count=int(info["size"]),
+                               offset=int(info["file_offset"]))
     return raw.view(torch_dtype(info["dtype"])).reshape(tuple(info["shape"]))
 
 

@@ -336,3 +336,74 @@ def test_mdl_loader_warm_install(rank):
     with pytest.raises(KeyError):
         MdlLoader(model, 0, 2).load_weights([("l.unknown.weight", mk(4, 4))])
     mdl.close()
+
+
+def test_place_captured_converts_batches_and_engine_leftovers(tmp_path):
+    """``place_captured`` on a hand-made engine model: a fused, tensor-parallel
+    loader, a checkpoint tensor served in bf16 for an fp32 parameter (staged and
+    cast on the device), a transposed expert stack, a scalar the loader reads with
+    ``.item()`` (handed to the loader itself afterwards), one source per dry-run
+    batch so that capture and placement interleave.  Every parameter must equal
+    what the same ``load_weights`` produces from the real tensors."""
+    import torch
+
+    from modelexpress_b200 import synth
+    from modelexpress_b200.loader import StrategyFailed, place_captured
+
+    class Engine(torch.nn.Module):
+        def __init__(self, rank):
+            super().__init__()
+            self.rank = rank
+            self.qkv = torch.nn.Parameter(torch.zeros(256 + 64 + 64, 512, dtype=torch.bfloat16))
+            self.down = torch.nn.Parameter(torch.zeros(512, 384, dtype=torch.bfloat16))
+            self.experts = torch.nn.Parameter(torch.zeros(4, 96, 512, dtype=torch.bfloat16))
+            self.router = torch.nn.Parameter(torch.zeros(4, 512, dtype=torch.float32))
+            self.embed = torch.nn.Parameter(torch.ones(1024, 512, dtype=torch.bfloat16))
+            self.scale = torch.nn.Parameter(torch.zeros(1, dtype=torch.float32))
+
+        def load_weights(self, weights):
+            r = self.rank
+            for name, w in weights:
+                if name in ("q", "k", "v"):
+                    rows = {"q": 256, "k": 64, "v": 64}[name]
+                    at = {"q": 0, "k": 256, "v": 320}[name]
+                    self.qkv.data.narrow(0, at, rows).copy_(w.narrow(0, r * rows, rows))
+                elif name == "down":
+                    self.down.data.copy_(w[:, r * 384:(r + 1) * 384])
+                elif name == "experts":          # stored (E, hidden, inter)
+                    for e, we in enumerate(w.unbind(0)):
+                        self.experts.data[e].copy_(we.t().narrow(0, r * 96, 96))
+                elif name == "router":
+                    self.router.data.copy_(w)
+                elif name == "embed":
+                    self.embed.data[: w.shape[0]].copy_(w)
+                    self.embed.data[w.shape[0]:].fill_(0)
+                elif name == "scale":
+                    self.scale.data.fill_(w.item())
+
+    tensors = [("q", (512, 512), "BF16", "matrix"), ("k", (128, 512), "BF16", "matrix"),
+               ("scale", (1,), "F32", "matrix"), ("v", (128, 512), "BF16", "matrix"),
+               ("down", (512, 768), "BF16", "matrix"), ("experts", (4, 512, 192), "BF16", "matrix"),
+               ("router", (4, 512), "BF16", "matrix"), ("embed", (1000, 512), "BF16", "matrix")]
+    d = str(tmp_path)
+    synth.write_checkpoint(d, tensors, 77, 2)
+    full = read_full_tensors(d)
+    for rank in (0, 1):
+        truth = Engine(rank).cuda()
+        truth.load_weights((n, torch.from_numpy(a.copy()).view(
+            torch.bfloat16 if a.dtype == np.uint16 else torch.float32)) for n, a in full.items())
+        model = Engine(rank).cuda()
+        got = place_captured(model, d, "cuda:0", first_batch=1, ring_bytes=8 << 20, ring_slots=4,
+                             host_threads=2)
+        assert got.engine_loaded == ["scale"] and "item" in got.reasons["scale"]
+        assert got.converted == ["router"]
+        assert got.written_params == {"qkv", "down", "experts", "router", "embed"}
+        assert got.copies == 3 + 1 + 4 + 1 + 1 and got.stats.chunks >= 4
+        torch.cuda.synchronize()
+        for (n, a), (_n, b) in zip(model.state_dict().items(), truth.state_dict().items()):
+            assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), (rank, n)
+    # a caller that wants every byte through the kernel is told before anything is written
+    model = Engine(0).cuda()
+    with pytest.raises(StrategyFailed) as e:
+        place_captured(model, d, "cuda:0", on_unsupported="raise", ring_bytes=8 << 20, ring_slots=4)
+    assert not e.value.mutated and float(model.qkv.detach().abs().sum()) == 0.0
