@@ -3,7 +3,9 @@
 SGLang instantiates the class from its ``remote_instance`` loader and hands it
 an ALREADY INITIALISED model: ``load_model(*, model, model_config,
 device_config) -> nn.Module``.  Here the weights are placed into that model's
-parameters by the scatter path.  SGLang is not installed where this library was
+parameters by the scatter path: planned from the model's own ``load_weights``
+when it has one (``B200CapturedStrategy``), else from the built-in layout rules
+(``B200ScatterStrategy``).  SGLang is not installed where this library was
 developed, so this adapter is covered only by a test with stand-in objects; the
 placement underneath is the same code the vLLM adapter exercises.
 """
@@ -12,7 +14,7 @@ from __future__ import annotations
 
 import logging
 
-from ...loader import B200ScatterStrategy, LoadResult, StrategyFailed
+from ...loader import B200CapturedStrategy, B200ScatterStrategy, LoadResult, StrategyFailed
 
 logger = logging.getLogger("modelexpress_b200.engines.sglang")
 
@@ -45,6 +47,7 @@ class MxModelLoader:
         self.load_config = load_config
         self._adapter = SglangScatterAdapter(tp_rank, tp_size)
         self._tensors: dict = {}
+        self.last_strategy: str | None = None
 
     def load_model(self, *, model, model_config, device_config):
         """Place the checkpoint at ``model_config.model_path`` (SGLang's field; ``model``
@@ -61,14 +64,20 @@ class MxModelLoader:
         gpu_id = getattr(device_config, "gpu_id", None)
         device_id = torch.cuda.current_device() if gpu_id in (None, -1) else int(gpu_id)
         ctx = _Ctx(_Cfg(), device_id, self._adapter)
-        strategy = B200ScatterStrategy()
-        if not strategy.is_available(ctx):
+        if not B200ScatterStrategy().is_available(ctx):
             raise RuntimeError("No loading strategy succeeded: CUDA library or device unavailable")
-        try:
-            strategy.load(LoadResult(value=model, model=model), ctx)
-        except StrategyFailed as e:
-            strategy.rollback(ctx)
-            raise RuntimeError(f"No loading strategy succeeded for model {path!r}: {e}") from e
+        errors = []
+        self.last_strategy = None
+        for strategy in (B200CapturedStrategy(), B200ScatterStrategy()):
+            try:
+                strategy.load(LoadResult(value=model, model=model), ctx)
+                self.last_strategy = strategy.name
+                break
+            except StrategyFailed as e:
+                strategy.rollback(ctx)
+                errors.append(f"{strategy.name}: {e}")
+        if self.last_strategy is None:
+            raise RuntimeError(f"No loading strategy succeeded for model {path!r}: " + "; ".join(errors))
         self._tensors = {n: p.data for n, p in model.named_parameters()}
         return model.eval()
 

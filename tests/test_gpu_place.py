@@ -266,9 +266,11 @@ def test_sglang_loader_signature_with_stand_ins(ckpts):
 
     model = Model()
     torch.cuda.synchronize()
-    out = MxModelLoader(object(), tp_rank=2, tp_size=4).load_model(
-        model=model, model_config=ModelConfig(), device_config=DeviceConfig())
+    loader = MxModelLoader(object(), tp_rank=2, tp_size=4)
+    out = loader.load_model(model=model, model_config=ModelConfig(), device_config=DeviceConfig())
     assert out is model and not model.training
+    # the stand-in has no load_weights to dry-run, so the layout rules planned this load
+    assert loader.last_strategy == "b200_scatter"
     want = R.load_and_shard(read_full_tensors(tiny), 2, 4)
     got = dict(model.named_parameters())
     for n, a in want.items():
