@@ -1,0 +1,247 @@
+"""RL refit, receiving side: published trainer shards -> this rank's live parameters.
+
+The reference's ``ReshardReceiver`` (refit/reshard/receiver.py:336-1043) does, per
+inference rank: discover the trainers' shard tables, dry-run the engine's loader
+to learn which slices it needs (``_capture``), plan byte segments
+(``plan_transfer``), RDMA them into receive buffers through NIXL every step
+(``update_weights``), cast the dtype-mismatched ones and install the buffers into
+the live parameters.  This module is the data-plane core of that cycle on one
+NVLink box, with the control plane left to the caller:
+
+* ``PublishedShard`` / ``PublishedTensor`` / ``merge_shard_tables`` /
+  ``build_sources`` are the shard-table types and helpers of
+  refit/reshard/rendezvous.py:68-272 with the same fields and rules, so tables
+  decoded by the reference's rendezvous can be passed in as they are;
+* ``ReshardReceiver.prepare`` captures the model's ``load_weights`` once
+  (``geometry.capture_geometry``), plans 2-D records against the shards
+  (``planner.plan_transfer_2d``) and uploads them as ONE resident table;
+* ``ReshardReceiver.update_weights(step)`` replays that table in one persistent
+  launch: trainer shards are read in place over NVLink (peer memory mapped by the
+  caller, e.g. with ``runtime.ipc_open``) and written straight into the live
+  parameters — there is no receive buffer and no install step for parameters kept
+  at the served dtype; dtype-changing copies go through a small staging buffer
+  and one cast each, as in the reference (receiver.py:964-971);
+* ``verify=True`` digests every published shard in place in one launch and compares
+  with the digest its publisher attached, before a byte is written (the strict gate
+  of modelexpress_rl/inference/nixl_staged_transfer.py:529-549).
+
+Quantised engines whose live parameters are not the load-time parameters need
+the engine's own post-load processing after the bytes land; that hook is the
+caller's (``install`` argument), as ``_install`` is the subclass's in the reference.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable
+
+from .planner import (ShardSpec, SourceSpec, apply_converts, convert_staging_bytes,
+                      plan_transfer_2d)
+from .runtime import Context, Table, default_context
+
+__all__ = ["PublishedShard", "PublishedTensor", "merge_shard_tables", "build_sources",
+           "ReshardReceiver"]
+
+
+@dataclass
+class PublishedShard:
+    """rendezvous.py:68-84: the sub-box one trainer rank owns and where to read it."""
+
+    agent_name: str
+    device_id: int
+    addr: int
+    shard_offset: tuple
+    shape: tuple
+    digest: str | None = None
+
+
+@dataclass
+class PublishedTensor:
+    """rendezvous.py:87-96: a full source tensor and the shards that cover it."""
+
+    name: str
+    dtype: str  # e.g. "torch.bfloat16"
+    elsize: int
+    full_shape: tuple
+    shards: list = field(default_factory=list)
+
+
+def merge_shard_tables(tables: list) -> list:
+    """Per-rank tables -> one table, shards of a name concatenated across ranks,
+    ONE representative per exact (offset, shape) so that replicated publishers
+    are read once; inconsistent shape/dtype across ranks raises ``ValueError``
+    (rendezvous.py:220-272)."""
+    merged: dict = {}
+    seen: dict = {}
+    for table in tables:
+        for t in table:
+            cur = merged.get(t.name)
+            if cur is None:
+                merged[t.name] = PublishedTensor(t.name, t.dtype, t.elsize, tuple(t.full_shape), [])
+                seen[t.name] = {}
+            elif tuple(cur.full_shape) != tuple(t.full_shape) or cur.dtype != t.dtype:
+                raise ValueError(
+                    f"tensor {t.name!r} published with inconsistent shape/dtype across ranks: "
+                    f"{cur.full_shape}/{cur.dtype} vs {t.full_shape}/{t.dtype}")
+            for shard in t.shards:
+                seen[t.name].setdefault((tuple(shard.shard_offset), tuple(shard.shape)), shard)
+    for name, tensor in merged.items():
+        tensor.shards.extend(seen[name].values())
+    return list(merged.values())
+
+
+def _torch_dtype(label: str):
+    import torch
+
+    return getattr(torch, str(label).replace("torch.", ""))
+
+
+def build_sources(tensors: list, map_address: Callable | None = None) -> dict:
+    """Published tensors -> ``{name: SourceSpec}`` for the planner
+    (rendezvous.py:184-217).  ``map_address(shard) -> int`` translates a
+    publisher's address into one this process can read (a CUDA IPC mapping of
+    the trainer's arena); without it addresses are taken as they are."""
+    sources = {}
+    for t in tensors:
+        shards = [ShardSpec(tuple(s.shard_offset), tuple(s.shape), s.agent_name,
+                            int(map_address(s)) if map_address is not None else int(s.addr),
+                            int(t.elsize), s.digest) for s in t.shards]
+        sources[t.name] = SourceSpec(tuple(t.full_shape), _torch_dtype(t.dtype), int(t.elsize), shards)
+    return sources
+
+
+class ReshardReceiver:
+    """One inference rank's refit cycle: ``prepare`` once, ``update_weights`` per step."""
+
+    def __init__(self, model, *, device=None, ctx: Context | None = None,
+                 load_weights: Callable | None = None, install: Callable | None = None):
+        import torch
+
+        self.model = model
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None \
+            else torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("ReshardReceiver needs a CUDA device (no CPU fallback)")
+        self._dev = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self.ctx = ctx if ctx is not None else default_context(self._dev)
+        self._load_weights = load_weights
+        self._install = install
+        self._table: Table | None = None
+        self._sources: dict = {}
+        self._converts: list = []
+        self._staging = None
+        self._dests: dict = {}
+        self.plan: dict = {}
+
+    # ------------------------------------------------------------------ prepare
+    def prepare(self, sources, map_address: Callable | None = None) -> dict:
+        """Capture, plan and upload.  ``sources`` is ``{name: SourceSpec}`` or a list
+        of ``PublishedTensor``.  Fails closed (``RuntimeError``) when a source the
+        loader uses cannot be planned, like the reference's receiver; returns the
+        plan summary also kept in ``self.plan``."""
+        import torch
+
+        from .geometry import capture_geometry
+        from .loader import model_destinations
+
+        t0 = time.perf_counter()
+        if not isinstance(sources, dict):
+            sources = build_sources(list(sources), map_address)
+        manifest = [(n, s.dtype, tuple(s.global_shape)) for n, s in sources.items()]
+        cap = capture_geometry(self.model, manifest, self._load_weights, device=self.device)
+        t_capture = time.perf_counter() - t0
+        dests = model_destinations(self.model)
+        nbytes = convert_staging_bytes(cap.copies, sources)
+        staging = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=self.device)
+        table, not_planned, converts = plan_transfer_2d(
+            cap.copies, sources, lambda n: dests[n].data_ptr(), staging.data_ptr() if nbytes else None)
+        reasons = dict(cap.unsupported_reasons)
+        for n in not_planned:
+            reasons.setdefault(n, "the copied window is not a box of the source tensor")
+        if reasons:
+            first = next(iter(reasons))
+            raise RuntimeError(f"reshard refit cannot plan {len(reasons)} source(s), e.g. "
+                               f"{first!r}: {reasons[first]}")
+        self.close()
+        self._table = self.ctx.table(table, self._dev) if len(table) else None
+        self._sources, self._converts, self._staging, self._dests = sources, converts, staging, dests
+        planned = {c.param_name for c in cap.copies}
+        total = sum(t.numel() * t.element_size() for t in
+                    {id(p): p for p in self.model.parameters()}.values())
+        moved = int((table[:, 2] * table[:, 3]).sum()) if len(table) else 0
+        used = {c.src_name for c in cap.copies}
+        self.plan = {
+            "copies": len(cap.copies), "records": int(len(table)), "bytes_per_step": moved,
+            "converts": [c.param_name for c in converts], "params_written": len(planned),
+            "coverage": (moved / total) if total else 1.0,
+            "sources_unused": sorted(set(sources) - used),
+            "engine": self._table.engine() if self._table is not None else "none",
+            "prepare_capture_s": round(t_capture, 6),
+            "prepare_total_s": round(time.perf_counter() - t0, 6)}
+        return self.plan
+
+    # ------------------------------------------------------------------- verify
+    def verify_published(self) -> int:
+        """Digest every published shard in place (one launch) and compare with the
+        digest its publisher attached; raises ``RuntimeError`` naming the first
+        shard that is missing a digest or differs.  Returns the shards checked."""
+        from .digest import digest_hex, scalars_from_record
+        from .runtime import DIGEST_ROWS
+
+        spans, labels, wants = [], [], []
+        for name, src in self._sources.items():
+            for sh in src.shards:
+                if not sh.digest:
+                    raise RuntimeError(f"source {name!r} did not publish a verification digest")
+                n = int(src.elsize)
+                for extent in sh.shape:
+                    n *= int(extent)
+                spans.append((int(sh.addr) if n else 0, n))
+                labels.append(f"{name}@{tuple(sh.shard_offset)}")
+                wants.append(sh.digest)
+        if not spans:
+            return 0
+        recs = self.ctx.digest(spans, DIGEST_ROWS, self._dev)
+        for label, want, rec in zip(labels, wants, recs):
+            have = digest_hex(scalars_from_record(rec))
+            if have != want:
+                raise RuntimeError(f"digest mismatch for shard {label}: published {want}, read {have}")
+        return len(spans)
+
+    # ------------------------------------------------------------------- update
+    def update_weights(self, step: int, *, verify: bool = False) -> dict:
+        """Pull this step's weights: one replay of the resident table (plus the
+        casts and the caller's install hook).  The trainers must have finished
+        writing their shards (the caller's barrier, as in the reference).  Returns
+        the stage record of the step."""
+        import torch
+
+        if self._table is None and not self.plan:
+            raise RuntimeError("prepare() has not been called")
+        stages = {"step": int(step)}
+        t0 = time.perf_counter()
+        torch.cuda.current_stream(self.device).synchronize()
+        if verify:
+            stages["shards_verified"] = self.verify_published()
+            stages["verify_s"] = time.perf_counter() - t0
+        t1 = time.perf_counter()
+        if self._table is not None:
+            self._table.launch()
+        stages["read_s"] = time.perf_counter() - t1
+        t2 = time.perf_counter()
+        if self._converts:
+            apply_converts(self._converts, self._staging, self._dests)
+        if self._install is not None:
+            self._install(self.model)
+        torch.cuda.current_stream(self.device).synchronize()
+        stages["install_s"] = time.perf_counter() - t2
+        stages["total_s"] = time.perf_counter() - t0
+        stages["bytes"] = self.plan.get("bytes_per_step", 0)
+        stages["gbps"] = stages["bytes"] / stages["read_s"] / 1e9 if stages["read_s"] > 0 else 0.0
+        return stages
+
+    def close(self) -> None:
+        if self._table is not None:
+            self._table.close()
+            self._table = None

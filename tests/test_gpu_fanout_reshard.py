@@ -229,3 +229,111 @@ def test_strict_verify_catches_a_misplaced_shard():
         verify.shard_region(full, (64, 1024), (1,), (2, 3))
     region = verify.shard_region(full.reshape(-1), (64, 1024), (1, 2), (2, 3))
     assert torch.equal(region, full[1:3, 2:5])
+
+
+def test_reshard_receiver_prepare_once_update_every_step():
+    """The refit cycle of refit/reshard/receiver.py:447-1043 on one GPU: four
+    emulated trainer ranks publish row shards (with digests) of every HF tensor,
+    the receiver captures the engine's loader once and replays one resident table
+    per step.  Parameters must equal what the loader makes of the assembled full
+    tensors, for the first step and after the trainers rewrote their shards in
+    place; a shard that no longer matches its published digest stops the step
+    before a byte is written."""
+    import torch
+
+    from modelexpress_b200.refit import (PublishedShard, PublishedTensor, ReshardReceiver,
+                                         merge_shard_tables)
+    from modelexpress_b200.verify import published_digests
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+
+    class Engine(torch.nn.Module):
+        def __init__(self, rank):
+            super().__init__()
+            self.rank = rank
+            self.qkv = torch.nn.Parameter(torch.zeros(256 + 64 + 64, 512, dtype=torch.bfloat16))
+            self.down = torch.nn.Parameter(torch.zeros(512, 384, dtype=torch.bfloat16))
+            self.router = torch.nn.Parameter(torch.zeros(4, 512, dtype=torch.float32))
+            self.norm = torch.nn.Parameter(torch.zeros(512, dtype=torch.bfloat16))
+
+        def load_weights(self, weights):
+            r = self.rank
+            for name, w in weights:
+                if name in ("q", "k", "v"):
+                    rows = {"q": 256, "k": 64, "v": 64}[name]
+                    at = {"q": 0, "k": 256, "v": 320}[name]
+                    self.qkv.data.narrow(0, at, rows).copy_(w.narrow(0, r * rows, rows))
+                elif name == "down":
+                    self.down.data.copy_(w[:, r * 384:(r + 1) * 384])
+                elif name == "router":
+                    self.router.data.copy_(w)
+                elif name == "norm":
+                    self.norm.data.copy_(w)
+
+    shapes = {"q": (512, 512), "k": (128, 512), "v": (128, 512), "down": (512, 768),
+              "router": (4, 512), "norm": (512,)}
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    world = 4
+    # trainer rank t owns rows [t*R/4, (t+1)*R/4) of every tensor, in its own buffer
+    shards = {n: [torch.randn((s[0] // world,) + s[1:], device="cuda", generator=g).to(torch.bfloat16)
+                  for _ in range(world)] for n, s in shapes.items()}
+
+    def tables():
+        digs = published_digests({(n, t): shards[n][t] for n in shapes for t in range(world)})
+        out = []
+        for t in range(world):
+            out.append([PublishedTensor(n, "torch.bfloat16", 2, shapes[n], [PublishedShard(
+                f"trainer{t}", 0, shards[n][t].data_ptr(),
+                (t * (shapes[n][0] // world),) + (0,) * (len(shapes[n]) - 1),
+                tuple(shards[n][t].shape), digs[(n, t)])]) for n in shapes])
+        # a replica of rank 0 publishing the same geometry again must not add reads
+        out.append(out[0])
+        return merge_shard_tables(out)
+
+    def truth(rank):
+        m = Engine(rank).cuda()
+        m.load_weights((n, torch.cat(shards[n], 0)) for n in shapes)
+        return m
+
+    for rank in (0, 1):
+        model = Engine(rank).cuda()
+        rx = ReshardReceiver(model, device="cuda:0")
+        plan = rx.prepare(tables())
+        assert plan["converts"] == ["router"] and plan["sources_unused"] == []
+        assert plan["copies"] == 6 and plan["coverage"] > 0.99
+        st = rx.update_weights(1, verify=True)
+        assert st["shards_verified"] == world * len(shapes) and st["bytes"] == plan["bytes_per_step"]
+        want = truth(rank)
+        for (n, a), (_n, b) in zip(model.state_dict().items(), want.state_dict().items()):
+            assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), (rank, n)
+        # next step: the trainers rewrite their shards in place, same addresses
+        for n in shapes:
+            for t in range(world):
+                shards[n][t].copy_(torch.randn(shards[n][t].shape, device="cuda", generator=g))
+        torch.cuda.synchronize()
+        rx.update_weights(2)
+        want = truth(rank)
+        for (n, a), (_n, b) in zip(model.state_dict().items(), want.state_dict().items()):
+            assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), (rank, n)
+        # the published digests are those of step 1: the strict gate refuses step 3 untouched
+        before = {n: p.detach().clone() for n, p in model.state_dict().items()}
+        with pytest.raises(RuntimeError, match="digest mismatch"):
+            rx.update_weights(3, verify=True)
+        for n, p in model.state_dict().items():
+            assert torch.equal(p, before[n]), n
+        rx.close()
+
+    # fail closed: a source the loader computes on cannot be planned
+    class Casting(Engine):
+        def load_weights(self, weights):
+            for name, w in weights:
+                if name == "norm":
+                    self.norm.data.copy_(w.float() * 2)
+
+    with pytest.raises(RuntimeError, match="cannot plan"):
+        ReshardReceiver(Casting(0).cuda(), device="cuda:0").prepare(tables())
+    with pytest.raises(ValueError, match="inconsistent shape/dtype"):
+        merge_shard_tables([[PublishedTensor("q", "torch.bfloat16", 2, (512, 512), [])],
+                            [PublishedTensor("q", "torch.bfloat16", 2, (256, 512), [])]])

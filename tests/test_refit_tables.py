@@ -1,0 +1,67 @@
+"""Shard-table helpers of the refit receiver (no GPU): replica de-duplication,
+cross-rank fan-in, consistency checks and address mapping — the behaviours the
+reference pins in tests/test_reshard_refit_replica_merge.py:90-200."""
+
+import numpy as np
+import pytest
+import torch
+
+from modelexpress_b200.planner import CopySpec, expand_records, plan_transfer_2d
+from modelexpress_b200.refit import (PublishedShard, PublishedTensor, build_sources,
+                                     merge_shard_tables)
+
+EL = 2
+
+
+def _replicas(n, shards_per_rank=2):
+    return [[PublishedTensor("weight", "torch.bfloat16", EL, (8, 4), [
+        PublishedShard(f"dp{dp}", dp, 1000 * (dp + 1) + 10 * i, (4 * i, 0), (4, 4))
+        for i in range(shards_per_rank)])] for dp in range(n)]
+
+
+def _fan_in(ranks=4):
+    return [[PublishedTensor("weight", "torch.bfloat16", EL, (16, 4), [
+        PublishedShard(f"r{r}", r, 1000 * (r + 1), (4 * r, 0), (4, 4))])] for r in range(ranks)]
+
+
+def test_replicas_collapse_to_the_first_publisher():
+    (t,) = merge_shard_tables(_replicas(8))
+    assert [(s.agent_name, s.shard_offset) for s in t.shards] == [("dp0", (0, 0)), ("dp0", (4, 0))]
+
+
+def test_dedup_removes_reads_not_only_offers():
+    copy = CopySpec("weight", (), "p", 0, (8, 4), (4, 1), torch.bfloat16)
+    for tables, n_reads in ((_replicas(1), 2), (_replicas(8), 2)):
+        sources = build_sources(merge_shard_tables(tables))
+        table, unsupported, converts = plan_transfer_2d([copy], sources, lambda n: 1 << 20)
+        assert not unsupported and not converts
+        runs = expand_records(table)
+        assert len(runs) == n_reads and sum(r[2] for r in runs) == 8 * 4 * EL
+
+
+def test_distinct_geometry_is_kept_for_every_rank():
+    (t,) = merge_shard_tables(_fan_in(4))
+    assert [s.agent_name for s in t.shards] == ["r0", "r1", "r2", "r3"]
+    # replicated fan-in: every region once, from its first publisher
+    (t,) = merge_shard_tables(_fan_in(4) + _fan_in(4))
+    assert [s.shard_offset for s in t.shards] == [(0, 0), (4, 0), (8, 0), (12, 0)]
+
+
+def test_inconsistent_shape_or_dtype_raises():
+    a = [PublishedTensor("w", "torch.bfloat16", 2, (8, 4), [])]
+    with pytest.raises(ValueError, match="inconsistent"):
+        merge_shard_tables([a, [PublishedTensor("w", "torch.bfloat16", 2, (4, 4), [])]])
+    with pytest.raises(ValueError, match="inconsistent"):
+        merge_shard_tables([a, [PublishedTensor("w", "torch.float16", 2, (8, 4), [])]])
+
+
+def test_names_are_independent_and_addresses_can_be_mapped():
+    tables = [[PublishedTensor("a", "torch.bfloat16", 2, (4, 4), [PublishedShard("r0", 0, 100, (0, 0), (4, 4), "d0")]),
+               PublishedTensor("b", "torch.float32", 4, (2,), [PublishedShard("r0", 0, 200, (0,), (2,))])]]
+    merged = merge_shard_tables(tables)
+    assert [t.name for t in merged] == ["a", "b"]
+    sources = build_sources(merged, map_address=lambda s: (1 << 30) + s.addr)
+    assert sources["a"].shards[0].addr == (1 << 30) + 100 and sources["a"].shards[0].digest == "d0"
+    assert sources["a"].dtype == torch.bfloat16 and sources["b"].dtype == torch.float32
+    assert sources["b"].global_shape == (2,) and sources["b"].elsize == 4
+    assert np.asarray(sources["a"].shards[0].shard_offset).tolist() == [0, 0]
