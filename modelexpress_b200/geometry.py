@@ -21,7 +21,11 @@ module reaches the same facts by a different route:
   tensor that is no parameter (a temporary the loader transforms afterwards)
   makes the source unsupported instead of silently incomplete;
 * all sources go through ONE ``load_weights`` call; a source that fails is
-  dropped and the call resumes behind it.
+  dropped and the call resumes behind it;
+* the dry run is watched: a real op that reads or writes a region some source
+  was already recorded into (a loader that rescales a parameter in place after
+  copying into it, or derives a second tensor from it) ran on bytes that had not
+  landed, so that source is given up too instead of ending up subtly wrong.
 
 The recorded ``ViewCopy`` holds the window as ``(offset, shape, stride)`` in
 elements of the full source tensor.  ``planner.plan_pull_2d`` turns it into
@@ -35,6 +39,7 @@ from dataclasses import dataclass, field
 from typing import Any, Callable, Iterable
 
 import torch
+import torch.utils._python_dispatch
 
 from .planner import UnsupportedReshard
 
@@ -97,6 +102,30 @@ class _Recorder:
             self.by_storage.setdefault(key, []).append((name, int(data.storage_offset()), span))
         self.copies: list = []
         self.unattributed = 0
+        self.written: dict = {}   # storage identity -> [(first element, one past last, source)]
+        self.tainted: dict = {}   # source -> why its recorded copies cannot be trusted
+        self.current = None       # the source most recently handed to the loader
+
+    def touch(self, t: torch.Tensor, what: str) -> None:
+        """A real op reads or writes ``t``: every source already recorded into an
+        overlapping region is tainted, because the op ran on bytes that will only
+        land later (a loader that rescales a parameter after copying into it)."""
+        try:
+            regions = self.written.get(t.untyped_storage()._cdata)
+        except (RuntimeError, NotImplementedError):   # a tensor type without storage
+            return
+        if not regions:
+            return
+        lo = int(t.storage_offset())
+        hi = lo + _extent(t)
+        for first, last, src in regions:
+            if lo < last and first < hi:
+                self.tainted.setdefault(src, f"the loader runs {what} on the destination after the copy")
+                # the source being loaded right now used those bytes: it has to run again
+                # once they are really there
+                if self.current is not None and self.current != src:
+                    self.tainted.setdefault(
+                        self.current, f"its loader runs {what} on bytes that {src!r} provides")
 
     def owner(self, dest: torch.Tensor):
         """(parameter name, offset of ``dest`` relative to it) or None."""
@@ -253,6 +282,9 @@ class TracedSource(torch.Tensor):
             self._fail("written into a tensor that is not a parameter or buffer of the model")
         name, offset = found
         w = self._window
+        lo = int(dest.storage_offset())
+        rec.written.setdefault(dest.untyped_storage()._cdata, []).append(
+            (lo, lo + _extent(dest), self._name))
         rec.copies.append(ViewCopy(
             src_name=self._name, src_offset=int(w.storage_offset()),
             src_shape=tuple(int(s) for s in w.shape), src_stride=tuple(int(s) for s in w.stride()),
@@ -260,6 +292,24 @@ class TracedSource(torch.Tensor):
             dest_shape=tuple(int(s) for s in dest.shape),
             dest_stride=tuple(int(s) for s in dest.stride()), dest_dtype=dest.dtype))
         return dest
+
+
+class _Watch(torch.utils._python_dispatch.TorchDispatchMode):
+    """Sees every real op the loader runs during the dry run.  Ops that only make
+    views are ignored; anything else that touches a region a source was already
+    recorded into taints that source (see ``_Recorder.touch``)."""
+
+    def __init__(self, rec: _Recorder):
+        super().__init__()
+        self.rec = rec
+
+    def __torch_dispatch__(self, func, types, args=(), kwargs=None):
+        kwargs = kwargs or {}
+        if self.rec.written and not getattr(func, "is_view", False):
+            for a in _leaves((args, kwargs)):
+                if not isinstance(a, TracedSource):
+                    self.rec.touch(a, str(func))
+        return func(*args, **kwargs)
 
 
 class _Unsupported(UnsupportedReshard):
@@ -294,7 +344,9 @@ def capture_geometry(model: torch.nn.Module, manifest: Iterable,
 
     def feed(seq):
         for name, dtype, shape in seq:
+            rec.current = name
             yield name, TracedSource.source(name, shape, dtype, device, rec)
+        rec.current = None
 
     def failed(name: str, why: str):
         if name not in result.unsupported_reasons:
@@ -302,10 +354,12 @@ def capture_geometry(model: torch.nn.Module, manifest: Iterable,
         result.unsupported_reasons[name] = why
         rec.copies = [c for c in rec.copies if c.src_name != name]
 
+    watch = _Watch(rec)
     if isolate:
         for item in items:
             try:
-                loader(feed([item]))
+                with watch:
+                    loader(feed([item]))
             except _Unsupported as e:
                 failed(e.src_name, str(e))
     else:
@@ -313,7 +367,8 @@ def capture_geometry(model: torch.nn.Module, manifest: Iterable,
         order = {name: i for i, (name, _d, _s) in enumerate(items)}
         while start < len(items):
             try:
-                loader(feed(items[start:]))
+                with watch:
+                    loader(feed(items[start:]))
                 break
             except _Unsupported as e:
                 at = order.get(e.src_name, start)
@@ -322,6 +377,8 @@ def capture_geometry(model: torch.nn.Module, manifest: Iterable,
                 later = {n for n, _d, _s in items[at + 1:]}
                 rec.copies = [c for c in rec.copies if c.src_name not in later]
                 start = max(at, start) + 1
+    for name, why in rec.tainted.items():
+        failed(name, why)
     result.copies = rec.copies
     result.unattributed = rec.unattributed
     for why, count in summarize_unsupported(result.unsupported_reasons):

@@ -283,6 +283,53 @@ def test_fused_gqa_trainer_storage_as_many_shards_per_source():
         assert torch.equal(model.qkv.data, truth.qkv.data), rank
 
 
+class PostProcessing(torch.nn.Module):
+    """Loaders that keep working on a parameter after copying into it."""
+
+    def __init__(self):
+        super().__init__()
+        self.scaled = torch.nn.Parameter(torch.zeros(8, 8))
+        self.plain = torch.nn.Parameter(torch.zeros(8, 8))
+        self.derived = torch.nn.Parameter(torch.zeros(8))
+        self.padded = torch.nn.Parameter(torch.ones(12, 8))
+
+    def load_weights(self, weights):
+        for name, w in weights:
+            if name == "scaled":
+                self.scaled.data.copy_(w)
+                self.scaled.data.mul_(0.5)                 # in place, after the copy
+            elif name == "plain":
+                self.plain.data.copy_(w)
+            elif name == "derived_from_plain":
+                self.derived.data.copy_(self.plain.data.sum(0))   # reads what "plain" wrote
+            elif name == "padded":
+                self.padded.data[:8].copy_(w)
+                self.padded.data[8:].fill_(0)              # other rows: harmless
+
+
+def test_work_on_a_destination_after_the_copy_gives_the_source_up():
+    manifest = [("scaled", torch.float32, (8, 8)), ("plain", torch.float32, (8, 8)),
+                ("padded", torch.float32, (8, 8)), ("derived_from_plain", torch.float32, (1,))]
+    cap = capture_geometry(PostProcessing(), manifest)
+    assert sorted(cap.unsupported) == ["derived_from_plain", "plain", "scaled"]
+    assert "mul_" in cap.unsupported_reasons["scaled"] and "after the copy" in cap.unsupported_reasons["scaled"]
+    assert "sum" in cap.unsupported_reasons["plain"]
+    assert "'plain' provides" in cap.unsupported_reasons["derived_from_plain"]
+    assert [c.src_name for c in cap.copies] == ["padded"]
+    # end to end: records for what was captured, the loader itself for the rest
+    image, index = _image(manifest[:3], seed=3)
+    truth = PostProcessing()
+    truth.load_weights([(n, _real_tensor(image, index[n], dt)) for n, dt, _s in manifest[:3]]
+                       + [("derived_from_plain", torch.zeros(1))])
+    model = PostProcessing()
+    index["derived_from_plain"] = {"file": "mem", "file_offset": 0, "size": 4, "dtype": "F32", "shape": [1]}
+    cap = _run_records(model, image, index, manifest)
+    # the dependent source is re-run by the loader after the bytes it reads are in place
+    assert sorted(cap.reasons) == ["derived_from_plain", "plain", "scaled"]
+    for (n, a), (_n, b) in zip(model.state_dict().items(), truth.state_dict().items()):
+        assert torch.equal(a, b), n
+
+
 # ---- real vLLM parallel layers, checked against outputs recorded from vLLM itself --------------
 
 def _vllm_mini(rank, tp, dims):
