@@ -12,6 +12,8 @@ Outputs (all small, committed):
   installer.json    MdlLoader TP-narrow / fused-offset / pre-merged arithmetic
   toy_reshard.json  capture_geometry -> plan_transfer -> memmove on the
                     reference's ToyModel (column, row, fused qkv, norm)
+  capture_pin.json  the reference's capture_geometry + resolve_slice on
+                    tests/hooked_model.py (boxes and landing places per copy)
   vllm_layers.npz   (only with --vllm) real vLLM parallel-layer weight_loaders
                     driven on CPU with a patched TP rank
 
@@ -306,6 +308,37 @@ def make_toy_reshard(torch, ref_root):
     return out
 
 
+def make_capture_pin(torch):
+    """The REFERENCE's capture_geometry + resolve_slice on tests/hooked_model.py
+    (a meta twin, as the reference's receiver captures): for every recorded copy
+    the source box, where it lands and the destination strides in source-dim
+    order.  The test runs this repository's capture on the same model and must
+    resolve to the same boxes."""
+    sys.path.insert(0, os.path.dirname(HERE))
+    import hooked_model as H
+    from modelexpress.refit.reshard.geometry import capture_geometry
+    from modelexpress.refit.reshard.slice_plan import resolve_slice
+    from modelexpress.refit.reshard.types import UnsupportedReshard
+
+    with torch.device("meta"):
+        twin = H.HookedModel()
+    man = H.manifest()
+    shapes = {n: s for n, _d, s in man}
+    cap = capture_geometry(twin, man, default_weight_loader=H.default_weight_loader)
+    out = {"unsupported": list(cap.unsupported), "unattributed": cap.unattributed, "copies": []}
+    for c in cap.copies:
+        rec = {"src": c.src_name, "param": c.param_name, "dest_offset": int(c.dest_offset),
+               "dest_shape": list(c.dest_shape)}
+        try:
+            box, dstride = resolve_slice(c, shapes[c.src_name])
+            rec["box"] = [list(b) for b in box]
+            rec["dest_stride_src"] = [int(x) for x in dstride]
+        except UnsupportedReshard as e:
+            rec["unsupported"] = str(e)
+        out["copies"].append(rec)
+    return out
+
+
 def make_vllm_layers(torch, out_path):
     """Drive real vLLM parallel layers' weight_loaders on CPU with the TP rank
     patched, for a tiny Llama-shaped layer set.  Records full inputs' seeds and
@@ -406,6 +439,7 @@ def main():
     dump("slice_plan.json", make_slice_plan(slice_plan, types))
     dump("installer.json", make_installer(torch, MdlLoader))
     dump("toy_reshard.json", make_toy_reshard(torch, args.reference))
+    dump("capture_pin.json", make_capture_pin(torch))
     if args.vllm:
         make_vllm_layers(torch, os.path.join(HERE, "vllm_layers.npz"))
         print("wrote vllm_layers.npz")

@@ -444,3 +444,39 @@ def test_whole_vllm_models_on_cpu_every_tp_rank():
     for arch in ("llama", "qwen2"):
         b = [res[f"{arch}/rank{r}"]["bytes"] for r in range(4)]
         assert b[0] == b[1] == b[2] and b[0] - b[3] == 2 * 24 * 256 * 2
+
+
+def test_capture_resolves_to_the_boxes_the_reference_resolves():
+    """Pinned against the reference itself: ``capture_pin.json`` holds what the
+    reference's capture_geometry + resolve_slice make of tests/hooked_model.py
+    (fused qkv with shard ids, gate/up, a pre-merged tensor split with chunk, row
+    and column parallel, a transposed source, per-expert tensors into a stacked
+    parameter, a padded vocabulary, a default-loader parameter).  This repository's
+    capture of the same model must resolve every copy to the same source box,
+    landing place and destination strides."""
+    import json
+    import sys
+
+    sys.path.insert(0, os.path.dirname(__file__))
+    import hooked_model as H
+    from modelexpress_b200.planner import resolve_slice
+
+    with open(os.path.join(G, "capture_pin.json")) as f:
+        pin = json.load(f)
+    assert pin["unsupported"] == [] and pin["unattributed"] == 0
+    shapes = {n: s for n, _d, s in H.manifest()}
+    for device in ("cpu", "meta"):
+        with torch.device(device):
+            model = H.HookedModel()
+        cap = capture_geometry(model, H.manifest())
+        assert cap.unsupported == [] and cap.unattributed == 0
+        got = []
+        for c in cap.copies:
+            box, dstride = resolve_slice(c, shapes[c.src_name])
+            got.append({"src": c.src_name, "param": c.param_name, "dest_offset": c.dest_offset,
+                        "dest_shape": list(c.dest_shape), "box": [list(b) for b in box],
+                        "dest_stride_src": list(dstride)})
+        want = [c for c in pin["copies"] if "unsupported" not in c]
+        assert len(want) == len(pin["copies"]) == len(got)
+        key = lambda r: (r["src"], r["param"], r["dest_offset"])  # noqa: E731
+        assert sorted(got, key=key) == sorted(want, key=key), device
