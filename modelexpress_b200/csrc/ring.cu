@@ -8,6 +8,8 @@
 // chunk c+1 overlaps the copy of chunk c; the scatter of chunk c overlaps the
 // copy of chunk c+1 (two device staging buffers).  In zero-copy mode the
 // scatter kernel reads the pinned slot directly and the copy engine is idle.
+#include <sys/mman.h>
+
 #include <chrono>
 #include <condition_variable>
 #include <thread>
@@ -122,6 +124,8 @@ struct mxb_ring {
     uint64_t slot_bytes = 0;
     uint32_t slots = 0;
     char *host = nullptr;           // pinned, slots * slot_bytes
+    void *host_map = nullptr;       // the mapping `host` lies in when it was pinned by registration
+    size_t host_map_bytes = 0;
     char *staging[2] = {nullptr, nullptr};  // device
     std::vector<cudaEvent_t> slot_free;     // slot may be overwritten by the host
     cudaEvent_t stage_free[2] = {nullptr, nullptr};
@@ -232,9 +236,41 @@ int32_t mxb_ring_create(mxb_ctx *ctx, int32_t dev, uint64_t ring_bytes, uint32_t
         mxb_ring_destroy(r);
         return rc;
     };
-    if (cudaHostAlloc((void **)&r->host, r->slot_bytes * slots, cudaHostAllocPortable) !=
-        cudaSuccess) {
-        set_error("cudaHostAlloc(%llu) failed", (unsigned long long)(r->slot_bytes * slots));
+    // Pinning sits inside a one-shot load's time to loaded weights.  cudaHostAlloc takes
+    // 0.4-0.5 ms per MiB here; an anonymous mapping advised to use huge pages, touched by
+    // several threads at once and then registered takes about a tenth of that and copies
+    // to the device as fast.  MXB_RING_PIN=alloc selects cudaHostAlloc.
+    const size_t ring_total = (size_t)r->slot_bytes * slots;
+    const char *pin_mode = getenv("MXB_RING_PIN");
+    if (!(pin_mode && !strcmp(pin_mode, "alloc"))) {
+        const size_t huge = size_t(2) << 20;
+        const size_t want = (ring_total + huge - 1) / huge * huge;
+        void *map = mmap(nullptr, want + huge, PROT_READ | PROT_WRITE, MAP_PRIVATE | MAP_ANONYMOUS,
+                         -1, 0);
+        if (map != MAP_FAILED) {
+            char *base = reinterpret_cast<char *>(((uintptr_t)map + huge - 1) / huge * huge);
+            madvise(base, want, MADV_HUGEPAGE);
+            unsigned nt = std::thread::hardware_concurrency();
+            nt = nt < 2 ? 2 : (nt > 16 ? 16 : nt);
+            std::vector<std::thread> touch;
+            for (unsigned t = 0; t < nt; ++t)
+                touch.emplace_back([=]() {
+                    const size_t lo = want / nt * t, hi = (t == nt - 1) ? want : want / nt * (t + 1);
+                    for (size_t o = lo; o < hi; o += 4096) base[o] = 0;
+                });
+            for (auto &th : touch) th.join();
+            if (cudaHostRegister(base, want, cudaHostRegisterPortable) == cudaSuccess) {
+                r->host = base;
+                r->host_map = map;
+                r->host_map_bytes = want + huge;
+            } else {
+                cudaGetLastError();
+                munmap(map, want + huge);
+            }
+        }
+    }
+    if (!r->host && cudaHostAlloc((void **)&r->host, ring_total, cudaHostAllocPortable) != cudaSuccess) {
+        set_error("cudaHostAlloc(%llu) failed", (unsigned long long)ring_total);
         cudaGetLastError();
         return fail(MXB_ERR_NOMEM);
     }
@@ -263,7 +299,12 @@ int32_t mxb_ring_destroy(mxb_ring *r) {
     cudaStreamSynchronize(r->dv->stream);
     cudaStreamSynchronize(r->dv->copy_stream);
     delete r->pool;
-    if (r->host) cudaFreeHost(r->host);
+    if (r->host_map) {
+        cudaHostUnregister(r->host);
+        munmap(r->host_map, r->host_map_bytes);
+    } else if (r->host) {
+        cudaFreeHost(r->host);
+    }
     for (int i = 0; i < 2; ++i) {
         if (r->staging[i]) cudaFree(r->staging[i]);
         if (r->stage_free[i]) cudaEventDestroy(r->stage_free[i]);
