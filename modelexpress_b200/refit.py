@@ -41,7 +41,10 @@ from .planner import (ShardSpec, SourceSpec, apply_converts, convert_staging_byt
 from .runtime import Context, Table, default_context
 
 __all__ = ["PublishedShard", "PublishedTensor", "merge_shard_tables", "build_sources",
-           "ReshardReceiver"]
+           "encode_shard_table", "decode_shard_table", "decode_shard_entries", "publish_local_shards",
+           "ReshardReceiver", "SHARD_TABLE_SCHEMA"]
+
+SHARD_TABLE_SCHEMA = "mx.reshard.shard_table.v1"   # rendezvous.py:52
 
 
 @dataclass
@@ -65,6 +68,70 @@ class PublishedTensor:
     elsize: int
     full_shape: tuple
     shards: list = field(default_factory=list)
+
+
+def encode_shard_table(tensors: list) -> bytes:
+    """The JSON blob a publisher hands to the rendezvous, byte for byte what
+    rendezvous.py:99-133 writes: ``digest`` is left out, not written as null,
+    when a shard has none."""
+    import json
+
+    def shard(s) -> dict:
+        out = {"agent_name": s.agent_name, "device_id": s.device_id, "addr": s.addr,
+               "shard_offset": list(s.shard_offset), "shape": list(s.shape)}
+        if s.digest is not None:
+            out["digest"] = s.digest
+        return out
+
+    payload = {"schema": SHARD_TABLE_SCHEMA,
+               "tensors": [{"name": t.name, "dtype": t.dtype, "elsize": t.elsize,
+                            "full_shape": list(t.full_shape),
+                            "shards": [shard(s) for s in t.shards]} for t in tensors]}
+    return json.dumps(payload).encode("utf-8")
+
+
+def decode_shard_entries(entries: list) -> list:
+    """Parsed shard-table entries -> ``PublishedTensor`` list (rendezvous.py:145-175)."""
+    return [PublishedTensor(t["name"], t["dtype"], int(t["elsize"]), tuple(t["full_shape"]),
+                            [PublishedShard(s["agent_name"], int(s["device_id"]), int(s["addr"]),
+                                            tuple(s["shard_offset"]), tuple(s["shape"]), s.get("digest"))
+                             for s in t["shards"]]) for t in entries]
+
+
+def decode_shard_table(blob: bytes) -> list:
+    """Inverse of ``encode_shard_table``; a blob of another schema raises
+    ``ValueError`` (rendezvous.py:136-142)."""
+    import json
+
+    payload = json.loads(blob.decode("utf-8"))
+    schema = payload.get("schema")
+    if schema != SHARD_TABLE_SCHEMA:
+        raise ValueError(f"unexpected shard-table schema {schema!r} (want {SHARD_TABLE_SCHEMA!r})")
+    return decode_shard_entries(payload["tensors"])
+
+
+def publish_local_shards(shards: dict, agent_name: str, *, digests: bool = True, ctx=None) -> list:
+    """A trainer rank's table: ``shards`` maps a source name to
+    ``(local CUDA tensor, full_shape, shard_offset)``.  All digests of the table
+    come from ONE launch of the digest kernel (the reference digests shard by
+    shard on the publisher, verify.py:186-196, and only when asked to)."""
+    from .digest import digest_many
+    from .runtime import DIGEST_ROWS
+
+    names = list(shards)
+    tensors = [shards[n][0] for n in names]
+    for n, t in zip(names, tensors):
+        if not t.is_cuda or not t.is_contiguous():
+            raise ValueError(f"{n}: a published shard must be a contiguous CUDA tensor")
+    digs = [r["tensor_digest"] for r in digest_many(tensors, DIGEST_ROWS, ctx)] if digests and tensors \
+        else [None] * len(names)
+    out = []
+    for n, t, dg in zip(names, tensors, digs):
+        _t, full_shape, offset = shards[n]
+        out.append(PublishedTensor(n, str(t.dtype), int(t.element_size()), tuple(int(x) for x in full_shape), [
+            PublishedShard(agent_name, int(t.device.index or 0), int(t.data_ptr()),
+                           tuple(int(x) for x in offset), tuple(int(x) for x in t.shape), dg)]))
+    return out
 
 
 def merge_shard_tables(tables: list) -> list:

@@ -14,6 +14,7 @@ Outputs (all small, committed):
                     reference's ToyModel (column, row, fused qkv, norm)
   capture_pin.json  the reference's capture_geometry + resolve_slice on
                     tests/hooked_model.py (boxes and landing places per copy)
+  shard_table.json  the reference's shard-table wire blob for a small table
   vllm_layers.npz   (only with --vllm) real vLLM parallel-layer weight_loaders
                     driven on CPU with a patched TP rank
 
@@ -339,6 +340,25 @@ def make_capture_pin(torch):
     return out
 
 
+def make_shard_table():
+    """The reference's shard-table wire blob for a small table (one shard with a
+    digest, one without, a replicated 1-D tensor)."""
+    from modelexpress.refit.reshard.rendezvous import (PublishedShard, PublishedTensor,
+                                                       decode_shard_table, encode_shard_table)
+
+    table = [
+        PublishedTensor("model.layers.0.self_attn.q_proj.weight", "torch.bfloat16", 2, (4096, 4096), [
+            PublishedShard("trainer-0", 0, 140000000000000, (0, 0), (512, 4096), "00112233445566778899aabbccddeeff"),
+            PublishedShard("trainer-1", 1, 140000004194304, (512, 0), (512, 4096), None)]),
+        PublishedTensor("model.norm.weight", "torch.float32", 4, (4096,), [
+            PublishedShard("trainer-0", 0, 140000008388608, (0,), (4096,), "ffeeddccbbaa99887766554433221100")]),
+    ]
+    blob = encode_shard_table(table)
+    back = decode_shard_table(blob)
+    assert [t.name for t in back] == [t.name for t in table]
+    return {"blob": blob.decode("utf-8")}
+
+
 def make_vllm_layers(torch, out_path):
     """Drive real vLLM parallel layers' weight_loaders on CPU with the TP rank
     patched, for a tiny Llama-shaped layer set.  Records full inputs' seeds and
@@ -440,6 +460,7 @@ def main():
     dump("installer.json", make_installer(torch, MdlLoader))
     dump("toy_reshard.json", make_toy_reshard(torch, args.reference))
     dump("capture_pin.json", make_capture_pin(torch))
+    dump("shard_table.json", make_shard_table())
     if args.vllm:
         make_vllm_layers(torch, os.path.join(HERE, "vllm_layers.npz"))
         print("wrote vllm_layers.npz")

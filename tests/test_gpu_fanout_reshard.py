@@ -241,8 +241,9 @@ def test_reshard_receiver_prepare_once_update_every_step():
     before a byte is written."""
     import torch
 
-    from modelexpress_b200.refit import (PublishedShard, PublishedTensor, ReshardReceiver,
-                                         merge_shard_tables)
+    from modelexpress_b200.refit import (PublishedTensor, ReshardReceiver, decode_shard_table,
+                                         encode_shard_table, merge_shard_tables,
+                                         publish_local_shards)
     from modelexpress_b200.verify import published_digests
 
     if not torch.cuda.is_available():
@@ -281,16 +282,18 @@ def test_reshard_receiver_prepare_once_update_every_step():
                   for _ in range(world)] for n, s in shapes.items()}
 
     def tables():
-        digs = published_digests({(n, t): shards[n][t] for n in shapes for t in range(world)})
-        out = []
+        # each trainer rank publishes its own table (digests from one launch), which
+        # travels as the wire blob and is decoded and merged on the receiving side
+        blobs = []
         for t in range(world):
-            out.append([PublishedTensor(n, "torch.bfloat16", 2, shapes[n], [PublishedShard(
-                f"trainer{t}", 0, shards[n][t].data_ptr(),
-                (t * (shapes[n][0] // world),) + (0,) * (len(shapes[n]) - 1),
-                tuple(shards[n][t].shape), digs[(n, t)])]) for n in shapes])
+            blobs.append(encode_shard_table(publish_local_shards(
+                {n: (shards[n][t], shapes[n],
+                     (t * (shapes[n][0] // world),) + (0,) * (len(shapes[n]) - 1)) for n in shapes},
+                f"trainer{t}")))
+        decoded = [decode_shard_table(b) for b in blobs]
+        assert decoded[1][0].shards[0].digest == published_digests({"x": shards["q"][1]})["x"]
         # a replica of rank 0 publishing the same geometry again must not add reads
-        out.append(out[0])
-        return merge_shard_tables(out)
+        return merge_shard_tables(decoded + [decoded[0]])
 
     def truth(rank):
         m = Engine(rank).cuda()

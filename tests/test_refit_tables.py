@@ -65,3 +65,28 @@ def test_names_are_independent_and_addresses_can_be_mapped():
     assert sources["a"].dtype == torch.bfloat16 and sources["b"].dtype == torch.float32
     assert sources["b"].global_shape == (2,) and sources["b"].elsize == 4
     assert np.asarray(sources["a"].shards[0].shard_offset).tolist() == [0, 0]
+
+
+def test_shard_table_wire_blob_is_the_references():
+    """``shard_table.json`` holds the blob the reference's encode_shard_table wrote
+    for this table; ours must be byte-identical and decode back to the same."""
+    import json
+    import os
+
+    from modelexpress_b200.refit import decode_shard_table, encode_shard_table
+
+    with open(os.path.join(os.path.dirname(__file__), "golden", "shard_table.json")) as f:
+        want = json.load(f)["blob"].encode("utf-8")
+    table = [
+        PublishedTensor("model.layers.0.self_attn.q_proj.weight", "torch.bfloat16", 2, (4096, 4096), [
+            PublishedShard("trainer-0", 0, 140000000000000, (0, 0), (512, 4096), "00112233445566778899aabbccddeeff"),
+            PublishedShard("trainer-1", 1, 140000004194304, (512, 0), (512, 4096), None)]),
+        PublishedTensor("model.norm.weight", "torch.float32", 4, (4096,), [
+            PublishedShard("trainer-0", 0, 140000008388608, (0,), (4096,), "ffeeddccbbaa99887766554433221100")]),
+    ]
+    assert encode_shard_table(table) == want
+    back = decode_shard_table(want)
+    assert back == table and back[0].shards[1].digest is None
+    assert b'"digest": null' not in want
+    with pytest.raises(ValueError, match="schema"):
+        decode_shard_table(want.replace(b"shard_table.v1", b"shard_table.v9"))
