@@ -45,7 +45,8 @@ from .planner import UnsupportedReshard
 
 logger = logging.getLogger("modelexpress_b200.geometry")
 
-__all__ = ["ViewCopy", "CaptureResult", "TracedSource", "capture_geometry", "summarize_unsupported"]
+__all__ = ["ViewCopy", "CaptureResult", "CaptureState", "TracedSource", "capture_geometry",
+           "summarize_unsupported"]
 
 
 @dataclass
@@ -318,9 +319,19 @@ class _Unsupported(UnsupportedReshard):
         self.src_name = src_name
 
 
+class CaptureState:
+    """What several ``capture_geometry`` calls over parts of one checkpoint share:
+    the regions already recorded into, so that a loader in a later part that works
+    on bytes an earlier part provides is still noticed."""
+
+    def __init__(self, model: torch.nn.Module):
+        self.recorder = _Recorder(model)
+        self.reported: set = set()
+
+
 def capture_geometry(model: torch.nn.Module, manifest: Iterable,
                      load_weights: Callable | None = None, device=None,
-                     isolate: bool = False) -> CaptureResult:
+                     isolate: bool = False, state: CaptureState | None = None) -> CaptureResult:
     """Dry-run the model's weight loading and return every recorded copy.
 
     ``manifest`` lists ``(name, dtype, shape)`` for every full source tensor
@@ -333,9 +344,14 @@ def capture_geometry(model: torch.nn.Module, manifest: Iterable,
     loader's ``.to(param.device)`` is the identity.  ``isolate`` feeds one
     source per ``load_weights`` call, as the reference does
     (geometry.py:282-293); by default one call takes them all and is resumed
-    behind a source that fails."""
+    behind a source that fails.  ``state`` carries what earlier calls over other
+    parts of the same checkpoint recorded; a source of an earlier call can then
+    turn up in ``unsupported`` here, when a loader of this part touched its bytes."""
     loader = load_weights if load_weights is not None else model.load_weights
-    rec = _Recorder(model)
+    if state is None:
+        state = CaptureState(model)
+    rec = state.recorder
+    first_copy = len(rec.copies)
     if device is None:
         first = next(iter(model.parameters()), None)
         device = first.device if first is not None else torch.device("cpu")
@@ -378,8 +394,12 @@ def capture_geometry(model: torch.nn.Module, manifest: Iterable,
                 rec.copies = [c for c in rec.copies if c.src_name not in later]
                 start = max(at, start) + 1
     for name, why in rec.tainted.items():
-        failed(name, why)
-    result.copies = rec.copies
+        if name not in state.reported:
+            state.reported.add(name)
+            failed(name, why)
+    mine = {n for n, _d, _s in items}
+    result.copies = [c for c in rec.copies[first_copy:] if c.src_name in mine]
+    rec.copies = rec.copies[:first_copy] + result.copies
     result.unattributed = rec.unattributed
     for why, count in summarize_unsupported(result.unsupported_reasons):
         logger.warning("capture: %d source(s) unsupported: %s", count, why)

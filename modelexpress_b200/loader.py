@@ -217,18 +217,19 @@ def model_destinations(model) -> dict:
 
 
 def captured_table(model, index: dict, file_address: dict, *, load_weights=None, device=None,
-                   alloc_staging=None, dests: dict | None = None) -> CapturedTable:
+                   alloc_staging=None, dests: dict | None = None, state=None) -> CapturedTable:
     """Dry-run ``load_weights`` over the checkpoint's header and compile what it
     copies into scatter records from ``file_address[file] + file_offset`` to the
     model's own tensors.  ``alloc_staging(nbytes) -> address`` provides the
     buffer dtype-changing copies are staged in; without it such copies are left
-    to the engine's loader."""
+    to the engine's loader.  ``state`` (``geometry.CaptureState``) is shared by the
+    calls that compile one checkpoint part by part."""
     from .geometry import capture_geometry
     from .planner import ShardSpec, SourceSpec, convert_staging_bytes, plan_transfer_2d
 
     loader = load_weights if load_weights is not None else model.load_weights
     manifest = [(n, torch_dtype(i["dtype"]), tuple(i["shape"])) for n, i in index.items()]
-    cap = capture_geometry(model, manifest, loader, device=device)
+    cap = capture_geometry(model, manifest, loader, device=device, state=state)
     if dests is None:
         dests = model_destinations(model)
     sources = {}
@@ -306,6 +307,9 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
             step *= 2
         if not pipeline or on_unsupported != "engine":
             cuts = [0, len(names)]       # one batch: nothing is written before all is planned
+        from .geometry import CaptureState
+
+        state = CaptureState(model)
         parts, pending, stagings = [], [], []
         timings = {"capture": 0.0, "ring_create": 0.0, "place_wait": 0.0, "engine": 0.0}
         t0 = time.perf_counter()
@@ -331,7 +335,7 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
             tc = time.perf_counter()
             cap = captured_table(model, {n: index[n] for n in names[lo:hi]}, addresses,
                                  load_weights=loader, device=dev, alloc_staging=alloc_staging,
-                                 dests=dests)
+                                 dests=dests, state=state)
             timings["capture"] += time.perf_counter() - tc
             parts.append(cap)
             if cap.reasons and on_unsupported != "engine":

@@ -330,6 +330,24 @@ def test_work_on_a_destination_after_the_copy_gives_the_source_up():
         assert torch.equal(a, b), n
 
 
+def test_parts_of_one_checkpoint_share_what_was_recorded():
+    """A checkpoint compiled part by part (as the pipelined load does): the loader of
+    a later part that reads bytes an earlier part provides is still noticed, and
+    the earlier source is reported by the later call."""
+    from modelexpress_b200.geometry import CaptureState
+
+    model = PostProcessing()
+    state = CaptureState(model)
+    first = capture_geometry(model, [("plain", torch.float32, (8, 8)), ("padded", torch.float32, (8, 8))],
+                             state=state)
+    assert first.unsupported == [] and [c.src_name for c in first.copies] == ["plain", "padded"]
+    second = capture_geometry(model, [("derived_from_plain", torch.float32, (1,))], state=state)
+    assert sorted(second.unsupported) == ["derived_from_plain", "plain"] and second.copies == []
+    # without the shared state the second call cannot know
+    alone = capture_geometry(PostProcessing(), [("derived_from_plain", torch.float32, (1,))])
+    assert alone.unsupported == []
+
+
 # ---- real vLLM parallel layers, checked against outputs recorded from vLLM itself --------------
 
 def _vllm_mini(rank, tp, dims):
