@@ -217,13 +217,17 @@ def model_destinations(model) -> dict:
 
 
 def captured_table(model, index: dict, file_address: dict, *, load_weights=None, device=None,
-                   alloc_staging=None, dests: dict | None = None, state=None) -> CapturedTable:
+                   alloc_staging=None, dests: dict | None = None, state=None,
+                   min_row_bytes: int = 16) -> CapturedTable:
     """Dry-run ``load_weights`` over the checkpoint's header and compile what it
     copies into scatter records from ``file_address[file] + file_offset`` to the
     model's own tensors.  ``alloc_staging(nbytes) -> address`` provides the
     buffer dtype-changing copies are staged in; without it such copies are left
     to the engine's loader.  ``state`` (``geometry.CaptureState``) is shared by the
-    calls that compile one checkpoint part by part."""
+    calls that compile one checkpoint part by part.  A copy that transposes its
+    source element by element (GPT-2's Conv1D weights) is a correct but wasteful
+    record list of rows narrower than ``min_row_bytes``; such sources are left to
+    the engine's loader (0 keeps them)."""
     from .geometry import capture_geometry
     from .planner import ShardSpec, SourceSpec, convert_staging_bytes, plan_transfer_2d
 
@@ -247,6 +251,22 @@ def captured_table(model, index: dict, file_address: dict, *, load_weights=None,
     for n in not_planned:
         reasons.setdefault(n, "the copied window is not a box of the source tensor, or changes dtype")
     dropped = set(not_planned)
+    if min_row_bytes and len(table):
+        # rows narrower than this, many of them: an element-wise transpose
+        narrow = (table[:, 3] < np.uint64(min_row_bytes)) & (table[:, 2] > np.uint64(64))
+        if narrow.any():
+            transposed = set()
+            for c in cap.copies:
+                if c.src_name in dropped or len(c.src_stride) < 2 or c.src_stride[-1] == 1:
+                    continue
+                transposed.add(c.src_name)
+            if transposed:
+                keep = [c for c in cap.copies if c.src_name not in transposed and c.src_name not in dropped]
+                table, _np2, converts = plan_transfer_2d(keep, sources, lambda n: dests[n].data_ptr(),
+                                                         convert_base)
+                for n in transposed:
+                    reasons.setdefault(n, "the copy transposes the source element by element")
+                dropped |= transposed
     planned = [c for c in cap.copies if c.src_name not in dropped]
     return CapturedTable(table, converts, staging_bytes, reasons, len(planned),
                          {c.param_name for c in planned})

@@ -437,8 +437,9 @@ def test_capture_of_real_vllm_layers_matches_recorded_vllm_outputs():
 
 
 def test_whole_vllm_models_on_cpu_every_tp_rank():
-    """Real vLLM ``LlamaForCausalLM`` and ``Qwen2ForCausalLM`` (q/k/v biases) built on
-    the CPU, tensor-parallel size 4, every rank: records compiled from the dry run
+    """Real vLLM ``LlamaForCausalLM``, ``Qwen2ForCausalLM`` (q/k/v biases),
+    ``Phi3ForCausalLM`` (projections fused on disk) and ``GPT2LMHeadModel`` (transposed
+    Conv1D weights, tied embeddings) built on the CPU, tensor-parallel size 4, every rank: records compiled from the dry run
     of the model's own ``load_weights`` reproduce what ``load_weights`` produces,
     bit for bit, with nothing left to the engine.  Runs in a child process (vLLM's
     parallel state is global)."""
@@ -453,10 +454,25 @@ def test_whole_vllm_models_on_cpu_every_tp_rank():
     if run.returncode != 0 or not lines:
         pytest.skip("vLLM could not build a model on the CPU here: " + run.stderr.strip()[-400:])
     res = json.loads(lines[-1][len("RESULT "):])
-    assert sorted(res) == [f"{a}/rank{r}" for a in ("llama", "qwen2") for r in range(4)]
-    for key, r in res.items():
-        assert r["mismatch"] == [] and r["engine"] == [], (key, r)
-        assert r["copies"] == r["records"] == (27 if key.startswith("qwen2") else 21), (key, r)
+    archs = ("llama", "qwen2", "phi3", "gpt2")
+    built = [a for a in archs if a not in res]          # an arch that could not be built is listed bare
+    assert {"llama", "qwen2"} <= set(built), res
+    for a in built:
+        for r in range(4):
+            got = res[f"{a}/rank{r}"]
+            assert got["mismatch"] == [] and got["engine"] == [], (a, r, got)
+    for a, copies in (("llama", 21), ("qwen2", 27), ("phi3", 21)):   # phi3: q/k/v and gate/up fused on disk
+        if a in built:
+            assert all(res[f"{a}/rank{r}"]["copies"] == res[f"{a}/rank{r}"]["records"] == copies
+                       and res[f"{a}/rank{r}"]["left_to_engine_by_default"] == [] for r in range(4)), a
+    if "gpt2" in built:
+        # Conv1D weights are transposed by the loader: exact as records (two-byte rows), but by
+        # default those eight tensors go to the engine's loader instead
+        g = res["gpt2/rank0"]
+        assert g["smallest_row"] == 2 and g["records"] > 1000
+        assert len(g["left_to_engine_by_default"]) == 8
+        assert all(n.endswith(("c_attn.weight", "c_proj.weight", "c_fc.weight"))
+                   for n in g["left_to_engine_by_default"])
     # vocabulary 1000 pads to 1024: the last rank's embed and lm_head shards hold 24 real rows
     # fewer (x 256 columns x 2 bytes x 2 tensors) than the other ranks'
     for arch in ("llama", "qwen2"):
