@@ -277,7 +277,7 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
                    host_threads: int | None = None, mode: int = PLACE_COPY_ENGINE,
                    ring_bytes: int = RING_BYTES, ring_slots: int = RING_SLOTS,
                    on_unsupported: str = "engine", pipeline: bool = True,
-                   first_batch: int = 32) -> CapturedPlacement:
+                   first_batch: int = 32, min_row_bytes: int = 16) -> CapturedPlacement:
     """Load a safetensors checkpoint into ``model`` for ANY architecture whose
     engine-side ``load_weights`` only slices and copies.
 
@@ -355,7 +355,7 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
             tc = time.perf_counter()
             cap = captured_table(model, {n: index[n] for n in names[lo:hi]}, addresses,
                                  load_weights=loader, device=dev, alloc_staging=alloc_staging,
-                                 dests=dests, state=state)
+                                 dests=dests, state=state, min_row_bytes=min_row_bytes)
             timings["capture"] += time.perf_counter() - tc
             parts.append(cap)
             if cap.reasons and on_unsupported != "engine":

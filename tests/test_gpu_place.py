@@ -395,8 +395,9 @@ def test_place_captured_converts_batches_and_engine_leftovers(tmp_path):
         truth.load_weights((n, torch.from_numpy(a.copy()).view(
             torch.bfloat16 if a.dtype == np.uint16 else torch.float32)) for n, a in full.items())
         model = Engine(rank).cuda()
+        # min_row_bytes=0: the transposed expert stack stays in the records (two-byte rows)
         got = place_captured(model, d, "cuda:0", first_batch=1, ring_bytes=8 << 20, ring_slots=4,
-                             host_threads=2)
+                             host_threads=2, min_row_bytes=0)
         assert got.engine_loaded == ["scale"] and "item" in got.reasons["scale"]
         assert got.converted == ["router"]
         assert got.written_params == {"qkv", "down", "experts", "router", "embed"}
@@ -404,6 +405,13 @@ def test_place_captured_converts_batches_and_engine_leftovers(tmp_path):
         torch.cuda.synchronize()
         for (n, a), (_n, b) in zip(model.state_dict().items(), truth.state_dict().items()):
             assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), (rank, n)
+    # by default an element-wise transpose is left to the engine's loader; same result
+    model = Engine(1).cuda()
+    got = place_captured(model, d, "cuda:0", ring_bytes=8 << 20, ring_slots=4, host_threads=2)
+    assert got.engine_loaded == ["scale", "experts"] and "transposes" in got.reasons["experts"]
+    torch.cuda.synchronize()
+    for (n, a), (_n, b) in zip(model.state_dict().items(), truth.state_dict().items()):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), n
     # a caller that wants every byte through the kernel is told before anything is written
     model = Engine(0).cuda()
     with pytest.raises(StrategyFailed) as e:
