@@ -12,7 +12,7 @@ rank r places TP rank r (weak scaling, no data-path collective).
   value  GB/s placed with the checkpoint image already resident in HBM: the
          scatter kernel alone, one persistent launch per step.
   e2e    the same bytes through the public API from HOST memory: mmap'ed
-         checkpoint files -> pinned 2 GiB ring (host gather threads) -> PCIe
+         checkpoint files -> pinned 128 MiB ring (host gather threads) -> PCIe
          (copy engine) -> scatter kernel -> shards, status read back per step.
 
 Rank 0 prints one JSON line.  ``--impl reference`` times the reference's
