@@ -153,10 +153,7 @@ def place_checkpoint(model_path: str, tp_rank: int, tp_size: int, device=None, *
         threads = host_threads or max(2, min(32, (os.cpu_count() or 8) * 3 // 4))
         stats = ring.place(items, threads, mode)
     finally:
-        for im in images.values():
-            im.close()
-        if own_ring:
-            _release(ring)
+        _release(ctx, images.values(), ring if own_ring else None)
     return PlacedCheckpoint(params, plan, stats)
 
 
@@ -174,11 +171,26 @@ class CapturedPlacement:
     timings: dict = field(default_factory=dict)   # seconds: capture, ring_create, place_wait, engine
 
 
-def _release(ring: Ring) -> None:
-    """Free a one-shot ring off the caller's path: unpinning host memory takes
-    tens of milliseconds and now and then most of a second, none of which the
-    loaded weights have to wait for."""
-    ring.ctx.release_later(ring)
+class _Leftovers:
+    def __init__(self, images, ring):
+        self.images, self.ring = list(images), ring
+
+    def close(self) -> None:
+        for im in self.images:
+            try:
+                im.close()
+            except BufferError:   # a tensor over the mapping is still alive: the GC unmaps it
+                pass
+        if self.ring is not None:
+            self.ring.close()
+
+
+def _release(ctx: Context, images, ring: Ring | None) -> None:
+    """What a load leaves behind is torn down off the caller's path: unmapping the
+    checkpoint files (tens of milliseconds of page-table work for a fresh mapping of
+    a tmpfs file) and unpinning a one-shot ring (tens of milliseconds, now and then
+    most of a second); the loaded weights wait for neither."""
+    ctx.release_later(_Leftovers(images, ring))
 
 
 def _engine_tensor(image: FileImage, info: dict):
@@ -390,10 +402,7 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
         torch.cuda.current_stream(dev).synchronize()
     finally:
         pool.shutdown(wait=True)
-        for im in images.values():
-            im.close()
-        if own_ring and made:
-            _release(made[0])
+        _release(ctx, images.values(), made[0] if own_ring and made else None)
     stats = PlaceResult(sum(r.bytes_placed for r in results), sum(r.chunks for r in results),
                         sum(r.launches for r in results), seconds,
                         sum(r.seconds_gather for r in results), sum(r.seconds_device for r in results))
