@@ -118,3 +118,108 @@ def test_bench_rank_mapping_and_reference_arm_ranks():
         assert bench.bench_reference(A()) is None  # rank != 0: no work, no output
     finally:
         os.environ.pop("RANK")
+
+
+REFIT_WORKER = textwrap.dedent('''
+    import os, sys, mmap
+    import numpy as np
+    import torch, torch.distributed as dist
+    sys.path.insert(0, ROOT); sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import hooked_model as H
+    from helpers import run_records_on_host
+    from modelexpress_b200.geometry import capture_geometry
+    from modelexpress_b200.planner import plan_transfer_2d
+    from modelexpress_b200.refit import (PublishedShard, PublishedTensor, build_sources,
+                                         decode_shard_table, encode_shard_table, merge_shard_tables)
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("gloo")
+    work = os.environ["MXB_TEST_DIR"]
+    H.TP, H.RANK = world, rank          # this process is inference TP rank `rank` ...
+    man = H.manifest()
+    g = torch.Generator().manual_seed(11)
+    full = {n: torch.randn(s, generator=g) for n, _d, s in man}   # same in every process
+
+    # ... and trainer rank `rank`: it owns row block `rank` of every tensor, laid out
+    # back to back in a file the other processes map (the stand-in for a CUDA IPC mapping)
+    def block(t, r):
+        rows = t.shape[0]
+        lo, hi = r * rows // world, (r + 1) * rows // world
+        return lo, t[lo:hi].contiguous()
+
+    total = sum(block(t, rank)[1].numel() * 4 for t in full.values())
+    path = os.path.join(work, f"trainer{rank}")
+    with open(path, "wb") as f:
+        f.truncate(total)
+    fh = open(path, "r+b")
+    mine = np.frombuffer(mmap.mmap(fh.fileno(), total), dtype=np.uint8)
+    table, at = [], 0
+    for n, t in full.items():
+        lo, piece = block(t, rank)
+        raw = piece.numpy().view(np.uint8).reshape(-1)
+        mine[at: at + raw.size] = raw
+        table.append(PublishedTensor(n, "torch.float32", 4, tuple(t.shape), [PublishedShard(
+            f"trainer{rank}", 0, mine.ctypes.data + at, (lo,) + (0,) * (t.dim() - 1), tuple(piece.shape))]))
+        at += raw.size
+    dist.barrier()                       # every trainer file is written
+
+    # rendezvous: wire blobs and each publisher's base address (an IPC handle + offset in real life)
+    blobs, bases = [None] * world, [None] * world
+    dist.all_gather_object(blobs, encode_shard_table(table))
+    dist.all_gather_object(bases, (total, mine.ctypes.data))
+    local = {}
+    for r, (nbytes, _addr) in enumerate(bases):
+        if r == rank:
+            local[f"trainer{r}"] = mine.ctypes.data
+        else:
+            f2 = open(os.path.join(work, f"trainer{r}"), "r+b")
+            m = np.frombuffer(mmap.mmap(f2.fileno(), nbytes), dtype=np.uint8)
+            local[f"trainer{r}"] = (m, m.ctypes.data)
+    def map_address(s):
+        r = int(s.agent_name[len("trainer"):])
+        here = local[s.agent_name]
+        here = here if isinstance(here, int) else here[1]
+        return here + (s.addr - bases[r][1])
+    merged = merge_shard_tables([decode_shard_table(b) for b in blobs])
+    assert all(len(t.shards) == world for t in merged)
+    sources = build_sources(merged, map_address)
+
+    model = H.HookedModel()
+    cap = capture_geometry(model, man)
+    assert cap.unsupported == []
+    params = dict(model.named_parameters())
+    recs, unsupported, converts = plan_transfer_2d(cap.copies, sources, lambda n: params[n].data_ptr())
+    assert not unsupported and not converts
+    run_records_on_host(recs)            # reads local and peer trainer memory
+    truth = H.HookedModel()
+    truth.load_weights(full.items())
+    for (n, a), (_n, b) in zip(model.state_dict().items(), truth.state_dict().items()):
+        assert torch.equal(a, b), (rank, n)
+    # bytes read from the peer: everything this rank needs that the other trainer owns
+    peer = sum(int(r[2]) * int(r[3]) for r in recs.tolist()
+               if not (mine.ctypes.data <= int(r[0]) < mine.ctypes.data + total))
+    tot = torch.tensor([peer], dtype=torch.int64)
+    dist.all_reduce(tot)
+    assert int(tot.item()) > 0
+    dist.barrier()
+    dist.destroy_process_group()
+    print("rank", rank, "ok")
+''')
+
+
+@pytest.mark.parametrize("world", [2])
+def test_refit_cycle_two_ranks_gloo(tmp_path, world):
+    """Two processes, each a trainer rank and an inference TP rank: shard tables
+    travel as wire blobs over gloo, are merged, mapped to local addresses and
+    planned from the captured loader; the CPU scatter then assembles every
+    parameter from local and peer trainer memory."""
+    script = tmp_path / "refit_worker.py"
+    script.write_text(f"ROOT = {ROOT!r}\n" + REFIT_WORKER)
+    env = dict(os.environ, MXB_TEST_DIR=str(tmp_path), MASTER_ADDR="127.0.0.1")
+    port = 29300 + (os.getpid() % 250)
+    proc = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+         "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
+        env=env, capture_output=True, text=True, timeout=240)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert proc.stdout.count("ok") == world
