@@ -514,3 +514,118 @@ def test_capture_resolves_to_the_boxes_the_reference_resolves():
         assert len(want) == len(pin["copies"]) == len(got)
         key = lambda r: (r["src"], r["param"], r["dest_offset"])  # noqa: E731
         assert sorted(got, key=key) == sorted(want, key=key), device
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_view_chains_move_what_torch_moves(seed):
+    """Fuzz: a random chain of view ops (narrow, slicing, transpose, permute, select,
+    unsqueeze/squeeze, chunk, unbind, t) applied to a placeholder and to a real
+    tensor, copied into a random strided window of a destination.  Whenever the
+    planner accepts the copy, the records executed by the CPU scatter must equal
+    torch's own ``copy_``; when it refuses, it must refuse before moving anything."""
+    from modelexpress_b200.planner import ShardSpec, SourceSpec, plan_transfer_2d
+
+    rng = np.random.default_rng(1000 + seed)
+    accepted = 0
+    for _case in range(40):
+        nd = int(rng.integers(1, 4))
+        shape = tuple(int(rng.integers(1, 7)) for _ in range(nd))
+        real = torch.arange(int(np.prod(shape)), dtype=torch.float32).reshape(shape) + 1
+
+        def chain(t):
+            ops = []
+            for _ in range(int(rng.integers(0, 4))):
+                kind = rng.choice(["narrow", "slice", "transpose", "permute", "select", "unsqueeze",
+                                   "squeeze", "chunk", "unbind", "t"])
+                d = int(rng.integers(0, max(1, t.dim()))) if t.dim() else 0
+                if kind == "narrow" and t.dim():
+                    lo = int(rng.integers(0, t.shape[d]))
+                    ops.append(("narrow", (d, lo, int(rng.integers(1, t.shape[d] - lo + 1)))))
+                elif kind == "slice" and t.dim():
+                    lo = int(rng.integers(0, t.shape[0]))
+                    ops.append(("getitem", (slice(lo, int(rng.integers(lo + 1, t.shape[0] + 1))),)))
+                elif kind == "transpose" and t.dim() >= 2:
+                    ops.append(("transpose", (d, int(rng.integers(0, t.dim())))))
+                elif kind == "permute" and t.dim() >= 2:
+                    ops.append(("permute", (tuple(int(x) for x in rng.permutation(t.dim())),)))
+                elif kind == "select" and t.dim() >= 2:
+                    ops.append(("select", (d, int(rng.integers(0, t.shape[d])))))
+                elif kind == "unsqueeze":
+                    ops.append(("unsqueeze", (int(rng.integers(0, t.dim() + 1)),)))
+                elif kind == "squeeze":
+                    ops.append(("squeeze", ()))
+                elif kind == "chunk" and t.dim() and t.shape[d] >= 2:
+                    ops.append(("chunk", (2, d, int(rng.integers(0, 2)))))
+                elif kind == "unbind" and t.dim() >= 2:
+                    ops.append(("unbind", (d, int(rng.integers(0, t.shape[d])))))
+                elif kind == "t" and t.dim() == 2:
+                    ops.append(("t", ()))
+                else:
+                    continue
+                t = apply(t, ops[-1])
+            return ops
+
+        def apply(t, op):
+            name, args = op
+            if name == "getitem":
+                return t[args[0]]
+            if name == "chunk":
+                return t.chunk(args[0], dim=args[1])[args[2]]
+            if name == "unbind":
+                return t.unbind(args[0])[args[1]]
+            return getattr(t, name)(*args)
+
+        ops = chain(real)
+        view = real
+        for op in ops:
+            view = apply(view, op)
+        if view.numel() == 0:
+            continue
+        # destination: a parameter with room for a strided window of the view's shape
+        pad = int(rng.integers(0, 3))
+        dest_full = torch.zeros(tuple(s + pad for s in view.shape) if view.dim() else (1 + pad,))
+
+        class One(torch.nn.Module):
+            def __init__(self):
+                super().__init__()
+                self.p = torch.nn.Parameter(dest_full.clone())
+
+            def window(self):
+                w = self.p.data
+                if view.dim() == 0:
+                    return w[pad]
+                for dim, n in enumerate(view.shape):
+                    w = w.narrow(dim, pad, n)
+                return w
+
+            def load_weights(self, weights):
+                for _name, w in weights:
+                    for op in ops:
+                        w = apply(w, op)
+                    self.window().copy_(w)
+
+        truth = One()
+        truth.load_weights([("w", real)])
+        model = One()
+        cap = capture_geometry(model, [("w", torch.float32, shape)])
+        assert cap.unsupported == [] and len(cap.copies) == 1
+        # the source is published whole, or cut into two or three shards along a random dim
+        keep, shards = [], []
+        cut_dim = int(rng.integers(0, nd))
+        pieces = int(rng.integers(1, 4))
+        edges = sorted({0, shape[cut_dim], *[int(x) for x in rng.integers(0, shape[cut_dim] + 1, pieces - 1)]})
+        for lo, hi in zip(edges[:-1], edges[1:]):
+            part = real.narrow(cut_dim, lo, hi - lo).contiguous()
+            keep.append(part)
+            off = [0] * nd
+            off[cut_dim] = lo
+            shards.append(ShardSpec(tuple(off), tuple(part.shape), f"s{lo}", part.data_ptr(), 4))
+        sources = {"w": SourceSpec(shape, torch.float32, 4, shards)}
+        table, unsupported, _cv = plan_transfer_2d(cap.copies, sources, lambda n: model.p.data_ptr())
+        if unsupported:
+            assert len(table) == 0 and float(model.p.detach().abs().sum()) == 0.0
+            continue
+        accepted += 1
+        c_port.scatter2d(table)
+        assert torch.equal(model.p.detach(), truth.p.detach()), (shape, ops)
+    assert accepted >= 20
