@@ -461,6 +461,8 @@ def test_whole_vllm_models_on_cpu_every_tp_rank():
         for r in range(4):
             got = res[f"{a}/rank{r}"]
             assert got["mismatch"] == [] and got["engine"] == [], (a, r, got)
+        # a twin of the model on `meta` (what a refit receiver captures on) records the same copies
+        assert res[f"{a}/rank0"]["meta_twin_same"] is True, a
     for a, copies in (("llama", 21), ("qwen2", 27), ("phi3", 21)):   # phi3: q/k/v and gate/up fused on disk
         if a in built:
             assert all(res[f"{a}/rank{r}"]["copies"] == res[f"{a}/rank{r}"]["records"] == copies

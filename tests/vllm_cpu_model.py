@@ -151,6 +151,22 @@ def run_arch(arch, cfg_json, make_tensors, out):
                                      min_row_bytes=0)
                 policy = captured_table(model, index, {path: image.address}, device=torch.device("cpu"))
                 c_port.scatter2d(cap.records)
+                twin_same = None
+                if rank == 0:
+                    # the refit receiver captures on a throw-away twin on `meta`
+                    # (engines/vllm/refit/receiver.py:61-119): same copies as on the live model
+                    from modelexpress_b200.geometry import capture_geometry
+                    from modelexpress_b200.loader import torch_dtype
+
+                    vc2 = VllmConfig(model_config=mc, device_config=DeviceConfig(device="cpu"),
+                                     load_config=LoadConfig(load_format="dummy"))
+                    with set_current_vllm_config(vc2):
+                        with set_default_torch_dtype(torch.bfloat16), torch.device("meta"):
+                            twin = initialize_model(vllm_config=vc2)
+                    man = [(n, torch_dtype(i["dtype"]), tuple(i["shape"])) for n, i in index.items()]
+                    live, meta = capture_geometry(model, man), capture_geometry(twin, man)
+                    twin_same = (live.copies == meta.copies and live.unsupported == meta.unsupported
+                                 and all(p.device.type == "meta" for p in twin.parameters()))
                 if cap.reasons:  # what the loader computes on goes through the loader itself
                     model.load_weights((n, w) for n, w in weights if n in cap.reasons)
             finally:
@@ -164,7 +180,7 @@ def run_arch(arch, cfg_json, make_tensors, out):
             "records": int(len(recs)), "engine": sorted(cap.reasons), "mismatch": bad,
             "bytes": int(sum(int(r[2]) * int(r[3]) for r in recs)),
             "smallest_row": int(min((int(r[3]) for r in recs), default=0)),
-            "left_to_engine_by_default": sorted(policy.reasons)}
+            "left_to_engine_by_default": sorted(policy.reasons), "meta_twin_same": twin_same}
     image.close()
 
 
