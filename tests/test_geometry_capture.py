@@ -631,3 +631,45 @@ def test_random_view_chains_move_what_torch_moves(seed):
         c_port.scatter2d(table)
         assert torch.equal(model.p.detach(), truth.p.detach()), (shape, ops)
     assert accepted >= 20
+
+
+def test_tied_and_arena_backed_parameters():
+    """Destinations are found by storage: a parameter registered under two names (tied
+    embeddings) and parameters that are views into one flat arena (storage offset
+    not zero) both resolve to offsets relative to the parameter itself."""
+    class Tied(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            arena = torch.zeros(4 * 8 + 6 * 8 + 5)
+            self.embed = torch.nn.Parameter(torch.zeros(4, 8))
+            self.head = self.embed                                  # tied
+            self.a = torch.nn.Parameter(torch.zeros(1))
+            self.b = torch.nn.Parameter(torch.zeros(1))
+            self.a.data = arena[5:5 + 32].view(4, 8)                # views into the arena
+            self.b.data = arena[5 + 32:5 + 32 + 48].view(6, 8)
+
+        def load_weights(self, weights):
+            for name, w in weights:
+                if name == "head":
+                    self.head.data.copy_(w)
+                elif name == "a":
+                    self.a.data.copy_(w)
+                elif name == "b_rows":
+                    self.b.data[2:5].copy_(w.narrow(0, 1, 3))
+
+    manifest = [("head", torch.float32, (4, 8)), ("a", torch.float32, (4, 8)),
+                ("b_rows", torch.float32, (6, 8))]
+    model = Tied()
+    cap = capture_geometry(model, manifest)
+    by = {c.src_name: c for c in cap.copies}
+    assert cap.unsupported == [] and by["head"].param_name in ("embed", "head")
+    assert (by["a"].param_name, by["a"].dest_offset) == ("a", 0)
+    assert (by["b_rows"].param_name, by["b_rows"].dest_offset, by["b_rows"].src_offset) == ("b", 16, 8)
+    image, index = _image(manifest, seed=9)
+    truth = Tied()
+    truth.load_weights((n, _real_tensor(image, index[n], dt)) for n, dt, _s in manifest)
+    cap = _run_records(model, image, index, manifest)
+    assert not cap.reasons
+    for name in ("embed", "a", "b"):
+        assert torch.equal(getattr(model, name).data, getattr(truth, name).data), name
+    assert model.head is model.embed
