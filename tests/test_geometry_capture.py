@@ -673,3 +673,41 @@ def test_tied_and_arena_backed_parameters():
     for name in ("embed", "a", "b"):
         assert torch.equal(getattr(model, name).data, getattr(truth, name).data), name
     assert model.head is model.embed
+
+
+def test_scalars_empty_tensors_and_integer_indices():
+    """Edge shapes: a 0-d source, a 0-d source viewed as (1,), an empty tensor (no
+    record at all) and an integer index that drops a dimension."""
+    from modelexpress_b200.planner import ShardSpec, SourceSpec, plan_transfer_2d
+
+    class Edge(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.s0 = torch.nn.Parameter(torch.zeros(()))
+            self.s1 = torch.nn.Parameter(torch.zeros(1))
+            self.e = torch.nn.Parameter(torch.zeros(0, 4))
+            self.v = torch.nn.Parameter(torch.zeros(3))
+
+        def load_weights(self, weights):
+            for n, w in weights:
+                if n == "s0":
+                    self.s0.data.copy_(w)
+                elif n == "s1":
+                    self.s1.data.copy_(w.view(self.s1.shape))
+                elif n == "e":
+                    self.e.data.copy_(w)
+                elif n == "v":
+                    self.v.data.copy_(w[2])
+
+    full = {"s0": torch.tensor(3.5), "s1": torch.tensor(7.25), "e": torch.zeros(0, 4),
+            "v": torch.arange(15.0).reshape(5, 3)}
+    model = Edge()
+    cap = capture_geometry(model, [(n, torch.float32, tuple(t.shape)) for n, t in full.items()])
+    assert cap.unsupported == [] and len(cap.copies) == 4
+    sources = {n: SourceSpec(tuple(t.shape), torch.float32, 4, [
+        ShardSpec((0,) * t.dim(), tuple(t.shape), "s", t.data_ptr(), 4)]) for n, t in full.items()}
+    dests = dict(model.named_parameters())
+    table, unsupported, converts = plan_transfer_2d(cap.copies, sources, lambda n: dests[n].data_ptr())
+    assert not unsupported and not converts and len(table) == 3     # nothing to move for "e"
+    c_port.scatter2d(table)
+    assert float(model.s0) == 3.5 and model.s1.tolist() == [7.25] and model.v.tolist() == [6.0, 7.0, 8.0]
