@@ -710,4 +710,4 @@ def test_scalars_empty_tensors_and_integer_indices():
     table, unsupported, converts = plan_transfer_2d(cap.copies, sources, lambda n: dests[n].data_ptr())
     assert not unsupported and not converts and len(table) == 3     # nothing to move for "e"
     c_port.scatter2d(table)
-    assert float(model.s0) == 3.5 and model.s1.tolist() == [7.25] and model.v.tolist() == [6.0, 7.0, 8.0]
+    assert float(model.s0.detach()) == 3.5 and model.s1.tolist() == [7.25] and model.v.tolist() == [6.0, 7.0, 8.0]
