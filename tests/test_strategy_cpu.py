@@ -1,0 +1,58 @@
+"""Load-strategy contract without a GPU: the misses that must be reported as
+``StrategyFailed(mutated=False)`` before anything is touched
+(load_strategy/base.py:37-76, adapter.py:24-34), and that there is no CPU fallback."""
+
+import pytest
+import torch
+
+from modelexpress_b200.loader import (B200CapturedStrategy, B200ScatterStrategy, LoadResult,
+                                      StrategyFailed, place_captured, place_checkpoint)
+
+
+class _Cfg:
+    def __init__(self, model):
+        self.model = model
+
+
+class _Ctx:
+    def __init__(self, model_dir, adapter=object()):
+        self.model_config, self.device_id, self.adapter = _Cfg(model_dir), 0, adapter
+
+
+class _WithLoader(torch.nn.Module):
+    def load_weights(self, weights):
+        return set()
+
+
+@pytest.mark.parametrize("strategy", [B200CapturedStrategy, B200ScatterStrategy])
+def test_missing_checkpoint_directory_is_an_expected_miss(strategy, tmp_path):
+    s = strategy()
+    assert s.requires == () and s.name in ("b200_captured", "b200_scatter")
+    for bad in (None, "", str(tmp_path / "nowhere")):
+        with pytest.raises(StrategyFailed) as e:
+            s.load(LoadResult(value=None, model=_WithLoader()), _Ctx(bad))
+        assert e.value.mutated is False
+    s.rollback(_Ctx(None))
+
+
+def test_captured_strategy_needs_a_loader_to_dry_run(tmp_path):
+    with pytest.raises(StrategyFailed, match="load_weights") as e:
+        B200CapturedStrategy().load(LoadResult(value=None, model=torch.nn.Linear(2, 2)), _Ctx(str(tmp_path)))
+    assert e.value.mutated is False
+
+
+def test_scatter_strategy_names_the_adapter_hook_it_lacks(tmp_path):
+    with pytest.raises(StrategyFailed, match="adapter") as e:
+        B200ScatterStrategy().load(LoadResult(value=None, model=_WithLoader()), _Ctx(str(tmp_path)))
+    assert e.value.mutated is False
+
+
+def test_strategies_are_unavailable_without_an_adapter():
+    assert B200ScatterStrategy().is_available(_Ctx("x", adapter=None)) is False
+
+
+def test_no_cpu_fallback():
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        place_checkpoint("/nonexistent", 0, 1, "cpu")
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        place_captured(_WithLoader(), "/nonexistent", "cpu")
