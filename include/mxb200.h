@@ -110,6 +110,21 @@ int32_t mxb_free(mxb_ctx *ctx, int32_t dev, uint64_t ptr);
 /* Pinned host memory. */
 int32_t mxb_host_alloc(uint64_t nbytes, uint64_t *out_ptr);
 int32_t mxb_host_free(uint64_t ptr);
+/* Pin host memory the caller already has (typically a mapped checkpoint file
+ * that stays in host memory between loads) so that the copy engine and the
+ * kernels can read it in place; mxb_place then moves slices of it with no host
+ * copy at all.  The range is widened to page boundaries; the widened range is
+ * returned and must be mapped readable AND writable (a private mapping of a
+ * read-only file qualifies; the device only reads it).  Pinning costs host time
+ * in proportion to the size, so it pays when the same bytes are loaded more
+ * than once (several replicas or refits from one host image).  Process-wide;
+ * ranges must not overlap.  Replaces the registration step the reference does
+ * for its transfer buffers (nixl_transfer.py:302-585, gds_transfer.py:60-99). */
+int32_t mxb_host_register(uint64_t addr, uint64_t nbytes, uint64_t *out_base, uint64_t *out_bytes);
+/* `base` as returned by mxb_host_register.  No copy from the range may be in flight. */
+int32_t mxb_host_unregister(uint64_t base);
+/* 1 if every byte of [addr, addr + nbytes) is pinned by mxb_host_register, else 0. */
+int32_t mxb_host_is_pinned(uint64_t addr, uint64_t nbytes);
 
 /* Extents the scatter entry points check destinations (and device sources)
  * against; with none registered only structural checks run.  Replaces the
@@ -180,23 +195,31 @@ typedef struct {
     uint64_t chunks;
     uint64_t launches;
     double seconds_total;   /* wall time of the call */
-    double seconds_gather;  /* summed host gather time (overlaps the copies) */
+    double seconds_gather;  /* host copy time of the busiest gather thread (overlaps the copies) */
     double seconds_device;  /* first H2D start to last scatter end, CUDA events */
+    uint64_t bytes_direct;  /* of bytes_placed: read from pinned sources, no host copy */
+    double seconds_plan;    /* chunking, table build and upload before the first copy */
 } mxb_place_stats;
 
-#define MXB_PLACE_COPY_ENGINE 0u /* slot -> device staging by cudaMemcpyAsync, then scatter */
-#define MXB_PLACE_ZERO_COPY 1u   /* scatter kernel reads the pinned slot directly */
+#define MXB_PLACE_COPY_ENGINE 0u /* host -> device staging by the copy engine, then scatter */
+#define MXB_PLACE_ZERO_COPY 1u   /* slices whose source is pinned (mxb_host_register) are read by
+                                    the scatter kernel where they lie: no staging, one launch;
+                                    other sources go through the ring as in mode 0 */
 
-/* A pinned host ring of `slots` equal slots (ring_bytes in total) plus, for the
- * copy-engine mode, two device staging buffers of one slot each. */
+/* A pinned host ring of ring_bytes in total plus two device staging buffers of
+ * ring_bytes / slots each (one chunk = one staging buffer = one scatter launch). */
 int32_t mxb_ring_create(mxb_ctx *ctx, int32_t dev, uint64_t ring_bytes, uint32_t slots,
                         mxb_ring **out);
 int32_t mxb_ring_destroy(mxb_ring *ring);
-/* Place `n` slices whose sources are ordinary host memory (a checkpoint file
- * image) and whose destinations are device addresses: host threads gather the
- * needed bytes of each chunk into a ring slot while the previous slot crosses
- * PCIe, and one scatter launch per chunk writes the shards.  Replaces the
- * host-staged path engines/vllm/adapter.py:316-329 and the file->GPU batches of
+/* Place `n` slices whose sources are host memory (a checkpoint file image) and
+ * whose destinations are device addresses.  Only the bytes this rank keeps
+ * cross PCIe.  Slices of pinned sources (mxb_host_register, mxb_host_alloc) are
+ * gathered by the copy engine itself; for ordinary pageable memory
+ * `host_threads` gather threads each copy a few MiB at a time into the pinned
+ * ring and queue their own H2D copy.  Either way the bytes land densely packed
+ * in a device staging buffer and one persistent scatter launch per chunk
+ * writes the shards while the next chunk arrives.  Replaces the host-staged
+ * path engines/vllm/adapter.py:316-329 and the file->GPU batches of
  * gds_loader.py:284-331 / gds_transfer.py:142-231. */
 int32_t mxb_place(mxb_ring *ring, const mxb_desc2d *items, uint64_t n, int32_t host_threads,
                   uint32_t mode, mxb_place_stats *stats);

@@ -47,7 +47,8 @@ class DigestOut(ctypes.Structure):
 class PlaceStats(ctypes.Structure):
     _fields_ = [("bytes_placed", u64), ("chunks", u64), ("launches", u64),
                 ("seconds_total", ctypes.c_double), ("seconds_gather", ctypes.c_double),
-                ("seconds_device", ctypes.c_double)]
+                ("seconds_device", ctypes.c_double), ("bytes_direct", u64),
+                ("seconds_plan", ctypes.c_double)]
 
 
 # name -> (restype, argtypes); every symbol include/mxb200.h declares
@@ -64,6 +65,9 @@ SIGNATURES = {
     "mxb_free": (i32, [_vp, i32, u64]),
     "mxb_host_alloc": (i32, [u64, _P(u64)]),
     "mxb_host_free": (i32, [u64]),
+    "mxb_host_register": (i32, [u64, u64, _P(u64), _P(u64)]),
+    "mxb_host_unregister": (i32, [u64]),
+    "mxb_host_is_pinned": (i32, [u64, u64]),
     "mxb_register_extent": (i32, [_vp, u64, u64]),
     "mxb_clear_extents": (i32, [_vp]),
     "mxb_ipc_export": (i32, [u64, _P(ctypes.c_uint8), _P(u64)]),

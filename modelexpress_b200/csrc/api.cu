@@ -57,6 +57,30 @@ int32_t check_status(DeviceState *d) {
     return MXB_OK;
 }
 
+// ---- pinned host ranges ---------------------------------------------------------------
+// Process-wide (page-locked memory is a property of the process, not of a context): the
+// ranges mxb_host_register pinned, disjoint and sorted by address.
+namespace {
+struct PinnedRange {
+    uint64_t lo, hi;
+};
+std::mutex g_pin_mu;
+std::vector<PinnedRange> g_pinned;
+}  // namespace
+
+bool host_range_pinned(uint64_t lo, uint64_t hi) {
+    std::lock_guard<std::mutex> lk(g_pin_mu);
+    // ranges registered back to back count as one
+    uint64_t need = lo;
+    for (const PinnedRange &r : g_pinned) {
+        if (r.hi <= need) continue;
+        if (r.lo > need) return false;
+        need = r.hi;
+        if (need >= hi) return true;
+    }
+    return false;
+}
+
 uint64_t tiles_of(const mxb_desc2d &d) {
     if (d.rows == 0 || d.row_bytes == 0) return 0;
     if (d.row_bytes >= kTileBytes) return d.rows * ((d.row_bytes + kTileBytes - 1) / kTileBytes);
@@ -264,6 +288,70 @@ int32_t mxb_host_alloc(uint64_t nbytes, uint64_t *out_ptr) {
 int32_t mxb_host_free(uint64_t ptr) {
     MXB_CUDA(cudaFreeHost((void *)(uintptr_t)ptr));
     return MXB_OK;
+}
+
+int32_t mxb_host_register(uint64_t addr, uint64_t nbytes, uint64_t *out_base, uint64_t *out_bytes) {
+    if (!addr || !nbytes) {
+        set_error("mxb_host_register: empty range");
+        return MXB_ERR_ARG;
+    }
+    const uint64_t page = 4096;
+    const uint64_t lo = addr & ~(page - 1), hi = (addr + nbytes + page - 1) & ~(page - 1);
+    {
+        std::lock_guard<std::mutex> lk(g_pin_mu);
+        for (const PinnedRange &r : g_pinned)
+            if (lo < r.hi && r.lo < hi) {
+                set_error("mxb_host_register: [%llx, %llx) overlaps the pinned range [%llx, %llx)",
+                          (unsigned long long)lo, (unsigned long long)hi, (unsigned long long)r.lo,
+                          (unsigned long long)r.hi);
+                return MXB_ERR_STATE;
+            }
+    }
+    // The device only ever reads these pages.  Saying so lets a mapping whose backing file
+    // must not change be pinned without the kernel breaking copy-on-write page by page;
+    // where the flag is refused the plain form is tried.
+    cudaError_t e = cudaHostRegister((void *)(uintptr_t)lo, hi - lo,
+                                     cudaHostRegisterPortable | cudaHostRegisterReadOnly);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        e = cudaHostRegister((void *)(uintptr_t)lo, hi - lo, cudaHostRegisterPortable);
+    }
+    if (e != cudaSuccess) {
+        set_error("cudaHostRegister(%llx, %llu): %s (the range must be mapped readable and writable)",
+                  (unsigned long long)lo, (unsigned long long)(hi - lo), cudaGetErrorString(e));
+        cudaGetLastError();
+        return e == cudaErrorMemoryAllocation ? MXB_ERR_NOMEM : MXB_ERR_CUDA;
+    }
+    {
+        std::lock_guard<std::mutex> lk(g_pin_mu);
+        auto it = g_pinned.begin();
+        while (it != g_pinned.end() && it->lo < lo) ++it;
+        g_pinned.insert(it, {lo, hi});
+    }
+    if (out_base) *out_base = lo;
+    if (out_bytes) *out_bytes = hi - lo;
+    return MXB_OK;
+}
+
+int32_t mxb_host_unregister(uint64_t base) {
+    {
+        std::lock_guard<std::mutex> lk(g_pin_mu);
+        auto it = g_pinned.begin();
+        while (it != g_pinned.end() && it->lo != base) ++it;
+        if (it == g_pinned.end()) {
+            set_error("mxb_host_unregister: %llx is not the base of a pinned range",
+                      (unsigned long long)base);
+            return MXB_ERR_STATE;
+        }
+        g_pinned.erase(it);
+    }
+    MXB_CUDA(cudaHostUnregister((void *)(uintptr_t)base));
+    return MXB_OK;
+}
+
+int32_t mxb_host_is_pinned(uint64_t addr, uint64_t nbytes) {
+    if (!addr || !nbytes) return 0;
+    return host_range_pinned(addr, addr + nbytes) ? 1 : 0;
 }
 
 int32_t mxb_register_extent(mxb_ctx *ctx, uint64_t base, uint64_t nbytes) {

@@ -125,5 +125,7 @@ int32_t launch_scatter_tiles(mxb_ctx *ctx, DeviceState *dv, const ScatterTable &
 int32_t launch_scatter(mxb_ctx *ctx, DeviceState *d, const mxb_desc2d *descs, uint64_t n,
                        uint32_t flags, cudaStream_t stream);
 int32_t validate_descs(mxb_ctx *ctx, const mxb_desc2d *descs, uint64_t n);
+// Whether every byte of the host range [lo, hi) lies in memory pinned by mxb_host_register.
+bool host_range_pinned(uint64_t lo, uint64_t hi);
 
 }  // namespace mxb

@@ -1,17 +1,25 @@
 // Pinned staging ring: host checkpoint bytes -> HBM shards.
 //
-// mxb_place cuts the requested slices into chunks of one ring slot.  For every
-// chunk the host threads gather exactly the bytes this rank keeps into the
-// slot (densely packed, rows re-pitched so that the 16-byte vector path holds),
-// the slot crosses PCIe once on the copy-engine stream, and one persistent
-// scatter launch writes the shards from the device staging buffer.  Gathering
-// chunk c+1 overlaps the copy of chunk c; the scatter of chunk c overlaps the
-// copy of chunk c+1 (two device staging buffers).  In zero-copy mode the
-// scatter kernel reads the pinned slot directly and the copy engine is idle.
+// mxb_place cuts the requested slices into chunks of one device staging buffer
+// (densely packed, rows re-pitched so that the 16-byte vector path holds) and
+// fills the two staging buffers alternately; one persistent scatter launch per
+// chunk writes the shards while the other buffer is being filled.
+//
+// How a chunk is filled depends on where its source bytes live:
+//   * sources inside memory pinned with mxb_host_register: the copy engine
+//     gathers them straight from the source (one 1-D or 2-D cudaMemcpyAsync per
+//     record); no host thread touches a byte;
+//   * ordinary (pageable) host memory, e.g. a mapped checkpoint file: the chunk
+//     is cut into units of a few MiB; each gather thread takes the next unit,
+//     copies exactly the bytes this rank keeps into a pinned sub-slot of the
+//     ring with streaming stores and sends that sub-slot over PCIe on its own
+//     stream.  Threads never wait for one another, only for a sub-slot or a
+//     staging buffer to come free.
 #include <sys/mman.h>
 
 #include <chrono>
 #include <condition_variable>
+#include <functional>
 #include <thread>
 
 #include "common.cuh"
@@ -21,31 +29,40 @@ namespace mxb {
 void stream_copy(void *dst, const void *src, size_t n);  // hostcopy.cpp
 void stream_fence();
 
-struct GatherOp {  // host memcpy work: rows of row_bytes from src (pitch) to slot offset
+struct GatherOp {  // rows of row_bytes from src (pitch) to an offset of the chunk's packed image
     const char *src;
     uint64_t slot_off;
     uint64_t rows, row_bytes, src_pitch, packed_pitch;
 };
 
-struct GatherPiece {
+struct GatherPiece {  // a bounded amount of host copy work; dst_off is relative to the chunk
     const char *src;
-    char *dst;
+    uint64_t dst_off;
     uint64_t rows, row_bytes, src_pitch, dst_pitch;
+    uint64_t span() const { return (rows - 1) * dst_pitch + row_bytes; }
 };
 
 struct Chunk {
     uint64_t op_begin = 0, op_end = 0;      // GatherOps
     uint64_t desc_begin = 0, desc_end = 0;  // scatter records
-    uint64_t bytes = 0;                     // packed bytes used in the slot
+    uint64_t bytes = 0;                     // packed bytes used in the staging buffer
+    bool direct = false;                    // sources are pinned: the copy engine gathers
+    uint64_t unit_begin = 0, unit_end = 0;  // Units (gathered chunks only)
 };
 
-// Minimal fork-join pool: run(pieces) executes them on the workers and the caller.
-class GatherPool {
+struct Unit {  // one gather thread's job: a contiguous span of one chunk's packed image
+    uint32_t chunk;
+    uint64_t lo, hi;
+    uint64_t piece_begin, piece_end;
+};
+
+// Persistent worker threads: start(fn) runs fn(worker index) on every worker, wait() joins the round.
+class WorkerPool {
   public:
-    explicit GatherPool(int threads) {
-        for (int i = 1; i < threads; ++i) workers_.emplace_back([this] { loop(); });
+    explicit WorkerPool(int threads) {
+        for (int i = 0; i < threads; ++i) workers_.emplace_back([this, i] { loop(i); });
     }
-    ~GatherPool() {
+    ~WorkerPool() {
         {
             std::lock_guard<std::mutex> lk(mu_);
             stop_ = true;
@@ -54,40 +71,23 @@ class GatherPool {
         cv_.notify_all();
         for (auto &t : workers_) t.join();
     }
-    int size() const { return (int)workers_.size() + 1; }
-    void run(const std::vector<GatherPiece> &pieces) {
-        if (pieces.empty()) return;
+    int size() const { return (int)workers_.size(); }
+    void start(std::function<void(int)> fn) {
         {
             std::lock_guard<std::mutex> lk(mu_);
-            pieces_ = &pieces;
-            next_.store(0);
+            fn_ = std::move(fn);
             pending_ = (int)workers_.size();
             ++generation_;
         }
         cv_.notify_all();
-        work();
+    }
+    void wait() {
         std::unique_lock<std::mutex> lk(mu_);
         done_cv_.wait(lk, [this] { return pending_ == 0; });
-        pieces_ = nullptr;
     }
 
   private:
-    void work() {
-        const std::vector<GatherPiece> &ps = *pieces_;
-        for (;;) {
-            size_t i = next_.fetch_add(1);
-            if (i >= ps.size()) break;
-            const GatherPiece &p = ps[i];
-            if (p.src_pitch == p.row_bytes && p.dst_pitch == p.row_bytes) {
-                stream_copy(p.dst, p.src, p.rows * p.row_bytes);
-            } else {
-                for (uint64_t r = 0; r < p.rows; ++r)
-                    stream_copy(p.dst + r * p.dst_pitch, p.src + r * p.src_pitch, p.row_bytes);
-            }
-        }
-        stream_fence();  // before the slot is handed to the copy engine / the kernel
-    }
-    void loop() {
+    void loop(int index) {
         uint64_t seen = 0;
         for (;;) {
             {
@@ -96,19 +96,18 @@ class GatherPool {
                 seen = generation_;
                 if (stop_) return;
             }
-            work();
+            fn_(index);
             {
                 std::lock_guard<std::mutex> lk(mu_);
                 --pending_;
             }
-            done_cv_.notify_one();
+            done_cv_.notify_all();
         }
     }
     std::vector<std::thread> workers_;
     std::mutex mu_;
     std::condition_variable cv_, done_cv_;
-    const std::vector<GatherPiece> *pieces_ = nullptr;
-    std::atomic<size_t> next_{0};
+    std::function<void(int)> fn_;
     int pending_ = 0;
     uint64_t generation_ = 0;
     bool stop_ = false;
@@ -121,18 +120,22 @@ using namespace mxb;
 struct mxb_ring {
     mxb_ctx *ctx = nullptr;
     DeviceState *dv = nullptr;
-    uint64_t slot_bytes = 0;
+    uint64_t slot_bytes = 0;  // size of one device staging buffer (= one chunk)
     uint32_t slots = 0;
-    char *host = nullptr;           // pinned, slots * slot_bytes
-    void *host_map = nullptr;       // the mapping `host` lies in when it was pinned by registration
+    char *host = nullptr;      // pinned, slots * slot_bytes, used as sub-slots of unit_bytes
+    void *host_map = nullptr;  // the mapping `host` lies in when it was pinned by registration
     size_t host_map_bytes = 0;
+    uint64_t unit_bytes = 0;
+    uint32_t sub_slots = 0;
     char *staging[2] = {nullptr, nullptr};  // device
-    std::vector<cudaEvent_t> slot_free;     // slot may be overwritten by the host
+    std::vector<cudaEvent_t> sub_done;      // the copy out of a sub-slot has finished
     cudaEvent_t stage_free[2] = {nullptr, nullptr};
+    cudaEvent_t dma_done[2] = {nullptr, nullptr};
     cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
+    std::vector<cudaStream_t> streams;  // one copy stream per gather thread
     void *table_dev = nullptr, *table_host = nullptr;
     size_t table_bytes = 0;
-    GatherPool *pool = nullptr;
+    WorkerPool *pool = nullptr;
     int pool_threads = 0;
 };
 
@@ -140,15 +143,19 @@ namespace {
 
 constexpr uint64_t kPackAlign = 256;
 constexpr uint64_t kGatherPiece = 1ull << 20;  // bytes of host memcpy per work item
+constexpr uint64_t kUnitBytes = 4ull << 20;    // packed bytes one gather thread sends per copy
 
 inline uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
 
 // Cut the items into chunks; emit gather ops and scatter records whose source
-// is an offset into the slot (rebased per chunk by the caller).
-int32_t plan_chunks(const mxb_desc2d *items, uint64_t n, uint64_t slot_bytes,
-                    std::vector<Chunk> &chunks, std::vector<GatherOp> &ops,
-                    std::vector<mxb_desc2d> &descs) {
+// is an offset into the chunk's packed image (rebased per chunk by the caller).
+void plan_chunks(const mxb_desc2d *items, const std::vector<uint64_t> &which, uint64_t slot_bytes,
+                 bool direct, std::vector<Chunk> &chunks, std::vector<GatherOp> &ops,
+                 std::vector<mxb_desc2d> &descs) {
     Chunk cur;
+    cur.direct = direct;
+    cur.op_begin = ops.size();
+    cur.desc_begin = descs.size();
     uint64_t used = 0;
     auto close = [&]() {
         cur.op_end = ops.size();
@@ -156,12 +163,13 @@ int32_t plan_chunks(const mxb_desc2d *items, uint64_t n, uint64_t slot_bytes,
         cur.bytes = used;
         if (cur.op_end > cur.op_begin) chunks.push_back(cur);
         cur = Chunk();
+        cur.direct = direct;
         cur.op_begin = ops.size();
         cur.desc_begin = descs.size();
         used = 0;
     };
-    for (uint64_t i = 0; i < n; ++i) {
-        const mxb_desc2d &it = items[i];
+    for (uint64_t idx : which) {
+        const mxb_desc2d &it = items[idx];
         if (it.rows == 0 || it.row_bytes == 0) continue;
         // packed pitch keeps (packed row address - dst row address) constant mod 16
         uint64_t pp = it.row_bytes;
@@ -174,7 +182,7 @@ int32_t plan_chunks(const mxb_desc2d *items, uint64_t n, uint64_t slot_bytes,
             const uint64_t off = align_up(used, kPackAlign) + phase;
             const uint64_t room = off < slot_bytes ? slot_bytes - off : 0;
             if (col == 0 && row_fits_empty) {
-                if (room < it.row_bytes) {  // the slot has data already: start a new chunk
+                if (room < it.row_bytes) {  // the chunk has data already: start a new one
                     close();
                     continue;
                 }
@@ -187,7 +195,7 @@ int32_t plan_chunks(const mxb_desc2d *items, uint64_t n, uint64_t slot_bytes,
                 used = off + (take - 1) * pp + it.row_bytes;
                 row += take;
             } else {
-                // a row larger than a slot: split it by bytes into 256-byte multiples
+                // a row larger than a chunk: split it by bytes into 256-byte multiples
                 const uint64_t want = it.row_bytes - col;
                 const uint64_t take = want <= room ? want : (room / kPackAlign) * kPackAlign;
                 if (take == 0) {
@@ -208,8 +216,71 @@ int32_t plan_chunks(const mxb_desc2d *items, uint64_t n, uint64_t slot_bytes,
         }
     }
     close();
-    return MXB_OK;
 }
+
+// Cut a gathered chunk's ops into pieces of about kGatherPiece bytes and group
+// consecutive pieces into units whose packed span fits one sub-slot.
+void plan_units(uint32_t chunk_index, Chunk &ch, const std::vector<GatherOp> &ops, uint64_t unit_bytes,
+                std::vector<GatherPiece> &pieces, std::vector<Unit> &units) {
+    ch.unit_begin = units.size();
+    Unit cur{chunk_index, 0, 0, pieces.size(), pieces.size()};
+    auto flush = [&]() {
+        if (cur.piece_end > cur.piece_begin) units.push_back(cur);
+        cur = Unit{chunk_index, 0, 0, pieces.size(), pieces.size()};
+    };
+    auto add = [&](const GatherPiece &p) {
+        const uint64_t lo = p.dst_off & ~uint64_t(15), hi = p.dst_off + p.span();
+        if (cur.piece_end > cur.piece_begin && hi - cur.lo > unit_bytes) flush();
+        if (cur.piece_end == cur.piece_begin) cur.lo = lo;
+        pieces.push_back(p);
+        cur.piece_end = pieces.size();
+        cur.hi = hi;
+    };
+    const uint64_t piece_cap = kGatherPiece < unit_bytes ? kGatherPiece : unit_bytes / 2;
+    for (uint64_t i = ch.op_begin; i < ch.op_end; ++i) {
+        const GatherOp &op = ops[i];
+        if (op.row_bytes > piece_cap) {
+            for (uint64_t r = 0; r < op.rows; ++r)
+                for (uint64_t b = 0; b < op.row_bytes; b += piece_cap) {
+                    const uint64_t len = piece_cap < op.row_bytes - b ? piece_cap : op.row_bytes - b;
+                    add({op.src + r * op.src_pitch + b, op.slot_off + r * op.packed_pitch + b, 1, len,
+                         len, len});
+                }
+        } else {
+            uint64_t rows_per = piece_cap / op.packed_pitch;
+            if (rows_per < 1) rows_per = 1;
+            for (uint64_t r0 = 0; r0 < op.rows; r0 += rows_per) {
+                const uint64_t take = rows_per < op.rows - r0 ? rows_per : op.rows - r0;
+                add({op.src + r0 * op.src_pitch, op.slot_off + r0 * op.packed_pitch, take,
+                     op.row_bytes, op.src_pitch, op.packed_pitch});
+            }
+        }
+    }
+    flush();
+    ch.unit_end = units.size();
+}
+
+void gather_piece(const GatherPiece &p, char *dst) {
+    if (p.src_pitch == p.row_bytes && p.dst_pitch == p.row_bytes) {
+        stream_copy(dst, p.src, p.rows * p.row_bytes);
+    } else {
+        for (uint64_t r = 0; r < p.rows; ++r)
+            stream_copy(dst + r * p.dst_pitch, p.src + r * p.src_pitch, p.row_bytes);
+    }
+}
+
+// What the gather threads and the launching thread of one mxb_place call share.
+struct PlaceShared {
+    std::mutex mu;
+    std::condition_variable cv;
+    std::vector<uint8_t> issued;        // per unit: its copy has been queued
+    std::vector<uint32_t> chunk_issued;  // per chunk: units queued so far
+    uint64_t launched = 0;               // chunks whose scatter has been queued
+    std::atomic<uint64_t> next_unit{0};
+    std::atomic<int> error{MXB_OK};
+    std::vector<double> busy;            // per thread: seconds spent copying
+    char err_text[256] = "";
+};
 
 }  // namespace
 
@@ -236,10 +307,10 @@ int32_t mxb_ring_create(mxb_ctx *ctx, int32_t dev, uint64_t ring_bytes, uint32_t
         mxb_ring_destroy(r);
         return rc;
     };
-    // Pinning sits inside a one-shot load's time to loaded weights.  cudaHostAlloc takes
-    // 0.4-0.5 ms per MiB here; an anonymous mapping advised to use huge pages, touched by
-    // several threads at once and then registered takes about a tenth of that and copies
-    // to the device as fast.  MXB_RING_PIN=alloc selects cudaHostAlloc.
+    // Pinning sits inside a one-shot load's time to loaded weights.  An anonymous mapping
+    // advised to use huge pages, touched by several threads at once and then registered is
+    // pinned several times faster than cudaHostAlloc pins the same amount, and copies to
+    // the device as fast.  MXB_RING_PIN=alloc selects cudaHostAlloc.
     const size_t ring_total = (size_t)r->slot_bytes * slots;
     const char *pin_mode = getenv("MXB_RING_PIN");
     if (!(pin_mode && !strcmp(pin_mode, "alloc"))) {
@@ -274,18 +345,22 @@ int32_t mxb_ring_create(mxb_ctx *ctx, int32_t dev, uint64_t ring_bytes, uint32_t
         cudaGetLastError();
         return fail(MXB_ERR_NOMEM);
     }
+    // the pinned memory is handed out in sub-slots: one per copy a gather thread has in flight
+    r->unit_bytes = kUnitBytes < r->slot_bytes ? kUnitBytes : r->slot_bytes;
+    r->sub_slots = (uint32_t)(ring_total / r->unit_bytes);
     for (int i = 0; i < 2; ++i) {
         if (cudaMalloc((void **)&r->staging[i], r->slot_bytes) != cudaSuccess) {
             set_error("cudaMalloc(staging) failed");
             cudaGetLastError();
             return fail(MXB_ERR_NOMEM);
         }
-        if (cudaEventCreateWithFlags(&r->stage_free[i], cudaEventDisableTiming) != cudaSuccess)
+        if (cudaEventCreateWithFlags(&r->stage_free[i], cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&r->dma_done[i], cudaEventDisableTiming) != cudaSuccess)
             return fail(MXB_ERR_CUDA);
     }
-    r->slot_free.resize(slots, nullptr);
-    for (uint32_t i = 0; i < slots; ++i)
-        if (cudaEventCreateWithFlags(&r->slot_free[i], cudaEventDisableTiming) != cudaSuccess)
+    r->sub_done.resize(r->sub_slots, nullptr);
+    for (uint32_t i = 0; i < r->sub_slots; ++i)
+        if (cudaEventCreateWithFlags(&r->sub_done[i], cudaEventDisableTiming) != cudaSuccess)
             return fail(MXB_ERR_CUDA);
     if (cudaEventCreate(&r->ev_begin) != cudaSuccess || cudaEventCreate(&r->ev_end) != cudaSuccess)
         return fail(MXB_ERR_CUDA);
@@ -299,6 +374,11 @@ int32_t mxb_ring_destroy(mxb_ring *r) {
     cudaStreamSynchronize(r->dv->stream);
     cudaStreamSynchronize(r->dv->copy_stream);
     delete r->pool;
+    for (cudaStream_t st : r->streams)
+        if (st) {
+            cudaStreamSynchronize(st);
+            cudaStreamDestroy(st);
+        }
     if (r->host_map) {
         cudaHostUnregister(r->host);
         munmap(r->host_map, r->host_map_bytes);
@@ -308,8 +388,9 @@ int32_t mxb_ring_destroy(mxb_ring *r) {
     for (int i = 0; i < 2; ++i) {
         if (r->staging[i]) cudaFree(r->staging[i]);
         if (r->stage_free[i]) cudaEventDestroy(r->stage_free[i]);
+        if (r->dma_done[i]) cudaEventDestroy(r->dma_done[i]);
     }
-    for (cudaEvent_t e : r->slot_free)
+    for (cudaEvent_t e : r->sub_done)
         if (e) cudaEventDestroy(e);
     if (r->ev_begin) cudaEventDestroy(r->ev_begin);
     if (r->ev_end) cudaEventDestroy(r->ev_end);
@@ -336,25 +417,37 @@ int32_t mxb_place(mxb_ring *r, const mxb_desc2d *items, uint64_t n, int32_t host
     DeviceGuard g(dv->device);
     std::lock_guard<std::mutex> lk(*dv->mu);
     if (host_threads < 1) host_threads = 1;
-    if (!r->pool || r->pool_threads != host_threads) {
-        delete r->pool;
-        r->pool = new GatherPool(host_threads);
-        r->pool_threads = host_threads;
-    }
+    if (host_threads > 64) host_threads = 64;
 
+    // ---- plan ---------------------------------------------------------------------------
+    std::vector<uint64_t> pinned_items, paged_items;
+    for (uint64_t i = 0; i < n; ++i) {
+        const mxb_desc2d &it = items[i];
+        if (it.rows == 0 || it.row_bytes == 0) continue;
+        const uint64_t lo = it.src, hi = it.src + (it.rows - 1) * it.src_pitch + it.row_bytes;
+        (host_range_pinned(lo, hi) ? pinned_items : paged_items).push_back(i);
+    }
+    const bool zero_copy = (mode == MXB_PLACE_ZERO_COPY);
     std::vector<Chunk> chunks;
     std::vector<GatherOp> ops;
     std::vector<mxb_desc2d> descs;
-    int32_t rc = plan_chunks(items, n, r->slot_bytes, chunks, ops, descs);
-    if (rc != MXB_OK) return rc;
-    const bool zero_copy = (mode == MXB_PLACE_ZERO_COPY);
-
-    // rebase every record's source onto the buffer its chunk will be read from
+    uint64_t direct_bytes = 0;
+    for (uint64_t i : pinned_items) direct_bytes += items[i].rows * items[i].row_bytes;
+    if (zero_copy) {
+        // the kernel reads pinned sources where they lie: their records need no staging
+        for (uint64_t i : pinned_items) descs.push_back(items[i]);
+    } else {
+        plan_chunks(items, pinned_items, r->slot_bytes, true, chunks, ops, descs);
+    }
+    const uint64_t zc_descs = zero_copy ? descs.size() : 0;
+    plan_chunks(items, paged_items, r->slot_bytes, false, chunks, ops, descs);
+    std::vector<GatherPiece> pieces;
+    std::vector<Unit> units;
     for (size_t c = 0; c < chunks.size(); ++c) {
-        const char *base = zero_copy ? r->host + (c % r->slots) * r->slot_bytes
-                                     : r->staging[c % 2];
+        if (!chunks[c].direct) plan_units((uint32_t)c, chunks[c], ops, r->unit_bytes, pieces, units);
+        // rebase every record's source onto the staging buffer its chunk goes through
         for (uint64_t i = chunks[c].desc_begin; i < chunks[c].desc_end; ++i)
-            descs[i].src += (uint64_t)(uintptr_t)base;
+            descs[i].src += (uint64_t)(uintptr_t)r->staging[c % 2];
     }
     // one table for all chunks, uploaded once
     const size_t tbytes = scatter_table_bytes(descs.data(), descs.size(), nullptr, nullptr);
@@ -371,6 +464,7 @@ int32_t mxb_place(mxb_ring *r, const mxb_desc2d *items, uint64_t n, int32_t host
     }
     ScatterTable tb;
     std::vector<uint64_t> bulk_begin(descs.size() + 1, 0), vec_begin(descs.size() + 1, 0);
+    int32_t rc = MXB_OK;
     if (!descs.empty()) {
         MXB_CUDA(cudaStreamSynchronize(dv->stream));
         rc = build_scatter_table(descs.data(), descs.size(), r->table_host, r->table_dev, &tb,
@@ -379,67 +473,186 @@ int32_t mxb_place(mxb_ring *r, const mxb_desc2d *items, uint64_t n, int32_t host
         MXB_CUDA(cudaMemcpyAsync(r->table_dev, r->table_host, tb.bytes, cudaMemcpyHostToDevice,
                                  dv->stream));
     }
+    const bool gathering = !units.empty();
+    if (gathering) {
+        if (!r->pool || r->pool_threads != host_threads) {
+            delete r->pool;
+            r->pool = new WorkerPool(host_threads);
+            r->pool_threads = host_threads;
+        }
+        while ((int)r->streams.size() < host_threads) {
+            cudaStream_t st = nullptr;
+            MXB_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+            r->streams.push_back(st);
+        }
+    }
+    const double plan_s = std::chrono::duration<double>(clk::now() - t0).count();
 
-    double gather_s = 0.0;
-    uint64_t placed = 0, launches = 0;
-    std::vector<GatherPiece> pieces;
+    uint64_t placed = direct_bytes, launches = 0;
+    for (const Unit &u : units)
+        for (uint64_t p = u.piece_begin; p < u.piece_end; ++p)
+            placed += pieces[p].rows * pieces[p].row_bytes;
     MXB_CUDA(cudaEventRecord(r->ev_begin, dv->stream));
-    std::vector<bool> slot_used(r->slots, false);
-    bool stage_used[2] = {false, false};
+    // every stream that writes a staging buffer starts behind whatever this ring's
+    // earlier call still has in flight on the compute stream
+    MXB_CUDA(cudaStreamWaitEvent(dv->copy_stream, r->ev_begin, 0));
+    if (zero_copy && zc_descs) {
+        rc = launch_scatter_tiles(r->ctx, dv, tb, bulk_begin[0], bulk_begin[zc_descs] - bulk_begin[0],
+                                  vec_begin[0], vec_begin[zc_descs] - vec_begin[0], MXB_SCATTER_VECTOR,
+                                  dv->stream);
+        if (rc != MXB_OK) return rc;
+        ++launches;
+    }
+
+    // ---- gather threads (pageable sources) ------------------------------------------------
+    PlaceShared sh;
+    sh.issued.assign(units.size(), 0);
+    sh.chunk_issued.assign(chunks.size(), 0);
+    sh.busy.assign(host_threads, 0.0);
+    const uint32_t nsub = r->sub_slots;
+    if (gathering) {
+        for (int t = 0; t < host_threads; ++t)
+            MXB_CUDA(cudaStreamWaitEvent(r->streams[t], r->ev_begin, 0));
+        const int device = dv->device;
+        r->pool->start([&, device](int t) {
+            cudaSetDevice(device);
+            cudaStream_t st = r->streams[t];
+            auto fail = [&](const char *what, cudaError_t e) {
+                std::lock_guard<std::mutex> l(sh.mu);
+                if (sh.error.load() == MXB_OK) {
+                    snprintf(sh.err_text, sizeof sh.err_text, "%s: %s", what, cudaGetErrorString(e));
+                    sh.error.store(MXB_ERR_CUDA);
+                }
+                sh.cv.notify_all();
+            };
+            for (;;) {
+                const uint64_t u = sh.next_unit.fetch_add(1);
+                if (u >= units.size() || sh.error.load() != MXB_OK) break;
+                const Unit &un = units[u];
+                const uint32_t sub = (uint32_t)(u % nsub);
+                char *slot = r->host + (uint64_t)sub * r->unit_bytes;
+                if (u >= nsub) {  // the sub-slot's previous copy must have left it
+                    {
+                        std::unique_lock<std::mutex> l(sh.mu);
+                        sh.cv.wait(l, [&] { return sh.issued[u - nsub] || sh.error.load() != MXB_OK; });
+                    }
+                    if (sh.error.load() != MXB_OK) break;
+                    cudaError_t e = cudaEventSynchronize(r->sub_done[sub]);
+                    if (e != cudaSuccess) {
+                        fail("cudaEventSynchronize(sub-slot)", e);
+                        break;
+                    }
+                }
+                const auto g0 = clk::now();
+                for (uint64_t p = un.piece_begin; p < un.piece_end; ++p)
+                    gather_piece(pieces[p], slot + (pieces[p].dst_off - un.lo));
+                stream_fence();  // before the sub-slot is handed to the copy engine
+                sh.busy[t] += std::chrono::duration<double>(clk::now() - g0).count();
+                const int stg = (int)(un.chunk % 2);
+                if (un.chunk >= 2) {  // the scatter that last read this staging buffer must be queued
+                    std::unique_lock<std::mutex> l(sh.mu);
+                    sh.cv.wait(l, [&] { return sh.launched + 1 >= un.chunk || sh.error.load() != MXB_OK; });
+                    if (sh.error.load() != MXB_OK) break;
+                }
+                cudaError_t e = cudaSuccess;
+                if (un.chunk >= 2) e = cudaStreamWaitEvent(st, r->stage_free[stg], 0);
+                if (e == cudaSuccess)
+                    e = cudaMemcpyAsync(r->staging[stg] + un.lo, slot, un.hi - un.lo,
+                                        cudaMemcpyHostToDevice, st);
+                if (e == cudaSuccess) e = cudaEventRecord(r->sub_done[sub], st);
+                if (e != cudaSuccess) {
+                    fail("queueing a sub-slot copy", e);
+                    break;
+                }
+                {
+                    std::lock_guard<std::mutex> l(sh.mu);
+                    sh.issued[u] = 1;
+                    ++sh.chunk_issued[un.chunk];
+                }
+                sh.cv.notify_all();
+            }
+        });
+    }
+
+    // ---- the launching thread: one scatter per chunk -------------------------------------
+    auto finish_workers = [&]() {
+        if (gathering) r->pool->wait();
+    };
+    auto abort_with = [&](int32_t code) {
+        {
+            std::lock_guard<std::mutex> l(sh.mu);
+            if (sh.error.load() == MXB_OK) sh.error.store(code);
+        }
+        sh.cv.notify_all();
+        finish_workers();
+        return code;
+    };
+#define MXB_PLACE_CUDA(call)                                                              \
+    do {                                                                                  \
+        cudaError_t _e = (call);                                                          \
+        if (_e != cudaSuccess) {                                                          \
+            set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(_e), __FILE__,   \
+                      __LINE__);                                                          \
+            return abort_with(MXB_ERR_CUDA);                                              \
+        }                                                                                 \
+    } while (0)
     for (size_t c = 0; c < chunks.size(); ++c) {
         const Chunk &ch = chunks[c];
-        const uint32_t slot = (uint32_t)(c % r->slots);
-        char *slot_base = r->host + (uint64_t)slot * r->slot_bytes;
-        if (slot_used[slot]) MXB_CUDA(cudaEventSynchronize(r->slot_free[slot]));
-        // gather
-        const auto g0 = clk::now();
-        pieces.clear();
-        for (uint64_t i = ch.op_begin; i < ch.op_end; ++i) {
-            const GatherOp &op = ops[i];
-            placed += op.rows * op.row_bytes;
-            uint64_t rows_per = op.row_bytes >= kGatherPiece ? 1 : kGatherPiece / op.row_bytes;
-            for (uint64_t r0 = 0; r0 < op.rows; r0 += rows_per) {
-                uint64_t take = rows_per < op.rows - r0 ? rows_per : op.rows - r0;
-                if (take == 1 && op.row_bytes > kGatherPiece) {
-                    for (uint64_t b = 0; b < op.row_bytes; b += kGatherPiece) {
-                        uint64_t len = kGatherPiece < op.row_bytes - b ? kGatherPiece : op.row_bytes - b;
-                        pieces.push_back({op.src + r0 * op.src_pitch + b,
-                                          slot_base + op.slot_off + r0 * op.packed_pitch + b, 1, len,
-                                          len, len});
-                    }
-                } else {
-                    pieces.push_back({op.src + r0 * op.src_pitch,
-                                      slot_base + op.slot_off + r0 * op.packed_pitch, take,
-                                      op.row_bytes, op.src_pitch, op.packed_pitch});
-                }
+        const int stg = (int)(c % 2);
+        if (ch.direct) {
+            if (c >= 2) MXB_PLACE_CUDA(cudaStreamWaitEvent(dv->copy_stream, r->stage_free[stg], 0));
+            for (uint64_t i = ch.op_begin; i < ch.op_end; ++i) {
+                const GatherOp &op = ops[i];
+                char *dst = r->staging[stg] + op.slot_off;
+                if (op.rows == 1 || (op.src_pitch == op.row_bytes && op.packed_pitch == op.row_bytes))
+                    MXB_PLACE_CUDA(cudaMemcpyAsync(dst, op.src, op.rows * op.row_bytes,
+                                                   cudaMemcpyHostToDevice, dv->copy_stream));
+                else if (op.src_pitch < (1ull << 31))
+                    MXB_PLACE_CUDA(cudaMemcpy2DAsync(dst, op.packed_pitch, op.src, op.src_pitch,
+                                                     op.row_bytes, op.rows, cudaMemcpyHostToDevice,
+                                                     dv->copy_stream));
+                else  // a pitch the 2-D copy does not take: row by row
+                    for (uint64_t row = 0; row < op.rows; ++row)
+                        MXB_PLACE_CUDA(cudaMemcpyAsync(dst + row * op.packed_pitch,
+                                                       op.src + row * op.src_pitch, op.row_bytes,
+                                                       cudaMemcpyHostToDevice, dv->copy_stream));
             }
+            MXB_PLACE_CUDA(cudaEventRecord(r->dma_done[stg], dv->copy_stream));
+            MXB_PLACE_CUDA(cudaStreamWaitEvent(dv->stream, r->dma_done[stg], 0));
+        } else {
+            {
+                std::unique_lock<std::mutex> l(sh.mu);
+                sh.cv.wait(l, [&] {
+                    return sh.chunk_issued[c] == ch.unit_end - ch.unit_begin || sh.error.load() != MXB_OK;
+                });
+            }
+            if (sh.error.load() != MXB_OK) {
+                set_error("%s", sh.err_text);
+                return abort_with(sh.error.load());
+            }
+            // a sub-slot's event may already stand for a later copy out of the same sub-slot;
+            // that copy was queued only after this chunk's had finished, so waiting on it is safe
+            for (uint64_t u = ch.unit_begin; u < ch.unit_end; ++u)
+                MXB_PLACE_CUDA(cudaStreamWaitEvent(dv->stream, r->sub_done[u % nsub], 0));
         }
-        r->pool->run(pieces);
-        gather_s += std::chrono::duration<double>(clk::now() - g0).count();
-
         const uint64_t b0 = bulk_begin[ch.desc_begin], b1 = bulk_begin[ch.desc_end];
         const uint64_t v0 = vec_begin[ch.desc_begin], v1 = vec_begin[ch.desc_end];
-        // the zero-copy source is pinned host memory: plain loads, not bulk copies
-        const uint32_t eng = zero_copy ? MXB_SCATTER_VECTOR : MXB_SCATTER_DEFAULT;
-        if (zero_copy) {
-            rc = launch_scatter_tiles(r->ctx, dv, tb, b0, b1 - b0, v0, v1 - v0, eng, dv->stream);
-            if (rc != MXB_OK) return rc;
-            MXB_CUDA(cudaEventRecord(r->slot_free[slot], dv->stream));
-        } else {
-            const int st = (int)(c % 2);
-            if (stage_used[st]) MXB_CUDA(cudaStreamWaitEvent(dv->copy_stream, r->stage_free[st], 0));
-            if (c == 0) MXB_CUDA(cudaStreamWaitEvent(dv->copy_stream, r->ev_begin, 0));
-            MXB_CUDA(cudaMemcpyAsync(r->staging[st], slot_base, ch.bytes, cudaMemcpyHostToDevice,
-                                     dv->copy_stream));
-            MXB_CUDA(cudaEventRecord(r->slot_free[slot], dv->copy_stream));
-            MXB_CUDA(cudaStreamWaitEvent(dv->stream, r->slot_free[slot], 0));
-            rc = launch_scatter_tiles(r->ctx, dv, tb, b0, b1 - b0, v0, v1 - v0, eng, dv->stream);
-            if (rc != MXB_OK) return rc;
-            MXB_CUDA(cudaEventRecord(r->stage_free[st], dv->stream));
-            stage_used[st] = true;
+        rc = launch_scatter_tiles(r->ctx, dv, tb, b0, b1 - b0, v0, v1 - v0, MXB_SCATTER_DEFAULT,
+                                  dv->stream);
+        if (rc != MXB_OK) return abort_with(rc);
+        MXB_PLACE_CUDA(cudaEventRecord(r->stage_free[stg], dv->stream));
+        {
+            std::lock_guard<std::mutex> l(sh.mu);
+            sh.launched = c + 1;
         }
-        slot_used[slot] = true;
+        sh.cv.notify_all();
         ++launches;
+    }
+#undef MXB_PLACE_CUDA
+    finish_workers();
+    if (sh.error.load() != MXB_OK) {
+        set_error("%s", sh.err_text);
+        return sh.error.load();
     }
     MXB_CUDA(cudaEventRecord(r->ev_end, dv->stream));
     rc = check_status(dv);
@@ -447,12 +660,16 @@ int32_t mxb_place(mxb_ring *r, const mxb_desc2d *items, uint64_t n, int32_t host
     if (stats) {
         float ms = 0.f;
         cudaEventElapsedTime(&ms, r->ev_begin, r->ev_end);
+        double busiest = 0.0;
+        for (double b : sh.busy) busiest = b > busiest ? b : busiest;
         stats->bytes_placed = placed;
         stats->chunks = chunks.size();
         stats->launches = launches;
-        stats->seconds_gather = gather_s;
+        stats->seconds_gather = busiest;
         stats->seconds_device = ms * 1e-3;
         stats->seconds_total = std::chrono::duration<double>(clk::now() - t0).count();
+        stats->bytes_direct = direct_bytes;
+        stats->seconds_plan = plan_s;
     }
     return MXB_OK;
 }

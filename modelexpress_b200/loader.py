@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import mmap
 import os
+import threading
 import time
 from concurrent.futures import ThreadPoolExecutor
 from dataclasses import dataclass, field
@@ -26,12 +27,13 @@ from typing import Any
 import numpy as np
 
 from .layout import CheckpointPlan, plan_checkpoint
-from .runtime import PLACE_COPY_ENGINE, Context, PlaceResult, Ring, default_context
+from .runtime import (PLACE_COPY_ENGINE, Context, PlaceResult, Ring, default_context, host_register,
+                      host_unregister)
 from .safetensors_index import SAFETENSORS_DTYPES, checkpoint_index
 
 
-# The ring a load creates for itself.  Pinning host memory costs about 0.4 ms per MiB, inside
-# the time to loaded weights, and the pipeline is as fast with four 32 MiB slots as with 2 GiB.
+# The ring a load creates for itself: pinning host memory sits inside the time to loaded
+# weights, and the pipeline is as fast with four 32 MiB chunks as with a ring of gigabytes.
 RING_BYTES = 128 << 20
 RING_SLOTS = 4
 
@@ -56,22 +58,232 @@ class LoadResult:
 
 
 class FileImage:
-    """A checkpoint file mapped read-only; ``address`` is the host address of byte 0."""
+    """A checkpoint file mapped into host memory; ``address`` is the host address of byte 0.
 
-    def __init__(self, path: str):
+    ``pinnable`` maps the file privately with write permission (which the file's own
+    mode does not need to allow, and which never writes: nothing stores through the
+    mapping), the form ``mxb_host_register`` can pin.  ``pin_spans`` then page-locks
+    the byte ranges a rank keeps, after which ``mxb_place`` reads them with the copy
+    engine directly and no host thread copies a byte."""
+
+    def __init__(self, path: str, pinnable: bool = False):
         self.path = path
         self._f = open(path, "rb")
         self.size = os.fstat(self._f.fileno()).st_size
-        self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)
+        if pinnable:
+            self._mm = mmap.mmap(self._f.fileno(), 0, flags=mmap.MAP_PRIVATE,
+                                 prot=mmap.PROT_READ | mmap.PROT_WRITE)
+        else:
+            self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)
+        self.pinnable = pinnable
         self._np = np.frombuffer(self._mm, dtype=np.uint8)
         self.address = self._np.ctypes.data
+        self._pinned: list = []           # (base, nbytes) ranges registered by this image
+        self._pin_lock = threading.Lock()
+        self.pinned_bytes = 0
+        self.pin_seconds = 0.0
+
+    def pin_spans(self, spans, merge_gap: int = 1 << 20) -> int:
+        """Pin the union of ``(offset, nbytes)`` ranges of the file (page-aligned,
+        neighbours closer than ``merge_gap`` joined) that is not pinned yet; returns
+        the bytes newly pinned."""
+        if not self.pinnable:
+            raise RuntimeError(f"{self.path} was not mapped pinnable")
+        with self._pin_lock:
+            return self._pin_spans(spans, merge_gap)
+
+    def _pin_spans(self, spans, merge_gap: int) -> int:
+        page = mmap.PAGESIZE
+        want = sorted((int(o) // page * page, min(self.size, -(-(int(o) + int(n)) // page) * page))
+                      for o, n in spans if n)
+        merged: list = []
+        for lo, hi in want:
+            if merged and lo <= merged[-1][1] + merge_gap:
+                merged[-1][1] = max(merged[-1][1], hi)
+            else:
+                merged.append([lo, hi])
+        have = sorted((b - self.address, b - self.address + n) for b, n in self._pinned)
+        t0 = time.perf_counter()
+        added = 0
+        def pin(lo: int, hi: int) -> int:
+            base, n = host_register(self.address + lo, hi - lo)
+            self._pinned.append((base, n))
+            return n
+
+        for lo, hi in merged:
+            cur = lo                      # carve out what earlier calls pinned already
+            for plo, phi in have:
+                if phi <= cur:
+                    continue
+                if plo >= hi:
+                    break
+                if plo > cur:
+                    added += pin(cur, plo)
+                cur = max(cur, phi)
+            if cur < hi:
+                added += pin(cur, hi)
+        self.pinned_bytes += added
+        self.pin_seconds += time.perf_counter() - t0
+        return added
+
+    def unpin(self) -> None:
+        for base, _n in self._pinned:
+            host_unregister(base)
+        self._pinned = []
+        self.pinned_bytes = 0
 
     def close(self):
+        self.unpin()
         self._np = None
         try:
             self._mm.close()
         finally:
             self._f.close()
+
+
+class HostImages:
+    """Checkpoint files kept mapped (and, where asked, pinned) between loads of the same
+    process: the second load of a checkpoint — another replica, a reload after a weight
+    swap, the next refit from a host copy — finds its bytes page-locked and goes over
+    PCIe with no host copy.  Keyed by path, size and modification time."""
+
+    def __init__(self):
+        self._images: dict = {}
+        self._plans: dict = {}
+        self._lock = threading.Lock()
+
+    def prepared(self, model_path: str, tp_rank: int, tp_size: int, family: str) -> "Prepared":
+        """The parsed headers and the rank's placement plan of a checkpoint, kept for
+        as long as its files keep their size and modification time (the reference
+        keeps its transfer plan between refits the same way, receiver.py:553)."""
+        key = (os.path.realpath(model_path), int(tp_rank), int(tp_size), family)
+        with self._lock:
+            hit = self._plans.get(key)
+        if hit is not None and hit.fresh():
+            return hit
+        prep = Prepared.build(model_path, tp_rank, tp_size, family)
+        with self._lock:
+            self._plans[key] = prep
+        return prep
+
+    def open(self, path: str) -> FileImage:
+        st = os.stat(path)
+        key = (os.path.realpath(path), st.st_size, st.st_mtime_ns)
+        with self._lock:
+            im = self._images.get(key)
+            if im is None:
+                for k in [k for k in self._images if k[0] == key[0]]:   # the file changed
+                    self._images.pop(k).close()
+                im = self._images[key] = FileImage(path, pinnable=True)
+            return im
+
+    @property
+    def pinned_bytes(self) -> int:
+        return sum(im.pinned_bytes for im in self._images.values())
+
+    def close(self) -> None:
+        with self._lock:
+            for im in self._images.values():
+                im.close()
+            self._images = {}
+            self._plans = {}
+
+
+@dataclass
+class Prepared:
+    """Headers and placement plan of one checkpoint for one rank, with the record
+    geometry as arrays so that a load only has to add base addresses."""
+
+    index: dict
+    plan: CheckpointPlan
+    files: list                 # absolute paths, sorted
+    geometry: np.ndarray        # (n, 6) uint64: file offset, parameter offset, rows, row_bytes, pitches
+    file_of: np.ndarray         # (n,) index into files
+    stamps: tuple               # (dir mtime, ((path, size, mtime_ns), ...)) the plan was built from
+    model_path: str = ""
+    pinned_in: tuple = ()       # ids of the FileImages this rank's ranges are already pinned in
+
+    @staticmethod
+    def _stamps(model_path: str, files) -> tuple:
+        per_file = []
+        for p in files:
+            st = os.stat(p)
+            per_file.append((p, st.st_size, st.st_mtime_ns))
+        return (os.stat(model_path).st_mtime_ns if os.path.isdir(model_path) else 0, tuple(per_file))
+
+    @classmethod
+    def build(cls, model_path: str, tp_rank: int, tp_size: int, family: str) -> "Prepared":
+        index = checkpoint_index(model_path)
+        plan = plan_checkpoint({n: {"shape": i["shape"], "dtype": i["dtype"]} for n, i in index.items()},
+                               tp_rank, tp_size, family)
+        files = sorted({i["file"] for i in index.values()})
+        check_index(index, {p: os.path.getsize(p) for p in files})
+        geometry = np.empty((len(plan.placements), 6), dtype=np.uint64)
+        file_of = np.empty(len(plan.placements), dtype=np.int64)
+        where = {p: k for k, p in enumerate(files)}
+        for k, pl in enumerate(plan.placements):
+            info = index[pl.src_name]
+            geometry[k] = pl.record(int(info["file_offset"]), 0)
+            file_of[k] = where[info["file"]]
+        return cls(index, plan, files, geometry, file_of, cls._stamps(model_path, files), model_path)
+
+    def fresh(self) -> bool:
+        try:
+            return self._stamps(self.model_path, self.files) == self.stamps
+        except OSError:
+            return False
+
+    def items(self, file_address: dict, params: dict) -> np.ndarray:
+        """(n, 6) uint64 records: host source address -> device destination address."""
+        dst = np.empty(len(self.plan.placements), dtype=np.uint64)
+        for k, pl in enumerate(self.plan.placements):
+            t = params[pl.dst_name]
+            spec = self.plan.params[pl.dst_name]
+            if tuple(t.shape) != tuple(spec.shape) or not t.is_contiguous():
+                raise ValueError(f"{pl.dst_name}: destination tensor must be contiguous with shape "
+                                 f"{tuple(spec.shape)}, got {tuple(t.shape)}")
+            if t.element_size() != SAFETENSORS_DTYPES[pl.dtype][0]:
+                raise ValueError(f"{pl.dst_name}: element size differs from the checkpoint's {pl.dtype}")
+            dst[k] = t.data_ptr()
+        out = self.geometry.copy()
+        out[:, 0] += np.array([file_address[p] for p in self.files], dtype=np.uint64)[self.file_of]
+        out[:, 1] += dst
+        return out
+
+
+host_images = HostImages()
+
+
+def check_index(index: dict, sizes: dict) -> None:
+    """Every tensor's byte range must lie inside its file and match its shape; a
+    truncated or half-written shard fails here (``ValueError``) instead of letting a
+    copy run past the end of the mapping."""
+    for name, info in index.items():
+        elsize = SAFETENSORS_DTYPES[info["dtype"]][0]
+        numel = 1
+        for extent in info["shape"]:
+            numel *= int(extent)
+        if int(info["size"]) != numel * elsize:
+            raise ValueError(f"{name}: header gives {info['size']} bytes for shape {list(info['shape'])} "
+                             f"of {info['dtype']}")
+        if int(info["file_offset"]) + int(info["size"]) > sizes[info["file"]]:
+            raise ValueError(f"{name}: bytes [{info['file_offset']}, "
+                             f"{int(info['file_offset']) + int(info['size'])}) lie beyond the end of "
+                             f"{info['file']} ({sizes[info['file']]} bytes): truncated file?")
+
+
+def item_spans(items: np.ndarray, file_address: dict, sizes: dict | None = None) -> dict:
+    """{file: [(offset, nbytes)]}: the source byte span of every record."""
+    out: dict = {p: [] for p in file_address}
+    bases = sorted((a, p) for p, a in file_address.items())
+    for src, _dst, rows, rb, sp, _dp in items.tolist():
+        if not rows or not rb:
+            continue
+        for a, p in reversed(bases):
+            if src >= a:
+                out[p].append((src - a, (rows - 1) * sp + rb))
+                break
+    return out
 
 
 def torch_dtype(tag: str):
@@ -113,48 +325,98 @@ class PlacedCheckpoint:
     params: dict
     plan: CheckpointPlan
     stats: PlaceResult
+    timings: dict = field(default_factory=dict)   # seconds per phase of the call
 
 
 def place_checkpoint(model_path: str, tp_rank: int, tp_size: int, device=None, *,
                      params: dict | None = None, ring: Ring | None = None,
                      ctx: Context | None = None, host_threads: int | None = None,
                      mode: int = PLACE_COPY_ENGINE, family: str = "auto",
-                     ring_bytes: int = RING_BYTES, ring_slots: int = RING_SLOTS) -> PlacedCheckpoint:
+                     ring_bytes: int = RING_BYTES, ring_slots: int = RING_SLOTS,
+                     pin: str = "off", images: HostImages | None = None) -> PlacedCheckpoint:
     """Load this rank's tensor-parallel shards of a safetensors checkpoint.
 
     ``params`` may hold pre-allocated destination tensors (an engine's own
     parameters, keyed by the engine's names); otherwise they are allocated.
+
+    ``pin`` decides what happens to the host copy of the checkpoint:
+    ``"off"``   map the files, gather through the pinned ring, unmap (a one-off load);
+    ``"keep"``  keep the files mapped in ``images`` (default: the process-wide
+                ``host_images``) and page-lock the ranges this rank reads before
+                placing them, so that this and every later load of the same files is
+                read by the copy engine in place;
+    ``"after"`` place through the ring now (pinning is slower than one load) and
+                page-lock the ranges on a background thread for the loads to come.
     """
     import torch
 
+    if pin not in ("off", "keep", "after"):
+        raise ValueError(f"pin must be 'off', 'keep' or 'after', not {pin!r}")
+    timings: dict = {}
+    t_start = time.perf_counter()
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     if dev.type != "cuda":
         raise RuntimeError("place_checkpoint needs a CUDA device (no CPU fallback)")
     dev_index = dev.index if dev.index is not None else torch.cuda.current_device()
-    index = checkpoint_index(model_path)
-    plan = plan_checkpoint({n: {"shape": i["shape"], "dtype": i["dtype"]} for n, i in index.items()},
-                           tp_rank, tp_size, family)
+    cache = (images if images is not None else host_images) if pin != "off" else None
+    prep = (cache.prepared(model_path, tp_rank, tp_size, family) if cache is not None
+            else Prepared.build(model_path, tp_rank, tp_size, family))
+    index, plan = prep.index, prep.plan
+    timings["index_and_plan"] = time.perf_counter() - t_start
     own_ring = ring is None
     if ctx is None:
         ctx = ring.ctx if ring is not None else default_context(dev_index)
+    t = time.perf_counter()
     if ring is None:
         ring = ctx.ring(ring_bytes, ring_slots, dev_index)
+    timings["ring_create"] = time.perf_counter() - t
     if params is None:
         params = allocate_params(plan, dev)
+    else:
+        # bytes the checkpoint does not cover (vocabulary padding rows) must read as zero,
+        # as they do after the engine's own loader
+        for name, spec in plan.params.items():
+            if spec.zero_fill and name in params:
+                params[name].zero_()
     # the library works on its own streams: whatever the caller queued on torch's
     # stream for these tensors (allocation fills, earlier writes) must be done first
     torch.cuda.current_stream(dev).synchronize()
-    images = {}
+    opened = {}
     try:
-        for path in sorted({i["file"] for i in index.values()}):
-            images[path] = FileImage(path)
-        items = placement_items(plan, index, {p: im.address for p, im in images.items()}, params)
+        t = time.perf_counter()
+        for path in prep.files:
+            opened[path] = cache.open(path) if cache is not None else FileImage(path)
+        timings["map"] = time.perf_counter() - t
+        addresses = {p: im.address for p, im in opened.items()}
+        items = prep.items(addresses, params)
+        timings["pin"] = 0.0
+        ids = tuple(id(opened[p]) for p in prep.files)
+        if pin == "keep" and prep.pinned_in != ids:
+            t = time.perf_counter()
+            for p, spans in item_spans(items, addresses, None).items():
+                opened[p].pin_spans(spans)
+            prep.pinned_in = ids
+            timings["pin"] = time.perf_counter() - t
         # three quarters of the cores: the gather threads share DRAM bandwidth with the PCIe DMA
         threads = host_threads or max(2, min(32, (os.cpu_count() or 8) * 3 // 4))
+        t = time.perf_counter()
         stats = ring.place(items, threads, mode)
+        timings["place"] = time.perf_counter() - t
+        if pin == "after" and prep.pinned_in != ids:
+            spans = item_spans(items, addresses, None)
+
+            def pin_later():
+                for p, sp in spans.items():
+                    opened[p].pin_spans(sp)
+                prep.pinned_in = ids
+
+            bg = threading.Thread(target=pin_later, name="mxb-pin", daemon=True)
+            bg.start()
+            ctx._background.append(bg)
     finally:
-        _release(ctx, images.values(), ring if own_ring else None)
-    return PlacedCheckpoint(params, plan, stats)
+        _release(ctx, opened.values() if cache is None else (), ring if own_ring else None)
+    timings["total"] = time.perf_counter() - t_start
+    return PlacedCheckpoint(params, plan, stats, {k: round(v, 6) for k, v in timings.items()})
 
 
 @dataclass
@@ -289,7 +551,8 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
                    host_threads: int | None = None, mode: int = PLACE_COPY_ENGINE,
                    ring_bytes: int = RING_BYTES, ring_slots: int = RING_SLOTS,
                    on_unsupported: str = "engine", pipeline: bool = True,
-                   first_batch: int = 32, min_row_bytes: int = 16) -> CapturedPlacement:
+                   first_batch: int = 32, min_row_bytes: int = 16, pin: str = "off",
+                   images: HostImages | None = None) -> CapturedPlacement:
     """Load a safetensors checkpoint into ``model`` for ANY architecture whose
     engine-side ``load_weights`` only slices and copies.
 
@@ -307,7 +570,10 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
     real host tensors afterwards (so where two sources write the same bytes,
     the engine-loaded one wins), with ``"raise"`` the call fails before any
     byte is written.  ``stats.seconds_total`` spans the dry run and the
-    placement, which overlap (``pipeline``)."""
+    placement, which overlap (``pipeline``).  ``pin`` as in ``place_checkpoint``.
+    An exception of the engine's loader that arrives after the first batch has been
+    handed to the ring is re-raised as ``StrategyFailed(mutated=True)``: parameter
+    bytes have been overwritten by then."""
     import torch
 
     from .planner import apply_converts
@@ -322,11 +588,16 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
     own_ring = ring is None
     if ctx is None:
         ctx = ring.ctx if ring is not None else default_context(dev_index)
-    images: dict = {}
+    if pin not in ("off", "keep", "after"):
+        raise ValueError(f"pin must be 'off', 'keep' or 'after', not {pin!r}")
+    cache = (images if images is not None else host_images) if pin != "off" else None
+    images = {}
     pool = ThreadPoolExecutor(1)          # the ring is one pipeline: its calls run in order
+    made: list = []
     try:
         for path in sorted({i["file"] for i in index.values()}):
-            images[path] = FileImage(path)
+            images[path] = cache.open(path) if cache is not None else FileImage(path)
+        check_index(index, {p: im.size for p, im in images.items()})
         addresses = {p: im.address for p, im in images.items()}
         threads = host_threads or max(2, min(32, (os.cpu_count() or 8) * 3 // 4))
         names = list(index)
@@ -345,7 +616,6 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
         parts, pending, stagings = [], [], []
         timings = {"capture": 0.0, "ring_create": 0.0, "place_wait": 0.0, "engine": 0.0}
         t0 = time.perf_counter()
-        made = []
 
         def make_ring():
             # first job of the placing thread: pinning the ring overlaps the first dry-run batch
@@ -365,9 +635,14 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
                 return held[0].data_ptr()
 
             tc = time.perf_counter()
-            cap = captured_table(model, {n: index[n] for n in names[lo:hi]}, addresses,
-                                 load_weights=loader, device=dev, alloc_staging=alloc_staging,
-                                 dests=dests, state=state, min_row_bytes=min_row_bytes)
+            try:
+                cap = captured_table(model, {n: index[n] for n in names[lo:hi]}, addresses,
+                                     load_weights=loader, device=dev, alloc_staging=alloc_staging,
+                                     dests=dests, state=state, min_row_bytes=min_row_bytes)
+            except Exception as e:
+                if pending:     # earlier batches are already being written
+                    raise StrategyFailed(f"{type(e).__name__}: {e}", mutated=True) from e
+                raise
             timings["capture"] += time.perf_counter() - tc
             parts.append(cap)
             if cap.reasons and on_unsupported != "engine":
@@ -382,6 +657,11 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
                 # real side effects, e.g. zeroed vocabulary padding) queued on torch's
                 # stream must be done before these destinations are written
                 torch.cuda.current_stream(dev).synchronize()
+                if pin == "keep":
+                    tp = time.perf_counter()
+                    for p, spans in item_spans(cap.records, addresses).items():
+                        images[p].pin_spans(spans)
+                    timings["pin"] = timings.get("pin", 0.0) + time.perf_counter() - tp
                 pending.append(pool.submit(place_batch, cap.records))
         tc = time.perf_counter()
         if ring_job is not None:
@@ -400,9 +680,18 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
             loader((n, _engine_tensor(images[index[n]["file"]], index[n])) for n in leftover)
             timings["engine"] = time.perf_counter() - tc
         torch.cuda.current_stream(dev).synchronize()
+        if pin == "after":
+            spans_all: dict = {}
+            for part in parts:
+                for p, spans in item_spans(part.records, addresses).items():
+                    spans_all.setdefault(p, []).extend(spans)
+            bg = threading.Thread(target=lambda: [images[p].pin_spans(sp) for p, sp in spans_all.items()],
+                                  name="mxb-pin", daemon=True)
+            bg.start()
+            ctx._background.append(bg)
     finally:
         pool.shutdown(wait=True)
-        _release(ctx, images.values(), made[0] if own_ring and made else None)
+        _release(ctx, images.values() if cache is None else (), made[0] if own_ring and made else None)
     stats = PlaceResult(sum(r.bytes_placed for r in results), sum(r.chunks for r in results),
                         sum(r.launches for r in results), seconds,
                         sum(r.seconds_gather for r in results), sum(r.seconds_device for r in results))

@@ -17,6 +17,7 @@ from ._lib import (DIGEST_BLOCK64, DIGEST_ROWS, DIGEST_SAFE32, PLACE_COPY_ENGINE
                    PLACE_ZERO_COPY, SCATTER_VECTOR, SCATTER_DEFAULT, SCATTER_NO_SYNC, check)
 
 __all__ = ["Context", "Ring", "Fanout", "Table", "PlaceResult", "default_context",
+           "host_register", "host_unregister", "host_is_pinned",
            "DIGEST_SAFE32", "DIGEST_ROWS", "DIGEST_BLOCK64", "SCATTER_DEFAULT", "SCATTER_VECTOR",
            "SCATTER_NO_SYNC", "PLACE_COPY_ENGINE", "PLACE_ZERO_COPY"]
 
@@ -32,6 +33,8 @@ class PlaceResult:
     seconds_total: float
     seconds_gather: float
     seconds_device: float
+    bytes_direct: int = 0        # of bytes_placed: read from pinned sources, no host copy
+    seconds_plan: float = 0.0
 
 
 class Context:
@@ -203,7 +206,7 @@ class Ring:
         check(self.ctx._lib.mxb_place(self._h, arr, n, int(host_threads), int(mode), ctypes.byref(st)),
               "mxb_place")
         return PlaceResult(st.bytes_placed, st.chunks, st.launches, st.seconds_total,
-                           st.seconds_gather, st.seconds_device)
+                           st.seconds_gather, st.seconds_device, st.bytes_direct, st.seconds_plan)
 
     def close(self):
         with _close_lock:            # a background release and __del__ may both get here
@@ -282,6 +285,24 @@ def ipc_open(handle: bytes, offset: int) -> int:
     out = ctypes.c_uint64()
     check(lib.mxb_ipc_open(h, int(offset), ctypes.byref(out)), "mxb_ipc_open")
     return out.value
+
+
+def host_register(addr: int, nbytes: int) -> tuple:
+    """Pin host memory in place (``mxb_host_register``); returns the page-aligned
+    ``(base, nbytes)`` actually pinned, to be handed to ``host_unregister``."""
+    lib = _lib.load()
+    base, size = ctypes.c_uint64(), ctypes.c_uint64()
+    check(lib.mxb_host_register(int(addr), int(nbytes), ctypes.byref(base), ctypes.byref(size)),
+          "mxb_host_register")
+    return base.value, size.value
+
+
+def host_unregister(base: int) -> None:
+    check(_lib.load().mxb_host_unregister(int(base)), "mxb_host_unregister")
+
+
+def host_is_pinned(addr: int, nbytes: int) -> bool:
+    return bool(_lib.load().mxb_host_is_pinned(int(addr), int(nbytes)))
 
 
 _default: dict = {}

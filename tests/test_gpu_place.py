@@ -19,9 +19,12 @@ def ckpts(tmp_path_factory):
     tiny = str(tmp_path_factory.mktemp("tiny"))
     cfg = tiny_dense_config()
     synth.write_checkpoint(tiny, synth.dense_tensors(cfg), cfg.seed, cfg.files)
-    # the CPU-runnable benchmark configuration, with fewer vocabulary rows to keep the test short
+    # the CPU-runnable benchmark configuration exactly as stated: 4 layers, hidden 1024,
+    # intermediate 2816, 16 q / 4 kv heads of 64, vocabulary 32000, untied lm_head, one file
     small = str(tmp_path_factory.mktemp("small"))
-    scfg = synth.scaled(synth.SMALL_LLAMA, layers=2, vocab=8000)
+    scfg = synth.SMALL_LLAMA
+    assert (scfg.layers, scfg.hidden, scfg.intermediate, scfg.q_heads, scfg.kv_heads, scfg.head_dim,
+            scfg.vocab, scfg.seed) == (4, 1024, 2816, 16, 4, 64, 32000, 0)
     synth.write_checkpoint(small, synth.dense_tensors(scfg), scfg.seed, 1)
     return tiny, small
 
@@ -75,14 +78,89 @@ def test_small_llama_tp1_byte_exact(ckpts):
 
     _, small = ckpts
     full = read_full_tensors(small)
+    assert len(full) == 39 and sum(a.nbytes for a in full.values()) == 221_267_968
     placed = place_checkpoint(small, 0, 1, "cuda:0", ring_bytes=64 << 20, ring_slots=4, host_threads=4)
     want = R.load_and_shard(full, 0, 1)
     _check(placed, want)
+    assert placed.stats.bytes_placed == 221_267_968
     names = sorted(want)
     res = digest.digest_many([placed.params[n] for n in names])
     for n, r in zip(names, res):
         assert r["safe_checksum"] == R.safe_checksum(want[n]), n
         assert r["tensor_digest"] == R.tensor_digest(want[n]), n
+
+
+@pytest.mark.parametrize("mode", ["copy_engine", "zero_copy"])
+def test_pinned_host_image_is_read_in_place(ckpts, mode):
+    """Files kept mapped and page-locked (pin="keep"): the copy engine (or, in
+    zero-copy mode, the kernel) reads the slices where they lie, no byte goes
+    through the ring, and the shards are the oracle's for every rank."""
+    from modelexpress_b200.loader import HostImages, place_checkpoint
+    from modelexpress_b200.runtime import PLACE_COPY_ENGINE, PLACE_ZERO_COPY, Context
+
+    tiny, _ = ckpts
+    full = read_full_tensors(tiny)
+    ctx = Context([0])
+    ring = ctx.ring(8 << 20, 4, 0)
+    images = HostImages()
+    m = PLACE_COPY_ENGINE if mode == "copy_engine" else PLACE_ZERO_COPY
+    try:
+        for tp in (1, 8):
+            for rank in range(tp):
+                placed = place_checkpoint(tiny, rank, tp, "cuda:0", ring=ring, host_threads=4, mode=m,
+                                          pin="keep", images=images)
+                _check(placed, R.load_and_shard(full, rank, tp))
+                assert placed.stats.bytes_direct == placed.stats.bytes_placed == placed.plan.bytes_placed
+        assert images.pinned_bytes > 0
+        # a second load of the same rank pins nothing new
+        before = images.pinned_bytes
+        placed = place_checkpoint(tiny, 0, 8, "cuda:0", ring=ring, mode=m, pin="keep", images=images)
+        assert images.pinned_bytes == before and placed.timings["pin"] < 0.05
+    finally:
+        ring.close()
+        images.close()
+        ctx.close()
+
+
+def test_pin_after_the_first_load_and_mixed_sources(ckpts):
+    """pin="after": the first load goes through the ring, later ones find the ranges
+    pinned.  A call whose sources are partly pinned, partly pageable places both."""
+    import time
+
+    from modelexpress_b200.loader import HostImages, place_checkpoint
+    from modelexpress_b200.runtime import Context
+
+    _, small = ckpts
+    full = read_full_tensors(small)
+    want = R.load_and_shard(full, 1, 4)
+    ctx = Context([0])
+    ring = ctx.ring(32 << 20, 4, 0)
+    images = HostImages()
+    try:
+        first = place_checkpoint(small, 1, 4, "cuda:0", ring=ring, host_threads=4, pin="after", images=images)
+        _check(first, want)
+        assert first.stats.bytes_direct == 0
+        for t in ctx._background:
+            t.join()
+        assert images.pinned_bytes > 0
+        second = place_checkpoint(small, 1, 4, "cuda:0", ring=ring, host_threads=4, pin="after", images=images)
+        _check(second, want)
+        assert second.stats.bytes_direct == second.stats.bytes_placed
+        for t in ctx._background:
+            t.join()
+        # another rank of the same files: its column/vocab slices are new (pageable), the
+        # row-parallel tensors were pinned whole by rank 1 -> a mixed call
+        third = place_checkpoint(small, 2, 4, "cuda:0", ring=ring, host_threads=4, pin="off")
+        _check(third, R.load_and_shard(full, 2, 4))
+        mixed = place_checkpoint(small, 2, 4, "cuda:0", ring=ring, host_threads=4, pin="after", images=images)
+        _check(mixed, R.load_and_shard(full, 2, 4))
+        assert 0 < mixed.stats.bytes_direct < mixed.stats.bytes_placed
+    finally:
+        for t in ctx._background:
+            t.join()
+        ring.close()
+        images.close()
+        ctx.close()
 
 
 def test_vocab_padding_rows_are_zero(tmp_path):

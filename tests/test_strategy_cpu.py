@@ -56,3 +56,35 @@ def test_no_cpu_fallback():
         place_checkpoint("/nonexistent", 0, 1, "cpu")
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         place_captured(_WithLoader(), "/nonexistent", "cpu")
+
+
+def test_truncated_shard_is_an_expected_miss(tmp_path):
+    """A half-written safetensors file must fail before any copy is planned
+    (ValueError -> StrategyFailed(mutated=False)), not run past the mapping."""
+    import os
+
+    import pytest
+
+    from modelexpress_b200 import synth
+    from modelexpress_b200.loader import FileImage, check_index
+    from modelexpress_b200.safetensors_index import checkpoint_index
+
+    cfg = synth.DenseConfig("trunc", 1, 64, 128, 2, 2, 32, 256, False, 5, 1)
+    d = str(tmp_path)
+    synth.write_checkpoint(d, synth.dense_tensors(cfg), cfg.seed, 1)
+    idx = checkpoint_index(d)
+    path = next(iter({i["file"] for i in idx.values()}))
+    check_index(idx, {path: os.path.getsize(path)})
+    with open(path, "r+b") as f:
+        f.truncate(os.path.getsize(path) - 100)
+    im = FileImage(path)
+    try:
+        with pytest.raises(ValueError, match="truncated"):
+            check_index(idx, {path: im.size})
+    finally:
+        im.close()
+    bad = {n: dict(i) for n, i in idx.items()}
+    first = next(iter(bad))
+    bad[first]["size"] = bad[first]["size"] + 2
+    with pytest.raises(ValueError, match="header gives"):
+        check_index(bad, {path: 1 << 40})
