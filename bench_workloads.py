@@ -78,7 +78,72 @@ def _peaks():
         return 6650.0, "fallback (6.65 TB/s)"
 
 
-NVLINK_PEER_GBS = 770.0  # measured peer copy on this pool, per direction per GPU
+NVLINK_NOMINAL_GBS = 900.0  # NVLink 5, per direction per GPU
+
+
+class _Holder:
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+def as_tensor(ptr: int, nbytes: int, device: int):
+    """uint8 tensor over a raw device range (to fill and inspect library-owned arenas)."""
+    import torch
+
+    return torch.as_tensor(_Holder(int(ptr), int(nbytes)), device=f"cuda:{device}")
+
+
+def nvlink_peaks(ctx, rank, world, local, nbytes=1 << 30, reps=3) -> dict:
+    """What the links give a plain copy in this run, per direction: a 16-byte
+    store kernel and the copy engine, one pair alone and every GPU sending to its
+    neighbour at once."""
+    import torch
+
+    base = ctx.alloc(2 * nbytes, local)
+    peers = _open_peers(ctx, base, world)
+    mine = as_tensor(base, 2 * nbytes, local)
+    mine.zero_()
+    torch.cuda.synchronize()
+    nxt = (rank + 1) % world
+    out = {}
+    # one pair alone: rank 0 stores into rank 1
+    _barrier(world)
+    ms = ctx.copy_probe(base, peers[1] + nbytes, nbytes, reps, local) if rank == 0 else 0.0
+    _barrier(world)
+    out["store_kernel_one_pair_gbs"] = round(nbytes / (_max(ms, world) * 1e-3) / 1e9, 1)
+    # every GPU stores into its neighbour at once (each link direction carries one stream)
+    _barrier(world)
+    ms = ctx.copy_probe(base, peers[nxt] + nbytes, nbytes, reps, local)
+    _barrier(world)
+    out["store_kernel_all_pairs_gbs"] = round(nbytes / (_max(ms, world) * 1e-3) / 1e9, 1)
+    # the copy engine over the same mapping
+    dst = as_tensor(peers[nxt] + nbytes, nbytes, local)
+    src = mine[:nbytes]
+    dst.copy_(src)
+    torch.cuda.synchronize()
+    _barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        dst.copy_(src)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    _barrier(world)
+    out["copy_engine_all_pairs_gbs"] = round(nbytes / (_max(ms, world) * 1e-3) / 1e9, 1)
+    # local HBM copy with the same kernel, for scale
+    ms = ctx.copy_probe(base, base + nbytes, nbytes, reps, local)
+    out["store_kernel_local_hbm_gbs_read_plus_write"] = round(2 * nbytes / (_max(ms, world) * 1e-3) / 1e9, 1)
+    out["how"] = (f"{nbytes >> 20} MiB, {reps} launches each, CUDA events, slowest rank; store kernel = the "
+                  "library's plain 16-byte copy kernel writing into the peer's memory; copy engine = "
+                  "cudaMemcpyAsync to the peer mapping")
+    out["peak_gbs"] = max(out["store_kernel_one_pair_gbs"], out["store_kernel_all_pairs_gbs"],
+                          out["copy_engine_all_pairs_gbs"])
+    del dst, src, mine
+    _barrier(world)
+    ctx.free(base, local)
+    return out
 
 
 def _base(metric, value, unit, world, args, ms_per_step, config, dtype="u8", scaling="weak"):
@@ -189,33 +254,24 @@ def _layout_ranges(sizes, align=256):
     return offs, pos
 
 
-def run_fanout(args):
+def fanout_measure(args, ctx, rank, world, local, nv=None) -> dict:
     """Broadcast the 8B weights (TP=1 copy on GPU 0) to every other GPU, sweeping
-    the chunk size; with >= 2 GPUs also the rank-matched pair copy (first half of
-    the GPUs -> second half, two TP=8 shards each at 8 GPUs)."""
+    the chunk size; with an even GPU count also the rank-matched pair copy (first
+    half of the GPUs -> second half, two TP=8 shards each at 8 GPUs).  Comparison
+    line: ncclBroadcast of the same bytes.  Every destination is checked."""
     import torch
 
     from modelexpress_b200 import synth
     from modelexpress_b200.fanout import topology
-    from modelexpress_b200.runtime import DIGEST_BLOCK64, DIGEST_SAFE32, Context
+    from modelexpress_b200.runtime import DIGEST_BLOCK64, DIGEST_SAFE32
 
-    rank, world, local = _dist()
-    if world < 2:
-        if rank == 0:
-            print(json.dumps({"metric": "fan-out GB/s per target", "unavailable":
-                              "needs at least 2 GPUs (one process per GPU)"}))
-        return
-    ctx = Context([local])
+    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 3))
     cfg = synth.scaled(synth.LLAMA3_8B, layers=_env_int("MXB_BENCH_LAYERS", 32))
     sizes = [synth.tensor_nbytes(s, d) for _n, s, d, _k in synth.dense_tensors(cfg)]
     offs, total = _layout_ranges(sizes)
     payload = sum(sizes)
     base = ctx.alloc(total, local)
-    arena = None
-    # view the library-owned arena as a torch tensor only to fill / check it
-    from modelexpress_b200.torch_view import as_tensor
-
-    arena = as_tensor(base, total, local)
+    arena = as_tensor(base, total, local)   # only to fill / check the library-owned arena
     if rank == 0:
         g = torch.Generator(device="cuda")
         g.manual_seed(1)
@@ -224,47 +280,71 @@ def run_fanout(args):
         arena.zero_()
     torch.cuda.synchronize()
     peers = _open_peers(ctx, base, world)
-    kind = os.environ.get("MXB_FANOUT_TOPOLOGY", "chain")
-    children = topology(kind, world, 0)
-    sweep = {}
+    spans = [(base + o, n) for o, n in zip(offs, sizes)]
+    topologies = {}
+    kinds = os.environ.get("MXB_FANOUT_TOPOLOGY", "chain").split(",")
     chunks_mib = [int(x) for x in os.environ.get("MXB_FANOUT_CHUNKS", "1,4,16,64").split(",")]
-    src_digest = None
-    for mib in chunks_mib:
-        spans = [(base + o, n) for o, n in zip(offs, sizes)]
-        node = ctx.fanout(spans, mib << 20, local)
-        ctrs = _open_peers(ctx, node.counters, world)
-        for c in children[rank]:
-            node.add_child([(peers[c] + o, n) for o, n in zip(offs, sizes)], ctrs[c])
-        _barrier(world)
-        times = []
-        for it in range(args.warmup + args.steps):
-            if rank != 0:
-                arena.zero_()
-                torch.cuda.synchronize()
+    launches = 0
+    for kind in kinds:
+        children = topology(kind, world, 0)
+        sweep = {}
+        for mib in chunks_mib:
+            node = ctx.fanout(spans, mib << 20, local)
+            ctrs = _open_peers(ctx, node.counters, world)
+            for c in children[rank]:
+                node.add_child([(peers[c] + o, n) for o, n in zip(offs, sizes)], ctrs[c])
             _barrier(world)
-            t0 = time.perf_counter()
-            node.run(rank == 0, 20000)
-            ms = node.wait()
-            wall = (time.perf_counter() - t0) * 1e3
-            ms = _max(ms, world)
-            wall = _max(wall, world)
-            if it >= args.warmup:
-                times.append((ms, wall))
-        dev_ms = sum(t[0] for t in times) / len(times)
-        wall_ms = sum(t[1] for t in times) / len(times)
-        sweep[str(mib)] = {"device_ms": round(dev_ms, 3), "wall_ms": round(wall_ms, 3),
-                           "gbs_per_target": round(payload / (dev_ms * 1e-3) / 1e9, 1),
-                           "gbs_aggregate": round(payload * (world - 1) / (dev_ms * 1e-3) / 1e9, 1)}
-        # every destination range must digest like the source's
-        recs = ctx.digest(spans, DIGEST_SAFE32 | DIGEST_BLOCK64, local)
-        mine = [(int(r.safe_checksum), int(r.block_hash)) for r in recs]
-        alld = _gather_objects(mine, world)
-        if rank == 0:
+            times = []
+            for it in range(warmup + steps):
+                if rank != 0:
+                    arena.zero_()
+                    torch.cuda.synchronize()
+                _barrier(world)
+                t0 = time.perf_counter()
+                node.run(rank == 0, 20000)
+                ms = node.wait()
+                wall = (time.perf_counter() - t0) * 1e3
+                ms = _max(ms, world)
+                wall = _max(wall, world)
+                launches += 1
+                if it >= warmup:
+                    times.append((ms, wall))
+            dev_ms = sum(t[0] for t in times) / len(times)
+            wall_ms = sum(t[1] for t in times) / len(times)
+            sweep[str(mib)] = {"device_ms": round(dev_ms, 3), "wall_ms": round(wall_ms, 3),
+                               "gbs_per_target": round(payload / (dev_ms * 1e-3) / 1e9, 1),
+                               "gbs_aggregate": round(payload * (world - 1) / (dev_ms * 1e-3) / 1e9, 1)}
+            # every destination range must digest like the source's
+            recs = ctx.digest(spans, DIGEST_SAFE32 | DIGEST_BLOCK64, local)
+            mine = [(int(r.safe_checksum), int(r.block_hash)) for r in recs]
+            alld = _gather_objects(mine, world)
             for r in range(1, world):
                 if alld[r] != alld[0]:
-                    raise SystemExit(f"fan-out: rank {r} digests differ from the source (chunk {mib} MiB)")
+                    raise SystemExit(f"fan-out ({kind}): rank {r} digests differ from the source (chunk {mib} MiB)")
+            _barrier(world)
+            node.close()
+        best = max(sweep, key=lambda k: sweep[k]["gbs_per_target"])
+        topologies[kind] = {"chunk_sweep_mib": sweep, "best_chunk_mib": int(best),
+                            "gbs_per_target": sweep[best]["gbs_per_target"],
+                            "device_ms": sweep[best]["device_ms"]}
+    # comparison line: ncclBroadcast of the same arena
+    import torch.distributed as dist
+
+    nccl = None
+    if world > 1:
+        for _ in range(2):
+            dist.broadcast(arena, src=0)
+        torch.cuda.synchronize()
         _barrier(world)
-        node.close()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            dist.broadcast(arena, src=0)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = _max(e0.elapsed_time(e1) / steps, world)
+        nccl = {"device_ms": round(ms, 3), "gbs_per_target": round(total / (ms * 1e-3) / 1e9, 1),
+                "what": "torch.distributed.broadcast (ncclBroadcast) of the same arena, CUDA events, slowest rank"}
     # rank-matched pair copy: the first half of the GPUs each hold two TP=8 shards and
     # replicate them to the matching GPU of the second half (independent 1-hop copies)
     pairs = None
@@ -273,54 +353,81 @@ def run_fanout(args):
         shard = 2008031232
         pay = 2 * shard if total >= 2 * shard else (total // 512) * 256
         pspans = [(base, pay)]
+        if rank < half:
+            g = torch.Generator(device="cuda")
+            g.manual_seed(100 + rank)
+            arena[:pay].copy_(torch.randint(0, 256, (pay,), dtype=torch.uint8, device="cuda", generator=g))
+        torch.cuda.synchronize()
         node = ctx.fanout(pspans, 16 << 20, local)
         ctrs = _open_peers(ctx, node.counters, world)
         if rank < half:
             node.add_child([(peers[rank + half], pay)], ctrs[rank + half])
         _barrier(world)
         times = []
-        for it in range(args.warmup + args.steps):
+        for it in range(warmup + steps):
             if rank >= half:
                 arena[:pay].zero_()
                 torch.cuda.synchronize()
             _barrier(world)
             node.run(rank < half, 20000)
             ms = _max(node.wait(), world)
-            if it >= args.warmup:
+            launches += 1
+            if it >= warmup:
                 times.append(ms)
         recs = ctx.digest(pspans, DIGEST_SAFE32 | DIGEST_BLOCK64, local)
         alld = _gather_objects((int(recs[0].safe_checksum), int(recs[0].block_hash)), world)
-        if rank == 0:
-            for r in range(half):
-                if alld[r] != alld[r + half]:
-                    raise SystemExit(f"pair copy: GPU {r + half} differs from GPU {r}")
+        for r in range(half):
+            if alld[r] != alld[r + half]:
+                raise SystemExit(f"pair copy: GPU {r + half} differs from GPU {r}")
         pms = sum(times) / len(times)
         pairs = {"pairs": half, "bytes_per_pair": pay, "device_ms": round(pms, 3),
                  "gbs_per_pair": round(pay / (pms * 1e-3) / 1e9, 1),
                  "gbs_aggregate": round(pay * half / (pms * 1e-3) / 1e9, 1)}
         _barrier(world)
         node.close()
-    best = max(sweep, key=lambda k: sweep[k]["gbs_per_target"])
-    dev_ms = sweep[best]["device_ms"]
-    per_target = sweep[best]["gbs_per_target"]
-    out = _base("fan-out GB/s delivered per target (8B bf16 weights, GPU 0 -> all others)",
-                per_target, "GB/s", world, args, dev_ms,
-                {"workload": "configs[2]: 16.06 GB TP=1 copy on GPU 0 broadcast over NVLink P2P stores",
-                 "topology": kind, "payload_bytes": payload, "ranges": len(sizes),
-                 "chunk_sweep_mib": sweep, "best_chunk_mib": int(best), "rank_matched_pairs": pairs,
-                 "check": "safe_checksum and 64-bit block hash of every destination range equal the source"},
-                scaling="strong")
-    out["gpu_launches"] = (args.warmup + args.steps) * len(chunks_mib)
-    out["roofline"] = {"bound": "nvlink", "achieved": per_target, "peak": NVLINK_PEER_GBS, "unit": "GB/s",
-                       "frac": round(per_target / NVLINK_PEER_GBS, 4), "traffic": None,
-                       "kernel": "fanout_kernel",
-                       "peak_source": "measured peer copy, 770 GB/s per direction per GPU (900 nominal)"}
-    if rank == 0:
-        print(json.dumps(out), flush=True)
+    first = topologies[kinds[0]]
+    peak = (nv or {}).get("peak_gbs")
+    res = {"workload": "configs[2]: 16.06 GB TP=1 copy on GPU 0 broadcast over NVLink P2P stores",
+           "payload_bytes": payload, "ranges": len(sizes), "topology": kinds[0],
+           "gbs_per_target": first["gbs_per_target"], "device_ms": first["device_ms"],
+           "best_chunk_mib": first["best_chunk_mib"], "topologies": topologies,
+           "rank_matched_pairs": pairs, "nccl_broadcast": nccl, "gpu_launches": launches,
+           "frac_of_nominal_900": round(first["gbs_per_target"] / NVLINK_NOMINAL_GBS, 4),
+           "frac_of_measured_peak": round(first["gbs_per_target"] / peak, 4) if peak else None,
+           "check": "ok: safe_checksum and 64-bit block hash of every destination range equal the source, "
+                    "every topology and chunk size; pair copies equal their sources"}
+    del arena
     ctx.free(base, local)
-    ctx.close()
+    return res
+
+
+def run_fanout(args):
     import torch.distributed as dist
 
+    from modelexpress_b200.runtime import Context
+
+    rank, world, local = _dist()
+    if world < 2:
+        if rank == 0:
+            print(json.dumps({"metric": "fan-out GB/s per target", "unavailable":
+                              "needs at least 2 GPUs (one process per GPU)"}))
+        return
+    ctx = Context([local])
+    nv = nvlink_peaks(ctx, rank, world, local)
+    res = fanout_measure(args, ctx, rank, world, local, nv)
+    out = _base("fan-out GB/s delivered per target (8B bf16 weights, GPU 0 -> all others)",
+                res["gbs_per_target"], "GB/s", world, args, res["device_ms"],
+                {k: v for k, v in res.items() if k not in ("gpu_launches",)}, scaling="strong")
+    out["config"]["nvlink_measured"] = nv
+    out["gpu_launches"] = res["gpu_launches"]
+    out["roofline"] = {"bound": "nvlink", "achieved": res["gbs_per_target"], "peak": nv["peak_gbs"],
+                       "unit": "GB/s", "frac": res["frac_of_measured_peak"], "traffic": None,
+                       "kernel": "fanout_kernel",
+                       "peak_source": "best plain peer copy measured in this run, per direction per GPU "
+                                      "(900 GB/s nominal)"}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    ctx.close()
     dist.destroy_process_group()
 
 
@@ -339,23 +446,22 @@ def _pattern_words(torch, param_id: int, w0: int, n: int, device):
     return ((idx * _PAT_A + param_id * _PAT_B) & 0xFFFFFFFF).to(torch.int32)
 
 
-def run_reshard(args):
+def reshard_measure(args, ctx, rank, world, local, nv=None) -> dict:
     """FSDP-8 flat shards -> TP-8 parameters with fused qkv_proj / gate_up_proj.
     The 8 trainer ranks and 8 inference ranks are spread round-robin over the
     available GPUs (8 GPUs: one each); every source rank pushes its records with
-    one scatter launch, stores to other GPUs crossing NVLink."""
+    one scatter launch, stores to other GPUs crossing NVLink.  Comparison line:
+    an all_to_all_single (NCCL grouped send/recv) of the bytes that cross."""
     import torch
 
     from modelexpress_b200 import layout, reshard, synth
-    from modelexpress_b200.torch_view import as_tensor
-    from modelexpress_b200.runtime import Context
+    from modelexpress_b200.runtime import SCATTER_VECTOR
 
-    rank, world, local = _dist()
+    steps, warmup = max(1, min(args.steps, 10)), max(1, min(args.warmup, 3))
     R = 8
     if R % world:
         raise SystemExit("reshard bench: the GPU count must divide 8")
-    ctx = Context([local])
-    cfg = synth.scaled(synth.QWEN25_32B, layers=_env_int("MXB_BENCH_LAYERS", 64))
+    cfg = synth.scaled(synth.QWEN25_32B, layers=_env_int("MXB_RESHARD_LAYERS", 64))
     tensors = synth.dense_tensors(cfg)
     index = {n: {"shape": list(s), "dtype": d} for n, s, d, _k in tensors}
     pid = {n: i for i, (n, _s, _d, _k) in enumerate(tensors)}
@@ -379,7 +485,7 @@ def run_reshard(args):
     peer_params = _open_peers(ctx, param_base, world)
     param_bases = [peer_params[t % world] + (t // world) * pa.total for t in range(R)]
     t0 = time.perf_counter()
-    tables, nbytes, remote, nrecs = [], 0, 0, 0
+    nbytes, remote, nrecs = 0, 0, 0
     all_recs = []
     for j, r in enumerate(mine):
         recs = reshard.plan_reshard(index, R, R, r, shard_base + j * sa.total, param_bases, "dense",
@@ -391,24 +497,21 @@ def run_reshard(args):
         remote += int((recs[far, 2] * recs[far, 3]).sum())
         all_recs.append(recs)
     # one resident table (one launch) per GPU for all the logical ranks it hosts
-    tables.append(ctx.table(np.concatenate(all_recs), local))
+    table = ctx.table(np.concatenate(all_recs), local)
     plan_s = time.perf_counter() - t0
-    from modelexpress_b200.runtime import SCATTER_VECTOR
-
     flags = SCATTER_VECTOR if os.environ.get("MXB_SCATTER", "auto") == "vec" else 0
     times = []
-    for it in range(args.warmup + args.steps):
+    for it in range(warmup + steps):
         _barrier(world)
         torch.cuda.synchronize()
         ctx.event_record(0, local)
-        for tb in tables:
-            tb.launch(flags)
+        table.launch(flags)
         ctx.event_record(1, local)
         ms = ctx.event_elapsed_ms(0, 1, local)
         ctx.sync(local)
         _barrier(world)
         ms = _max(ms, world)
-        if it >= args.warmup:
+        if it >= warmup:
             times.append(ms)
     ms = sum(times) / len(times)
     # check every destination parameter hosted here against the pattern
@@ -417,7 +520,6 @@ def run_reshard(args):
         plan = plans[t]
         for pl in plan.placements:
             so, do, rows, rb, sp, dp = pl.geometry()
-            base_w = 0
             dst0 = j * pa.total + pa.offsets[pl.dst_name] + do
             # compare row by row in bulk: build expected words for the strided source region
             r_idx = torch.arange(rows, dtype=torch.int64, device="cuda").unsqueeze(1)
@@ -434,41 +536,102 @@ def run_reshard(args):
     bad = int(_max(float(bad), world))
     if bad:
         raise SystemExit(f"reshard bench: {bad} placements differ from the expected pattern")
+    engine = table.engine(flags)
+    table.close()
+    # comparison line: the bytes that cross NVLink as one all_to_all_single (the local HBM
+    # copies and the fused concat would come on top of it)
+    nccl = None
+    if world > 1:
+        import torch.distributed as dist
+
+        per_peer = (remote // max(1, world - 1)) // 256 * 256
+        send = params_t[: per_peer * world]
+        recv = shards_t[: per_peer * world]
+        for _ in range(2):
+            dist.all_to_all_single(recv, send)
+        torch.cuda.synchronize()
+        _barrier(world)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            dist.all_to_all_single(recv, send)
+        e1.record()
+        torch.cuda.synchronize()
+        a2a = _max(e0.elapsed_time(e1) / steps, world)
+        nccl = {"device_ms": round(a2a, 3), "bytes_per_peer": per_peer,
+                "gbs_received_per_gpu": round(per_peer * (world - 1) / (a2a * 1e-3) / 1e9, 1),
+                "what": "torch.distributed.all_to_all_single (NCCL grouped send/recv) of the cross-GPU bytes "
+                        "only; the reshard's local copies and concatenation are not in it"}
     total_bytes = sum(p.bytes_placed for p in plans)
-    written_per_gpu = nbytes
+    peak_hbm, src = _peaks()
+    link = (nv or {}).get("peak_gbs") or NVLINK_NOMINAL_GBS
+    # per GPU: local records are read and written here; remote ones are read here, and as many
+    # bytes arrive from the peers and are written here
+    hbm_time = 2.0 * nbytes / (peak_hbm * 1e9)
+    bound_meas = max(hbm_time, remote / (link * 1e9))
+    bound_nom = max(hbm_time, remote / (NVLINK_NOMINAL_GBS * 1e9))
+    res = {"workload": "configs[3]: Qwen2.5-32B shapes, 771 parameters, 65.5 GB, flat 8-way FSDP shards -> "
+                       "vLLM TP=8 layout with fused qkv_proj / gate_up_proj",
+           "layers": cfg.layers, "seconds": round(ms * 1e-3, 6), "device_ms": round(ms, 4),
+           "bytes_written_total": total_bytes, "bytes_pushed_per_gpu": nbytes,
+           "bytes_crossing_nvlink_per_gpu": remote, "records_per_gpu": nrecs,
+           "plan_seconds": round(plan_s, 3),
+           "gbs_written_aggregate": round(total_bytes / (ms * 1e-3) / 1e9, 1),
+           "nvlink_gbs_per_gpu": round(remote / (ms * 1e-3) / 1e9, 1),
+           "engine": engine, "gpu_launches": warmup + steps,
+           "bound_seconds_measured_peaks": round(bound_meas, 6),
+           "bound_seconds_nominal_900": round(bound_nom, 6),
+           "frac_of_measured_bound": round(bound_meas / (ms * 1e-3), 4),
+           "frac_of_nominal_bound": round(bound_nom / (ms * 1e-3), 4),
+           "bound_how": f"max(HBM: 2 x bytes pushed per GPU / {peak_hbm} GB/s {src}; NVLink: bytes "
+                        f"crossing per GPU / link rate ({link} GB/s measured in this run, 900 nominal))",
+           "nccl_all_to_all": nccl,
+           "check": "ok: every destination word equals the position pattern of its source element"}
+    del shards_t, params_t
+    ctx.free(shard_base, local)
+    ctx.free(param_base, local)
+    return res, cfg, R
+
+
+def run_reshard(args):
+    from modelexpress_b200.runtime import Context
+
+    rank, world, local = _dist()
+    ctx = Context([local])
+    nv = nvlink_peaks(ctx, rank, world, local) if world > 1 else None
+    res, cfg, R = reshard_measure(args, ctx, rank, world, local, nv)
     out = _base("refit reshard seconds (Qwen2.5-32B bf16, FSDP-8 -> TP-8, fused qkv/gate_up)",
-                ms * 1e-3, "s", world, args, ms,
-                {"workload": "configs[3]: 771 parameters, 65.5 GB, flat 8-way shards -> vLLM TP=8 layout",
-                 "layers": cfg.layers, "bytes_written_total": total_bytes,
-                 "bytes_pushed_per_gpu": written_per_gpu, "bytes_crossing_nvlink_per_gpu": remote,
-                 "records_per_gpu": nrecs, "plan_seconds": round(plan_s, 3),
-                 "gbs_written_aggregate": round(total_bytes / (ms * 1e-3) / 1e9, 1),
-                 "check": "every destination word equals the position pattern of its source element"},
-                scaling="strong")
+                res["seconds"], "s", world, args, res["device_ms"],
+                {k: v for k, v in res.items() if k != "gpu_launches"}, scaling="strong")
+    out["config"]["nvlink_measured"] = nv
     out["higher_is_better"] = False
-    out["gpu_launches"] = len(tables) * (args.warmup + args.steps)
-    peak, src = _peaks()
-    hbm_time = 2.0 * (written_per_gpu - remote) / (peak * 1e9) + 1.0 * remote / (peak * 1e9)
-    link_time = remote / (NVLINK_PEER_GBS * 1e9)
-    bound = max(hbm_time, link_time)
-    out["roofline"] = {"bound": "nvlink" if link_time > hbm_time else "hbm",
-                       "achieved": round(ms * 1e-3, 6), "peak": round(bound, 6), "unit": "s",
-                       "frac": round(bound / (ms * 1e-3), 4), "traffic": None,
-                       "kernel": "scatter_bulk_kernel (+ scatter_vec_kernel for unaligned records)"
-                       if tables and tables[0].engine(flags) != "vector" else "scatter_vec_kernel",
-                       "peak_source": f"max(local copy bytes x2 / {peak} GB/s {src}, NVLink bytes / "
-                                      f"{NVLINK_PEER_GBS} GB/s measured peer copy)"}
+    out["gpu_launches"] = res["gpu_launches"]
+    out["roofline"] = {"bound": "nvlink" if world > 1 else "hbm", "achieved": res["seconds"],
+                       "peak": res["bound_seconds_measured_peaks"], "unit": "s",
+                       "frac": res["frac_of_measured_bound"], "traffic": None,
+                       "kernel": "scatter_bulk_kernel + scatter_vec_kernel" if res["engine"] != "vector"
+                       else "scatter_vec_kernel", "peak_source": res["bound_how"]}
     if rank == 0 and world == 1 and os.environ.get("MXB_BENCH_SKIP_CPU") != "1":
         out["cpu_baseline"] = _reshard_cpu_baseline(cfg, R)
     if rank == 0:
         print(json.dumps(out), flush=True)
-    for tb in tables:
-        tb.close()
     ctx.close()
     if world > 1:
         import torch.distributed as dist
 
         dist.destroy_process_group()
+
+
+def multi_gpu_section(args, ctx, rank, world, local) -> dict:
+    """Fan-out and refit reshard on the GPUs of this run, with the link rates a plain
+    copy reaches measured first; attached to the placement line when N > 1."""
+    out = {"gpus": world}
+    nv = nvlink_peaks(ctx, rank, world, local)
+    out["nvlink_measured"] = nv
+    out["fanout"] = fanout_measure(args, ctx, rank, world, local, nv)
+    if 8 % world == 0:
+        out["reshard"] = reshard_measure(args, ctx, rank, world, local, nv)[0]
+    return out
 
 
 def _reshard_cpu_baseline(cfg, R):

@@ -183,6 +183,14 @@ uint64_t mxb_table_bytes(mxb_table *t);
 int32_t mxb_table_engine(mxb_table *t, uint32_t flags);
 int32_t mxb_table_destroy(mxb_table *t);
 
+/* Measurement aid (no counterpart in the reference): `reps` launches of a plain
+ * 16-byte load/store copy kernel from `src` to `dst` (multiples of 16 bytes)
+ * on `dev`, timed with CUDA events; either side may be a peer GPU's memory.
+ * Gives the rate a straightforward kernel reaches on the same memory path, the
+ * yardstick the scatter, fan-out and reshard rates are reported against. */
+int32_t mxb_copy_probe(mxb_ctx *ctx, int32_t dev, uint64_t src, uint64_t dst, uint64_t nbytes,
+                       int32_t reps, float *ms_per_rep);
+
 /* Timing on the context's compute stream of `dev`: record event `slot`
  * (0..15); elapsed waits for event `b` and returns b - a in milliseconds. */
 int32_t mxb_event_record(mxb_ctx *ctx, int32_t dev, int32_t slot);
@@ -255,11 +263,13 @@ int32_t mxb_block_hashes(mxb_ctx *ctx, int32_t dev, uint64_t ptr, uint64_t nbyte
  * Limits, checked before anything is queued (MXB_ERR_ARG with a message): at
  * most 256 ranges and at most 16384 tiles of 64 KiB (1 GiB) per call; larger
  * jobs are split by the caller.  The first call on a device looks up the
- * array's device address; make that call outside any stream capture.  All
- * calls on a device share the one array (it keeps the previous call's
- * contents; the accumulators a call uses are cleared by that call), so the
- * library serialises callers on the host; work that a caller queues on other
- * streams to run at the same time against this array would race. */
+ * array's device address.  Every call copies its small tables from and to
+ * ordinary host memory and waits for `stream` to drain, so no call may be made
+ * while `stream` (or any stream of the device) is being captured.  All calls on
+ * a device share the one array (it keeps the previous call's contents; the
+ * accumulators a call uses are cleared by that call), so the library
+ * serialises callers on the host; work that a caller queues on other streams
+ * to run at the same time against this array would race. */
 int32_t mxb_digest_noalloc(int32_t dev, const mxb_span *spans, uint64_t n, uint32_t modes,
                            mxb_digest_out *out, void *stream);
 

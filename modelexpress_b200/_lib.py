@@ -81,6 +81,7 @@ SIGNATURES = {
     "mxb_table_bytes": (u64, [_vp]),
     "mxb_table_engine": (i32, [_vp, u32]),
     "mxb_table_destroy": (i32, [_vp]),
+    "mxb_copy_probe": (i32, [_vp, i32, u64, u64, u64, i32, _P(ctypes.c_float)]),
     "mxb_event_record": (i32, [_vp, i32, i32]),
     "mxb_event_elapsed": (i32, [_vp, i32, i32, i32, _P(ctypes.c_float)]),
     "mxb_ring_create": (i32, [_vp, i32, u64, u32, _P(_vp)]),

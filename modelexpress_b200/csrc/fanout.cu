@@ -159,6 +159,9 @@ __global__ void __launch_bounds__(32) fanout_bulk_kernel(FanArgs a) {
     if (first >= a.n_pieces) return;
     const uint64_t mine = (a.n_pieces - first + gridDim.x - 1) / gridDim.x;
     bool failed = false;
+    // A ragged piece takes its stage without loading into it, so a stage's barrier phase
+    // follows the number of loads that went through that stage, not the piece index.
+    uint32_t waits_done[kFanStages] = {};
 
     // wait for the piece's chunk (unless root) and start its load; warp-uniform result
     auto start_piece = [&](uint64_t k) -> bool {
@@ -195,7 +198,8 @@ __global__ void __launch_bounds__(32) fanout_bulk_kernel(FanArgs a) {
         }
         if (a.n_children) {
             if ((pc.nbytes & 15u) == 0) {
-                const uint32_t parity = (uint32_t)((k / kFanStages) & 1);
+                const uint32_t parity = waits_done[s] & 1u;
+                ++waits_done[s];
                 bool ok = false;
                 for (uint32_t spin = 0; spin < (1u << 24); ++spin) {
                     ok = __all_sync(0xffffffffu, mbar_try_wait(&full[s], parity));

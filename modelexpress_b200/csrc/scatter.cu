@@ -321,6 +321,23 @@ scatter_bulk_kernel(const mxb_desc2d *__restrict__ descs, const Tile *__restrict
     }
 }
 
+// A plain copy: 16-byte loads and stores, four in flight per thread, grid-stride.  The
+// yardstick the other kernels' achieved rates are compared with on the same memory path
+// (HBM to HBM, or stores into a peer over NVLink).
+__global__ void __launch_bounds__(512) copy_probe_kernel(const uint4 *__restrict__ src,
+                                                         uint4 *__restrict__ dst, uint64_t n16) {
+    const uint64_t stride = (uint64_t)gridDim.x * 512;
+    uint64_t i = (uint64_t)blockIdx.x * 512 + threadIdx.x;
+    for (; i + 3 * stride < n16; i += 4 * stride) {
+        const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], e = src[i + 3 * stride];
+        dst[i] = a;
+        dst[i + stride] = b;
+        dst[i + 2 * stride] = c;
+        dst[i + 3 * stride] = e;
+    }
+    for (; i < n16; i += stride) dst[i] = src[i];
+}
+
 // ---------------------------------------------------------------------------
 // launcher
 // ---------------------------------------------------------------------------
@@ -588,6 +605,46 @@ int32_t mxb_table_destroy(mxb_table *t) {
     cudaStreamSynchronize(t->dv->stream);
     if (t->dev_buf) cudaFree(t->dev_buf);
     delete t;
+    return MXB_OK;
+}
+
+int32_t mxb_copy_probe(mxb_ctx *ctx, int32_t dev, uint64_t src, uint64_t dst, uint64_t nbytes,
+                       int32_t reps, float *ms_per_rep) {
+    if (!ctx || !src || !dst || !ms_per_rep || reps < 1 || nbytes < 16 || ((src | dst | nbytes) & 15u)) {
+        set_error("mxb_copy_probe: addresses and size must be multiples of 16 bytes");
+        return MXB_ERR_ARG;
+    }
+    DeviceState *d = ctx->find(dev);
+    if (!d) {
+        set_error("device %d is not part of this context", dev);
+        return MXB_ERR_ARG;
+    }
+    DeviceGuard g(dev);
+    std::lock_guard<std::mutex> lk(*d->mu);
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    MXB_CUDA(cudaEventCreate(&e0));
+    MXB_CUDA(cudaEventCreate(&e1));
+    const uint64_t n16 = nbytes / 16;
+    const unsigned grid = (unsigned)d->sm_count * 4;
+    copy_probe_kernel<<<grid, 512, 0, d->stream>>>(reinterpret_cast<const uint4 *>(src),
+                                                   reinterpret_cast<uint4 *>(dst), n16);  // warm
+    cudaEventRecord(e0, d->stream);
+    for (int32_t r = 0; r < reps; ++r)
+        copy_probe_kernel<<<grid, 512, 0, d->stream>>>(reinterpret_cast<const uint4 *>(src),
+                                                       reinterpret_cast<uint4 *>(dst), n16);
+    cudaEventRecord(e1, d->stream);
+    cudaError_t e = cudaEventSynchronize(e1);
+    float ms = 0.f;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (e != cudaSuccess) {
+        set_error("mxb_copy_probe: %s", cudaGetErrorString(e));
+        cudaGetLastError();
+        return MXB_ERR_CUDA;
+    }
+    ctx->launches.fetch_add((uint64_t)reps + 1);
+    *ms_per_rep = ms / reps;
     return MXB_OK;
 }
 

@@ -363,12 +363,11 @@ def place_checkpoint(model_path: str, tp_rank: int, tp_size: int, device=None, *
             else Prepared.build(model_path, tp_rank, tp_size, family))
     index, plan = prep.index, prep.plan
     timings["index_and_plan"] = time.perf_counter() - t_start
-    own_ring = ring is None
     if ctx is None:
         ctx = ring.ctx if ring is not None else default_context(dev_index)
     t = time.perf_counter()
     if ring is None:
-        ring = ctx.ring(ring_bytes, ring_slots, dev_index)
+        ring = ctx.cached_ring(ring_bytes, ring_slots, dev_index)   # made once, kept for later loads
     timings["ring_create"] = time.perf_counter() - t
     if params is None:
         params = allocate_params(plan, dev)
@@ -414,7 +413,7 @@ def place_checkpoint(model_path: str, tp_rank: int, tp_size: int, device=None, *
             bg.start()
             ctx._background.append(bg)
     finally:
-        _release(ctx, opened.values() if cache is None else (), ring if own_ring else None)
+        _release(ctx, opened.values() if cache is None else (), None)
     timings["total"] = time.perf_counter() - t_start
     return PlacedCheckpoint(params, plan, stats, {k: round(v, 6) for k, v in timings.items()})
 
@@ -449,9 +448,8 @@ class _Leftovers:
 
 def _release(ctx: Context, images, ring: Ring | None) -> None:
     """What a load leaves behind is torn down off the caller's path: unmapping the
-    checkpoint files (tens of milliseconds of page-table work for a fresh mapping of
-    a tmpfs file) and unpinning a one-shot ring (tens of milliseconds, now and then
-    most of a second); the loaded weights wait for neither."""
+    checkpoint files is tens of milliseconds of page-table work for a fresh mapping of
+    a tmpfs file; the loaded weights do not wait for it."""
     ctx.release_later(_Leftovers(images, ring))
 
 
@@ -585,7 +583,6 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
     loader = load_weights if load_weights is not None else model.load_weights
     index = checkpoint_index(model_path)
     dests = model_destinations(model)
-    own_ring = ring is None
     if ctx is None:
         ctx = ring.ctx if ring is not None else default_context(dev_index)
     if pin not in ("off", "keep", "after"):
@@ -620,7 +617,7 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
         def make_ring():
             # first job of the placing thread: pinning the ring overlaps the first dry-run batch
             tc = time.perf_counter()
-            made.append(ctx.ring(ring_bytes, ring_slots, dev_index))
+            made.append(ctx.cached_ring(ring_bytes, ring_slots, dev_index))
             timings["ring_create"] = time.perf_counter() - tc
 
         def place_batch(records):
@@ -691,7 +688,7 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
             ctx._background.append(bg)
     finally:
         pool.shutdown(wait=True)
-        _release(ctx, images.values() if cache is None else (), made[0] if own_ring and made else None)
+        _release(ctx, images.values() if cache is None else (), None)
     stats = PlaceResult(sum(r.bytes_placed for r in results), sum(r.chunks for r in results),
                         sum(r.launches for r in results), seconds,
                         sum(r.seconds_gather for r in results), sum(r.seconds_device for r in results))

@@ -32,6 +32,10 @@ caller's (``install`` argument), as ``_install`` is the subclass's in the refere
 
 from __future__ import annotations
 
+import json
+import logging
+import math
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Callable
@@ -40,7 +44,8 @@ from .planner import (ShardSpec, SourceSpec, apply_converts, convert_staging_byt
                       plan_transfer_2d)
 from .runtime import Context, Table, default_context
 
-__all__ = ["PublishedShard", "PublishedTensor", "merge_shard_tables", "build_sources",
+__all__ = ["IncompleteRefit", "check_coverage", "check_throughput_ceiling",
+           "PublishedShard", "PublishedTensor", "merge_shard_tables", "build_sources",
            "encode_shard_table", "decode_shard_table", "decode_shard_entries", "publish_local_shards",
            "ReshardReceiver", "SHARD_TABLE_SCHEMA"]
 
@@ -178,6 +183,72 @@ def build_sources(tensors: list, map_address: Callable | None = None) -> dict:
     return sources
 
 
+logger = logging.getLogger("modelexpress_b200.refit")
+
+
+class IncompleteRefit(RuntimeError):
+    """The refit was planned without error and still writes too few of the engine's
+    parameter bytes (refit/reshard/types.py:27-35): not a geometry problem, so it is
+    a type of its own that handlers for unplannable sources do not swallow."""
+
+
+_TRUTHY = ("1", "true", "yes", "on")
+
+
+def _env(name: str, default: str = "") -> str:
+    """``MXB_<name>``, else the reference's ``MX_<name>`` (envs.py:65-75), read at call time."""
+    v = os.environ.get("MXB_" + name)
+    return v if v is not None else os.environ.get("MX_" + name, default)
+
+
+def _env_float(name: str, default: float) -> float:
+    try:
+        return float(_env(name, str(default)))
+    except ValueError:
+        return default
+
+
+def check_coverage(coverage: float, written_bytes: int, engine_bytes: int, missed: list,
+                   n_params: int) -> None:
+    """The coverage gate of refit/reshard/receiver.py:746-755.  Opt-in
+    (``RESHARD_REQUIRE_FULL_COVERAGE``): partial refits are a feature, but a refit
+    that is meant to be complete and leaves parameters at their previous values
+    passes every digest check, because bytes that are never requested are never
+    checked.  ``RESHARD_COVERAGE_FLOOR`` (default 0.995) leaves room for derived
+    buffers that are not refit material."""
+    if _env("RESHARD_REQUIRE_FULL_COVERAGE").strip().lower() not in _TRUTHY:
+        return
+    floor = _env_float("RESHARD_COVERAGE_FLOOR", 0.995)
+    if coverage < floor:
+        raise IncompleteRefit(
+            f"refit covers {100.0 * coverage:.2f}% of the engine's parameter bytes "
+            f"({written_bytes} of {engine_bytes}); {len(missed)} of {n_params} params would keep their "
+            f"previous values, e.g. {sorted(missed)[:5]}. Set MXB_RESHARD_REQUIRE_FULL_COVERAGE=0 for "
+            f"an intentionally partial refit.")
+
+
+def check_throughput_ceiling(step: int, wire_bytes: int, wire_s: float, rank: int = 0) -> None:
+    """Refuse a rate the links cannot produce (refit/reshard/receiver.py:1045-1106):
+    such a step did not move its payload, whatever the completions say, so it is
+    reported as failed instead of being filed as the fastest one.  The ceiling
+    (``RESHARD_MAX_GBPS``, gigabits per second per rank, 0 or a non-finite value =
+    off) is the operator's: on one box it is NVLink ingress plus local HBM."""
+    ceiling = _env_float("RESHARD_MAX_GBPS", 0.0)
+    if not math.isfinite(ceiling) or ceiling <= 0 or wire_bytes <= 0 or wire_s <= 0:
+        return
+    implied = wire_bytes * 8 / wire_s / 1e9
+    if implied <= ceiling:
+        return
+    detail = {"schema": "refit-impossible-throughput-v1", "rank": rank, "step": step,
+              "wire_bytes": wire_bytes, "wire_s": round(wire_s, 6), "implied_gbps": round(implied, 1),
+              "ceiling_gbps": ceiling}
+    logger.warning("MX_REFIT_IMPOSSIBLE_THROUGHPUT %s", json.dumps(detail))
+    raise RuntimeError(
+        f"[reshard] step {step} moved {wire_bytes} bytes in {wire_s:.4f}s, an implied {implied:.1f} Gbps "
+        f"against a per-rank ceiling of {ceiling:.1f} Gbps. The links cannot deliver that, so the step "
+        f"did not move its payload. Treat this refit as failed, not fast.")
+
+
 class ReshardReceiver:
     """One inference rank's refit cycle: ``prepare`` once, ``update_weights`` per step."""
 
@@ -238,6 +309,8 @@ class ReshardReceiver:
                     {id(p): p for p in self.model.parameters()}.values())
         moved = int((table[:, 2] * table[:, 3]).sum()) if len(table) else 0
         used = {c.src_name for c in cap.copies}
+        all_params = {id(p): n for n, p in self.model.named_parameters()}
+        missed = sorted(set(all_params.values()) - planned)
         self.plan = {
             "copies": len(cap.copies), "records": int(len(table)), "bytes_per_step": moved,
             "converts": [c.param_name for c in converts], "params_written": len(planned),
@@ -245,7 +318,13 @@ class ReshardReceiver:
             "sources_unused": sorted(set(sources) - used),
             "engine": self._table.engine() if self._table is not None else "none",
             "prepare_capture_s": round(t_capture, 6),
+            "params_missed": missed,
             "prepare_total_s": round(time.perf_counter() - t0, 6)}
+        try:
+            check_coverage(self.plan["coverage"], moved, total, missed, len(all_params))
+        except IncompleteRefit:
+            self.close()
+            raise
         return self.plan
 
     # ------------------------------------------------------------------- verify
@@ -295,7 +374,12 @@ class ReshardReceiver:
         t1 = time.perf_counter()
         if self._table is not None:
             self._table.launch()
+            # the launch only queues the kernel on the library's own stream: wait for it (and
+            # learn of a device-side wait that ran out) before anything reads what it wrote
+            self.ctx.sync(self._dev)
         stages["read_s"] = time.perf_counter() - t1
+        # before anything reads or installs what the step wrote
+        check_throughput_ceiling(int(step), int(self.plan.get("bytes_per_step", 0)), stages["read_s"])
         t2 = time.perf_counter()
         if self._converts:
             apply_converts(self._converts, self._staging, self._dests)

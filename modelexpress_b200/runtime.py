@@ -48,12 +48,32 @@ class Context:
         check(self._lib.mxb_ctx_create(ids, len(self.devices), ctypes.byref(h)), "mxb_ctx_create")
         self._h = h
         self._background: list = []   # threads still releasing objects of this context
+        self._rings: dict = {}        # (dev, bytes, slots) -> Ring kept between loads
+        self._rings_lock = threading.Lock()
+
+    def cached_ring(self, ring_bytes: int, slots: int, dev: int | None = None) -> "Ring":
+        """The staging ring loads of this context share.  Pinning host memory and allocating
+        the device staging cost more than a tenth of a 2 GB load, so the ring a load makes is
+        kept for the next one (``drop_cached_rings`` gives the memory back)."""
+        key = (self._dev(dev), int(ring_bytes), int(slots))
+        with self._rings_lock:
+            ring = self._rings.get(key)
+            if ring is None or ring._h is None:
+                ring = self._rings[key] = Ring(self, key[0], key[1], key[2])
+            return ring
+
+    def drop_cached_rings(self) -> None:
+        with self._rings_lock:
+            rings, self._rings = list(self._rings.values()), {}
+        for r in rings:
+            r.close()
 
     def close(self):
         if getattr(self, "_h", None):
             for t in self._background:
                 t.join()
             self._background = []
+            self.drop_cached_rings()
             self._lib.mxb_ctx_destroy(self._h)
             self._h = None
 
@@ -121,6 +141,13 @@ class Context:
 
     def table(self, descs, dev: int | None = None) -> "Table":
         return Table(self, self._dev(dev), descs)
+
+    def copy_probe(self, src: int, dst: int, nbytes: int, reps: int = 3, dev: int | None = None) -> float:
+        """Milliseconds per launch of the plain copy kernel (``mxb_copy_probe``)."""
+        ms = ctypes.c_float(0.0)
+        check(self._lib.mxb_copy_probe(self._h, self._dev(dev), int(src), int(dst), int(nbytes), int(reps),
+                                       ctypes.byref(ms)), "mxb_copy_probe")
+        return float(ms.value)
 
     def event_record(self, slot: int, dev: int | None = None) -> None:
         check(self._lib.mxb_event_record(self._h, self._dev(dev), int(slot)), "mxb_event_record")

@@ -23,9 +23,14 @@ def torch_mod():
     return torch
 
 
-def test_golden_digests_through_the_kernel(torch_mod):
+@pytest.mark.parametrize("engine", ["vector", "bulk"])
+def test_golden_digests_through_the_kernel(torch_mod, engine, monkeypatch):
+    """Both tile engines (the default vector one and the shared-memory-staged one
+    that MXB_DIGEST_ENGINE=bulk selects for full tiles of aligned ranges)."""
     torch = torch_mod
     from modelexpress_b200 import digest
+
+    monkeypatch.setenv("MXB_DIGEST_ENGINE", engine)
 
     cases = json.load(open(os.path.join(G, "digests.json")))
     tensors = [torch.from_numpy(digest_case_bytes(c).copy()).cuda() for c in cases]
@@ -46,9 +51,12 @@ def test_golden_digests_through_the_kernel(torch_mod):
         digest.safe_checksum(torch.zeros(4))  # CPU tensor: no fallback
 
 
-def test_large_seeded_tensor_matches_oracle(torch_mod):
+@pytest.mark.parametrize("engine", ["vector", "bulk"])
+def test_large_seeded_tensor_matches_oracle(torch_mod, engine, monkeypatch):
     torch = torch_mod
     from modelexpress_b200 import digest
+
+    monkeypatch.setenv("MXB_DIGEST_ENGINE", engine)
 
     b = golden_bytes(42, (64 << 20) + 4096 * 3 + 1234 * 4 + 3)
     t = torch.from_numpy(b).cuda()

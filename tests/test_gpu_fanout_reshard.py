@@ -16,16 +16,21 @@ def _spans(torch, tensors):
     return [(t.data_ptr(), t.numel() * t.element_size()) for t in tensors]
 
 
-def test_fanout_single_gpu_loopback():
+@pytest.mark.parametrize("engine", ["vector", "bulk"])
+def test_fanout_single_gpu_loopback(engine, monkeypatch):
     """Root pushes to a 'child' on the same device; then the child's kernel runs
-    and finds every chunk counter already satisfied."""
+    and finds every chunk counter already satisfied.  Both copy engines; the ranges
+    whose size is not a multiple of 16 are followed by a range of a thousand pieces,
+    so that every CTA of the bulk engine reuses each of its shared-memory stages
+    after a piece that took a stage without loading into it."""
     import torch
 
     from modelexpress_b200 import digest
     from modelexpress_b200.runtime import Context
 
+    monkeypatch.setenv("MXB_FANOUT_ENGINE", engine)
     ctx = Context([0])
-    sizes = [1 << 20, 4096 + 16, 333 * 16, 100, 5 << 20, 48]
+    sizes = [1 << 20, 4096 + 16, 333 * 16, 100, 5 << 20, 52, 64 << 20, 48]
     src = [torch.from_numpy(golden_bytes(20 + i, n)).cuda() for i, n in enumerate(sizes)]
     dst = [torch.zeros(n, dtype=torch.uint8, device="cuda") for n in sizes]
     torch.cuda.synchronize()
@@ -340,3 +345,71 @@ def test_reshard_receiver_prepare_once_update_every_step():
     with pytest.raises(ValueError, match="inconsistent shape/dtype"):
         merge_shard_tables([[PublishedTensor("q", "torch.bfloat16", 2, (512, 512), [])],
                             [PublishedTensor("q", "torch.bfloat16", 2, (256, 512), [])]])
+
+
+@pytest.mark.gpu
+def test_update_weights_returns_with_the_bytes_in_place():
+    """update_weights must not return before the scatter kernel has finished: a
+    payload of several hundred MB with a dtype-changing source (staged, then cast)
+    is compared right after the call returns, and the reported read time must be
+    that of the copy, not of its enqueue."""
+    import torch
+
+    from modelexpress_b200.planner import ShardSpec, SourceSpec
+    from modelexpress_b200.refit import IncompleteRefit, ReshardReceiver
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    rows, cols = 16384, 8192                      # 256 MiB of bf16
+
+    class Engine(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.big = torch.nn.Parameter(torch.zeros(rows, cols, dtype=torch.bfloat16))
+            self.gate = torch.nn.Parameter(torch.zeros(2048, cols, dtype=torch.float32))   # cast on the way in
+            self.untouched = torch.nn.Parameter(torch.ones(4096, dtype=torch.bfloat16))
+
+        def load_weights(self, weights):
+            for name, w in weights:
+                if name == "big":
+                    self.big.data.copy_(w)
+                elif name == "gate":
+                    self.gate.data.copy_(w)
+
+    g = torch.Generator(device="cuda")
+    g.manual_seed(11)
+    big = torch.randn(rows, cols, device="cuda", generator=g).to(torch.bfloat16)
+    gate = torch.randn(2048, cols, device="cuda", generator=g).to(torch.bfloat16)
+    sources = {
+        "big": SourceSpec((rows, cols), torch.bfloat16, 2,
+                          [ShardSpec((0, 0), (rows, cols), "t0", big.data_ptr(), 2)]),
+        "gate": SourceSpec((2048, cols), torch.bfloat16, 2,
+                           [ShardSpec((0, 0), (2048, cols), "t0", gate.data_ptr(), 2)]),
+    }
+    model = Engine().cuda()
+    rx = ReshardReceiver(model, device="cuda:0")
+    plan = rx.prepare(sources)
+    assert plan["converts"] == ["gate"] and plan["params_missed"] == ["untouched"]
+    for step in range(3):
+        model.big.data.zero_()
+        model.gate.data.zero_()
+        torch.cuda.synchronize()
+        st = rx.update_weights(step)
+        # no synchronize here: what the call returned must already be true
+        assert torch.equal(model.big.data, big), step
+        assert torch.equal(model.gate.data, gate.float()), step
+        assert st["read_s"] > 50e-6 and st["gbps"] < 20000, st     # a copy of 288 MiB, not an enqueue
+        big.add_(1.0)
+        gate.mul_(0.5)
+        torch.cuda.synchronize()
+    rx.close()
+    # the coverage gate: 'untouched' keeps its old value, which an opted-in complete refit refuses
+    import os
+
+    os.environ["MXB_RESHARD_REQUIRE_FULL_COVERAGE"] = "1"
+    os.environ["MXB_RESHARD_COVERAGE_FLOOR"] = "0.999999"
+    try:
+        with pytest.raises(IncompleteRefit, match="untouched"):
+            ReshardReceiver(model, device="cuda:0").prepare(sources)
+    finally:
+        del os.environ["MXB_RESHARD_REQUIRE_FULL_COVERAGE"], os.environ["MXB_RESHARD_COVERAGE_FLOOR"]

@@ -90,3 +90,48 @@ def test_shard_table_wire_blob_is_the_references():
     assert b'"digest": null' not in want
     with pytest.raises(ValueError, match="schema"):
         decode_shard_table(want.replace(b"shard_table.v1", b"shard_table.v9"))
+
+
+def test_coverage_gate_is_opt_in_and_names_what_is_missed(monkeypatch):
+    """receiver.py:746-755: off by default (partial refits are a feature); with the
+    switch on, a plan below the floor raises IncompleteRefit, not a planning error."""
+    from modelexpress_b200.refit import IncompleteRefit, check_coverage
+
+    monkeypatch.delenv("MXB_RESHARD_REQUIRE_FULL_COVERAGE", raising=False)
+    monkeypatch.delenv("MX_RESHARD_REQUIRE_FULL_COVERAGE", raising=False)
+    check_coverage(0.5, 50, 100, ["a", "b"], 4)                      # off: nothing happens
+    monkeypatch.setenv("MXB_RESHARD_REQUIRE_FULL_COVERAGE", "true")
+    check_coverage(0.9999, 9999, 10000, [], 4)                       # above the default floor 0.995
+    with pytest.raises(IncompleteRefit, match=r"50.00%.*2 of 4 params.*\['a', 'b'\]"):
+        check_coverage(0.5, 50, 100, ["b", "a"], 4)
+    assert not issubclass(IncompleteRefit, ValueError) and issubclass(IncompleteRefit, RuntimeError)
+    monkeypatch.setenv("MXB_RESHARD_COVERAGE_FLOOR", "0.4")
+    check_coverage(0.5, 50, 100, ["a"], 4)                           # floor lowered per model
+    # the reference's own variable names are honoured where ours are unset
+    monkeypatch.delenv("MXB_RESHARD_REQUIRE_FULL_COVERAGE")
+    monkeypatch.delenv("MXB_RESHARD_COVERAGE_FLOOR")
+    monkeypatch.setenv("MX_RESHARD_REQUIRE_FULL_COVERAGE", "1")
+    with pytest.raises(IncompleteRefit):
+        check_coverage(0.9, 90, 100, ["a"], 4)
+
+
+def test_throughput_ceiling_refuses_an_impossible_step(monkeypatch, caplog):
+    """receiver.py:1045-1106 with fabricated timings: off unless configured, a
+    non-finite ceiling disables it, a rate above it aborts after logging the record."""
+    import logging
+
+    from modelexpress_b200.refit import check_throughput_ceiling
+
+    monkeypatch.delenv("MXB_RESHARD_MAX_GBPS", raising=False)
+    monkeypatch.delenv("MX_RESHARD_MAX_GBPS", raising=False)
+    check_throughput_ceiling(1, 40_610_000_000, 0.84)                # off
+    for off in ("nan", "inf", "0", "-5", "junk"):
+        monkeypatch.setenv("MXB_RESHARD_MAX_GBPS", off)
+        check_throughput_ceiling(1, 40_610_000_000, 0.0001)
+    monkeypatch.setenv("MXB_RESHARD_MAX_GBPS", "191")
+    check_throughput_ceiling(2, 40_610_000_000, 2.0)                 # 162 Gbps: fine
+    check_throughput_ceiling(2, 0, 0.001)                            # nothing moved: nothing to judge
+    with caplog.at_level(logging.WARNING, logger="modelexpress_b200.refit"):
+        with pytest.raises(RuntimeError, match=r"implied 386\.8 Gbps against a per-rank ceiling of 191\.0"):
+            check_throughput_ceiling(3, 40_610_000_000, 0.84)        # the reference's own anecdote
+    assert "MX_REFIT_IMPOSSIBLE_THROUGHPUT" in caplog.text and '"step": 3' in caplog.text

@@ -5,8 +5,10 @@ engine whose KV cache already owns every free byte of HBM, for one), so
 ``mxb_digest_noalloc`` works out of a fixed array inside the library.  This
 test calls it through the C ABI twice in a row on different data and checks
 every field against ``mxb_digest``; the second call also proves that what the
-first call left in the shared array does not leak into the next result.  It is
-collected last on purpose."""
+first call left in the shared array does not leak into the next result.  The
+second round also reads the device's free memory immediately before and after
+the allocation-free calls (the first round has loaded every kernel they use):
+the figure must not move.  It is collected last on purpose."""
 
 import ctypes
 
@@ -32,7 +34,6 @@ def test_noalloc_digest_matches_the_allocating_entry_point():
     assert torch.cuda.is_available()
     lib = _lib.load()
     ctx = Context([0])
-    free_before = torch.cuda.mem_get_info(0)[0]
     for call, seed in enumerate((301, 302)):
         sizes = [5 << 20, 4096 * 3 + 7, 65536, 1, 0, (1 << 20) + 4 * 511 + 2, 100_000 + call]
         bufs = [torch.from_numpy(golden_bytes(seed + i, n)).cuda() for i, n in enumerate(sizes)]
@@ -42,15 +43,20 @@ def test_noalloc_digest_matches_the_allocating_entry_point():
         want = ctx.digest(spans, 7, 0)
         arr, n = _lib.span_array(spans)
         out = (_lib.DigestOut * n)()
+        out2 = (_lib.DigestOut * n)()
+        s = torch.cuda.Stream()
+        torch.cuda.synchronize()
+        # nothing between the two readings allocates on the host side of this test either
+        free_before = torch.cuda.mem_get_info(0)[0]
         rc = lib.mxb_digest_noalloc(0, arr, n, 7, out, None)
-        assert rc == 0, lib.mxb_last_error()
+        # on a caller-provided stream too
+        rc2 = lib.mxb_digest_noalloc(0, arr, n, 2, out2, ctypes.c_void_p(s.cuda_stream))
+        free_after = torch.cuda.mem_get_info(0)[0]
+        assert rc == 0 and rc2 == 0, lib.mxb_last_error()
+        if call == 1:   # round 0 loaded the kernels; from here on the device's free memory must not move
+            assert free_after == free_before, (free_before, free_after)
         for i in range(n):
             assert _records_equal(out[i], want[i]), (call, i, sizes[i] if i < len(sizes) else "view")
-        # on a caller-provided stream too
-        s = torch.cuda.Stream()
-        out2 = (_lib.DigestOut * n)()
-        rc = lib.mxb_digest_noalloc(0, arr, n, 2, out2, ctypes.c_void_p(s.cuda_stream))
-        assert rc == 0, lib.mxb_last_error()
         for i in range(n):
             assert int(out2[i].row_sum) == int(want[i].row_sum)
             assert int(out2[i].row_sum_w) == int(want[i].row_sum_w)
@@ -67,4 +73,3 @@ def test_noalloc_digest_matches_the_allocating_entry_point():
     del bufs, views, big
     torch.cuda.synchronize()
     ctx.close()
-    assert free_before > 0
