@@ -35,6 +35,8 @@ extern "C" {
 #define MXB_ERR_PEER (-6)    /* peer access / IPC mapping unavailable */
 #define MXB_ERR_NOMEM (-7)
 #define MXB_ERR_STATE (-8)   /* object used in the wrong state */
+#define MXB_ERR_UNSUPPORTED (-9) /* geometry that is not a permuted box of its source
+                                    (UnsupportedReshard, refit/reshard/types.py:21-24) */
 
 typedef struct mxb_ctx mxb_ctx;
 typedef struct mxb_ring mxb_ring;
@@ -140,6 +142,65 @@ int32_t mxb_ipc_open(const uint8_t handle[64], uint64_t offset, uint64_t *out_pt
 int32_t mxb_ipc_close(uint64_t ptr, uint64_t offset);
 
 /* ---- descriptor compiler (host) ---------------------------------------- */
+
+#define MXB_MAX_DIMS 8
+
+/* A strided window of a row-major source tensor and where it lands: what a
+ * loader's chain of view ops (narrow, slicing, transpose, permute, select)
+ * leaves of a checkpoint tensor, i.e. RecordedCopy after its op-chain has been
+ * replayed (refit/reshard/types.py:57-70, slice_plan.py:136-168).  Offsets,
+ * shapes and strides are in elements. */
+typedef struct {
+    int32_t ndim_src;                    /* rank of the full source tensor */
+    int32_t ndim_win;                    /* rank of the window = rank of the destination view */
+    int32_t keep_rank;                   /* 1: the window must have the source's rank (the
+                                            reference's rule); 0: size-1 window dims are ignored
+                                            and source dims the window does not walk have extent 1 */
+    uint32_t elsize;                     /* bytes per element */
+    int64_t global_shape[MXB_MAX_DIMS];  /* shape of the full source tensor */
+    int64_t win_offset;                  /* first element of the window in the full tensor */
+    int64_t win_shape[MXB_MAX_DIMS];
+    int64_t win_stride[MXB_MAX_DIMS];    /* in elements of the full tensor */
+    int64_t dst_offset;                  /* element offset from the destination base */
+    int64_t dst_stride[MXB_MAX_DIMS];    /* destination stride of each window dim */
+} mxb_window;
+
+/* One published shard: a box of the full tensor held contiguously (row-major)
+ * at `addr` (Shard, refit/reshard/slice_plan.py:54-70). */
+typedef struct {
+    int32_t ndim;
+    int32_t reserved;
+    int64_t offset[MXB_MAX_DIMS];
+    int64_t shape[MXB_MAX_DIMS];
+    uint64_t addr;
+} mxb_shard;
+
+/* Records that read exactly the window `w` out of `shards` and write it at
+ * `dst_base` (+ w->dst_offset elements): the box of the window in source
+ * coordinates, intersected with every shard box, one record per innermost
+ * strided dimension; expanding the records row by row gives the run list of
+ * plan_pull (refit/reshard/slice_plan.py:227-339: resolve_slice,
+ * _view_to_box_perm, intersect, paired_runs) in the same order.  `out_shard`
+ * (optional, cap entries) receives the index of the shard each record reads.
+ * *n_out is the number of records the plan has; MXB_ERR_NOMEM if cap is
+ * smaller (the first cap records are written), MXB_ERR_UNSUPPORTED if the
+ * window is not a permuted box of the source. */
+int32_t mxb_plan_pull(const mxb_window *w, const mxb_shard *shards, uint64_t n_shards,
+                      uint64_t dst_base, mxb_desc2d *out, uint32_t *out_shard, uint64_t cap,
+                      uint64_t *n_out);
+
+/* The part of `n` strided regions of a flat tensor that one rank's contiguous
+ * piece [shard_lo, shard_hi) of that tensor holds: regions[i].src is a byte
+ * offset inside the full tensor, regions[i].dst the destination address of
+ * the region's first byte.  Emitted records read from src_base + (byte -
+ * shard_lo) and keep the region's destination layout; records larger than
+ * max_record_bytes (0 = no limit) are cut into whole rows or 256-byte
+ * multiples.  This is the push-side plan of the refit reshard for the flat
+ * FSDP shard geometry of modelexpress_rl/train/engines/fsdp/publisher.py:71-147
+ * (the reference plans the same slices as pulls, slice_plan.py:297-339). */
+int32_t mxb_plan_reshard(const mxb_desc2d *regions, uint64_t n, uint64_t shard_lo, uint64_t shard_hi,
+                         uint64_t src_base, uint64_t max_record_bytes, mxb_desc2d *out, uint64_t cap,
+                         uint64_t *n_out);
 
 /* Fold consecutive runs of equal length and constant src/dst stride into 2-D
  * records, preserving order.  Returns the number of records written (<= cap),

@@ -15,7 +15,9 @@ LIB_PATH = os.path.join(PKG, "libmxb200.so")
 
 OK = 0
 ERR_NAMES = {-1: "MXB_ERR_ARG", -2: "MXB_ERR_BOUNDS", -3: "MXB_ERR_ALIGN", -4: "MXB_ERR_CUDA",
-             -5: "MXB_ERR_TIMEOUT", -6: "MXB_ERR_PEER", -7: "MXB_ERR_NOMEM", -8: "MXB_ERR_STATE"}
+             -5: "MXB_ERR_TIMEOUT", -6: "MXB_ERR_PEER", -7: "MXB_ERR_NOMEM", -8: "MXB_ERR_STATE",
+             -9: "MXB_ERR_UNSUPPORTED"}
+MAX_DIMS = 8
 
 DIGEST_SAFE32, DIGEST_ROWS, DIGEST_BLOCK64 = 1, 2, 4
 SCATTER_DEFAULT, SCATTER_VECTOR, SCATTER_NO_SYNC = 0, 1, 2
@@ -42,6 +44,17 @@ class DigestOut(ctypes.Structure):
     _fields_ = [("nbytes", u64), ("row_sum", u64), ("row_sum_w", u64), ("tail_sum", u64),
                 ("tail_sum_w", u64), ("ragged_sum", u64), ("block_hash", u64),
                 ("safe_checksum", u32), ("reserved", u32)]
+
+
+class Window(ctypes.Structure):
+    _fields_ = [("ndim_src", i32), ("ndim_win", i32), ("keep_rank", i32), ("elsize", u32),
+                ("global_shape", i64 * MAX_DIMS), ("win_offset", i64), ("win_shape", i64 * MAX_DIMS),
+                ("win_stride", i64 * MAX_DIMS), ("dst_offset", i64), ("dst_stride", i64 * MAX_DIMS)]
+
+
+class Shard(ctypes.Structure):
+    _fields_ = [("ndim", i32), ("reserved", i32), ("offset", i64 * MAX_DIMS), ("shape", i64 * MAX_DIMS),
+                ("addr", u64)]
 
 
 class PlaceStats(ctypes.Structure):
@@ -74,6 +87,8 @@ SIGNATURES = {
     "mxb_ipc_open": (i32, [_P(ctypes.c_uint8), u64, _P(u64)]),
     "mxb_ipc_close": (i32, [u64, u64]),
     "mxb_coalesce_runs": (i64, [_P(Run), u64, _P(Desc2D), u64]),
+    "mxb_plan_pull": (i32, [_P(Window), _P(Shard), u64, u64, _P(Desc2D), _P(u32), u64, _P(u64)]),
+    "mxb_plan_reshard": (i32, [_P(Desc2D), u64, u64, u64, u64, u64, _P(Desc2D), u64, _P(u64)]),
     "mxb_scatter": (i32, [_vp, i32, _P(Desc2D), u64, u32]),
     "mxb_read_runs": (i32, [_vp, i32, _P(Run), u64]),
     "mxb_table_create": (i32, [_vp, i32, _P(Desc2D), u64, _P(_vp)]),

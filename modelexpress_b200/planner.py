@@ -234,12 +234,61 @@ def box_records(overlap, src_origin, src_strides, dst_origin, dst_strides, elsiz
     return out
 
 
+def copy_window(copy, global_shape) -> tuple:
+    """(offset, shape, stride, keep_rank) of the source window ``copy`` reads: the
+    reference's op-chain replayed (slice_plan.py:136-168), or the window a
+    ``geometry.ViewCopy`` already carries."""
+    if hasattr(copy, "src_stride"):
+        offset, shape, stride, keep_rank = copy.src_offset, copy.src_shape, copy.src_stride, False
+    else:
+        view = _View(global_shape)
+        for op, args, _kw in copy.op_chain:
+            view.apply(op, args)
+        offset, shape, stride, keep_rank = view.offset, view.shape, view.stride, True
+    if len(shape) == len(copy.dest_shape) and tuple(copy.dest_shape) != tuple(shape):
+        raise UnsupportedReshard(
+            f"{copy.param_name}: destination {tuple(copy.dest_shape)} != view {tuple(shape)}")
+    if len(shape) != len(copy.dest_shape):
+        raise UnsupportedReshard("rank change")
+    return int(offset), [int(x) for x in shape], [int(x) for x in stride], keep_rank
+
+
 def plan_pull_2d(copy, global_shape, src_dtype, elsize, shards, dst_base: int):
     """Records that read exactly the slice ``copy`` needs out of ``shards`` and
     write it at ``dst_base`` (the parameter's data pointer).  Returns a list of
     ``(session, records)`` in shard order; raises ``UnsupportedReshard`` for a
     dtype mismatch or a non-view op-chain, ``ValueError`` for rank-mismatched
-    shard geometry (as the reference does)."""
+    shard geometry (as the reference does).  The geometry is compiled by the
+    library (``mxb_plan_pull``); ``plan_pull_2d_py`` is the same in Python."""
+    from . import _lib
+    from .runtime import plan_pull
+
+    if src_dtype != copy.dest_dtype:
+        raise UnsupportedReshard(f"{copy.param_name}: dtype conversion required")
+    offset, shape, stride, keep_rank = copy_window(copy, global_shape)
+    nd = len(global_shape)
+    if max(nd, len(shape)) > _lib.MAX_DIMS:
+        return plan_pull_2d_py(copy, global_shape, src_dtype, elsize, shards, dst_base)
+    for sh in shards:
+        if not len(sh.shard_offset) == len(sh.shape) == nd:
+            raise ValueError("shard rank does not match the source rank")
+    try:
+        recs, which = plan_pull(global_shape, int(elsize), offset, shape, stride, int(copy.dest_offset),
+                                [int(x) for x in copy.dest_stride],
+                                [(sh.shard_offset, sh.shape, int(sh.addr)) for sh in shards],
+                                int(dst_base), keep_rank)
+    except _lib.MxbError as e:
+        if e.code == -9:
+            raise UnsupportedReshard(str(e)) from e
+        raise
+    out = []
+    for k in sorted(set(which.tolist())):
+        out.append((shards[k].session, recs[which == k]))
+    return out
+
+
+def plan_pull_2d_py(copy, global_shape, src_dtype, elsize, shards, dst_base: int):
+    """``plan_pull_2d`` without the library (the planner's Python statement)."""
     if src_dtype != copy.dest_dtype:
         raise UnsupportedReshard(f"{copy.param_name}: dtype conversion required")
     needed, dst_strides = resolve_slice(copy, global_shape)

@@ -127,6 +127,8 @@ def plan_reshard(index: dict, world: int, tp_size: int, src_rank: int, shard_bas
     """Records rank ``src_rank`` must push: sources inside its shard arena at
     ``shard_base``, destinations inside rank t's parameter arena at
     ``param_bases[t]`` (addresses valid in this process).  (n, 6) uint64."""
+    from .runtime import plan_reshard as clip_native   # mxb_plan_reshard: clip + split in the library
+
     shards = shards or shard_arena(index, world)
     per_dst = []
     for t in range(tp_size):
@@ -137,10 +139,9 @@ def plan_reshard(index: dict, world: int, tp_size: int, src_rank: int, shard_bas
             so, do, rows, rb, sp, dp = pl.geometry()
             per = shards.sizes[pl.src_name]
             lo, hi = src_rank * per, (src_rank + 1) * per
-            for rec in clip_records(so, do, rows, rb, sp, dp, lo, hi,
-                                    shard_base + shards.offsets[pl.src_name],
-                                    param_bases[t] + pa.offsets[pl.dst_name]):
-                recs += split_record(rec)
+            got = clip_native([(so, param_bases[t] + pa.offsets[pl.dst_name] + do, rows, rb, sp, dp)],
+                              lo, hi, shard_base + shards.offsets[pl.src_name], 8 << 20)
+            recs += [tuple(r) for r in got.tolist()]
         per_dst.append(recs)
     # All-to-all schedule.  The kernel walks the table in order, so table order is
     # link order: the destinations' record lists are merged by progress (the list

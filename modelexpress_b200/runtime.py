@@ -17,7 +17,7 @@ from ._lib import (DIGEST_BLOCK64, DIGEST_ROWS, DIGEST_SAFE32, PLACE_COPY_ENGINE
                    PLACE_ZERO_COPY, SCATTER_VECTOR, SCATTER_DEFAULT, SCATTER_NO_SYNC, check)
 
 __all__ = ["Context", "Ring", "Fanout", "Table", "PlaceResult", "default_context",
-           "host_register", "host_unregister", "host_is_pinned",
+           "host_register", "host_unregister", "host_is_pinned", "plan_pull", "plan_reshard",
            "DIGEST_SAFE32", "DIGEST_ROWS", "DIGEST_BLOCK64", "SCATTER_DEFAULT", "SCATTER_VECTOR",
            "SCATTER_NO_SYNC", "PLACE_COPY_ENGINE", "PLACE_ZERO_COPY"]
 
@@ -177,6 +177,70 @@ def coalesce_runs(runs) -> np.ndarray:
     res = np.zeros((m, 6), dtype=np.uint64)
     if m:
         ctypes.memmove(res.ctypes.data, out, m * ctypes.sizeof(_lib.Desc2D))
+    return res
+
+
+def plan_pull(global_shape, elsize: int, win_offset: int, win_shape, win_stride, dst_offset: int,
+              dst_stride, shards, dst_base: int, keep_rank: bool = True) -> tuple:
+    """Host-only: the descriptor compiler behind the C ABI (``mxb_plan_pull``).
+    ``shards`` is a list of ``(offset tuple, shape tuple, addr)``.  Returns
+    ``(records (m, 6) uint64, shard index of each record (m,) uint32)``; raises
+    ``MxbError`` with code -9 for a window that is not a permuted box of its source."""
+    lib = _lib.load()
+    w = _lib.Window()
+    w.ndim_src, w.ndim_win, w.keep_rank, w.elsize = len(global_shape), len(win_shape), int(keep_rank), int(elsize)
+    if max(w.ndim_src, w.ndim_win) > _lib.MAX_DIMS:
+        raise ValueError(f"at most {_lib.MAX_DIMS} dims")
+    for d, v in enumerate(global_shape):
+        w.global_shape[d] = int(v)
+    for d in range(len(win_shape)):
+        w.win_shape[d], w.win_stride[d], w.dst_stride[d] = int(win_shape[d]), int(win_stride[d]), int(dst_stride[d])
+    w.win_offset, w.dst_offset = int(win_offset), int(dst_offset)
+    arr = (_lib.Shard * max(1, len(shards)))()
+    for k, (off, shp, addr) in enumerate(shards):
+        arr[k].ndim = len(off)
+        if len(off) != len(shp) or len(off) > _lib.MAX_DIMS:
+            raise ValueError("shard rank does not match the source rank")
+        for d in range(len(off)):
+            arr[k].offset[d], arr[k].shape[d] = int(off[d]), int(shp[d])
+        arr[k].addr = int(addr)
+    cap = 64
+    while True:
+        out = (_lib.Desc2D * cap)()
+        which = (ctypes.c_uint32 * cap)()
+        n = ctypes.c_uint64()
+        rc = lib.mxb_plan_pull(ctypes.byref(w), arr, len(shards), int(dst_base), out, which, cap,
+                               ctypes.byref(n))
+        if rc == -7 and n.value > cap:
+            cap = int(n.value)
+            continue
+        check(rc, "mxb_plan_pull")
+        break
+    res = np.zeros((n.value, 6), dtype=np.uint64)
+    if n.value:
+        ctypes.memmove(res.ctypes.data, out, n.value * ctypes.sizeof(_lib.Desc2D))
+    return res, np.array(which[: n.value], dtype=np.uint32)
+
+
+def plan_reshard(regions, shard_lo: int, shard_hi: int, src_base: int, max_record_bytes: int = 0) -> np.ndarray:
+    """Host-only: ``mxb_plan_reshard``; ``regions`` are ``(byte offset in the flat
+    tensor, dst address, rows, row_bytes, src_pitch, dst_pitch)``."""
+    lib = _lib.load()
+    arr, n_in = _lib.desc_array(regions)
+    cap = max(16, 4 * n_in)
+    while True:
+        out = (_lib.Desc2D * cap)()
+        n = ctypes.c_uint64()
+        rc = lib.mxb_plan_reshard(arr, n_in, int(shard_lo), int(shard_hi), int(src_base),
+                                  int(max_record_bytes), out, cap, ctypes.byref(n))
+        if rc == -7 and n.value > cap:
+            cap = int(n.value)
+            continue
+        check(rc, "mxb_plan_reshard")
+        break
+    res = np.zeros((n.value, 6), dtype=np.uint64)
+    if n.value:
+        ctypes.memmove(res.ctypes.data, out, n.value * ctypes.sizeof(_lib.Desc2D))
     return res
 
 

@@ -110,3 +110,141 @@ def test_vllm_import_path_shim_exposes_the_loader_class():
         sys.path.remove(shim)
         for k in [k for k in sys.modules if k == "modelexpress" or k.startswith("modelexpress.")]:
             del sys.modules[k]
+
+
+# ---------------------------------------------------------------------------
+# the descriptor compiler behind the C ABI (mxb_plan_pull / mxb_plan_reshard)
+# ---------------------------------------------------------------------------
+
+
+def _window_of(case):
+    """Replay the case's op-chain (host side, as a binding would) into a strided window."""
+    from modelexpress_b200 import planner
+    from test_oracle_golden import _chain
+
+    view = planner._View(case["global_shape"])
+    for op, args, _kw in _chain(case["op_chain"]):
+        view.apply(op, args)
+    return view.offset, view.shape, view.stride
+
+
+def _golden_cases():
+    from test_oracle_golden import _load
+
+    return _load("slice_plan.json")
+
+
+@pytest.mark.parametrize("case", _golden_cases(), ids=lambda c: c["tag"])
+def test_plan_pull_through_the_abi_expands_to_the_reference_runs(lib, case):
+    """tests/golden/slice_plan.json holds the reference's own plan_pull output (62 cases,
+    the reference tests' hand-computed ones among them): the C planner's records,
+    expanded row by row, must be those runs in that order."""
+    from modelexpress_b200 import planner
+    from modelexpress_b200._lib import MxbError
+    from modelexpress_b200.runtime import plan_pull
+
+    try:
+        off, shape, stride = _window_of(case)
+    except planner.UnsupportedReshard:
+        assert case["error"]          # the op-chain itself is not a view: nothing reaches the ABI
+        return
+    shards = [(tuple(o), tuple(s), addr) for o, s, _sess, addr in case["shards"]]
+    sessions = [sess for _o, _s, sess, _a in case["shards"]]
+    rank_ok = len(shape) == len(case["dest_shape"]) and tuple(shape) == tuple(case["dest_shape"])
+    if case["error"]:
+        if rank_ok:
+            with pytest.raises(MxbError) as e:
+                plan_pull(case["global_shape"], case["elsize"], off, shape, stride, case["dest_offset"],
+                          case["dest_stride"], shards, 0)
+            assert e.value.code == -9
+        return
+    recs, which = plan_pull(case["global_shape"], case["elsize"], off, shape, stride, case["dest_offset"],
+                            case["dest_stride"], shards, 0)
+    got = []
+    for rec, k in zip(recs.tolist(), which.tolist()):
+        src, dst, rows, rb, sp, dp = rec
+        got += [[sessions[k], src + r * sp, dst + r * dp, rb] for r in range(rows)]
+    assert got == case["segments"]
+
+
+def test_plan_pull_agrees_with_the_python_planner_on_random_windows(lib):
+    from modelexpress_b200 import planner
+    from modelexpress_b200._lib import MxbError
+    from modelexpress_b200.runtime import plan_pull
+
+    rng = np.random.default_rng(7)
+    checked = refused = 0
+    for _ in range(400):
+        nd = int(rng.integers(1, 5))
+        gshape = [int(rng.integers(1, 7)) for _ in range(nd)]
+        view = planner._View(gshape)
+        for _op in range(int(rng.integers(0, 4))):
+            kind = rng.integers(0, 3)
+            if kind == 0:
+                d = int(rng.integers(0, nd))
+                if view.shape[d] == 0:
+                    continue
+                start = int(rng.integers(0, view.shape[d]))
+                size = int(rng.integers(1, view.shape[d] - start + 1))
+                view.apply("narrow", (d, start, size))
+            elif kind == 1 and nd >= 2:
+                a, b = (int(x) for x in rng.choice(nd, 2, replace=False))
+                view.apply("transpose", (a, b))
+            elif kind == 2:
+                view.apply("permute", (tuple(int(x) for x in rng.permutation(nd)),))
+        dest_shape = tuple(view.shape)
+        dstride = planner._strides_of([s + int(rng.integers(0, 3)) for s in dest_shape])
+        dest_off = int(rng.integers(0, 5))
+        el = int(rng.choice([1, 2, 4]))
+        # shards: split dim 0 of the source in two (or one shard)
+        cut = int(rng.integers(0, gshape[0] + 1))
+        boxes = [((0,) * nd, tuple([cut] + gshape[1:]), 4096), ((cut,) + (0,) * (nd - 1),
+                 tuple([gshape[0] - cut] + gshape[1:]), 1 << 20)]
+        boxes = [b for b in boxes if b[1][0] > 0]
+        copy = planner.CopySpec("s", (), "p", dest_off, dest_shape, tuple(dstride), "dt")
+        copy.src_offset, copy.src_shape, copy.src_stride = view.offset, tuple(view.shape), tuple(view.stride)
+        shard_specs = [planner.ShardSpec(o, s, f"s{k}", a, el) for k, (o, s, a) in enumerate(boxes)]
+        try:
+            want = planner.plan_pull_2d(copy, gshape, "dt", el, shard_specs, 1 << 30)
+        except planner.UnsupportedReshard:
+            with pytest.raises(MxbError):
+                plan_pull(gshape, el, view.offset, view.shape, view.stride, dest_off, dstride, boxes,
+                          1 << 30, keep_rank=False)
+            refused += 1
+            continue
+        recs, _which = plan_pull(gshape, el, view.offset, view.shape, view.stride, dest_off, dstride, boxes,
+                                 1 << 30, keep_rank=False)
+        flat = np.concatenate([r for _s, r in want]) if want else np.zeros((0, 6), dtype=np.uint64)
+        assert planner.expand_records(recs) == planner.expand_records(flat)
+        checked += 1
+    assert checked > 200
+
+
+def test_plan_reshard_agrees_with_the_python_clip(lib):
+    from modelexpress_b200 import reshard
+    from modelexpress_b200.runtime import plan_reshard
+
+    rng = np.random.default_rng(11)
+    for _ in range(500):
+        rows = int(rng.integers(1, 40))
+        rb = int(rng.integers(1, 300))
+        sp = rb + int(rng.integers(0, 200)) if rows > 1 else rb
+        dp = rb + int(rng.integers(0, 64)) if rows > 1 else rb
+        so = int(rng.integers(0, 500))
+        total = so + (rows - 1) * sp + rb + int(rng.integers(0, 100))
+        lo = int(rng.integers(0, total))
+        hi = int(rng.integers(lo, total + 1))
+        dst0 = 1 << 20
+        want = reshard.clip_records(so, 0, rows, rb, sp, dp, lo, hi, 5000, dst0)
+        got = plan_reshard([(so, dst0, rows, rb, sp, dp)], lo, hi, 5000)
+        from modelexpress_b200.planner import expand_records
+
+        assert expand_records(got) == expand_records(np.array(want, dtype=np.uint64).reshape(-1, 6)), \
+            (so, rows, rb, sp, dp, lo, hi)
+    # splitting keeps the byte map
+    big = plan_reshard([(0, 1 << 20, 1, 1 << 22, 1 << 22, 1 << 22), (64, 1 << 30, 100, 4096, 8192, 4096)],
+                       0, 1 << 23, 0, max_record_bytes=1 << 20)
+    whole = plan_reshard([(0, 1 << 20, 1, 1 << 22, 1 << 22, 1 << 22), (64, 1 << 30, 100, 4096, 8192, 4096)],
+                         0, 1 << 23, 0)
+    assert len(big) > len(whole) and int((big[:, 2] * big[:, 3]).max()) <= 1 << 20
+    assert int((big[:, 2] * big[:, 3]).sum()) == int((whole[:, 2] * whole[:, 3]).sum())

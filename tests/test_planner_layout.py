@@ -16,8 +16,11 @@ from oracle import ref_port as R
 from test_oracle_golden import _chain, _load
 
 
+@pytest.mark.parametrize("plan_pull", ["library", "python"])
 @pytest.mark.parametrize("case", _load("slice_plan.json"), ids=lambda c: c["tag"])
-def test_records_expand_to_the_reference_runs(case):
+def test_records_expand_to_the_reference_runs(case, plan_pull, monkeypatch):
+    if plan_pull == "python":   # the planner's Python statement instead of mxb_plan_pull
+        monkeypatch.setattr(planner, "plan_pull_2d", planner.plan_pull_2d_py)
     copy = planner.CopySpec("src", _chain(case["op_chain"]), "p", case["dest_offset"],
                             tuple(case["dest_shape"]), tuple(case["dest_stride"]), "dt")
     shards = [planner.ShardSpec(tuple(o), tuple(s), sess, addr, case["elsize"])
