@@ -125,13 +125,13 @@ def measured_peak():
         with open(p) as f:
             return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs, copy read+write)"
     except Exception:
-        return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+        return FALLBACK_HBM_GBS, "fallback (6.65 TB/s; MEASURED_PEAKS.json was not found)"
 
 
-# DRAM bytes moved per byte placed, from the committed ncu captures of the 4-layer case
-# (profiles/scatter_bulk_kernel_*.md, profiles/scatter_vec_kernel_*.md): read + written bytes of
-# one resident-table launch divided by the 480,845,824 bytes it places.  Every byte is read once
-# and written once, so the traffic of a larger launch is this ratio times its bytes placed.
+# DRAM bytes moved per byte placed, from ncu captures (--set full) of the 4-layer case: read +
+# written bytes of one resident-table launch divided by the 480,845,824 bytes it places.  Every
+# byte is read once and written once, so the traffic of a larger launch is this ratio times its
+# bytes placed.
 NCU_DRAM_BYTES_PER_BYTE_PLACED = {
     "scatter_bulk_kernel": (480.93e6 + 430.71e6) / 480845824,
     "scatter_vec_kernel": (480.94e6 + 432.56e6) / 480845824,
@@ -350,7 +350,9 @@ def bench_place(args):
                 single_s /= min(3, args.steps)
             barrier(world)
             single_s = max_over_ranks(single_s or 0.0, world)
+        mapping = sorted({"shared" if images.open(p).shared else "private" for p in prep.files})
         mem = {"first_s": first_s, "first_timings": first[0].timings, "pinned_bytes": pinned_bytes,
+               "mapping": "+".join(mapping),
                "s": mem_s, "stats": mem_stats, "launches": mem_launches, "single_s": single_s}
 
     # ---- file -> HBM: the same files as ordinary pageable memory (page cache / tmpfs): gather
@@ -508,6 +510,7 @@ def bench_place(args):
         out["config"]["pinning"] = {
             "first_load_s": round(mem["first_s"], 4), "first_load_timings": mem["first_timings"],
             "pinned_bytes_per_rank": int(mem["pinned_bytes"]),
+            "mapping": mem["mapping"],
             "what": "first place_checkpoint(pin='keep') of the process: maps the files, page-locks the byte "
                     "ranges this rank reads (whole row-parallel tensors, since their slices touch every "
                     "page), then places; max over ranks"}

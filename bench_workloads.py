@@ -499,21 +499,36 @@ def reshard_measure(args, ctx, rank, world, local, nv=None) -> dict:
     # one resident table (one launch) per GPU for all the logical ranks it hosts
     table = ctx.table(np.concatenate(all_recs), local)
     plan_s = time.perf_counter() - t0
-    flags = SCATTER_VECTOR if os.environ.get("MXB_SCATTER", "auto") == "vec" else 0
-    times = []
-    for it in range(warmup + steps):
-        _barrier(world)
-        torch.cuda.synchronize()
-        ctx.event_record(0, local)
-        table.launch(flags)
-        ctx.event_record(1, local)
-        ms = ctx.event_elapsed_ms(0, 1, local)
-        ctx.sync(local)
-        _barrier(world)
-        ms = _max(ms, world)
-        if it >= warmup:
-            times.append(ms)
-    ms = sum(times) / len(times)
+    from modelexpress_b200.runtime import SCATTER_OVERLAP
+
+    schedules = {"two kernels side by side": SCATTER_OVERLAP, "one kernel after the other": 0}
+    if os.environ.get("MXB_SCATTER", "auto") == "vec":
+        schedules = {"vector engine only": SCATTER_VECTOR}
+    per_schedule = {}
+    for label, flags in schedules.items():
+        times = []
+        for it in range(warmup + steps):
+            _barrier(world)
+            torch.cuda.synchronize()
+            ctx.event_record(0, local)
+            table.launch(flags)
+            ctx.event_record(1, local)
+            ms = ctx.event_elapsed_ms(0, 1, local)
+            ctx.sync(local)
+            _barrier(world)
+            ms = _max(ms, world)
+            if it >= warmup:
+                times.append(ms)
+        per_schedule[label] = round(sum(times) / len(times), 4)
+    best_label = min(per_schedule, key=per_schedule.get)
+    ms, flags = per_schedule[best_label], schedules[best_label]
+    # the pattern check below reads what the last launch wrote; make that the reported schedule
+    params_t.zero_()
+    torch.cuda.synchronize()
+    _barrier(world)
+    table.launch(flags)
+    ctx.sync(local)
+    _barrier(world)
     # check every destination parameter hosted here against the pattern
     bad = 0
     for j, t in enumerate(mine):
@@ -578,7 +593,8 @@ def reshard_measure(args, ctx, rank, world, local, nv=None) -> dict:
            "plan_seconds": round(plan_s, 3),
            "gbs_written_aggregate": round(total_bytes / (ms * 1e-3) / 1e9, 1),
            "nvlink_gbs_per_gpu": round(remote / (ms * 1e-3) / 1e9, 1),
-           "engine": engine, "gpu_launches": warmup + steps,
+           "engine": engine, "schedule": best_label, "device_ms_per_schedule": per_schedule,
+           "gpu_launches": (warmup + steps) * len(schedules) + 1,
            "bound_seconds_measured_peaks": round(bound_meas, 6),
            "bound_seconds_nominal_900": round(bound_nom, 6),
            "frac_of_measured_bound": round(bound_meas / (ms * 1e-3), 4),

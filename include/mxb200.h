@@ -215,6 +215,9 @@ int64_t mxb_coalesce_runs(const mxb_run *runs, uint64_t n, mxb_desc2d *out, uint
                                   of at least 1 KiB; vector engine for the rest */
 #define MXB_SCATTER_VECTOR 1u  /* vector engine (16-byte loads/stores) for everything */
 #define MXB_SCATTER_NO_SYNC 2u /* return after enqueueing on the context stream */
+#define MXB_SCATTER_OVERLAP 4u /* mxb_table_launch: run the bulk-engine and the vector-engine part
+                                  of a table as two concurrent kernels (worth it when both have
+                                  much to do, e.g. local copies next to peer stores) */
 
 /* One persistent launch on `dev` moves every record of the host table
  * `descs[0..n)`: sources and destinations may be local HBM, a peer GPU's HBM

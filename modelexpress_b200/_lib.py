@@ -20,7 +20,7 @@ ERR_NAMES = {-1: "MXB_ERR_ARG", -2: "MXB_ERR_BOUNDS", -3: "MXB_ERR_ALIGN", -4: "
 MAX_DIMS = 8
 
 DIGEST_SAFE32, DIGEST_ROWS, DIGEST_BLOCK64 = 1, 2, 4
-SCATTER_DEFAULT, SCATTER_VECTOR, SCATTER_NO_SYNC = 0, 1, 2
+SCATTER_DEFAULT, SCATTER_VECTOR, SCATTER_NO_SYNC, SCATTER_OVERLAP = 0, 1, 2, 4
 PLACE_COPY_ENGINE, PLACE_ZERO_COPY = 0, 1
 FANOUT_MAX_CHILDREN = 7
 

@@ -1,4 +1,5 @@
 // Context, memory, IPC and the host-side descriptor compiler of mxb200.
+#include <chrono>
 #include <thread>
 
 #include "common.cuh"
@@ -211,6 +212,8 @@ int32_t mxb_ctx_destroy(mxb_ctx *ctx) {
         if (d.status_host) cudaFreeHost(d.status_host);
         for (cudaEvent_t e : d.events)
             if (e) cudaEventDestroy(e);
+        if (d.fork_ev) cudaEventDestroy(d.fork_ev);
+        if (d.join_ev) cudaEventDestroy(d.join_ev);
         if (d.stream) cudaStreamDestroy(d.stream);
         if (d.copy_stream) cudaStreamDestroy(d.copy_stream);
     }
@@ -312,6 +315,7 @@ int32_t mxb_host_register(uint64_t addr, uint64_t nbytes, uint64_t *out_base, ui
     // Page-locking a range that has never been touched through this mapping faults its pages
     // in one by one inside the driver call, several times slower than doing it up front on a
     // few threads: read one byte of every page first.
+    const auto t_touch0 = std::chrono::steady_clock::now();
     {
         unsigned nt = std::thread::hardware_concurrency() / 2;
         nt = nt < 1 ? 1 : (nt > 8 ? 8 : nt);
@@ -331,11 +335,17 @@ int32_t mxb_host_register(uint64_t addr, uint64_t nbytes, uint64_t *out_base, ui
     // The device only ever reads these pages.  Saying so lets a private mapping of a file
     // that must not change be pinned without the kernel breaking copy-on-write page by page;
     // where the flag is refused the plain form is tried.
+    const auto t_reg0 = std::chrono::steady_clock::now();
     cudaError_t e = cudaHostRegister((void *)(uintptr_t)lo, hi - lo,
                                      cudaHostRegisterPortable | cudaHostRegisterReadOnly);
-    if (getenv("MXB_VERBOSE"))
-        fprintf(stderr, "[mxb200] cudaHostRegister(%llu bytes, portable|read-only): %s\n",
-                (unsigned long long)(hi - lo), cudaGetErrorString(e));
+    if (getenv("MXB_VERBOSE")) {
+        const auto t_reg1 = std::chrono::steady_clock::now();
+        fprintf(stderr, "[mxb200] cudaHostRegister(%llu bytes, portable|read-only): %s; touch %.1f ms, "
+                        "register %.1f ms\n",
+                (unsigned long long)(hi - lo), cudaGetErrorString(e),
+                std::chrono::duration<double, std::milli>(t_reg0 - t_touch0).count(),
+                std::chrono::duration<double, std::milli>(t_reg1 - t_reg0).count());
+    }
     if (e != cudaSuccess) {
         cudaGetLastError();
         e = cudaHostRegister((void *)(uintptr_t)lo, hi - lo, cudaHostRegisterPortable);

@@ -51,6 +51,7 @@ struct DeviceState {
     void *digest_host = nullptr;
     size_t digest_host_bytes = 0;
     cudaEvent_t events[16] = {};  // user timing events on `stream`
+    cudaEvent_t fork_ev = nullptr, join_ev = nullptr;  // two-kernel scatter launches (stream <-> copy_stream)
     // serialises the entry points that share this device's scratch (tables, accumulators)
     std::unique_ptr<std::mutex> mu{new std::mutex()};
 };

@@ -556,13 +556,10 @@ static int32_t run_digest(mxb_ctx *ctx, int32_t dev, const mxb_span *spans, uint
     DigestAcc *dacc = reinterpret_cast<DigestAcc *>(d->digest);
     unsigned long long *dblk = reinterpret_cast<unsigned long long *>(block_out);
     if (n_full && use_bulk) {
-        static bool attr_set[64][8] = {};
         const size_t smem = (size_t)kDigestStages * kDigestTile;
         digest_bulk_fn fn = digest_bulk_variant(modes);
-        if (d->device < 64 && !attr_set[d->device][modes & 7]) {
-            MXB_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr_set[d->device][modes & 7] = true;
-        }
+        // idempotent and cheap: set on every launch rather than keep a flag several threads share
+        MXB_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         uint64_t grid = (uint64_t)d->sm_count;
         if (grid > n_full) grid = n_full;
         fn<<<(unsigned)grid, kDigestThreads, smem, d->stream>>>(dspans, dtiles, n_full, dacc, dblk,

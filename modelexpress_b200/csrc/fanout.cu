@@ -419,19 +419,16 @@ int32_t mxb_fanout_run(mxb_fanout *f, int32_t is_root, uint32_t timeout_ms) {
     const bool bulk = eng && !strcmp(eng, "bulk");
     MXB_CUDA(cudaEventRecord(f->ev0, dv->stream));
     if (bulk) {
-        static bool attr_set[64] = {};
         const size_t smem = (size_t)kFanStages * kFanPiece;
-        if (dv->device < 64 && !attr_set[dv->device]) {
-            MXB_CUDA(cudaFuncSetAttribute(fanout_bulk_kernel,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr_set[dv->device] = true;
-        }
+        // idempotent and cheap: set on every launch rather than keep a flag several threads share
+        MXB_CUDA(cudaFuncSetAttribute(fanout_bulk_kernel,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         uint64_t grid = (uint64_t)dv->sm_count;
         if (grid > np) grid = np;
         fanout_bulk_kernel<<<(unsigned)grid, 32, smem, dv->stream>>>(a);
     } else {
-        // 4 resident CTAs of 512 threads per SM measured best for NVLink stores
-        // (682 GB/s per target against 644 with 2, 16 GB payload, 2 GPUs)
+        // 4 resident CTAs of 512 threads per SM: more warps posting stores keep the links fuller
+        // than 2 per SM do
         int per_sm = 4;
         if (const char *g = getenv("MXB_FANOUT_CTAS_PER_SM")) per_sm = atoi(g) > 0 ? atoi(g) : 4;
         if (per_sm > 4) per_sm = 4;

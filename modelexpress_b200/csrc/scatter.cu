@@ -13,6 +13,8 @@
 //     global->shared->global through a 3-stage 64 KiB ring, for tables whose
 //     addresses, pitches and row sizes are all multiples of 16.
 #include "bulk.cuh"
+#include <mutex>
+
 #include "common.cuh"
 
 namespace mxb {
@@ -351,11 +353,11 @@ static bool bulk_shape_ok(const mxb_desc2d &d) {
     return d.row_bytes >= 1024;
 }
 
-// Which addresses belong to another GPU.  Stores to a peer over NVLink measured
-// faster from the vector engine (many warps posting 16-byte stores) than from
-// the bulk engine (14.8 against 13.3 TB/s aggregate on the 8-GPU reshard), so
-// records that touch peer memory are routed to the vector engine.  Allocations
-// are few (one arena per peer), so a small cache of ranges answers per record.
+// Which addresses belong to another GPU.  Stores to a peer over NVLink go faster
+// from the vector engine (many warps posting 16-byte stores) than from the bulk
+// engine (one warp per SM issuing bulk copies), so records that touch peer memory
+// are routed to the vector engine.  Allocations are few (one arena per peer), so
+// a small cache of ranges answers per record.
 class PeerRanges {
   public:
     explicit PeerRanges(int device) : device_(device) {
@@ -467,9 +469,9 @@ int32_t build_scatter_table(const mxb_desc2d *descs, uint64_t n, void *host_buf,
 }
 
 static int32_t launch_vec(mxb_ctx *ctx, DeviceState *dv, const mxb_desc2d *dd, const Tile *dt,
-                          uint64_t count, cudaStream_t stream) {
+                          uint64_t count, cudaStream_t stream, int ctas_per_sm = 4) {
     if (!count) return MXB_OK;
-    uint64_t grid = (uint64_t)dv->sm_count * 4;
+    uint64_t grid = (uint64_t)dv->sm_count * ctas_per_sm;
     if (grid > count) grid = count;
     scatter_vec_kernel<<<(unsigned)grid, kVecThreads, 0, stream>>>(dd, dt, count);
     MXB_CUDA(cudaGetLastError());
@@ -480,12 +482,15 @@ static int32_t launch_vec(mxb_ctx *ctx, DeviceState *dv, const mxb_desc2d *dd, c
 static int32_t launch_bulk(mxb_ctx *ctx, DeviceState *dv, const mxb_desc2d *dd, const Tile *dt,
                            uint64_t count, cudaStream_t stream) {
     if (!count) return MXB_OK;
-    static bool attr_set[64] = {};
+    static std::once_flag attr_once[64];
     const size_t smem = (size_t)kBulkStages * kTileBytes;
-    if (dv->device < 64 && !attr_set[dv->device]) {
-        MXB_CUDA(cudaFuncSetAttribute(scatter_bulk_kernel,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set[dv->device] = true;
+    if (dv->device < 64) {
+        cudaError_t attr_rc = cudaSuccess;
+        std::call_once(attr_once[dv->device], [&]() {
+            attr_rc = cudaFuncSetAttribute(scatter_bulk_kernel,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        });
+        MXB_CUDA(attr_rc);
     }
     uint64_t grid = (uint64_t)dv->sm_count;
     if (grid > count) grid = count;
@@ -501,12 +506,36 @@ int32_t launch_scatter_tiles(mxb_ctx *ctx, DeviceState *dv, const ScatterTable &
     const Tile *bulk_tiles = reinterpret_cast<const Tile *>(tb.tiles) + bulk_begin;
     const Tile *vec_tiles = reinterpret_cast<const Tile *>(tb.tiles) + tb.n_bulk + vec_begin;
     int32_t rc;
-    if (flags & MXB_SCATTER_VECTOR)
+    if (flags & MXB_SCATTER_VECTOR) {
         rc = launch_vec(ctx, dv, tb.descs, bulk_tiles, bulk_count, stream);
-    else
+        if (rc != MXB_OK) return rc;
+        return launch_vec(ctx, dv, tb.descs, vec_tiles, vec_count, stream);
+    }
+    // Two engines, two kernels.  One after the other they add their times; a table with much
+    // work for both (a reshard: local copies on the bulk engine, peer stores on the vector
+    // engine) runs them side by side instead: the bulk kernel first (one warp and most of the
+    // shared memory of every SM), the vector kernel on a second stream with three CTAs per SM,
+    // which is what still fits beside it, so that HBM copies hide under the slower link.
+    const bool overlap = (flags & MXB_SCATTER_OVERLAP) && stream == dv->stream &&
+                         bulk_count >= (uint64_t)dv->sm_count && vec_count >= (uint64_t)dv->sm_count;
+    if (!overlap) {
         rc = launch_bulk(ctx, dv, tb.descs, bulk_tiles, bulk_count, stream);
+        if (rc != MXB_OK) return rc;
+        return launch_vec(ctx, dv, tb.descs, vec_tiles, vec_count, stream);
+    }
+    if (!dv->fork_ev) {
+        MXB_CUDA(cudaEventCreateWithFlags(&dv->fork_ev, cudaEventDisableTiming));
+        MXB_CUDA(cudaEventCreateWithFlags(&dv->join_ev, cudaEventDisableTiming));
+    }
+    MXB_CUDA(cudaEventRecord(dv->fork_ev, stream));
+    MXB_CUDA(cudaStreamWaitEvent(dv->copy_stream, dv->fork_ev, 0));
+    rc = launch_bulk(ctx, dv, tb.descs, bulk_tiles, bulk_count, stream);
     if (rc != MXB_OK) return rc;
-    return launch_vec(ctx, dv, tb.descs, vec_tiles, vec_count, stream);
+    rc = launch_vec(ctx, dv, tb.descs, vec_tiles, vec_count, dv->copy_stream, 3);
+    if (rc != MXB_OK) return rc;
+    MXB_CUDA(cudaEventRecord(dv->join_ev, dv->copy_stream));
+    MXB_CUDA(cudaStreamWaitEvent(stream, dv->join_ev, 0));
+    return MXB_OK;
 }
 
 int32_t launch_scatter(mxb_ctx *ctx, DeviceState *dv, const mxb_desc2d *descs, uint64_t n,

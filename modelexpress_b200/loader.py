@@ -60,18 +60,31 @@ class LoadResult:
 class FileImage:
     """A checkpoint file mapped into host memory; ``address`` is the host address of byte 0.
 
-    ``pinnable`` maps the file privately with write permission (which the file's own
-    mode does not need to allow, and which never writes: nothing stores through the
-    mapping), the form ``mxb_host_register`` can pin.  ``pin_spans`` then page-locks
-    the byte ranges a rank keeps, after which ``mxb_place`` reads them with the copy
-    engine directly and no host thread copies a byte."""
+    ``pinnable`` maps the file readable and writable, the form ``mxb_host_register``
+    can pin; nothing ever stores through the mapping.  Where the file may be opened
+    for writing the mapping is shared: its page-cache pages are pinned where they
+    are.  A file that is read-only to this process is mapped privately instead, which
+    still pins but makes the kernel give the mapping its own copy of every pinned
+    page first (several times slower, and the pinned ranges then exist twice in host
+    memory).  ``pin_spans`` page-locks the byte ranges a rank keeps, after which
+    ``mxb_place`` reads them with the copy engine directly and no host thread copies
+    a byte."""
 
     def __init__(self, path: str, pinnable: bool = False):
         self.path = path
-        self._f = open(path, "rb")
+        self.shared = False
+        if pinnable:
+            try:
+                self._f = open(path, "r+b")
+                self.shared = True
+            except OSError:
+                self._f = open(path, "rb")
+        else:
+            self._f = open(path, "rb")
         self.size = os.fstat(self._f.fileno()).st_size
         if pinnable:
-            self._mm = mmap.mmap(self._f.fileno(), 0, flags=mmap.MAP_PRIVATE,
+            self._mm = mmap.mmap(self._f.fileno(), 0,
+                                 flags=mmap.MAP_SHARED if self.shared else mmap.MAP_PRIVATE,
                                  prot=mmap.PROT_READ | mmap.PROT_WRITE)
         else:
             self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)

@@ -14,12 +14,13 @@ import numpy as np
 
 from . import _lib
 from ._lib import (DIGEST_BLOCK64, DIGEST_ROWS, DIGEST_SAFE32, PLACE_COPY_ENGINE,
-                   PLACE_ZERO_COPY, SCATTER_VECTOR, SCATTER_DEFAULT, SCATTER_NO_SYNC, check)
+                   PLACE_ZERO_COPY, SCATTER_VECTOR, SCATTER_DEFAULT, SCATTER_NO_SYNC, SCATTER_OVERLAP,
+                   check)
 
 __all__ = ["Context", "Ring", "Fanout", "Table", "PlaceResult", "default_context",
            "host_register", "host_unregister", "host_is_pinned", "plan_pull", "plan_reshard",
            "DIGEST_SAFE32", "DIGEST_ROWS", "DIGEST_BLOCK64", "SCATTER_DEFAULT", "SCATTER_VECTOR",
-           "SCATTER_NO_SYNC", "PLACE_COPY_ENGINE", "PLACE_ZERO_COPY"]
+           "SCATTER_NO_SYNC", "SCATTER_OVERLAP", "PLACE_COPY_ENGINE", "PLACE_ZERO_COPY"]
 
 
 _close_lock = threading.Lock()

@@ -48,3 +48,27 @@ def test_bulk_engine_matches_vector_engine(env):
     assert ctx.launch_count > 0
 
 
+
+
+def test_both_engines_side_by_side(env):
+    """MXB_SCATTER_OVERLAP: a table with hundreds of tiles for each engine runs the
+    bulk kernel and the vector kernel as two concurrent launches; same bytes."""
+    ctx, torch = env
+    from modelexpress_b200.runtime import SCATTER_DEFAULT, SCATTER_OVERLAP
+
+    rng = np.random.default_rng(21)
+    src = golden_bytes(78, 96 << 20)
+    recs, dpos = [], 0
+    for k in range(24):      # 24 x 2 MiB aligned (bulk engine) + 24 x ~2 MiB at odd offsets (vector engine)
+        rows, rb = 512, 4096
+        s0 = 16 * int(rng.integers(0, (src.size - rows * 8192) // 16))
+        recs.append((s0, dpos, rows, rb, 8192, 4096))
+        dpos += rows * 4096
+        rows, rb = 500, 4099
+        s1 = int(rng.integers(0, src.size - rows * 8200)) | 1
+        recs.append((s1, dpos + 5, rows, rb, 8200, 4112))
+        dpos += (5 + rows * 4112 + 255) // 256 * 256
+    want = None
+    for flags in (SCATTER_DEFAULT, SCATTER_OVERLAP, SCATTER_OVERLAP):
+        got, want = _run_both(ctx, torch, src, dpos, recs, flags)
+        assert np.array_equal(got, want)
