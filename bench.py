@@ -319,9 +319,9 @@ def bench_place(args):
             dt = max_over_ranks(dt, world)
         return dt, out
 
-    # ---- memory -> HBM: the checkpoint files stay mapped and page-locked in host memory; every
-    # step is the public call, which lets the copy engine gather this rank's slices straight
-    # from the file image into device staging and the scatter kernel write the shards ----------
+    # ---- memory -> HBM: this rank's bytes are kept page-locked in host memory, packed as they
+    # cross PCIe (made by the first load).  Every step is the public call: one contiguous
+    # copy-engine transfer per chunk into device staging, the scatter kernel writes the shards --
     images = loader.HostImages()
 
     def load_pinned():
@@ -331,16 +331,16 @@ def bench_place(args):
     sampler = ClockSampler(local)
     mem = {}
     if not skip_e2e:
-        first_s, first = timed(load_pinned, 1)      # maps the files and pins this rank's ranges
-        pinned_bytes = images.pinned_bytes
+        first_s, first = timed(load_pinned, 1)      # gathers into the page-locked image that is kept
+        pinned_bytes = images.packed_bytes
         for _ in range(args.warmup):
             load_pinned()
         launches0 = ctx.launch_count
         sampler.start()
         mem_s, mem_stats = timed(load_pinned, args.steps)
         mem_launches = ctx.launch_count - launches0
-        if any(p.stats.bytes_direct != bytes_placed or p.stats.bytes_placed != bytes_placed for p in mem_stats):
-            raise SystemExit("bench: a pinned load went through the gather ring")
+        if any(p.stats.bytes_direct != bytes_placed or p.stats.seconds_gather for p in mem_stats):
+            raise SystemExit("bench: a load from the kept image went through the gather threads")
         d_mem = _digests(ctx, params, names)
         single_s = None
         if world > 1:   # the same load with the other ranks idle: what one GPU gets from the box alone
@@ -350,10 +350,35 @@ def bench_place(args):
                 single_s /= min(3, args.steps)
             barrier(world)
             single_s = max_over_ranks(single_s or 0.0, world)
-        mapping = sorted({"shared" if images.open(p).shared else "private" for p in prep.files})
         mem = {"first_s": first_s, "first_timings": first[0].timings, "pinned_bytes": pinned_bytes,
-               "mapping": "+".join(mapping),
                "s": mem_s, "stats": mem_stats, "launches": mem_launches, "single_s": single_s}
+
+    # ---- for comparison, one GPU only (pinning 6 GB of page cache per rank takes seconds): the
+    # files' own pages page-locked and read in place by the copy engine (2-D gathers) -----------
+    pages = None
+    if not skip_e2e and (world == 1 or os.environ.get("MXB_BENCH_PAGES") == "1") and \
+            os.environ.get("MXB_BENCH_PAGES") != "0":
+        zero_params()
+        pg_images = loader.HostImages()
+
+        def load_pages():
+            return loader.place_checkpoint(ckpt, tp_rank, TP, dev, params=params, ring=ring, ctx=ctx,
+                                           host_threads=threads, mode=mode, pin="pages", images=pg_images)
+
+        pg_first_s, pg_first = timed(load_pages, 1)
+        load_pages()
+        pg_s, pg_stats = timed(load_pages, min(5, args.steps))
+        if _digests(ctx, params, names) != d_mem:
+            raise SystemExit("bench: the page-locked file path placed different bytes")
+        pages = {"value": round(total_bytes * min(5, args.steps) / pg_s / 1e9, 2), "unit": "GB/s",
+                 "first_load_s": round(pg_first_s, 4), "pin_s": pg_first[0].timings["pin"],
+                 "pinned_bytes_per_rank": int(pg_images.pinned_bytes),
+                 "mapping": "+".join(sorted({"shared" if pg_images.open(p).shared else "private"
+                                             for p in prep.files})),
+                 "what": "place_checkpoint(pin='pages'): the checkpoint files' own page-cache pages are "
+                         "page-locked (whole row-parallel tensors, since a rank's slice touches every "
+                         "page of them) and the copy engine gathers the slices from there"}
+        pg_images.close()
 
     # ---- file -> HBM: the same files as ordinary pageable memory (page cache / tmpfs): gather
     # threads copy the rank's bytes into the pinned ring, their own streams carry them over PCIe -
@@ -490,9 +515,10 @@ def bench_place(args):
             "workload": WORKLOAD_MOE if moe else WORKLOAD_DENSE,
             "layers": layers, "bytes_placed_per_gpu_per_step": bytes_placed,
             "tensors": len(idx), "records_per_step": len(plan.placements),
-            "source_for_value": "checkpoint files mapped and page-locked in host memory (pinned once, before "
-                                "the timed steps; its cost is config.pinning); every step is one "
-                                "place_checkpoint() call: copy engine -> device staging -> scatter kernel",
+            "source_for_value": "this rank's checkpoint bytes kept page-locked in host memory, packed as they "
+                                "cross PCIe (made by the first load, whose cost is config.pinning); every "
+                                "step is one place_checkpoint(pin='keep') call: copy engine -> device "
+                                "staging -> scatter kernel",
             "l2": "inputs larger than L2 (every step reads and writes bytes_placed, far above 126 MB)",
             "ring": {"bytes": ring_bytes, "slots": slots, "host_threads": threads,
                      "mode": "zero_copy" if mode == PLACE_ZERO_COPY else "copy_engine"},
@@ -510,13 +536,13 @@ def bench_place(args):
         out["config"]["pinning"] = {
             "first_load_s": round(mem["first_s"], 4), "first_load_timings": mem["first_timings"],
             "pinned_bytes_per_rank": int(mem["pinned_bytes"]),
-            "mapping": mem["mapping"],
-            "what": "first place_checkpoint(pin='keep') of the process: maps the files, page-locks the byte "
-                    "ranges this rank reads (whole row-parallel tensors, since their slices touch every "
-                    "page), then places; max over ranks"}
+            "what": "first place_checkpoint(pin='keep') of the process: allocates the page-locked image, "
+                    "gathers this rank's bytes into it through the gather threads and places them from "
+                    "there; max over ranks"}
         out["e2e"] = {"value": round(value, 2), "unit": "GB/s",
                       "h2d_bytes_per_step": int(bytes_placed), "d2h_bytes_per_step": 4,
-                      "source": "memory -> HBM: page-locked checkpoint image, public place_checkpoint() per step",
+                      "source": "memory -> HBM: page-locked packed image of the rank's bytes, public "
+                                "place_checkpoint() per step",
                       "device_s_per_step": round(sum(p.stats.seconds_device for p in mem["stats"]) / args.steps, 4),
                       "host_copy_bytes_per_step": 0,
                       "chunks_per_step": int(mem["stats"][0].stats.chunks),
@@ -539,6 +565,8 @@ def bench_place(args):
             "bound": "host memory: every byte is read and written by a core and read again by the DMA; "
                      "pinning the pages instead costs more than one load (config.pinning)",
             "seconds_to_loaded_one_shot": fil["one_shot"]}
+        if pages is not None:
+            out["pinned_file_pages"] = pages
         out["gpu_launches"] = int(mem["launches"])
     else:
         out["value"] = round(total_bytes / (kern_ms * 1e-3) / 1e9, 2)

@@ -42,6 +42,7 @@ typedef struct mxb_ctx mxb_ctx;
 typedef struct mxb_ring mxb_ring;
 typedef struct mxb_fanout mxb_fanout;
 typedef struct mxb_table mxb_table;
+typedef struct mxb_image mxb_image;
 
 /* One contiguous byte run.  Mirrors ReadDescriptor(session, src_addr, dst_addr,
  * nbytes) of refit/reshard/transport/base.py:26-35 with the session resolved
@@ -295,6 +296,29 @@ int32_t mxb_ring_destroy(mxb_ring *ring);
  * gds_loader.py:284-331 / gds_transfer.py:142-231. */
 int32_t mxb_place(mxb_ring *ring, const mxb_desc2d *items, uint64_t n, int32_t host_threads,
                   uint32_t mode, mxb_place_stats *stats);
+
+/* A rank's slices kept in page-locked host memory, packed exactly as they cross
+ * PCIe (the pinned ring of the host-staged path, made as large as the rank's
+ * shard and kept).  mxb_image_create is a load like mxb_place whose gather
+ * threads write every chunk into its own place in the image instead of a ring
+ * slot; from then on mxb_image_place loads the same slices again with one
+ * contiguous copy-engine transfer and one scatter launch per chunk: no host
+ * thread, no source file, nothing read from the page cache.  Meant for weights
+ * that are loaded more than once from the same host (replicas started one
+ * after the other, reloads after a weight swap, refits from a host copy).
+ * `items` of mxb_image_place may carry new destination addresses for the same
+ * slices (NULL keeps the previous ones); a destination whose address phase
+ * (mod 16) or pitch changed needs a new image (MXB_ERR_STATE).  The image
+ * uses its ring's staging buffers and must be destroyed before the ring.
+ * Replaces the per-load re-read of the checkpoint files by
+ * engines/vllm/adapter.py:316-329 for every load after the first. */
+int32_t mxb_image_create(mxb_ring *ring, const mxb_desc2d *items, uint64_t n, int32_t host_threads,
+                         mxb_image **out, mxb_place_stats *stats);
+int32_t mxb_image_place(mxb_image *image, const mxb_desc2d *items, uint64_t n,
+                        mxb_place_stats *stats);
+/* Page-locked host bytes the image holds. */
+uint64_t mxb_image_bytes(mxb_image *image);
+int32_t mxb_image_destroy(mxb_image *image);
 
 /* ---- kernel 4: integrity digests ---------------------------------------- */
 

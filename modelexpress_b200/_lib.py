@@ -102,6 +102,10 @@ SIGNATURES = {
     "mxb_ring_create": (i32, [_vp, i32, u64, u32, _P(_vp)]),
     "mxb_ring_destroy": (i32, [_vp]),
     "mxb_place": (i32, [_vp, _P(Desc2D), u64, i32, u32, _P(PlaceStats)]),
+    "mxb_image_create": (i32, [_vp, _P(Desc2D), u64, i32, _P(_vp), _P(PlaceStats)]),
+    "mxb_image_place": (i32, [_vp, _P(Desc2D), u64, _P(PlaceStats)]),
+    "mxb_image_bytes": (u64, [_vp]),
+    "mxb_image_destroy": (i32, [_vp]),
     "mxb_digest": (i32, [_vp, i32, _P(Span), u64, u32, _P(DigestOut)]),
     "mxb_block_hashes": (i32, [_vp, i32, u64, u64, u64]),
     "mxb_digest_noalloc": (i32, [i32, _P(Span), u64, u32, _P(DigestOut), _vp]),

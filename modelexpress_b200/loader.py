@@ -27,6 +27,7 @@ from typing import Any
 import numpy as np
 
 from .layout import CheckpointPlan, plan_checkpoint
+from ._lib import MxbError
 from .runtime import (PLACE_COPY_ENGINE, Context, PlaceResult, Ring, default_context, host_register,
                       host_unregister)
 from .safetensors_index import SAFETENSORS_DTYPES, checkpoint_index
@@ -36,6 +37,7 @@ from .safetensors_index import SAFETENSORS_DTYPES, checkpoint_index
 # weights, and the pipeline is as fast with four 32 MiB chunks as with a ring of gigabytes.
 RING_BYTES = 128 << 20
 RING_SLOTS = 4
+PIN_MODES = ("off", "keep", "pages", "pages_after")
 
 
 class StrategyFailed(Exception):
@@ -83,18 +85,34 @@ class FileImage:
             self._f = open(path, "rb")
         self.size = os.fstat(self._f.fileno()).st_size
         if pinnable:
-            self._mm = mmap.mmap(self._f.fileno(), 0,
-                                 flags=mmap.MAP_SHARED if self.shared else mmap.MAP_PRIVATE,
-                                 prot=mmap.PROT_READ | mmap.PROT_WRITE)
+            self._map(self.shared)
+            if self.shared and self.size >= mmap.PAGESIZE:
+                # A shared writable mapping can be page-locked only where the file system allows
+                # long-term pins of its pages (memory file systems do, disk-backed ones refuse):
+                # try one page now, before anyone has been given an address.
+                try:
+                    base, _n = host_register(self.address, mmap.PAGESIZE)
+                    host_unregister(base)
+                except MxbError:
+                    self._np = None
+                    self._mm.close()
+                    self.shared = False
+                    self._map(False)
         else:
             self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)
+            self._np = np.frombuffer(self._mm, dtype=np.uint8)
+            self.address = self._np.ctypes.data
         self.pinnable = pinnable
-        self._np = np.frombuffer(self._mm, dtype=np.uint8)
-        self.address = self._np.ctypes.data
         self._pinned: list = []           # (base, nbytes) ranges registered by this image
         self._pin_lock = threading.Lock()
         self.pinned_bytes = 0
         self.pin_seconds = 0.0
+
+    def _map(self, shared: bool) -> None:
+        self._mm = mmap.mmap(self._f.fileno(), 0, flags=mmap.MAP_SHARED if shared else mmap.MAP_PRIVATE,
+                             prot=mmap.PROT_READ | mmap.PROT_WRITE)
+        self._np = np.frombuffer(self._mm, dtype=np.uint8)
+        self.address = self._np.ctypes.data
 
     def pin_spans(self, spans, merge_gap: int = 1 << 20) -> int:
         """Pin the union of ``(offset, nbytes)`` ranges of the file (page-aligned,
@@ -194,8 +212,16 @@ class HostImages:
     def pinned_bytes(self) -> int:
         return sum(im.pinned_bytes for im in self._images.values())
 
+    @property
+    def packed_bytes(self) -> int:
+        return sum(img.nbytes for prep in self._plans.values() for img in prep.packed.values())
+
     def close(self) -> None:
         with self._lock:
+            for prep in self._plans.values():
+                for img in prep.packed.values():
+                    img.close()
+                prep.packed = {}
             for im in self._images.values():
                 im.close()
             self._images = {}
@@ -215,6 +241,7 @@ class Prepared:
     stamps: tuple               # (dir mtime, ((path, size, mtime_ns), ...)) the plan was built from
     model_path: str = ""
     pinned_in: tuple = ()       # ids of the FileImages this rank's ranges are already pinned in
+    packed: dict = field(default_factory=dict)   # device index -> runtime.PackedImage of this rank's bytes
 
     @staticmethod
     def _stamps(model_path: str, files) -> tuple:
@@ -352,19 +379,24 @@ def place_checkpoint(model_path: str, tp_rank: int, tp_size: int, device=None, *
     ``params`` may hold pre-allocated destination tensors (an engine's own
     parameters, keyed by the engine's names); otherwise they are allocated.
 
-    ``pin`` decides what happens to the host copy of the checkpoint:
-    ``"off"``   map the files, gather through the pinned ring, unmap (a one-off load);
-    ``"keep"``  keep the files mapped in ``images`` (default: the process-wide
-                ``host_images``) and page-lock the ranges this rank reads before
-                placing them, so that this and every later load of the same files is
-                read by the copy engine in place;
-    ``"after"`` place through the ring now (pinning is slower than one load) and
-                page-lock the ranges on a background thread for the loads to come.
+    ``pin`` decides what is kept in host memory for later loads of the same files:
+    ``"off"``          nothing: map the files, gather through the pinned ring, unmap;
+    ``"keep"``         this rank's bytes, packed as they cross PCIe, in page-locked memory
+                       (as large as the rank's shard).  The first load gathers into that
+                       image instead of the ring; every later load is one contiguous
+                       copy-engine transfer and one scatter launch per chunk, with no host
+                       thread and no file access;
+    ``"pages"``        the files stay mapped in ``images`` (default: the process-wide
+                       ``host_images``) and the page ranges this rank reads are page-locked
+                       before placing, so that the copy engine gathers from the files' own
+                       pages; costs no extra memory but far more time to pin;
+    ``"pages_after"``  place through the ring now and page-lock the ranges on a background
+                       thread for the loads to come.
     """
     import torch
 
-    if pin not in ("off", "keep", "after"):
-        raise ValueError(f"pin must be 'off', 'keep' or 'after', not {pin!r}")
+    if pin not in PIN_MODES:
+        raise ValueError(f"pin must be one of {PIN_MODES}, not {pin!r}")
     timings: dict = {}
     t_start = time.perf_counter()
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
@@ -403,7 +435,7 @@ def place_checkpoint(model_path: str, tp_rank: int, tp_size: int, device=None, *
         items = prep.items(addresses, params)
         timings["pin"] = 0.0
         ids = tuple(id(opened[p]) for p in prep.files)
-        if pin == "keep" and prep.pinned_in != ids:
+        if pin == "pages" and prep.pinned_in != ids:
             t = time.perf_counter()
             for p, spans in item_spans(items, addresses, None).items():
                 opened[p].pin_spans(spans)
@@ -412,9 +444,22 @@ def place_checkpoint(model_path: str, tp_rank: int, tp_size: int, device=None, *
         # three quarters of the cores: the gather threads share DRAM bandwidth with the PCIe DMA
         threads = host_threads or max(2, min(32, (os.cpu_count() or 8) * 3 // 4))
         t = time.perf_counter()
-        stats = ring.place(items, threads, mode)
+        stats = None
+        if pin == "keep":
+            packed = prep.packed.get(dev_index)
+            if packed is not None and packed._h:
+                try:
+                    stats = packed.place(items)
+                except MxbError as e:
+                    if e.code != -8:      # anything but "the destinations no longer fit this image"
+                        raise
+                    packed.close()
+            if stats is None:
+                prep.packed[dev_index], stats = ring.keep(items, threads)
+        else:
+            stats = ring.place(items, threads, mode)
         timings["place"] = time.perf_counter() - t
-        if pin == "after" and prep.pinned_in != ids:
+        if pin == "pages_after" and prep.pinned_in != ids:
             spans = item_spans(items, addresses, None)
 
             def pin_later():
@@ -581,7 +626,8 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
     real host tensors afterwards (so where two sources write the same bytes,
     the engine-loaded one wins), with ``"raise"`` the call fails before any
     byte is written.  ``stats.seconds_total`` spans the dry run and the
-    placement, which overlap (``pipeline``).  ``pin`` as in ``place_checkpoint``.
+    placement, which overlap (``pipeline``).  ``pin``: ``"off"``, ``"pages"`` or
+    ``"pages_after"`` as in ``place_checkpoint``.
     An exception of the engine's loader that arrives after the first batch has been
     handed to the ring is re-raised as ``StrategyFailed(mutated=True)``: parameter
     bytes have been overwritten by then."""
@@ -598,8 +644,8 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
     dests = model_destinations(model)
     if ctx is None:
         ctx = ring.ctx if ring is not None else default_context(dev_index)
-    if pin not in ("off", "keep", "after"):
-        raise ValueError(f"pin must be 'off', 'keep' or 'after', not {pin!r}")
+    if pin not in ("off", "pages", "pages_after"):
+        raise ValueError(f"pin must be 'off', 'pages' or 'pages_after' here, not {pin!r}")
     cache = (images if images is not None else host_images) if pin != "off" else None
     images = {}
     pool = ThreadPoolExecutor(1)          # the ring is one pipeline: its calls run in order
@@ -667,7 +713,7 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
                 # real side effects, e.g. zeroed vocabulary padding) queued on torch's
                 # stream must be done before these destinations are written
                 torch.cuda.current_stream(dev).synchronize()
-                if pin == "keep":
+                if pin == "pages":
                     tp = time.perf_counter()
                     for p, spans in item_spans(cap.records, addresses).items():
                         images[p].pin_spans(spans)
@@ -690,7 +736,7 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
             loader((n, _engine_tensor(images[index[n]["file"]], index[n])) for n in leftover)
             timings["engine"] = time.perf_counter() - tc
         torch.cuda.current_stream(dev).synchronize()
-        if pin == "after":
+        if pin == "pages_after":
             spans_all: dict = {}
             for part in parts:
                 for p, spans in item_spans(part.records, addresses).items():

@@ -17,7 +17,7 @@ from ._lib import (DIGEST_BLOCK64, DIGEST_ROWS, DIGEST_SAFE32, PLACE_COPY_ENGINE
                    PLACE_ZERO_COPY, SCATTER_VECTOR, SCATTER_DEFAULT, SCATTER_NO_SYNC, SCATTER_OVERLAP,
                    check)
 
-__all__ = ["Context", "Ring", "Fanout", "Table", "PlaceResult", "default_context",
+__all__ = ["Context", "Ring", "PackedImage", "Fanout", "Table", "PlaceResult", "default_context",
            "host_register", "host_unregister", "host_is_pinned", "plan_pull", "plan_reshard",
            "DIGEST_SAFE32", "DIGEST_ROWS", "DIGEST_BLOCK64", "SCATTER_DEFAULT", "SCATTER_VECTOR",
            "SCATTER_NO_SYNC", "SCATTER_OVERLAP", "PLACE_COPY_ENGINE", "PLACE_ZERO_COPY"]
@@ -290,6 +290,7 @@ class Ring:
         check(ctx._lib.mxb_ring_create(ctx._h, dev, int(ring_bytes), int(slots), ctypes.byref(h)),
               "mxb_ring_create")
         self._h = h
+        self._images: list = []      # kept images use this ring's staging buffers
 
     def place(self, items, host_threads: int = 8, mode: int = PLACE_COPY_ENGINE) -> PlaceResult:
         """items: (host_src, device_dst, rows, row_bytes, src_pitch, dst_pitch) records."""
@@ -300,7 +301,22 @@ class Ring:
         return PlaceResult(st.bytes_placed, st.chunks, st.launches, st.seconds_total,
                            st.seconds_gather, st.seconds_device, st.bytes_direct, st.seconds_plan)
 
+    def keep(self, items, host_threads: int = 8) -> tuple:
+        """Place ``items`` and keep their packed bytes page-locked for later loads:
+        ``(PackedImage, PlaceResult)`` (``mxb_image_create``)."""
+        arr, n = _lib.desc_array(items)
+        st = _lib.PlaceStats()
+        h = ctypes.c_void_p()
+        check(self.ctx._lib.mxb_image_create(self._h, arr, n, int(host_threads), ctypes.byref(h),
+                                             ctypes.byref(st)), "mxb_image_create")
+        img = PackedImage(self, h)
+        self._images.append(img)
+        return img, PlaceResult(st.bytes_placed, st.chunks, st.launches, st.seconds_total,
+                                st.seconds_gather, st.seconds_device, st.bytes_direct, st.seconds_plan)
+
     def close(self):
+        for img in list(getattr(self, "_images", [])):
+            img.close()
         with _close_lock:            # a background release and __del__ may both get here
             h, self._h = getattr(self, "_h", None), None
         if h:
@@ -308,6 +324,46 @@ class Ring:
             # nothing left to release
             if getattr(self.ctx, "_h", None):
                 self.ctx._lib.mxb_ring_destroy(h)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class PackedImage:
+    """A rank's slices kept page-locked in host memory as they cross PCIe; ``place``
+    loads them again with no host copy (``mxb_image_place``)."""
+
+    def __init__(self, ring: Ring, handle):
+        self.ring, self._h = ring, handle
+
+    @property
+    def nbytes(self) -> int:
+        return int(self.ring.ctx._lib.mxb_image_bytes(self._h)) if self._h else 0
+
+    def place(self, items=None) -> PlaceResult:
+        """``items``: the same slices with (possibly) new destination addresses."""
+        if not self._h:
+            raise RuntimeError("the image has been released")
+        st = _lib.PlaceStats()
+        if items is None:
+            rc = self.ring.ctx._lib.mxb_image_place(self._h, None, 0, ctypes.byref(st))
+        else:
+            arr, n = _lib.desc_array(items)
+            rc = self.ring.ctx._lib.mxb_image_place(self._h, arr, n, ctypes.byref(st))
+        check(rc, "mxb_image_place")
+        return PlaceResult(st.bytes_placed, st.chunks, st.launches, st.seconds_total,
+                           st.seconds_gather, st.seconds_device, st.bytes_direct, st.seconds_plan)
+
+    def close(self):
+        h, self._h = self._h, None
+        if h:
+            if self in self.ring._images:
+                self.ring._images.remove(self)
+            if getattr(self.ring, "_h", None) and getattr(self.ring.ctx, "_h", None):
+                self.ring.ctx._lib.mxb_image_destroy(h)
 
     def __del__(self):
         try:

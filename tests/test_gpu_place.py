@@ -92,7 +92,7 @@ def test_small_llama_tp1_byte_exact(ckpts):
 
 @pytest.mark.parametrize("mode", ["copy_engine", "zero_copy"])
 def test_pinned_host_image_is_read_in_place(ckpts, mode):
-    """Files kept mapped and page-locked (pin="keep"): the copy engine (or, in
+    """Files kept mapped and page-locked (pin="pages"): the copy engine (or, in
     zero-copy mode, the kernel) reads the slices where they lie, no byte goes
     through the ring, and the shards are the oracle's for every rank."""
     from modelexpress_b200.loader import HostImages, place_checkpoint
@@ -108,13 +108,13 @@ def test_pinned_host_image_is_read_in_place(ckpts, mode):
         for tp in (1, 8):
             for rank in range(tp):
                 placed = place_checkpoint(tiny, rank, tp, "cuda:0", ring=ring, host_threads=4, mode=m,
-                                          pin="keep", images=images)
+                                          pin="pages", images=images)
                 _check(placed, R.load_and_shard(full, rank, tp))
                 assert placed.stats.bytes_direct == placed.stats.bytes_placed == placed.plan.bytes_placed
         assert images.pinned_bytes > 0
         # a second load of the same rank pins nothing new
         before = images.pinned_bytes
-        placed = place_checkpoint(tiny, 0, 8, "cuda:0", ring=ring, mode=m, pin="keep", images=images)
+        placed = place_checkpoint(tiny, 0, 8, "cuda:0", ring=ring, mode=m, pin="pages", images=images)
         assert images.pinned_bytes == before and placed.timings["pin"] < 0.05
     finally:
         ring.close()
@@ -123,8 +123,8 @@ def test_pinned_host_image_is_read_in_place(ckpts, mode):
 
 
 def test_pin_after_the_first_load_and_mixed_sources(ckpts):
-    """pin="after": the first load goes through the ring, later ones find the ranges
-    pinned.  A call whose sources are partly pinned, partly pageable places both."""
+    """pin="pages_after": the first load goes through the ring, later ones find the
+    ranges pinned.  A call whose sources are partly pinned, partly pageable places both."""
     import time
 
     from modelexpress_b200.loader import HostImages, place_checkpoint
@@ -137,13 +137,13 @@ def test_pin_after_the_first_load_and_mixed_sources(ckpts):
     ring = ctx.ring(32 << 20, 4, 0)
     images = HostImages()
     try:
-        first = place_checkpoint(small, 1, 4, "cuda:0", ring=ring, host_threads=4, pin="after", images=images)
+        first = place_checkpoint(small, 1, 4, "cuda:0", ring=ring, host_threads=4, pin="pages_after", images=images)
         _check(first, want)
         assert first.stats.bytes_direct == 0
         for t in ctx._background:
             t.join()
         assert images.pinned_bytes > 0
-        second = place_checkpoint(small, 1, 4, "cuda:0", ring=ring, host_threads=4, pin="after", images=images)
+        second = place_checkpoint(small, 1, 4, "cuda:0", ring=ring, host_threads=4, pin="pages_after", images=images)
         _check(second, want)
         assert second.stats.bytes_direct == second.stats.bytes_placed
         for t in ctx._background:
@@ -152,7 +152,7 @@ def test_pin_after_the_first_load_and_mixed_sources(ckpts):
         # row-parallel tensors were pinned whole by rank 1 -> a mixed call
         third = place_checkpoint(small, 2, 4, "cuda:0", ring=ring, host_threads=4, pin="off")
         _check(third, R.load_and_shard(full, 2, 4))
-        mixed = place_checkpoint(small, 2, 4, "cuda:0", ring=ring, host_threads=4, pin="after", images=images)
+        mixed = place_checkpoint(small, 2, 4, "cuda:0", ring=ring, host_threads=4, pin="pages_after", images=images)
         _check(mixed, R.load_and_shard(full, 2, 4))
         assert 0 < mixed.stats.bytes_direct < mixed.stats.bytes_placed
     finally:
@@ -160,6 +160,63 @@ def test_pin_after_the_first_load_and_mixed_sources(ckpts):
             t.join()
         ring.close()
         images.close()
+        ctx.close()
+
+
+def test_kept_packed_image_replays_without_the_files(ckpts, tmp_path):
+    """pin="keep": the first load gathers into a page-locked image of the rank's packed
+    bytes; later loads replay it (no gather, no file read), also into parameters at
+    other addresses."""
+    import shutil
+
+    import torch
+
+    from modelexpress_b200.loader import HostImages, allocate_params, place_checkpoint
+    from modelexpress_b200.runtime import Context
+
+    _, small = ckpts
+    work = str(tmp_path / "ckpt")
+    shutil.copytree(small, work)
+    full = read_full_tensors(work)
+    ctx = Context([0])
+    ring = ctx.ring(32 << 20, 4, 0)
+    images = HostImages()
+    try:
+        for rank in (0, 3):
+            want = R.load_and_shard(full, rank, 4)
+            first = place_checkpoint(work, rank, 4, "cuda:0", ring=ring, host_threads=4, pin="keep", images=images)
+            _check(first, want)
+            assert first.stats.bytes_direct == 0 and first.stats.seconds_gather > 0
+            for v in first.params.values():
+                v.zero_()
+            again = place_checkpoint(work, rank, 4, "cuda:0", ring=ring, params=first.params, pin="keep",
+                                     images=images)
+            _check(again, want)
+            assert again.stats.bytes_direct == again.stats.bytes_placed and again.stats.seconds_gather == 0
+            # other destination tensors (other addresses): the image is retargeted, not rebuilt
+            other = allocate_params(again.plan, "cuda:0")
+            pad = torch.empty(4096 + 16 * rank, dtype=torch.uint8, device="cuda")  # shift the allocator
+            moved = place_checkpoint(work, rank, 4, "cuda:0", ring=ring, params=other, pin="keep", images=images)
+            _check(moved, want)
+            assert moved.stats.seconds_gather == 0
+            del pad
+        assert images.packed_bytes > 0
+        # a destination at another 16-byte phase cannot reuse the packing: a new image is made
+        plan = moved.plan
+        skew = {}
+        for n, spec in plan.params.items():
+            numel = 1
+            for e in spec.shape:
+                numel *= int(e)
+            raw = torch.zeros(numel * 2 + 8, dtype=torch.uint8, device="cuda")
+            skew[n] = raw[8: 8 + numel * 2].view(torch.bfloat16).reshape(tuple(spec.shape))
+        skewed = place_checkpoint(work, 3, 4, "cuda:0", ring=ring, params=skew, host_threads=4, pin="keep",
+                                  images=images)
+        _check(skewed, R.load_and_shard(full, 3, 4))
+        assert skewed.stats.seconds_gather > 0
+    finally:
+        images.close()
+        ring.close()
         ctx.close()
 
 
