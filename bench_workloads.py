@@ -504,8 +504,11 @@ def reshard_measure(args, ctx, rank, world, local, nv=None) -> dict:
     schedules = {"two kernels side by side": SCATTER_OVERLAP, "one kernel after the other": 0}
     if os.environ.get("MXB_SCATTER", "auto") == "vec":
         schedules = {"vector engine only": SCATTER_VECTOR}
+    parts = {}
+    if os.environ.get("MXB_RESHARD_PARTS") == "1":   # each engine's share of the table alone
+        parts = {"bulk-engine part alone (local copies)": 8, "vector-engine part alone (peer stores)": 16}
     per_schedule = {}
-    for label, flags in schedules.items():
+    for label, flags in {**parts, **schedules}.items():
         times = []
         for it in range(warmup + steps):
             _barrier(world)
@@ -520,7 +523,7 @@ def reshard_measure(args, ctx, rank, world, local, nv=None) -> dict:
             if it >= warmup:
                 times.append(ms)
         per_schedule[label] = round(sum(times) / len(times), 4)
-    best_label = min(per_schedule, key=per_schedule.get)
+    best_label = min(schedules, key=per_schedule.get)
     ms, flags = per_schedule[best_label], schedules[best_label]
     # the pattern check below reads what the last launch wrote; make that the reported schedule
     params_t.zero_()

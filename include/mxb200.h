@@ -220,6 +220,9 @@ int64_t mxb_coalesce_runs(const mxb_run *runs, uint64_t n, mxb_desc2d *out, uint
                                   of a table as two concurrent kernels (worth it when both have
                                   much to do, e.g. local copies next to peer stores) */
 
+#define MXB_SCATTER_BULK_PART 8u    /* measurement aid: launch only the bulk-engine part of a table */
+#define MXB_SCATTER_VECTOR_PART 16u /* measurement aid: launch only the vector-engine part */
+
 /* One persistent launch on `dev` moves every record of the host table
  * `descs[0..n)`: sources and destinations may be local HBM, a peer GPU's HBM
  * or pinned host memory.  Stands in for Transport.read(descriptors)

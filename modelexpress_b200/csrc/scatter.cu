@@ -516,6 +516,11 @@ int32_t launch_scatter_tiles(mxb_ctx *ctx, DeviceState *dv, const ScatterTable &
     // engine) runs them side by side instead: the bulk kernel first (one warp and most of the
     // shared memory of every SM), the vector kernel on a second stream with three CTAs per SM,
     // which is what still fits beside it, so that HBM copies hide under the slower link.
+    if (flags & (MXB_SCATTER_BULK_PART | MXB_SCATTER_VECTOR_PART)) {  // one half only (measurements)
+        if (flags & MXB_SCATTER_BULK_PART)
+            return launch_bulk(ctx, dv, tb.descs, bulk_tiles, bulk_count, stream);
+        return launch_vec(ctx, dv, tb.descs, vec_tiles, vec_count, stream);
+    }
     const bool overlap = (flags & MXB_SCATTER_OVERLAP) && stream == dv->stream &&
                          bulk_count >= (uint64_t)dv->sm_count && vec_count >= (uint64_t)dv->sm_count;
     if (!overlap) {

@@ -52,6 +52,7 @@ class Placement:
     dst_name: str
     dst_shape: tuple
     dst_start: int
+    dst_extra: int = 0  # further element offset into the destination (a slot of a stacked parameter)
 
     def geometry(self) -> tuple:
         """(src_byte_off, dst_byte_off, rows, row_bytes, src_pitch, dst_pitch)."""
@@ -67,11 +68,11 @@ class Placement:
         row_bytes = self.size * inner * el
         src_pitch = int(shape[self.axis]) * inner * el
         dst_pitch = int(dshape[self.axis]) * inner * el
+        dst_off = (self.dst_start * inner + self.dst_extra) * el
         if outer == 1 or (src_pitch == row_bytes and dst_pitch == row_bytes):
-            return (self.start * inner * el, self.dst_start * inner * el, 1, outer * row_bytes,
+            return (self.start * inner * el, dst_off, 1, outer * row_bytes,
                     outer * row_bytes, outer * row_bytes)
-        return (self.start * inner * el, self.dst_start * inner * el, outer, row_bytes, src_pitch,
-                dst_pitch)
+        return (self.start * inner * el, dst_off, outer, row_bytes, src_pitch, dst_pitch)
 
     def record(self, src_base: int, dst_base: int) -> tuple:
         so, do, rows, rb, sp, dp = self.geometry()
@@ -183,15 +184,19 @@ _MLA_A = re.compile(r"(.*\.self_attn\.)(q_a_proj|kv_a_proj_with_mqa)\.(weight|we
 
 
 def plan_moe(index: dict, tp_rank: int, tp_size: int, ep_rank: int | None = None,
-             ep_size: int | None = None) -> CheckpointPlan:
+             ep_size: int | None = None, expert_tp: tuple = (0, 1)) -> CheckpointPlan:
     """DeepSeek-V3-style block-FP8 MoE: routed experts expert-parallel into
     ``experts.w13_weight[slot, half]`` / ``w2_weight[slot]`` with their
     ``weight_scale_inv`` blocks alongside (installer.py:695-771: gate is the low
     half of w13, up the high half, slot = global id - first local id); the shared
     expert and MLA projections tensor-parallel with scale rows/cols split in
-    step (128-blocks); q_a/kv_a fused and replicated; the rest replicated."""
+    step (128-blocks); q_a/kv_a fused and replicated; the rest replicated.
+    ``expert_tp = (rank, size)`` additionally splits every routed expert
+    tensor-parallel (gate/up rows, down columns; installer.py:737-768), for
+    engines that do not run their experts expert-parallel."""
     ep_rank = tp_rank if ep_rank is None else ep_rank
     ep_size = tp_size if ep_size is None else ep_size
+    et_rank, et_size = int(expert_tp[0]), int(expert_tp[1])
     plan = CheckpointPlan()
     experts: dict = {}
     dense_part: dict = {}
@@ -251,9 +256,10 @@ def plan_moe(index: dict, tp_rank: int, tp_size: int, ep_rank: int | None = None
         suffix = "weight" if kind == "weight" else "weight_scale_inv"
         w13 = f"{prefix}experts.w13_{suffix}"
         w2 = f"{prefix}experts.w2_{suffix}"
-        half = g[1][0]
+        half = _split(g[1][0], et_size, f"{prefix}experts gate rows")
+        down_cols = _split(dn[1][1], et_size, f"{prefix}experts down columns") if len(dn[1]) > 1 else 1
         w13_shape = (per, 2 * half) + tuple(g[1][1:])
-        w2_shape = (per,) + tuple(dn[1])
+        w2_shape = (per, dn[1][0], down_cols) + tuple(dn[1][2:]) if len(dn[1]) > 1 else (per,) + tuple(dn[1])
         plan.params[w13] = ParamSpec(w13, w13_shape, dtype)
         plan.params[w2] = ParamSpec(w2, w2_shape, dn[2])
         for slot in range(per):
@@ -263,12 +269,21 @@ def plan_moe(index: dict, tp_rank: int, tp_size: int, ep_rank: int | None = None
                 # the slot is a [2*half, ...] matrix inside the 3-D parameter: address it
                 # as axis 0 of a flattened (per*2*half, ...) view
                 flat = (per * 2 * half,) + tuple(shape[1:])
-                plan.placements.append(Placement(name, shape, dtype, 0, 0, shape[0], w13, flat,
+                plan.placements.append(Placement(name, shape, dtype, 0, et_rank * half, half, w13, flat,
                                                  slot * 2 * half + lo))
             name, shape, _dt = members[(e, "down_proj")]
-            flat = (per * shape[0],) + tuple(shape[1:])
-            plan.placements.append(Placement(name, shape, dn[2], 0, 0, shape[0], w2, flat,
-                                             slot * shape[0]))
+            if et_size == 1 or len(shape) < 2:
+                flat = (per * shape[0],) + tuple(shape[1:])
+                plan.placements.append(Placement(name, shape, dn[2], 0, 0, shape[0], w2, flat,
+                                                 slot * shape[0]))
+            else:
+                # a column block of every row, landing in slot `slot` of [per, rows, cols/size]
+                inner = 1
+                for extent in shape[2:]:
+                    inner *= int(extent)
+                plan.placements.append(Placement(name, shape, dn[2], 1, et_rank * down_cols, down_cols, w2,
+                                                 (shape[0], down_cols) + tuple(shape[2:]), 0,
+                                                 slot * shape[0] * down_cols * inner))
     return plan
 
 

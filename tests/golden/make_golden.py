@@ -10,6 +10,9 @@ Outputs (all small, committed):
   digests.json      safe_checksum / tensor_digest of seeded byte strings
   slice_plan.json   plan_pull segments for hand-written and random copies
   installer.json    MdlLoader TP-narrow / fused-offset / pre-merged arithmetic
+  expert_slots.json MdlLoader.load_weights on FusedMoE-style stand-ins: FP8 expert
+                    weights and block scales into w13 / w2 slots, expert-parallel
+                    (global -> local expert id) and tensor-parallel inside an expert
   toy_reshard.json  capture_geometry -> plan_transfer -> memmove on the
                     reference's ToyModel (column, row, fused qkv, norm)
   capture_pin.json  the reference's capture_geometry + resolve_slice on
@@ -252,6 +255,96 @@ def make_installer(torch, MdlLoader):
     return out
 
 
+def expert_case_tensors(seed: int, experts: int, inter: int, hidden: int, block: int) -> dict:
+    """The checkpoint side of an expert-slot case, rebuilt from its numbers alone:
+    per expert gate/up ``[inter, hidden]`` and down ``[hidden, inter]`` as raw FP8
+    bytes, block scales ``[inter/block, hidden/block]`` / ``[hidden/block, inter/block]``
+    as float32 (small integers over 8, exact in every format)."""
+    rng = np.random.default_rng(seed)
+    out = {}
+    for e in range(experts):
+        pre = f"model.layers.0.mlp.experts.{e}."
+        for name, shape in (("gate_proj", (inter, hidden)), ("up_proj", (inter, hidden)),
+                            ("down_proj", (hidden, inter))):
+            # byte values that are finite, distinct FP8 numbers (avoid 0x7f/0xff NaN patterns)
+            out[pre + name + ".weight"] = rng.integers(1, 0x70, size=shape, dtype=np.uint8)
+            sshape = (shape[0] // block, shape[1] // block)
+            out[pre + name + ".weight_scale_inv"] = (rng.integers(1, 64, size=sshape) / 8.0).astype(np.float32)
+    return out
+
+
+def make_expert_slots(torch, MdlLoader):
+    """Drive the reference's MdlLoader (engines/vllm/refit/installer.py:86-191, expert
+    slots :695-771) on stand-ins shaped like vLLM's FusedMoE parameters, the way the
+    reference's own tests do (tests/test_mdl_fp8.py:279-357), and record what lands
+    in w13 / w2 and their block scales."""
+    F8 = torch.float8_e4m3fn
+    cases = []
+    for tag, experts, ep, tp, inter, hidden, block, seed in [
+        ("ep4_of_8", 8, 4, 1, 4, 6, 2, 101),
+        ("ep2_of_6", 6, 2, 1, 8, 4, 2, 102),
+        ("ep1_of_3", 3, 1, 1, 4, 4, 1, 103),
+        ("tp2_inside_experts", 2, 1, 2, 8, 8, 2, 104),   # the TP2 shape collision of the reference's test
+    ]:
+        tensors = expert_case_tensors(seed, experts, inter, hidden, block)
+        per = experts // ep
+        for rank in range(max(ep, tp)):
+            ep_rank = rank if ep > 1 else 0
+            tp_rank = rank if tp > 1 else 0
+            li, lh = inter // tp, hidden   # column split of gate/up rows, row split of down cols
+            model = torch.nn.Module()
+            model.model = torch.nn.Module()
+            model.model.layers = torch.nn.ModuleList([torch.nn.Module()])
+            mlp = torch.nn.Module()
+            model.model.layers[0].mlp = mlp
+            ex = torch.nn.Module()
+            mlp.experts = ex
+
+            def par(shape, dtype=torch.float32):
+                return torch.nn.Parameter(torch.zeros(shape, dtype=dtype), requires_grad=False)
+
+            ex.w13_weight = par((per, 2 * li, lh), F8)
+            ex.w2_weight = par((per, hidden, li), F8)
+            ex.w13_weight_scale = par((per, 2 * li // block, lh // block))
+            ex.w2_weight_scale = par((per, hidden // block, li // block))
+            lo = ep_rank * per
+            ex._map_global_expert_id_to_local_expert_id = (
+                lambda gid, lo=lo, per=per: gid - lo if lo <= gid < lo + per else -1)
+
+            def load_weights(*, weights):
+                raise AttributeError("processed FP8 parameters are not re-entrant")
+
+            model.load_weights = load_weights
+            prefix = "model.layers.0.mlp."
+            mapping = []
+            for e in range(experts):
+                mapping += [(prefix + "experts.w13_", prefix + f"experts.{e}.gate_proj.", e, "w1"),
+                            (prefix + "experts.w2_", prefix + f"experts.{e}.down_proj.", e, "w2"),
+                            (prefix + "experts.w13_", prefix + f"experts.{e}.up_proj.", e, "w3")]
+            model.get_expert_mapping = lambda mapping=mapping: mapping
+            os.environ["MX_LOAD_MODE"] = "direct"
+            os.environ["MX_FP8_LOADERLESS"] = "1"
+            ld = MdlLoader(model)
+            ld._tp_size, ld._tp_rank = tp, tp_rank
+            weights = []
+            for e in range(lo, lo + per):       # an expert-parallel rank is fed its own experts
+                for name in ("gate_proj", "up_proj", "down_proj"):
+                    for suffix in ("weight", "weight_scale_inv"):
+                        key = f"{prefix}experts.{e}.{name}.{suffix}"
+                        t = torch.from_numpy(tensors[key].copy())
+                        weights.append((key, t.view(F8) if suffix == "weight" else t))
+            ld.load_weights(weights)
+            cases.append({
+                "tag": tag, "experts": experts, "ep": ep, "tp": tp, "rank": rank, "inter": inter,
+                "hidden": hidden, "block": block, "seed": seed,
+                "w13_weight": ex.w13_weight.data.view(torch.uint8).tolist(),
+                "w2_weight": ex.w2_weight.data.view(torch.uint8).tolist(),
+                "w13_scale": ex.w13_weight_scale.data.tolist(),
+                "w2_scale": ex.w2_weight_scale.data.tolist(),
+            })
+    return cases
+
+
 def make_toy_reshard(torch, ref_root):
     sys.path.insert(0, ref_root)
     from tests.test_reshard_refit_geometry import ToyModel, _manifest
@@ -458,6 +551,7 @@ def main():
     dump("digests.json", make_digests(torch, safe_checksum, tensor_digest))
     dump("slice_plan.json", make_slice_plan(slice_plan, types))
     dump("installer.json", make_installer(torch, MdlLoader))
+    dump("expert_slots.json", make_expert_slots(torch, MdlLoader))
     dump("toy_reshard.json", make_toy_reshard(torch, args.reference))
     dump("capture_pin.json", make_capture_pin(torch))
     dump("shard_table.json", make_shard_table())

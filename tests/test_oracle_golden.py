@@ -207,3 +207,46 @@ def test_regather_and_reslice_equals_load_and_shard():
         assert a.keys() == b.keys()
         for n in a:
             assert np.array_equal(a[n], b[n])
+
+
+def _expert_case_arrays(case):
+    from make_golden import expert_case_tensors
+
+    tensors = expert_case_tensors(case["seed"], case["experts"], case["inter"], case["hidden"], case["block"])
+    ep = (case["rank"] if case["ep"] > 1 else 0, case["ep"])
+    et = (case["rank"] if case["tp"] > 1 else 0, case["tp"])
+    want = {"experts.w13_weight": np.array(case["w13_weight"], dtype=np.uint8),
+            "experts.w2_weight": np.array(case["w2_weight"], dtype=np.uint8),
+            "experts.w13_weight_scale_inv": np.array(case["w13_scale"], dtype=np.float32),
+            "experts.w2_weight_scale_inv": np.array(case["w2_scale"], dtype=np.float32)}
+    return tensors, ep, et, want
+
+
+@pytest.mark.parametrize("case", _load("expert_slots.json"), ids=lambda c: f'{c["tag"]}-r{c["rank"]}')
+def test_expert_slots_match_the_reference_loader(case):
+    """expert_slots.json is what the reference's MdlLoader (installer.py:695-771) wrote
+    into FusedMoE-style w13 / w2 parameters and their block scales, expert-parallel
+    and with tensor-parallel experts: the oracle's load_and_shard_moe and the
+    product's layout rules (records executed by the oracle's C loop) must give the
+    same bytes."""
+    from helpers import run_records_on_host
+    from modelexpress_b200 import layout
+
+    tensors, ep, et, want = _expert_case_arrays(case)
+    got = R.load_and_shard_moe(tensors, 0, 1, ep=ep, expert_tp=et)
+    pre = "model.layers.0.mlp."
+    for key, w in want.items():
+        assert got[pre + key].shape == w.shape, key
+        assert np.array_equal(got[pre + key], w), (case["tag"], case["rank"], key)
+    # the product's placement rules on the same checkpoint
+    index = {n: {"shape": list(a.shape), "dtype": "F8_E4M3" if a.dtype == np.uint8 else "F32"}
+             for n, a in tensors.items()}
+    plan = layout.plan_moe(index, 0, 1, ep_rank=ep[0], ep_size=ep[1], expert_tp=et)
+    bufs = {n: np.zeros(s.shape, dtype=np.uint8 if s.dtype == "F8_E4M3" else np.float32)
+            for n, s in plan.params.items()}
+    srcs = {n: np.ascontiguousarray(a) for n, a in tensors.items()}
+    run_records_on_host([pl.record(srcs[pl.src_name].ctypes.data, bufs[pl.dst_name].ctypes.data)
+                         for pl in plan.placements])
+    for key, w in want.items():
+        assert bufs[pre + key].shape == w.shape, key
+        assert np.array_equal(bufs[pre + key], w), (case["tag"], case["rank"], key)
