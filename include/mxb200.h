@@ -368,6 +368,27 @@ int32_t mxb_digest_noalloc(int32_t dev, const mxb_span *spans, uint64_t n, uint3
 
 #define MXB_FANOUT_MAX_CHILDREN 7
 
+/* One piece of a fan-out payload: `nbytes` (<= 64 KiB) at `offset` inside range
+ * `range`, belonging to chunk `chunk`. */
+typedef struct {
+    uint64_t range;
+    uint64_t offset;
+    uint32_t nbytes;
+    uint32_t chunk;
+} mxb_fanout_piece;
+
+/* Host only: how a payload of `n` ranges is cut into pieces and chunks of
+ * `chunk_bytes` (only the sizes of `local` matter, so every GPU of a broadcast
+ * cuts alike).  chunk_pieces[c] is the number of pieces of chunk c: the value a
+ * child's arrival counter c reaches per broadcast.  *n_pieces / *n_chunks give
+ * the full counts; MXB_ERR_NOMEM if a cap is smaller.  This is the transfer
+ * plan of the peer pull (nixl_transfer.py:769-952 posts one READ per matched
+ * tensor; here a tensor is cut so that chunks can be forwarded while later
+ * ones are still arriving). */
+int32_t mxb_fanout_plan(const mxb_span *local, uint64_t n, uint64_t chunk_bytes,
+                        mxb_fanout_piece *pieces, uint64_t piece_cap, uint64_t *n_pieces,
+                        uint32_t *chunk_pieces, uint64_t chunk_cap, uint64_t *n_chunks);
+
 /* A fan-out node: this GPU's copy of the payload is the ranges
  * `local[0..n)`, cut into chunks of `chunk_bytes`.  The node waits for each
  * chunk to arrive from its parent (unless it is the root), stores it into

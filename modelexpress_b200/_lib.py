@@ -57,6 +57,10 @@ class Shard(ctypes.Structure):
                 ("addr", u64)]
 
 
+class FanoutPiece(ctypes.Structure):
+    _fields_ = [("range", u64), ("offset", u64), ("nbytes", u32), ("chunk", u32)]
+
+
 class PlaceStats(ctypes.Structure):
     _fields_ = [("bytes_placed", u64), ("chunks", u64), ("launches", u64),
                 ("seconds_total", ctypes.c_double), ("seconds_gather", ctypes.c_double),
@@ -109,6 +113,7 @@ SIGNATURES = {
     "mxb_digest": (i32, [_vp, i32, _P(Span), u64, u32, _P(DigestOut)]),
     "mxb_block_hashes": (i32, [_vp, i32, u64, u64, u64]),
     "mxb_digest_noalloc": (i32, [i32, _P(Span), u64, u32, _P(DigestOut), _vp]),
+    "mxb_fanout_plan": (i32, [_P(Span), u64, u64, _P(FanoutPiece), u64, _P(u64), _P(u32), u64, _P(u64)]),
     "mxb_fanout_create": (i32, [_vp, i32, _P(Span), u64, u64, _P(_vp)]),
     "mxb_fanout_counters": (u64, [_vp]),
     "mxb_fanout_set_child": (i32, [_vp, i32, _P(Span), u64, u64]),

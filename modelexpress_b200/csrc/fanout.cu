@@ -274,7 +274,61 @@ struct mxb_fanout {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
 };
 
+namespace {
+
+// Pieces of a payload: walk the concatenated byte space of the ranges; cut at range ends,
+// chunk ends and 64 KiB.  Every piece start stays 16-byte aligned inside its range: only a
+// range's last piece may be ragged.  Depends on the range sizes alone, so every GPU of a
+// broadcast (same sizes, own addresses) cuts the same pieces and counts the same chunks.
+void plan_pieces(const mxb_span *local, uint64_t n, uint64_t chunk_bytes,
+                 std::vector<mxb_fanout_piece> &pieces, std::vector<uint32_t> &chunk_pieces) {
+    uint64_t vpos = 0;
+    for (uint64_t i = 0; i < n; ++i) {
+        uint64_t off = 0;
+        while (off < local[i].nbytes) {
+            const uint64_t chunk = vpos / chunk_bytes;
+            const uint64_t to_chunk_end = (chunk + 1) * chunk_bytes - vpos;
+            uint64_t len = local[i].nbytes - off;
+            if (len > to_chunk_end) len = to_chunk_end;
+            if (len > kFanPiece) len = kFanPiece;
+            if (len < local[i].nbytes - off) len &= ~uint64_t(15);
+            if (len == 0) len = local[i].nbytes - off < 16 ? local[i].nbytes - off : 16;
+            pieces.push_back({i, off, (uint32_t)len, (uint32_t)chunk});
+            if (chunk_pieces.size() <= chunk) chunk_pieces.resize(chunk + 1, 0);
+            chunk_pieces[chunk] += 1;
+            off += len;
+            vpos += len;
+        }
+    }
+}
+
+}  // namespace
+
 extern "C" {
+
+int32_t mxb_fanout_plan(const mxb_span *local, uint64_t n, uint64_t chunk_bytes,
+                        mxb_fanout_piece *pieces, uint64_t piece_cap, uint64_t *n_pieces,
+                        uint32_t *chunk_pieces, uint64_t chunk_cap, uint64_t *n_chunks) {
+    if ((!local && n) || !n_pieces || !n_chunks || chunk_bytes < 4096 || (chunk_bytes & 15u) ||
+        (!pieces && piece_cap) || (!chunk_pieces && chunk_cap)) {
+        set_error("mxb_fanout_plan: bad arguments (chunk must be a multiple of 16, >= 4096)");
+        return MXB_ERR_ARG;
+    }
+    std::vector<mxb_fanout_piece> plan;
+    std::vector<uint32_t> per_chunk;
+    plan_pieces(local, n, chunk_bytes, plan, per_chunk);
+    *n_pieces = plan.size();
+    *n_chunks = per_chunk.size();
+    for (uint64_t i = 0; i < plan.size() && i < piece_cap; ++i) pieces[i] = plan[i];
+    for (uint64_t i = 0; i < per_chunk.size() && i < chunk_cap; ++i) chunk_pieces[i] = per_chunk[i];
+    if (plan.size() > piece_cap || per_chunk.size() > chunk_cap) {
+        set_error("mxb_fanout_plan: %llu pieces in %llu chunks, room for %llu and %llu",
+                  (unsigned long long)plan.size(), (unsigned long long)per_chunk.size(),
+                  (unsigned long long)piece_cap, (unsigned long long)chunk_cap);
+        return MXB_ERR_NOMEM;
+    }
+    return MXB_OK;
+}
 
 int32_t mxb_fanout_create(mxb_ctx *ctx, int32_t dev, const mxb_span *local, uint64_t n,
                           uint64_t chunk_bytes, mxb_fanout **out) {
@@ -298,27 +352,12 @@ int32_t mxb_fanout_create(mxb_ctx *ctx, int32_t dev, const mxb_span *local, uint
     f->dv = dv;
     f->local.assign(local, local + n);
     f->chunk_bytes = chunk_bytes;
-    // pieces: walk the concatenated byte space; cut at range ends, chunk ends, 64 KiB
-    uint64_t vpos = 0;
-    for (uint64_t i = 0; i < n; ++i) {
-        uint64_t off = 0;
-        while (off < local[i].nbytes) {
-            uint64_t chunk = vpos / chunk_bytes;
-            uint64_t to_chunk_end = (chunk + 1) * chunk_bytes - vpos;
-            uint64_t len = local[i].nbytes - off;
-            if (len > to_chunk_end) len = to_chunk_end;
-            if (len > kFanPiece) len = kFanPiece;
-            // keep every piece start 16-byte aligned: only a range's last piece may be ragged
-            if (len < local[i].nbytes - off) len &= ~uint64_t(15);
-            if (len == 0) len = local[i].nbytes - off < 16 ? local[i].nbytes - off : 16;
-            f->pieces.push_back({local[i].ptr + off, (uint32_t)len, (uint32_t)chunk});
-            f->piece_range.push_back(i);
-            f->piece_off.push_back(off);
-            if (f->chunk_pieces.size() <= chunk) f->chunk_pieces.resize(chunk + 1, 0);
-            f->chunk_pieces[chunk] += 1;
-            off += len;
-            vpos += len;
-        }
+    std::vector<mxb_fanout_piece> plan;
+    plan_pieces(local, n, chunk_bytes, plan, f->chunk_pieces);
+    for (const mxb_fanout_piece &p : plan) {
+        f->pieces.push_back({local[p.range].ptr + p.offset, p.nbytes, p.chunk});
+        f->piece_range.push_back(p.range);
+        f->piece_off.push_back(p.offset);
     }
     DeviceGuard g(dev);
     const size_t nchunks = f->chunk_pieces.size() ? f->chunk_pieces.size() : 1;

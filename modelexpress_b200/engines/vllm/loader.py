@@ -7,8 +7,10 @@ reference's class (engines/vllm/loader.py:62-183) initialises the model, runs
 its strategy chain and returns ``model.eval()``.  This class keeps that surface
 — ``__init__(load_config)``, ``load_model(vllm_config, model_config, prefix)``,
 ``download_model(model_config)``, ``load_weights(model, model_config)``, the
-``nixl_manager`` / ``tensors`` properties — and runs a three-entry chain:
-``B200CapturedStrategy`` (the model's own ``load_weights`` dry-run over
+``nixl_manager`` / ``tensors`` properties — and runs a chain of strategies:
+``B200FanoutStrategy`` (a serving peer on the same box has published its weights
+in the rendezvous directory ``MXB_FANOUT_DIR``: they arrive over NVLink, the
+checkpoint is not read at all), ``B200CapturedStrategy`` (the model's own ``load_weights`` dry-run over
 byte-less placeholders tells which window of which checkpoint tensor lands
 where, for any architecture vLLM can load; safetensors -> pinned ring -> PCIe
 -> scatter kernel, straight into the engine's parameters), then
@@ -24,6 +26,7 @@ import copy
 import logging
 import os
 
+from ...fanout import B200FanoutStrategy
 from ...loader import B200CapturedStrategy, B200ScatterStrategy, LoadResult, StrategyFailed
 
 logger = logging.getLogger("modelexpress_b200.engines.vllm")
@@ -51,10 +54,14 @@ class VllmScatterAdapter:
 
 
 class _Ctx:
-    def __init__(self, model_config, device_id: int):
+    def __init__(self, model_config, device_id: int, reinit=None):
         self.model_config = model_config
         self.device_id = device_id
         self.adapter = VllmScatterAdapter()
+        if reinit is not None:
+            # adapter.py:24-34 of the reference: after a strategy failed having written into
+            # the model, the next one starts from a freshly initialised model
+            self.adapter.reinit_for_retry = reinit
 
 
 class MxModelLoader(BaseModelLoader):
@@ -74,32 +81,39 @@ class MxModelLoader(BaseModelLoader):
             return
         self._native().download_model(model_config)
 
-    def load_weights(self, model, model_config) -> None:
-        """Load weights into an already-initialised model (standalone API)."""
+    def load_weights(self, model, model_config, reinit=None):
+        """Load weights into an already-initialised model (standalone API).  ``reinit``
+        (``LoadResult -> LoadResult``) re-initialises the model after a strategy failed
+        having written into it (load_strategy/__init__.py:95-131); without it the next
+        strategy starts from the model as the failed one left it, which is safe only
+        because every strategy after the first writes every parameter it loads.
+        Returns the model that holds the weights (another object after a reinit)."""
         import torch
 
         device_id = torch.cuda.current_device()
         result = LoadResult(value=model, model=model)
-        ctx = _Ctx(model_config, device_id)
+        ctx = _Ctx(model_config, device_id, reinit)
         self.last_strategy = None
-        for strategy in (B200CapturedStrategy(), B200ScatterStrategy()):
+        for strategy in (B200FanoutStrategy(), B200CapturedStrategy(), B200ScatterStrategy()):
             try:
                 if not strategy.is_available(ctx):
-                    raise StrategyFailed("CUDA library or device unavailable", mutated=False)
-                strategy.load(result, ctx)
+                    raise StrategyFailed("not available here", mutated=False)
+                result = strategy.load(result, ctx) or result
                 self.last_strategy = strategy.name
                 self.last_metadata = result.metadata.get(strategy.name)
                 logger.info("weights placed by %s: %s", strategy.name, result.metadata.get(strategy.name))
                 break
             except StrategyFailed as e:
                 strategy.rollback(ctx)
-                # after a failure that touched weights every later strategy rewrites all of them
                 level = logger.warning if e.mutated else logger.info
                 level("%s did not load the model (%s); trying the next strategy", strategy.name, e)
+                if e.mutated and reinit is not None:
+                    result = reinit(result)
         if self.last_strategy is None:
-            self._native().load_weights(model, model_config)
+            self._native().load_weights(result.model, model_config)
             self.last_strategy = "default"
-        self._tensors = {n: p.data for n, p in model.named_parameters()}
+        self._tensors = {n: p.data for n, p in result.model.named_parameters()}
+        return result.model
 
     def load_model(self, vllm_config, model_config, prefix: str = ""):
         import torch
@@ -110,9 +124,15 @@ class MxModelLoader(BaseModelLoader):
         device_config = vllm_config.device_config
         target_device = torch.device(device_config.device)
         with set_default_torch_dtype(model_config.dtype):
-            with target_device:
-                model = initialize_model(vllm_config=vllm_config, model_config=model_config, prefix=prefix)
-            self.load_weights(model, model_config)
+            def fresh_model():
+                with target_device:
+                    return initialize_model(vllm_config=vllm_config, model_config=model_config, prefix=prefix)
+
+            def reinit(result):
+                model = fresh_model()
+                return LoadResult(value=model, model=model, metadata=result.metadata)
+
+            model = self.load_weights(fresh_model(), model_config, reinit)
             process_weights_after_loading(model, model_config, target_device)
         return model.eval()
 

@@ -223,3 +223,109 @@ def test_refit_cycle_two_ranks_gloo(tmp_path, world):
         env=env, capture_output=True, text=True, timeout=240)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert proc.stdout.count("ok") == world
+
+
+FANOUT_WORKER = textwrap.dedent('''
+    import os, sys, mmap, ctypes
+    import numpy as np
+    import torch, torch.distributed as dist
+    sys.path.insert(0, ROOT); sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from modelexpress_b200.fanout import (ManifestMismatchError, TensorDescriptor, match_manifests,
+                                          plan_pieces, topology)
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("gloo")
+    work = os.environ["MXB_TEST_DIR"]
+    sizes = [3 << 20, 4096 + 16, 100, 333 * 16, 1 << 20, 52, 700_000]
+    names = [f"t{i}" for i in range(len(sizes))]
+    CHUNK = 256 << 10
+
+    def shared(name, nbytes, create):
+        path = os.path.join(work, name)
+        if create:
+            with open(path, "wb") as f:
+                f.truncate(nbytes)
+        f = open(path, "r+b")
+        return np.frombuffer(mmap.mmap(f.fileno(), nbytes), dtype=np.uint8)
+
+    offs, pos = [], 0
+    for n in sizes:
+        offs.append(pos)
+        pos = (pos + n + 255) // 256 * 256
+    pieces, chunk_pieces = plan_pieces(sizes, CHUNK)
+    # every rank owns a payload arena and its arrival counters; peers map both (the IPC stand-in)
+    own = shared(f"arena{rank}", pos, True)
+    ctr = shared(f"ctr{rank}", 4 * len(chunk_pieces), True).view(np.uint32)
+    if rank == 0:
+        rng = np.random.default_rng(3)
+        own[:] = rng.integers(0, 256, pos, dtype=np.uint8)
+    dist.barrier()
+    arenas = [own if r == rank else shared(f"arena{r}", pos, False) for r in range(world)]
+    ctrs = [ctr if r == rank else shared(f"ctr{r}", 4 * len(chunk_pieces), False).view(np.uint32)
+            for r in range(world)]
+    # the manifests travel between the ranks; every target matches the root's against its own
+    mine = [TensorDescriptor(n, int(arenas[rank].ctypes.data) + o, s, rank, "torch.uint8")
+            for n, o, s in zip(names, offs, sizes)]
+    everyone = [None] * world
+    dist.all_gather_object(everyone, [(d.name, d.size, d.dtype) for d in mine])
+    root_rows = [TensorDescriptor(n, 0, s, 0, dt) for n, s, dt in everyone[0]]
+    matched = match_manifests(root_rows, mine)
+    assert [m[0] for m in matched] == names and [m[3] for m in matched] == sizes
+    try:
+        match_manifests(root_rows[:-1], mine)
+        raise SystemExit("a missing tensor went unnoticed")
+    except ManifestMismatchError:
+        pass
+    try:
+        match_manifests([TensorDescriptor("t0", 0, sizes[0] + 2, 0, "torch.uint8")] + root_rows[1:], mine)
+        raise SystemExit("a size mismatch went unnoticed")
+    except ManifestMismatchError:
+        pass
+    # the piece plan depends on sizes only: every rank cut the same pieces
+    plans = [None] * world
+    dist.all_gather_object(plans, (pieces, chunk_pieces))
+    assert all(p == plans[0] for p in plans)
+    assert sum(p[2] for p in pieces) == sum(sizes) and max(p[2] for p in pieces) <= 65536
+    assert all(p[1] % 16 == 0 for p in pieces) and sum(chunk_pieces) == len(pieces)
+    # one broadcast down the chain, executed piece by piece on the host the way a node's kernel
+    # does it: wait for the chunk's counter (not the root), store to the child, raise its counter
+    children = topology("chain", world, 0)
+    run_index = 1
+    for rng_i, off, nbytes, chunk in pieces:
+        if rank != 0:
+            import time
+            t0 = time.time()
+            while int(ctrs[rank][chunk]) < run_index * chunk_pieces[chunk]:
+                assert time.time() - t0 < 60, "chunk never arrived"
+                time.sleep(0.0002)
+        for c in children[rank]:
+            a = offs[rng_i] + off
+            arenas[c][a: a + nbytes] = arenas[rank][a: a + nbytes]
+        # all of a chunk's pieces stored before its counter moves: here one piece at a time
+        for c in children[rank]:
+            ctrs[c][chunk] += 1
+    dist.barrier()
+    if rank != 0:
+        for o, s in zip(offs, sizes):
+            assert np.array_equal(arenas[rank][o: o + s], arenas[0][o: o + s])
+        assert [int(x) for x in ctrs[rank]] == chunk_pieces
+    dist.barrier()
+    dist.destroy_process_group()
+    print("rank", rank, "ok")
+''')
+
+
+def test_fanout_host_logic_two_ranks_gloo(tmp_path):
+    """Topology, manifest exchange and matching, the piece / chunk plan of the library
+    and the arrival-counter bookkeeping of one chain broadcast, two processes over gloo
+    with /dev/shm-style shared files standing in for peer-mapped GPU memory."""
+    script = tmp_path / "fanout_worker.py"
+    script.write_text(f"ROOT = {ROOT!r}\n" + FANOUT_WORKER)
+    env = dict(os.environ, MXB_TEST_DIR=str(tmp_path), MASTER_ADDR="127.0.0.1")
+    port = 29300 + (os.getpid() % 300)
+    proc = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+         "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
+        env=env, capture_output=True, text=True, timeout=240)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert proc.stdout.count("ok") == 2
