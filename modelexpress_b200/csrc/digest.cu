@@ -9,8 +9,9 @@
 //   ROWS    - signed int32 row sums widened to 64 bit, folded into
 //             sum(row) and sum(row * (k+1)) mod 2^64, plus the word tail and
 //             ragged-byte terms;
-//   BLOCK64 - a 64-bit hash per 4 KiB block: per-lane xxHash64 rounds over its
-//             16 words, avalanched with the block index, lanes summed.
+//   BLOCK64 - a 64-bit hash per 4 KiB block: per lane two 32-bit accumulators take
+//             xxHash32 rounds over its 32 words, the pair is avalanched (64 bit) with
+//             the block index, lanes summed.
 // All three are sums in a wrap-around ring, so partial results are merged with
 // atomics in any order and the answer is exact.
 #include <cstdlib>
@@ -37,8 +38,10 @@ constexpr uint64_t kP3 = 0x165667B19E3779F9ull;
 constexpr uint64_t kP4 = 0x85EBCA77C2B2AE63ull;
 constexpr uint64_t kP5 = 0x27D4EB2F165667C5ull;
 constexpr uint32_t kKnuth = 2654435761u;
+constexpr uint32_t kQ1 = 0x9E3779B1u, kQ2 = 0x85EBCA77u, kQ3 = 0xC2B2AE3Du, kQ4 = 0x27D4EB2Fu,
+                   kQ5 = 0x165667B1u;
 
-__device__ __forceinline__ uint64_t rotl64(uint64_t x, int r) { return (x << r) | (x >> (64 - r)); }
+__device__ __forceinline__ uint32_t rotl32(uint32_t x, int r) { return __funnelshift_l(x, x, r); }
 __device__ __forceinline__ uint64_t avalanche(uint64_t h) {
     h ^= h >> 33;
     h *= kP2;
@@ -252,14 +255,18 @@ __device__ __forceinline__ void digest_row(const RowMeta &m, const uint4 (&v)[8]
         }
     }
     if (MODES & MXB_DIGEST_BLOCK64) {
-        uint64_t h = kP5 + (uint64_t)lane * kP4;
+        // two 32-bit accumulators per lane (xxHash32 rounds: one multiply-add, one funnel
+        // shift, one multiply per word), even words into the first, odd words into the
+        // second; together they are the lane's 64-bit state
+        uint32_t a0 = kQ5 + lane * kQ4, a1 = kQ3 ^ (lane * kQ1);
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
-            const uint64_t x0 = (uint64_t)v[s].x | ((uint64_t)v[s].y << 32);
-            const uint64_t x1 = (uint64_t)v[s].z | ((uint64_t)v[s].w << 32);
-            h = rotl64(h + x0 * kP2, 31) * kP1;
-            h = rotl64(h + x1 * kP2, 31) * kP1;
+            a0 = rotl32(a0 + v[s].x * kQ2, 13) * kQ1;
+            a1 = rotl32(a1 + v[s].y * kQ2, 13) * kQ1;
+            a0 = rotl32(a0 + v[s].z * kQ2, 13) * kQ1;
+            a1 = rotl32(a1 + v[s].w * kQ2, 13) * kQ1;
         }
+        const uint64_t h = ((uint64_t)a0 << 32) | (uint64_t)a1;
         // the lane's share of block `row`; the block hash is the sum of its 32 lane shares
         const uint64_t share = avalanche(h + (m.row + 1) * kP1);
         if (block_out) {

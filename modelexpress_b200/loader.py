@@ -181,6 +181,7 @@ class HostImages:
     def __init__(self):
         self._images: dict = {}
         self._plans: dict = {}
+        self._captured: dict = {}     # (checkpoint path, device) -> _KeptCapture
         self._lock = threading.Lock()
 
     def prepared(self, model_path: str, tp_rank: int, tp_size: int, family: str) -> "Prepared":
@@ -214,7 +215,8 @@ class HostImages:
 
     @property
     def packed_bytes(self) -> int:
-        return sum(img.nbytes for prep in self._plans.values() for img in prep.packed.values())
+        return (sum(img.nbytes for prep in self._plans.values() for img in prep.packed.values())
+                + sum(img.nbytes for kept in self._captured.values() for img, _r, _w in kept.batches))
 
     def close(self) -> None:
         with self._lock:
@@ -222,10 +224,31 @@ class HostImages:
                 for img in prep.packed.values():
                     img.close()
                 prep.packed = {}
+            for kept in self._captured.values():
+                kept.close()
+            self._captured = {}
             for im in self._images.values():
                 im.close()
             self._images = {}
             self._plans = {}
+
+
+@dataclass
+class _KeptCapture:
+    """What a captured load leaves behind for the next load of the same checkpoint into a
+    model of the same shapes: the packed images of its batches, where every record lands
+    (destination tensor name + byte offset), the staged casts and the engine-loaded rest."""
+
+    stamps: tuple
+    batches: list                # [(PackedImage, records (n, 6), [(dest name, byte offset)])]
+    stagings: list               # [(converts, staging tensor)]
+    leftover: list               # source names the engine's loader handles
+    summary: dict                # copies, records, reasons, written_params
+
+    def close(self) -> None:
+        for img, _r, _w in self.batches:
+            img.close()
+        self.batches = []
 
 
 @dataclass
@@ -626,8 +649,10 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
     real host tensors afterwards (so where two sources write the same bytes,
     the engine-loaded one wins), with ``"raise"`` the call fails before any
     byte is written.  ``stats.seconds_total`` spans the dry run and the
-    placement, which overlap (``pipeline``).  ``pin``: ``"off"``, ``"pages"`` or
-    ``"pages_after"`` as in ``place_checkpoint``.
+    placement, which overlap (``pipeline``).  ``pin`` as in ``place_checkpoint``; with
+    ``"keep"`` a later load of the same files into a model of the same shapes skips the
+    dry run and the gather and replays the kept images (engines that reload weights
+    into a live model, e.g. after a sleep, take this path).
     An exception of the engine's loader that arrives after the first batch has been
     handed to the ring is re-raised as ``StrategyFailed(mutated=True)``: parameter
     bytes have been overwritten by then."""
@@ -644,14 +669,25 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
     dests = model_destinations(model)
     if ctx is None:
         ctx = ring.ctx if ring is not None else default_context(dev_index)
-    if pin not in ("off", "pages", "pages_after"):
-        raise ValueError(f"pin must be 'off', 'pages' or 'pages_after' here, not {pin!r}")
+    if pin not in PIN_MODES:
+        raise ValueError(f"pin must be one of {PIN_MODES}, not {pin!r}")
     cache = (images if images is not None else host_images) if pin != "off" else None
+    files = sorted({i["file"] for i in index.values()})
+    stamps = Prepared._stamps(model_path, files)
+    kept_key = (os.path.realpath(model_path), dev_index)
+    if pin == "keep":
+        kept = cache._captured.get(kept_key)
+        if kept is not None and kept.stamps == stamps:
+            replay = _replay_captured(kept, model, dests, loader, index, cache, dev)
+            if replay is not None:
+                return replay
+        if kept is not None:
+            cache._captured.pop(kept_key).close()
     images = {}
     pool = ThreadPoolExecutor(1)          # the ring is one pipeline: its calls run in order
     made: list = []
     try:
-        for path in sorted({i["file"] for i in index.values()}):
+        for path in files:
             images[path] = cache.open(path) if cache is not None else FileImage(path)
         check_index(index, {p: im.size for p, im in images.items()})
         addresses = {p: im.address for p, im in images.items()}
@@ -679,8 +715,15 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
             made.append(ctx.cached_ring(ring_bytes, ring_slots, dev_index))
             timings["ring_create"] = time.perf_counter() - tc
 
+        kept_batches: list = []
+
         def place_batch(records):
-            return (ring if ring is not None else made[0]).place(records, threads, mode)
+            r = ring if ring is not None else made[0]
+            if pin != "keep":
+                return r.place(records, threads, mode)
+            img, stats = r.keep(records, threads)
+            kept_batches.append((img, records, _record_homes(records, dests, stagings)))
+            return stats
 
         ring_job = pool.submit(make_ring) if ring is None else None
         for lo, hi in zip(cuts[:-1], cuts[1:]):
@@ -736,6 +779,14 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
             loader((n, _engine_tensor(images[index[n]["file"]], index[n])) for n in leftover)
             timings["engine"] = time.perf_counter() - tc
         torch.cuda.current_stream(dev).synchronize()
+        if pin == "keep":
+            written_now = set()
+            for cap in parts:
+                written_now |= cap.written_params
+            cache._captured[kept_key] = _KeptCapture(
+                stamps, kept_batches, list(stagings), list(leftover),
+                {"copies": sum(c.copies for c in parts), "records": sum(len(c.records) for c in parts),
+                 "reasons": dict(reasons), "written_params": written_now})
         if pin == "pages_after":
             spans_all: dict = {}
             for part in parts:
@@ -759,6 +810,70 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
                              written, {k: round(v, 4) for k, v in timings.items()})
 
 
+def _record_homes(records: np.ndarray, dests: dict, stagings: list) -> list:
+    """(destination name, byte offset) of every record: which parameter, buffer or cast
+    staging buffer its destination address lies in."""
+    spans = []
+    for name, t in dests.items():
+        n = t.numel() * t.element_size()
+        if n:
+            spans.append((t.data_ptr(), t.data_ptr() + n, name))
+    for k, (_conv, buf) in enumerate(stagings):
+        spans.append((buf.data_ptr(), buf.data_ptr() + buf.numel(), f"\0staging{k}"))
+    spans.sort()
+    starts = np.array([s[0] for s in spans], dtype=np.uint64)
+    homes = []
+    for dst in records[:, 1].tolist():
+        k = int(np.searchsorted(starts, np.uint64(dst), side="right")) - 1
+        if k < 0 or dst >= spans[k][1]:
+            raise RuntimeError("a record's destination lies in no known tensor")
+        homes.append((spans[k][2], int(dst - spans[k][0])))
+    return homes
+
+
+def _replay_captured(kept: _KeptCapture, model, dests: dict, loader, index: dict, cache, dev):
+    """A load from kept images: no dry run, no gather.  Returns ``None`` when the model no
+    longer fits what was kept (another shape, or a destination at another 16-byte phase)."""
+    import torch
+
+    from .planner import apply_converts
+
+    t0 = time.perf_counter()
+    bases = {name: t.data_ptr() for name, t in dests.items()}
+    for k, (_conv, buf) in enumerate(kept.stagings):
+        bases[f"\0staging{k}"] = buf.data_ptr()
+    torch.cuda.current_stream(dev).synchronize()
+    results = []
+    try:
+        for img, records, homes in kept.batches:
+            items = records.copy()
+            items[:, 1] = np.array([bases[name] + off for name, off in homes], dtype=np.uint64)
+            results.append(img.place(items))
+    except (KeyError, MxbError) as e:
+        if isinstance(e, MxbError) and e.code != -8:
+            raise
+        if results:      # some batches were written before the mismatch showed
+            raise StrategyFailed(f"kept image no longer fits the model: {e}", mutated=True) from e
+        return None
+    for converts, buf in kept.stagings:
+        apply_converts(converts, buf, dests)
+    timings = {"capture": 0.0, "ring_create": 0.0, "place_wait": round(time.perf_counter() - t0, 4),
+               "engine": 0.0}
+    if kept.leftover:
+        tc = time.perf_counter()
+        opened = {p: cache.open(p) for p in sorted({index[n]["file"] for n in kept.leftover})}
+        loader((n, _engine_tensor(opened[index[n]["file"]], index[n])) for n in kept.leftover)
+        timings["engine"] = round(time.perf_counter() - tc, 4)
+    torch.cuda.current_stream(dev).synchronize()
+    seconds = time.perf_counter() - t0
+    stats = PlaceResult(sum(r.bytes_placed for r in results), sum(r.chunks for r in results),
+                        sum(r.launches for r in results), seconds, 0.0,
+                        sum(r.seconds_device for r in results), sum(r.bytes_direct for r in results), 0.0)
+    return CapturedPlacement(stats, kept.summary["copies"], kept.summary["records"],
+                             [c.param_name for cv, _b in kept.stagings for c in cv], list(kept.leftover),
+                             dict(kept.summary["reasons"]), set(kept.summary["written_params"]), timings)
+
+
 class B200ScatterStrategy:
     """Load strategy placing weights with the scatter kernel.
 
@@ -773,8 +888,12 @@ class B200ScatterStrategy:
     name = "b200_scatter"
     requires: tuple = ()
 
-    def __init__(self, ring_bytes: int = RING_BYTES, ring_slots: int = RING_SLOTS, host_threads: int | None = None):
+    def __init__(self, ring_bytes: int = RING_BYTES, ring_slots: int = RING_SLOTS, host_threads: int | None = None,
+                 pin: str | None = None):
         self.ring_bytes, self.ring_slots, self.host_threads = ring_bytes, ring_slots, host_threads
+        # what to keep in host memory for later loads (place_checkpoint's ``pin``); MXB_PIN=keep
+        # suits engines that reload weights into a live model
+        self.pin = pin if pin is not None else os.environ.get("MXB_PIN", "off")
         self._touched = False
 
     def is_available(self, ctx) -> bool:
@@ -802,7 +921,8 @@ class B200ScatterStrategy:
             self._touched = True
             placed = place_checkpoint(model_dir, tp_rank, tp_size, f"cuda:{ctx.device_id}",
                                       params=params, ring_bytes=self.ring_bytes,
-                                      ring_slots=self.ring_slots, host_threads=self.host_threads)
+                                      ring_slots=self.ring_slots, host_threads=self.host_threads,
+                                      pin=self.pin)
         except (KeyError, ValueError) as e:
             # layout could not be expressed: nothing was written yet
             raise StrategyFailed(str(e), mutated=False) from e
@@ -838,7 +958,7 @@ class B200CapturedStrategy(B200ScatterStrategy):
         try:
             placed = place_captured(model, model_dir, f"cuda:{ctx.device_id}",
                                     ring_bytes=self.ring_bytes, ring_slots=self.ring_slots,
-                                    host_threads=self.host_threads)
+                                    host_threads=self.host_threads, pin=self.pin)
         except StrategyFailed:
             raise
         except (KeyError, ValueError, FileNotFoundError) as e:

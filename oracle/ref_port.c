@@ -143,7 +143,12 @@ uint32_t orc_digest_scalars_mt(const uint8_t *p, uint64_t n, uint64_t out[7]) {
 #define P4 0x85EBCA77C2B2AE63ull
 #define P5 0x27D4EB2F165667C5ull
 
-static inline uint64_t rotl64(uint64_t x, int r) { return (x << r) | (x >> (64 - r)); }
+#define Q1 0x9E3779B1u
+#define Q2 0x85EBCA77u
+#define Q3 0xC2B2AE3Du
+#define Q4 0x27D4EB2Fu
+#define Q5 0x165667B1u
+static inline uint32_t rotl32(uint32_t x, int r) { return (x << r) | (x >> (32 - r)); }
 static inline uint64_t avalanche(uint64_t h) {
     h ^= h >> 33; h *= P2; h ^= h >> 29; h *= P3; h ^= h >> 32;
     return h;
@@ -157,14 +162,15 @@ static uint64_t one_block(const uint8_t *p, uint64_t avail, uint64_t b) {
         p = buf;
     }
     uint64_t h = 0;
-    for (int lane = 0; lane < 32; ++lane) {
-        uint64_t acc = P5 + (uint64_t)lane * P4;
+    for (uint32_t lane = 0; lane < 32; ++lane) {
+        uint32_t a[2] = {Q5 + lane * Q4, Q3 ^ (lane * Q1)};
         for (int step = 0; step < 8; ++step)
-            for (int k = 0; k < 2; ++k) {
-                uint64_t x;
-                memcpy(&x, p + step * 512 + lane * 16 + k * 8, 8);
-                acc = rotl64(acc + x * P2, 31) * P1;
+            for (int k = 0; k < 4; ++k) {
+                uint32_t x;
+                memcpy(&x, p + step * 512 + lane * 16 + k * 4, 4);
+                a[k & 1] = rotl32(a[k & 1] + x * Q2, 13) * Q1;
             }
+        uint64_t acc = ((uint64_t)a[0] << 32) | a[1];
         h += avalanche(acc + (b + 1) * P1); /* the lane's share of block b */
     }
     return h;

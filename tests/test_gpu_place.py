@@ -552,3 +552,44 @@ def test_place_captured_converts_batches_and_engine_leftovers(tmp_path):
     with pytest.raises(StrategyFailed) as e:
         place_captured(model, d, "cuda:0", on_unsupported="raise", ring_bytes=8 << 20, ring_slots=4)
     assert not e.value.mutated and float(model.qkv.detach().abs().sum()) == 0.0
+
+
+def test_captured_load_keeps_images_and_replays_into_a_new_model(tmp_path):
+    """place_captured(pin="keep"): the first load dry-runs the engine's loader and gathers
+    into kept images; the next load of the same files, even into another model object
+    of the same shapes, skips both and replays; parameters are what the loader itself
+    makes of the real tensors."""
+    import torch
+    from safetensors.torch import save_file
+
+    import hooked_model as H
+    from modelexpress_b200.loader import HostImages, place_captured
+    from modelexpress_b200.runtime import Context
+
+    g = torch.Generator().manual_seed(13)
+    tensors = {n: torch.randn(shape, generator=g, dtype=dt) for n, dt, shape in H.manifest()}
+    d = str(tmp_path)
+    save_file(tensors, f"{d}/model.safetensors")
+    truth = H.HookedModel()
+    truth.load_weights(tensors.items())
+    want = {n: t.clone() for n, t in truth.state_dict().items()}
+    ctx = Context([0])
+    ring = ctx.ring(8 << 20, 4, 0)
+    images = HostImages()
+    try:
+        for attempt in range(3):
+            model = H.HookedModel().cuda()       # a new object (new addresses) every time
+            got = place_captured(model, d, "cuda:0", ring=ring, host_threads=2, pin="keep", images=images)
+            for n, t in model.state_dict().items():
+                assert torch.equal(t.cpu(), want[n]), (attempt, n)
+            assert got.engine_loaded == []
+            if attempt == 0:
+                assert got.stats.seconds_gather > 0 and got.timings["capture"] > 0
+            else:
+                assert got.stats.seconds_gather == 0 and got.timings["capture"] == 0.0
+                assert got.stats.bytes_direct == got.stats.bytes_placed
+        assert images.packed_bytes > 0
+    finally:
+        images.close()
+        ring.close()
+        ctx.close()
