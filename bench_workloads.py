@@ -117,6 +117,15 @@ def nvlink_peaks(ctx, rank, world, local, nbytes=1 << 30, reps=3) -> dict:
     ms = ctx.copy_probe(base, peers[nxt] + nbytes, nbytes, reps, local)
     _barrier(world)
     out["store_kernel_all_pairs_gbs"] = round(nbytes / (_max(ms, world) * 1e-3) / 1e9, 1)
+    # the same with 32-byte stores
+    os.environ["MXB_PROBE_WIDTH"] = "32"
+    try:
+        _barrier(world)
+        ms = ctx.copy_probe(base, peers[nxt] + nbytes, nbytes, reps, local)
+        _barrier(world)
+    finally:
+        os.environ.pop("MXB_PROBE_WIDTH", None)
+    out["store_kernel_32B_all_pairs_gbs"] = round(nbytes / (_max(ms, world) * 1e-3) / 1e9, 1)
     # the copy engine over the same mapping
     dst = as_tensor(peers[nxt] + nbytes, nbytes, local)
     src = mine[:nbytes]
@@ -139,7 +148,7 @@ def nvlink_peaks(ctx, rank, world, local, nbytes=1 << 30, reps=3) -> dict:
                   "library's plain 16-byte copy kernel writing into the peer's memory; copy engine = "
                   "cudaMemcpyAsync to the peer mapping")
     out["peak_gbs"] = max(out["store_kernel_one_pair_gbs"], out["store_kernel_all_pairs_gbs"],
-                          out["copy_engine_all_pairs_gbs"])
+                          out["store_kernel_32B_all_pairs_gbs"], out["copy_engine_all_pairs_gbs"])
     del dst, src, mine
     _barrier(world)
     ctx.free(base, local)
@@ -283,13 +292,14 @@ def fanout_measure(args, ctx, rank, world, local, nv=None) -> dict:
     spans = [(base + o, n) for o, n in zip(offs, sizes)]
     topologies = {}
     kinds = os.environ.get("MXB_FANOUT_TOPOLOGY", "chain").split(",")
-    chunks_mib = [int(x) for x in os.environ.get("MXB_FANOUT_CHUNKS", "1,4,16,64").split(",")]
+    # the sweep the benchmark configuration names (1, 4, 16, 64 MiB) plus one finer point
+    chunks_mib = [float(x) for x in os.environ.get("MXB_FANOUT_CHUNKS", "0.25,1,4,16,64").split(",")]
     launches = 0
     for kind in kinds:
         children = topology(kind, world, 0)
         sweep = {}
         for mib in chunks_mib:
-            node = ctx.fanout(spans, mib << 20, local)
+            node = ctx.fanout(spans, int(mib * (1 << 20)) // 65536 * 65536, local)
             ctrs = _open_peers(ctx, node.counters, world)
             for c in children[rank]:
                 node.add_child([(peers[c] + o, n) for o, n in zip(offs, sizes)], ctrs[c])
@@ -311,7 +321,7 @@ def fanout_measure(args, ctx, rank, world, local, nv=None) -> dict:
                     times.append((ms, wall))
             dev_ms = sum(t[0] for t in times) / len(times)
             wall_ms = sum(t[1] for t in times) / len(times)
-            sweep[str(mib)] = {"device_ms": round(dev_ms, 3), "wall_ms": round(wall_ms, 3),
+            sweep[f"{mib:g}"] = {"device_ms": round(dev_ms, 3), "wall_ms": round(wall_ms, 3),
                                "gbs_per_target": round(payload / (dev_ms * 1e-3) / 1e9, 1),
                                "gbs_aggregate": round(payload * (world - 1) / (dev_ms * 1e-3) / 1e9, 1)}
             # every destination range must digest like the source's
@@ -320,11 +330,11 @@ def fanout_measure(args, ctx, rank, world, local, nv=None) -> dict:
             alld = _gather_objects(mine, world)
             for r in range(1, world):
                 if alld[r] != alld[0]:
-                    raise SystemExit(f"fan-out ({kind}): rank {r} digests differ from the source (chunk {mib} MiB)")
+                    raise SystemExit(f"fan-out ({kind}): rank {r} digests differ from the source (chunk {mib:g} MiB)")
             _barrier(world)
             node.close()
         best = max(sweep, key=lambda k: sweep[k]["gbs_per_target"])
-        topologies[kind] = {"chunk_sweep_mib": sweep, "best_chunk_mib": int(best),
+        topologies[kind] = {"chunk_sweep_mib": sweep, "best_chunk_mib": float(best),
                             "gbs_per_target": sweep[best]["gbs_per_target"],
                             "device_ms": sweep[best]["device_ms"]}
     # comparison line: ncclBroadcast of the same arena

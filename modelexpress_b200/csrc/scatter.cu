@@ -340,6 +340,33 @@ __global__ void __launch_bounds__(512) copy_probe_kernel(const uint4 *__restrict
     for (; i < n16; i += stride) dst[i] = src[i];
 }
 
+// The same with 32-byte (256-bit) loads and stores, which sm_100 has for global memory.
+__global__ void __launch_bounds__(512) copy_probe_kernel_32(const uint4 *__restrict__ src,
+                                                            uint4 *__restrict__ dst, uint64_t n32) {
+    const uint64_t stride = (uint64_t)gridDim.x * 512;
+    for (uint64_t i = (uint64_t)blockIdx.x * 512 + threadIdx.x; i < n32; i += 2 * stride) {
+        uint32_t a[8], b[8];
+        const bool two = i + stride < n32;
+        asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                     : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]),
+                       "=r"(a[7])
+                     : "l"(src + 2 * i));
+        if (two)
+            asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                         : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]), "=r"(b[4]), "=r"(b[5]),
+                           "=r"(b[6]), "=r"(b[7])
+                         : "l"(src + 2 * (i + stride)));
+        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst + 2 * i), "r"(a[0]),
+                     "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7])
+                     : "memory");
+        if (two)
+            asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst + 2 * (i + stride)),
+                         "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(b[4]), "r"(b[5]), "r"(b[6]),
+                         "r"(b[7])
+                         : "memory");
+    }
+}
+
 // ---------------------------------------------------------------------------
 // launcher
 // ---------------------------------------------------------------------------
@@ -660,12 +687,20 @@ int32_t mxb_copy_probe(mxb_ctx *ctx, int32_t dev, uint64_t src, uint64_t dst, ui
     MXB_CUDA(cudaEventCreate(&e1));
     const uint64_t n16 = nbytes / 16;
     const unsigned grid = (unsigned)d->sm_count * 4;
-    copy_probe_kernel<<<grid, 512, 0, d->stream>>>(reinterpret_cast<const uint4 *>(src),
-                                                   reinterpret_cast<uint4 *>(dst), n16);  // warm
+    // MXB_PROBE_WIDTH=32: 256-bit loads and stores (addresses and size multiples of 32 bytes)
+    const char *width = getenv("MXB_PROBE_WIDTH");
+    const bool wide = width && !strcmp(width, "32") && !((src | dst | nbytes) & 31u);
+    auto launch = [&]() {
+        if (wide)
+            copy_probe_kernel_32<<<grid, 512, 0, d->stream>>>(reinterpret_cast<const uint4 *>(src),
+                                                              reinterpret_cast<uint4 *>(dst), n16 / 2);
+        else
+            copy_probe_kernel<<<grid, 512, 0, d->stream>>>(reinterpret_cast<const uint4 *>(src),
+                                                           reinterpret_cast<uint4 *>(dst), n16);
+    };
+    launch();  // warm
     cudaEventRecord(e0, d->stream);
-    for (int32_t r = 0; r < reps; ++r)
-        copy_probe_kernel<<<grid, 512, 0, d->stream>>>(reinterpret_cast<const uint4 *>(src),
-                                                       reinterpret_cast<uint4 *>(dst), n16);
+    for (int32_t r = 0; r < reps; ++r) launch();
     cudaEventRecord(e1, d->stream);
     cudaError_t e = cudaEventSynchronize(e1);
     float ms = 0.f;
