@@ -124,7 +124,8 @@ class _View:
             raise UnsupportedReshard(f"op {op!r} is not a pure view")
 
 
-def window_box(offset, shape, stride, global_shape, dest_stride, keep_rank: bool = True):
+def window_box(offset, shape, stride, global_shape, dest_stride, keep_rank: bool = True,
+               with_perm: bool = False):
     """A strided window of a row-major tensor -> (box in source coordinates,
     destination strides in source-dim order); slice_plan.py:170-225.
 
@@ -166,6 +167,8 @@ def window_box(offset, shape, stride, global_shape, dest_stride, keep_rank: bool
     for d, s in enumerate(perm):
         if s is not None:
             dst_stride[s] = int(dest_stride[d])
+    if with_perm:
+        return [(lo[s], hi[s]) for s in range(nd)], dst_stride, perm
     return [(lo[s], hi[s]) for s in range(nd)], dst_stride
 
 
@@ -335,6 +338,49 @@ class ConvertSpec:
     src_dtype: Any
     staging_offset: int  # byte offset in the convert staging buffer
     nbytes: int
+    # a transposing copy is staged as the box it reads, in the source's own dim order:
+    box_shape: tuple | None = None   # shape of that box in staging (None: staged in dest_shape)
+    box_perm: tuple | None = None    # per destination dim, the staging dim it walks (None: extent 1)
+
+
+TRANSPOSE_MIN_ELEMENTS = 4096   # below this a transposing copy stays a list of narrow records
+
+
+def transposed_box(copy, global_shape):
+    """``(box_shape, box_perm, corner_offset)`` when ``copy`` walks its source against the
+    grain: the source's innermost walked dim does not land with stride 1, so its records
+    would be one element wide.  ``None`` for every other copy (and for small ones)."""
+    try:
+        offset, shape, stride, keep_rank = copy_window(copy, global_shape)
+        box, dst_strides, perm = window_box(offset, shape, stride, global_shape, copy.dest_stride,
+                                            keep_rank, with_perm=True)
+    except UnsupportedReshard:
+        return None
+    sizes = [hi - lo for lo, hi in box]
+    walked = [s for s in range(len(sizes)) if sizes[s] > 1]
+    if not walked or dst_strides[walked[-1]] == 1:
+        return None
+    n = 1
+    for extent in sizes:
+        n *= extent
+    if n < TRANSPOSE_MIN_ELEMENTS:
+        return None
+    return tuple(sizes), tuple(perm), int(offset)
+
+
+def _box_copy(copy, src, box_shape, corner: int):
+    """The same source box landing contiguously, in source dim order, at offset 0."""
+    staged = _copy.copy(copy)
+    staged.src_offset = corner
+    staged.src_shape = tuple(box_shape)
+    staged.src_stride = tuple(_strides_of(src.global_shape))
+    staged.dest_offset = 0
+    staged.dest_shape = tuple(box_shape)
+    staged.dest_stride = tuple(_strides_of(box_shape))
+    staged.dest_dtype = src.dtype
+    if hasattr(staged, "op_chain"):
+        staged.op_chain = ()
+    return staged
 
 
 def plan_transfer_2d(copies, sources: dict, resolve_param_ptr, convert_base: int | None = None) -> tuple:
@@ -357,7 +403,19 @@ def plan_transfer_2d(copies, sources: dict, resolve_param_ptr, convert_base: int
             unsupported.append(copy.src_name)
             continue
         try:
-            if src.dtype != copy.dest_dtype:
+            tbox = transposed_box(copy, src.global_shape) if convert_base is not None else None
+            if tbox is not None:
+                # staged as the box it reads (wide rows), transposed (and cast) on the device
+                box_shape, box_perm, corner = tbox
+                n = int(np.prod(box_shape))
+                off = (staged + 255) // 256 * 256
+                parts = plan_pull_2d(_box_copy(copy, src, box_shape, corner), src.global_shape, src.dtype,
+                                     src.elsize, src.shards, int(convert_base) + off)
+                converts.append(ConvertSpec(copy.param_name, tuple(copy.dest_shape),
+                                            tuple(copy.dest_stride), int(copy.dest_offset), src.dtype,
+                                            off, n * int(src.elsize), box_shape, box_perm))
+                staged = off + n * int(src.elsize)
+            elif src.dtype != copy.dest_dtype:
                 if convert_base is None:
                     raise UnsupportedReshard("dtype conversion required and no staging given")
                 n = int(np.prod(copy.dest_shape)) if len(copy.dest_shape) else 1
@@ -389,20 +447,33 @@ def convert_staging_bytes(copies, sources: dict) -> int:
     total = 0
     for copy in copies:
         src = sources.get(copy.src_name)
-        if src is not None and src.dtype != copy.dest_dtype:
+        if src is None:
+            continue
+        tbox = transposed_box(copy, src.global_shape)
+        if tbox is not None:
+            total = (total + 255) // 256 * 256 + int(np.prod(tbox[0])) * int(src.elsize)
+        elif src.dtype != copy.dest_dtype:
             n = int(np.prod(copy.dest_shape)) if len(copy.dest_shape) else 1
             total = (total + 255) // 256 * 256 + n * int(src.elsize)
     return total
 
 
 def apply_converts(converts, staging, params: dict) -> None:
-    """Cast the staged sources into their parameters (receiver.py:964-971): the
-    one step left to torch, for the few tensors (a bf16-served router feeding an
-    fp32 parameter) that need it."""
+    """Cast (and, for staged boxes, transpose) the staged sources into their parameters
+    (receiver.py:964-971): the one step left to torch, for the few tensors that need it
+    (a bf16-served router feeding an fp32 parameter; weights stored transposed)."""
     import torch
 
     for c in converts:
-        src = staging[c.staging_offset: c.staging_offset + c.nbytes].view(c.src_dtype).reshape(c.dest_shape)
+        src = staging[c.staging_offset: c.staging_offset + c.nbytes].view(c.src_dtype)
+        if c.box_shape is None:
+            src = src.reshape(c.dest_shape)
+        else:
+            # the staged box in the source's dim order -> the destination's: walked dims in
+            # destination order first, the box's extent-1 dims last, then only size-1 dims differ
+            walked = [s for s in c.box_perm if s is not None]
+            rest = [d for d in range(len(c.box_shape)) if d not in walked]
+            src = src.reshape(c.box_shape).permute(walked + rest).reshape(c.dest_shape)
         p = params[c.param_name]
         dst = torch.as_strided(p, c.dest_shape, c.dest_stride, p.storage_offset() + c.dest_offset)
         dst.copy_(src)

@@ -475,6 +475,16 @@ def test_whole_vllm_models_on_cpu_every_tp_rank():
         assert len(g["left_to_engine_by_default"]) == 8
         assert all(n.endswith(("c_attn.weight", "c_proj.weight", "c_fc.weight"))
                    for n in g["left_to_engine_by_default"])
+        # with a staging buffer the same eight tensors are staged as wide boxes and transposed on
+        # the device: nothing is left to the engine and no narrow record remains
+        for r in range(4):
+            gs = res[f"gpt2/rank{r}"]
+            # 12 copies: c_attn lands as q, k and v, the other three Conv1D weights as one each
+            assert gs["staged_mismatch"] == [] and gs["staged_engine"] == [] and gs["staged_transposes"] == 12
+            assert gs["staged_smallest_row"] >= 64
+    for a in built:
+        for r in range(4):
+            assert res[f"{a}/rank{r}"]["staged_mismatch"] == [], (a, r)
     # vocabulary 1000 pads to 1024: the last rank's embed and lm_head shards hold 24 real rows
     # fewer (x 256 columns x 2 bytes x 2 tensors) than the other ranks'
     for arch in ("llama", "qwen2"):
@@ -711,3 +721,44 @@ def test_scalars_empty_tensors_and_integer_indices():
     assert not unsupported and not converts and len(table) == 3     # nothing to move for "e"
     c_port.scatter2d(table)
     assert float(model.s0.detach()) == 3.5 and model.s1.tolist() == [7.25] and model.v.tolist() == [6.0, 7.0, 8.0]
+
+
+def test_transposing_copies_are_staged_as_wide_boxes_and_transposed_on_the_device():
+    """A loader that transposes its source (GPT-2's Conv1D weights are stored (in, out)):
+    as plain records the copy is one element per row; with a staging buffer it is planned
+    as the box it reads, in the source's own row order (wide rows), and transposed by the
+    one torch copy that also does the casts.  Same bytes as the loader itself produces,
+    also through a 3-D source, a column split and a dtype change."""
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.conv = torch.nn.Parameter(torch.zeros(128, 96, dtype=torch.bfloat16))      # (out/2, in)
+            self.stack = torch.nn.Parameter(torch.zeros(3, 64, 80, dtype=torch.bfloat16))   # (E, out, in)
+            self.wide = torch.nn.Parameter(torch.zeros(64, 96, dtype=torch.float32))        # cast as well
+            self.plain = torch.nn.Parameter(torch.zeros(96, 256, dtype=torch.bfloat16))
+
+        def load_weights(self, weights):
+            for name, w in weights:
+                if name == "conv":          # stored (in=96, out=256): this rank's half of the outputs
+                    self.conv.data.copy_(w.t().narrow(0, 128, 128))
+                elif name == "stack":       # stored (E, in=80, out=64)
+                    self.stack.data.copy_(w.transpose(1, 2))
+                elif name == "wide":        # stored (in=96, out=64) in bf16, parameter fp32
+                    self.wide.data.copy_(w.t())
+                elif name == "plain":
+                    self.plain.data.copy_(w)
+
+    manifest = [("conv", torch.bfloat16, (96, 256)), ("stack", torch.bfloat16, (3, 80, 64)),
+                ("wide", torch.bfloat16, (96, 64)), ("plain", torch.bfloat16, (96, 256))]
+    image, index = _image(manifest, seed=5)
+    truth = M()
+    truth.load_weights((n, _real_tensor(image, index[n], dt)) for n, dt, _s in manifest)
+    # without staging: exact, but one element per row
+    bare = captured_table(M(), index, {"mem": image.ctypes.data}, device=torch.device("cpu"), min_row_bytes=0)
+    assert int(bare.records[:, 3].min()) == 2 and len(bare.records) > 1000
+    model = M()
+    cap = _run_records(model, image, index, manifest)
+    assert not cap.reasons and sorted(c.param_name for c in cap.converts) == ["conv", "stack", "wide"]
+    assert len(cap.records) <= 8 and int(cap.records[:, 3].min()) >= 128      # a handful of wide rows
+    for (n, a), (_n, b) in zip(model.state_dict().items(), truth.state_dict().items()):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), n

@@ -169,6 +169,29 @@ def run_arch(arch, cfg_json, make_tensors, out):
                                  and all(p.device.type == "meta" for p in twin.parameters()))
                 if cap.reasons:  # what the loader computes on goes through the loader itself
                     model.load_weights((n, w) for n, w in weights if n in cap.reasons)
+                # the same load with a staging buffer: transposing copies are staged as wide boxes
+                from modelexpress_b200.planner import apply_converts
+
+                twin_params = {n: p.detach().clone() for n, p in model.named_parameters()}
+                for p in model.parameters():
+                    p.data.zero_()
+                held = []
+
+                def alloc(nbytes):
+                    held.append(torch.zeros(nbytes, dtype=torch.uint8))
+                    return held[0].data_ptr()
+
+                staged = captured_table(model, index, {path: image.address}, device=torch.device("cpu"),
+                                        alloc_staging=alloc)
+                c_port.scatter2d(staged.records)
+                if staged.converts:
+                    apply_converts(staged.converts, held[0], {n: p.data for n, p in model.named_parameters()})
+                if staged.reasons:
+                    model.load_weights((n, w) for n, w in weights if n in staged.reasons)
+                staged_bad = [n for n, p in model.named_parameters()
+                              if not torch.equal(p.data.view(torch.int16), truth[n].view(torch.int16))]
+                for n, p in model.named_parameters():
+                    p.data.copy_(twin_params[n])
             finally:
                 for p in patches:
                     p.stop()
@@ -180,7 +203,10 @@ def run_arch(arch, cfg_json, make_tensors, out):
             "records": int(len(recs)), "engine": sorted(cap.reasons), "mismatch": bad,
             "bytes": int(sum(int(r[2]) * int(r[3]) for r in recs)),
             "smallest_row": int(min((int(r[3]) for r in recs), default=0)),
-            "left_to_engine_by_default": sorted(policy.reasons), "meta_twin_same": twin_same}
+            "left_to_engine_by_default": sorted(policy.reasons), "meta_twin_same": twin_same,
+            "staged_mismatch": staged_bad, "staged_engine": sorted(staged.reasons),
+            "staged_transposes": len([c for c in staged.converts if c.box_shape is not None]),
+            "staged_smallest_row": int(min((int(r[3]) for r in staged.records), default=0))}
     image.close()
 
 
