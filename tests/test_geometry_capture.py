@@ -755,7 +755,8 @@ def test_transposing_copies_are_staged_as_wide_boxes_and_transposed_on_the_devic
     truth.load_weights((n, _real_tensor(image, index[n], dt)) for n, dt, _s in manifest)
     # without staging: exact, but one element per row
     bare = captured_table(M(), index, {"mem": image.ctypes.data}, device=torch.device("cpu"), min_row_bytes=0)
-    assert int(bare.records[:, 3].min()) == 2 and len(bare.records) > 1000
+    narrow = bare.records[bare.records[:, 3] == 2]
+    assert len(narrow) and int(narrow[:, 2].sum()) > 30000       # tens of thousands of two-byte rows
     model = M()
     cap = _run_records(model, image, index, manifest)
     assert not cap.reasons and sorted(c.param_name for c in cap.converts) == ["conv", "stack", "wide"]
