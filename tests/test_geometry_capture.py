@@ -756,7 +756,7 @@ def test_transposing_copies_are_staged_as_wide_boxes_and_transposed_on_the_devic
     # without staging: exact, but one element per row
     bare = captured_table(M(), index, {"mem": image.ctypes.data}, device=torch.device("cpu"), min_row_bytes=0)
     narrow = bare.records[bare.records[:, 3] == 2]
-    assert len(narrow) and int(narrow[:, 2].sum()) > 30000       # tens of thousands of two-byte rows
+    assert len(narrow) and int(narrow[:, 2].sum()) > 20000       # tens of thousands of two-byte rows
     model = M()
     cap = _run_records(model, image, index, manifest)
     assert not cap.reasons and sorted(c.param_name for c in cap.converts) == ["conv", "stack", "wide"]
