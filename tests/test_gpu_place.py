@@ -478,7 +478,8 @@ def test_mdl_loader_warm_install(rank):
 def test_place_captured_converts_batches_and_engine_leftovers(tmp_path):
     """``place_captured`` on a hand-made engine model: a fused, tensor-parallel
     loader, a checkpoint tensor served in bf16 for an fp32 parameter (staged and
-    cast on the device), a transposed expert stack, a scalar the loader reads with
+    cast on the device), a transposed expert stack (staged as the boxes it reads and
+    transposed on the device), a scalar the loader reads with
     ``.item()`` (handed to the loader itself afterwards), one source per dry-run
     batch so that capture and placement interleave.  Every parameter must equal
     what the same ``load_weights`` produces from the real tensors."""
@@ -530,20 +531,19 @@ def test_place_captured_converts_batches_and_engine_leftovers(tmp_path):
         truth.load_weights((n, torch.from_numpy(a.copy()).view(
             torch.bfloat16 if a.dtype == np.uint16 else torch.float32)) for n, a in full.items())
         model = Engine(rank).cuda()
-        # min_row_bytes=0: the transposed expert stack stays in the records (two-byte rows)
         got = place_captured(model, d, "cuda:0", first_batch=1, ring_bytes=8 << 20, ring_slots=4,
                              host_threads=2, min_row_bytes=0)
         assert got.engine_loaded == ["scale"] and "item" in got.reasons["scale"]
-        assert got.converted == ["router"]
+        assert got.converted == ["experts"] * 4 + ["router"]
         assert got.written_params == {"qkv", "down", "experts", "router", "embed"}
         assert got.copies == 3 + 1 + 4 + 1 + 1 and got.stats.chunks >= 4
         torch.cuda.synchronize()
         for (n, a), (_n, b) in zip(model.state_dict().items(), truth.state_dict().items()):
             assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), (rank, n)
-    # by default an element-wise transpose is left to the engine's loader; same result
+    # the default settings: the same, in doubling batches
     model = Engine(1).cuda()
     got = place_captured(model, d, "cuda:0", ring_bytes=8 << 20, ring_slots=4, host_threads=2)
-    assert got.engine_loaded == ["scale", "experts"] and "transposes" in got.reasons["experts"]
+    assert got.engine_loaded == ["scale"] and got.converted == ["experts"] * 4 + ["router"]
     torch.cuda.synchronize()
     for (n, a), (_n, b) in zip(model.state_dict().items(), truth.state_dict().items()):
         assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), n
