@@ -88,3 +88,50 @@ def test_truncated_shard_is_an_expected_miss(tmp_path):
     bad[first]["size"] = bad[first]["size"] + 2
     with pytest.raises(ValueError, match="header gives"):
         check_index(bad, {path: 1 << 40})
+
+
+def test_prepared_plan_is_cached_until_the_files_change(tmp_path):
+    """HostImages.prepared: the parsed headers and the rank's plan are kept while the
+    checkpoint files keep their size and modification time, rebuilt when one changes;
+    its record arrays are what placement_items computes tensor by tensor."""
+    import os
+    import time
+
+    import numpy as np
+
+    from modelexpress_b200 import synth
+    from modelexpress_b200.loader import HostImages, Prepared, placement_items
+
+    cfg = synth.DenseConfig("prep", 2, 64, 128, 4, 4, 16, 256, False, 9, 2)
+    d = str(tmp_path)
+    synth.write_checkpoint(d, synth.dense_tensors(cfg), cfg.seed, cfg.files)
+    images = HostImages()
+    a = images.prepared(d, 1, 2, "auto")
+    assert images.prepared(d, 1, 2, "auto") is a and images.prepared(d, 0, 2, "auto") is not a
+    assert a.fresh() and len(a.files) == 2 and a.geometry.shape == (len(a.plan.placements), 6)
+
+    class FakeTensor:          # only what items() asks of a destination
+        def __init__(self, spec, ptr):
+            self.shape, self._ptr = tuple(spec.shape), ptr
+            self._el = {"BF16": 2, "F32": 4}[spec.dtype]
+
+        def is_contiguous(self):
+            return True
+
+        def element_size(self):
+            return self._el
+
+        def data_ptr(self):
+            return self._ptr
+
+    params = {n: FakeTensor(s, 1 << 40 | (k << 24)) for k, (n, s) in enumerate(a.plan.params.items())}
+    addresses = {p: (7 << 32) + 4096 * k for k, p in enumerate(a.files)}
+    assert np.array_equal(a.items(addresses, params), placement_items(a.plan, a.index, addresses, params))
+    # a rewritten file (same size, later mtime) invalidates the plan
+    path = a.files[0]
+    st = os.stat(path)
+    os.utime(path, ns=(st.st_atime_ns, st.st_mtime_ns + 5_000_000_000))
+    assert not a.fresh()
+    b = images.prepared(d, 1, 2, "auto")
+    assert b is not a and b.fresh()
+    images.close()
