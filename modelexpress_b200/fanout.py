@@ -244,7 +244,7 @@ class FanoutSource:
     replicas that ask (``serve``).  ``tensors`` is ``{name: CUDA tensor}``."""
 
     def __init__(self, tensors: dict, rendezvous_dir: str, source_id: str, ctx: Context | None = None,
-                 device: int | None = None, chunk_bytes: int = 1 << 20, digests: bool = True):
+                 device: int | None = None, chunk_bytes: int = 256 << 10, digests: bool = True):
         import torch
 
         from .runtime import default_context
