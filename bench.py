@@ -2,7 +2,7 @@
 """Benchmark of the weight-placement hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload place|moe|fanout|reshard|digest|vllm]
+                    [--workload place|moe|fanout|reshard|digest|vllm|convert]
 
 Default workload (the headline): a Llama-3-8B-shaped bf16 synthetic checkpoint
 (4 safetensors files, ~16 GB, seed 1) placed into tensor-parallel TP=8 shards.
@@ -709,7 +709,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="place", choices=["place", "moe", "fanout", "reshard", "digest", "vllm"])
+    ap.add_argument("--workload", default="place", choices=["place", "moe", "fanout", "reshard", "digest", "vllm", "convert"])
     args = ap.parse_args()
     if args.impl == "reference":
         return bench_reference(args)

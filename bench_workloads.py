@@ -292,51 +292,60 @@ def fanout_measure(args, ctx, rank, world, local, nv=None) -> dict:
     spans = [(base + o, n) for o, n in zip(offs, sizes)]
     topologies = {}
     kinds = os.environ.get("MXB_FANOUT_TOPOLOGY", "chain").split(",")
-    # the sweep the benchmark configuration names (1, 4, 16, 64 MiB) plus one finer point
-    chunks_mib = [float(x) for x in os.environ.get("MXB_FANOUT_CHUNKS", "0.25,1,4,16,64").split(",")]
+    # the sweep the benchmark configuration names (1, 4, 16, 64 MiB) plus two finer points (a chunk
+    # of one 64 KiB piece is the finest the counters resolve)
+    chunks_mib = {"vector": [float(x) for x in os.environ.get("MXB_FANOUT_CHUNKS", "0.0625,0.25,1,4,16,64").split(",")]}
+    engines = os.environ.get("MXB_FANOUT_ENGINES", "vector").split(",")
     launches = 0
     for kind in kinds:
         children = topology(kind, world, 0)
-        sweep = {}
-        for mib in chunks_mib:
-            node = ctx.fanout(spans, int(mib * (1 << 20)) // 65536 * 65536, local)
-            ctrs = _open_peers(ctx, node.counters, world)
-            for c in children[rank]:
-                node.add_child([(peers[c] + o, n) for o, n in zip(offs, sizes)], ctrs[c])
-            _barrier(world)
-            times = []
-            for it in range(warmup + steps):
-                if rank != 0:
-                    arena.zero_()
-                    torch.cuda.synchronize()
+        by_engine = {}
+        for engine in engines:
+            sweep = {}
+            for mib in chunks_mib.get(engine, chunks_mib["vector"]):
+                node = ctx.fanout(spans, int(mib * (1 << 20)) // 4096 * 4096, local)
+                node.set_engine(engine)
+                ctrs = _open_peers(ctx, node.counters, world)
+                for c in children[rank]:
+                    node.add_child([(peers[c] + o, n) for o, n in zip(offs, sizes)], ctrs[c])
                 _barrier(world)
-                t0 = time.perf_counter()
-                node.run(rank == 0, 20000)
-                ms = node.wait()
-                wall = (time.perf_counter() - t0) * 1e3
-                ms = _max(ms, world)
-                wall = _max(wall, world)
-                launches += 1
-                if it >= warmup:
-                    times.append((ms, wall))
-            dev_ms = sum(t[0] for t in times) / len(times)
-            wall_ms = sum(t[1] for t in times) / len(times)
-            sweep[f"{mib:g}"] = {"device_ms": round(dev_ms, 3), "wall_ms": round(wall_ms, 3),
-                               "gbs_per_target": round(payload / (dev_ms * 1e-3) / 1e9, 1),
-                               "gbs_aggregate": round(payload * (world - 1) / (dev_ms * 1e-3) / 1e9, 1)}
-            # every destination range must digest like the source's
-            recs = ctx.digest(spans, DIGEST_SAFE32 | DIGEST_BLOCK64, local)
-            mine = [(int(r.safe_checksum), int(r.block_hash)) for r in recs]
-            alld = _gather_objects(mine, world)
-            for r in range(1, world):
-                if alld[r] != alld[0]:
-                    raise SystemExit(f"fan-out ({kind}): rank {r} digests differ from the source (chunk {mib:g} MiB)")
-            _barrier(world)
-            node.close()
-        best = max(sweep, key=lambda k: sweep[k]["gbs_per_target"])
-        topologies[kind] = {"chunk_sweep_mib": sweep, "best_chunk_mib": float(best),
-                            "gbs_per_target": sweep[best]["gbs_per_target"],
-                            "device_ms": sweep[best]["device_ms"]}
+                times = []
+                for it in range(warmup + steps):
+                    if rank != 0:
+                        arena.zero_()
+                        torch.cuda.synchronize()
+                    _barrier(world)
+                    t0 = time.perf_counter()
+                    before = ctx.launch_count
+                    node.run(rank == 0, 20000)
+                    ms = node.wait()
+                    wall = (time.perf_counter() - t0) * 1e3
+                    ms = _max(ms, world)
+                    wall = _max(wall, world)
+                    launches += ctx.launch_count - before
+                    if it >= warmup:
+                        times.append((ms, wall))
+                dev_ms = sum(t[0] for t in times) / len(times)
+                wall_ms = sum(t[1] for t in times) / len(times)
+                sweep[f"{mib:g}"] = {"device_ms": round(dev_ms, 3), "wall_ms": round(wall_ms, 3),
+                                   "gbs_per_target": round(payload / (dev_ms * 1e-3) / 1e9, 1),
+                                   "gbs_aggregate": round(payload * (world - 1) / (dev_ms * 1e-3) / 1e9, 1)}
+                # every destination range must digest like the source's
+                recs = ctx.digest(spans, DIGEST_SAFE32 | DIGEST_BLOCK64, local)
+                mine = [(int(r.safe_checksum), int(r.block_hash)) for r in recs]
+                alld = _gather_objects(mine, world)
+                for r in range(1, world):
+                    if alld[r] != alld[0]:
+                        raise SystemExit(f"fan-out ({kind}, {engine}): rank {r} digests differ from the source "
+                                         f"(chunk {mib:g} MiB)")
+                _barrier(world)
+                node.close()
+            best = max(sweep, key=lambda k: sweep[k]["gbs_per_target"])
+            by_engine[engine] = {"chunk_sweep_mib": sweep, "best_chunk_mib": float(best),
+                                 "gbs_per_target": sweep[best]["gbs_per_target"],
+                                 "device_ms": sweep[best]["device_ms"]}
+        top = max(by_engine, key=lambda e: by_engine[e]["gbs_per_target"])
+        topologies[kind] = dict(by_engine[top], engine=top, engines=by_engine)
     # comparison line: ncclBroadcast of the same arena
     import torch.distributed as dist
 
@@ -400,7 +409,8 @@ def fanout_measure(args, ctx, rank, world, local, nv=None) -> dict:
     res = {"workload": "configs[2]: 16.06 GB TP=1 copy on GPU 0 broadcast over NVLink P2P stores",
            "payload_bytes": payload, "ranges": len(sizes), "topology": kinds[0],
            "gbs_per_target": first["gbs_per_target"], "device_ms": first["device_ms"],
-           "best_chunk_mib": first["best_chunk_mib"], "topologies": topologies,
+           "best_chunk_mib": first["best_chunk_mib"], "engine": first["engine"],
+           "topologies": topologies,
            "rank_matched_pairs": pairs, "nccl_broadcast": nccl, "gpu_launches": launches,
            "frac_of_nominal_900": round(first["gbs_per_target"] / NVLINK_NOMINAL_GBS, 4),
            "frac_of_measured_peak": round(first["gbs_per_target"] / peak, 4) if peak else None,
@@ -817,9 +827,98 @@ def run_vllm(args):
     print(json.dumps(out), flush=True)
 
 
+def run_convert(args):
+    """The box-convert kernel on the parameter list of a Llama-3-8B-shaped model (every 2-D
+    weight and the norms): cast fp32 -> bf16 (a trainer that serves fp32 masters), transposed
+    bf16 (weights stored transposed) and both at once, one launch per case; beside each the
+    per-tensor ``dst.copy_(src)`` loop the reference leaves to torch (receiver.py:964-971).
+    Every case is compared bit for bit with torch's result before it is timed."""
+    import torch
+
+    from modelexpress_b200 import synth
+    from modelexpress_b200.runtime import Context
+
+    rank, world, local = _dist()
+    ctx = Context([local])
+    layers = _env_int("MXB_CONVERT_LAYERS", 8)
+    cfg = synth.scaled(synth.LLAMA3_8B, layers=layers)
+    shapes = [tuple(s) for _n, s, _d, _k in synth.dense_tensors(cfg)]
+    elems = sum(int(torch.Size(s).numel()) for s in shapes)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5 + rank)
+    src32 = torch.randn(elems, dtype=torch.float32, device="cuda", generator=g)
+    src16 = src32.to(torch.bfloat16)
+    dst16 = torch.zeros(elems, dtype=torch.bfloat16, device="cuda")
+    want = torch.zeros(elems, dtype=torch.bfloat16, device="cuda")
+    peak, peak_src = _peaks()
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+    cases = {}
+    for label, src, transposed in (("cast fp32 -> bf16", src32, False), ("transpose bf16", src16, True),
+                                   ("transpose + cast fp32 -> bf16", src32, True)):
+        boxes, views, pos = [], [], 0
+        for shp in shapes:
+            n = int(torch.Size(shp).numel())
+            two_d = transposed and len(shp) == 2
+            strides = [1, shp[0]] if two_d else [int(torch.Size(shp[k + 1:]).numel()) for k in range(len(shp))]
+            kinds = ("f32", "bf16") if src.dtype == torch.float32 else ("raw", "raw")
+            boxes.append((src.data_ptr() + pos * src.element_size(), dst16.data_ptr() + pos * 2, list(shp), strides,
+                          kinds[0], kinds[1], src.element_size()))
+            s_view = src[pos: pos + n].view(shp)
+            views.append((s_view, torch.as_strided(want, shp, strides, pos)))
+            pos += n
+        # torch's loop: the check and the comparison line
+        def torch_loop():
+            for s_view, d_view in views:
+                d_view.copy_(s_view)
+        for _ in range(warmup):
+            torch_loop()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            torch_loop()
+        e1.record()
+        torch.cuda.synchronize()
+        torch_ms = _max(e0.elapsed_time(e1) / steps, world)
+        dst16.zero_()
+        torch.cuda.synchronize()
+        moved = ctx.convert_boxes(boxes, local)
+        if not torch.equal(dst16.view(torch.int16), want.view(torch.int16)):
+            raise SystemExit(f"convert bench ({label}): kernel result differs from torch's copy")
+        prepared = ctx.convert_array(boxes)
+        for _ in range(warmup):
+            ctx.convert_boxes(prepared, local)
+        _barrier(world)
+        total_ms = 0.0
+        for _ in range(steps):   # table upload + kernel of each call, on the library's stream
+            ctx.event_record(0, local)
+            ctx.convert_boxes(prepared, local)
+            ctx.event_record(1, local)
+            total_ms += ctx.event_elapsed_ms(0, 1, local)
+        ms = _max(total_ms / steps, world)
+        cases[label] = {"ms": round(ms, 4), "gbs": round(moved / (ms * 1e-3) / 1e9, 1),
+                        "frac_of_hbm_peak": round(moved / (ms * 1e-3) / 1e9 / peak, 4),
+                        "bytes_read_plus_written": moved, "launches_per_step": 1,
+                        "torch_copy_loop_ms": round(torch_ms, 4), "torch_launches_per_step": len(views),
+                        "torch_gbs": round(moved / (torch_ms * 1e-3) / 1e9, 1), "check": "bit-identical to torch"}
+    head = cases["cast fp32 -> bf16"]
+    out = _base("GB/s converted (bytes read + written, box-convert kernel, one launch)", head["gbs"] * world,
+                "GB/s", world, args, head["ms"],
+                {"workload": f"Llama-3-8B parameter list, {layers} layers, {len(shapes)} tensors, "
+                             f"{elems} elements resident in HBM", "l2": "input larger than L2", "cases": cases},
+                dtype="f32->bf16")
+    out["gpu_launches"] = steps * len(cases)
+    out["roofline"] = {"bound": "hbm", "achieved": head["gbs"], "peak": peak, "unit": "GB/s",
+                       "frac": head["frac_of_hbm_peak"], "traffic": None, "kernel": "convert_kernel",
+                       "peak_source": peak_src, "algorithmic_bytes_per_launch": head["bytes_read_plus_written"]}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    ctx.close()
+
+
 def run(args):
     fn = {"digest": run_digest, "fanout": run_fanout, "reshard": run_reshard,
-          "vllm": run_vllm}.get(args.workload)
+          "vllm": run_vllm, "convert": run_convert}.get(args.workload)
     if fn is None:
         raise SystemExit(f"unknown workload {args.workload!r}")
     return fn(args)

@@ -364,6 +364,39 @@ int32_t mxb_block_hashes(mxb_ctx *ctx, int32_t dev, uint64_t ptr, uint64_t nbyte
 int32_t mxb_digest_noalloc(int32_t dev, const mxb_span *spans, uint64_t n, uint32_t modes,
                            mxb_digest_out *out, void *stream);
 
+/* ---- box convert: staged boxes -> live parameters, transposed and cast ----- */
+
+#define MXB_ELEM_RAW 0  /* `elem_bytes` bytes moved unchanged (1, 2, 4 or 8) */
+#define MXB_ELEM_F32 1
+#define MXB_ELEM_F16 2
+#define MXB_ELEM_BF16 3
+
+/* One staged box.  `src` holds the box contiguously, row-major over
+ * extent[0..ndim) (the source tensor's own dim order, element size given by
+ * `src_kind`); the element at box index (i0, i1, ...) lands at
+ * dst + sum(i_d * dst_stride[d]) destination elements (`dst_kind`).  This is the
+ * copy the reference leaves to torch after a pull: `dst.copy_(staged)` for a
+ * served dtype that differs from the parameter's (refit/reshard/receiver.py:964-971)
+ * and the permuted boxes of refit/reshard/slice_plan.py:170-224. */
+typedef struct {
+    uint64_t src;
+    uint64_t dst;
+    uint32_t ndim;
+    uint32_t src_kind;  /* MXB_ELEM_* */
+    uint32_t dst_kind;  /* MXB_ELEM_*: equal to src_kind, or a float pair (F32, F16, BF16) */
+    uint32_t elem_bytes; /* MXB_ELEM_RAW only */
+    uint64_t extent[MXB_MAX_DIMS];
+    int64_t dst_stride[MXB_MAX_DIMS]; /* destination elements, >= 0 */
+} mxb_convert;
+
+/* One launch over `n` boxes on the context's stream of `dev`; waits unless
+ * MXB_SCATTER_NO_SYNC.  Casts round to nearest even like torch's device copy.
+ * *bytes_out (optional) = bytes read + written.  MXB_ERR_UNSUPPORTED for a pair
+ * of kinds outside the table above or a box that needs more than four dims after
+ * merging; MXB_ERR_ALIGN for an address not aligned to its element. */
+int32_t mxb_convert_boxes(mxb_ctx *ctx, int32_t dev, const mxb_convert *items, uint64_t n,
+                          uint32_t flags, uint64_t *bytes_out);
+
 /* ---- kernel 2: serving-peer fan-out -------------------------------------- */
 
 #define MXB_FANOUT_MAX_CHILDREN 7
@@ -403,6 +436,16 @@ uint64_t mxb_fanout_counters(mxb_fanout *f);
  * as addresses valid in this process. */
 int32_t mxb_fanout_set_child(mxb_fanout *f, int32_t k, const mxb_span *child, uint64_t n,
                              uint64_t child_counters);
+/* How a node moves its chunks (default: VECTOR, or what the environment variable
+ * MXB_FANOUT_ENGINE = "vector" | "bulk" names when the node is created).
+ *   VECTOR  one persistent kernel, 16-byte peer stores straight from HBM;
+ *   BULK    one persistent kernel, pieces staged through shared memory with bulk copies.
+ * Both speak the same counters, so the nodes of one broadcast may differ.  The
+ * reference has no counterpart: its pull is one RDMA READ per tensor with no
+ * forwarding (nixl_transfer.py:769-952). */
+#define MXB_FANOUT_ENGINE_VECTOR 0
+#define MXB_FANOUT_ENGINE_BULK 1
+int32_t mxb_fanout_set_engine(mxb_fanout *f, int32_t engine);
 /* Launch this node's kernel for one broadcast.  `is_root`: has no parent.
  * `timeout_ms` bounds every device-side wait. */
 int32_t mxb_fanout_run(mxb_fanout *f, int32_t is_root, uint32_t timeout_ms);

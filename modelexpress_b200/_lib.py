@@ -61,6 +61,11 @@ class FanoutPiece(ctypes.Structure):
     _fields_ = [("range", u64), ("offset", u64), ("nbytes", u32), ("chunk", u32)]
 
 
+class ConvertBox(ctypes.Structure):
+    _fields_ = [("src", u64), ("dst", u64), ("ndim", u32), ("src_kind", u32), ("dst_kind", u32),
+                ("elem_bytes", u32), ("extent", u64 * MAX_DIMS), ("dst_stride", i64 * MAX_DIMS)]
+
+
 class PlaceStats(ctypes.Structure):
     _fields_ = [("bytes_placed", u64), ("chunks", u64), ("launches", u64),
                 ("seconds_total", ctypes.c_double), ("seconds_gather", ctypes.c_double),
@@ -113,10 +118,12 @@ SIGNATURES = {
     "mxb_digest": (i32, [_vp, i32, _P(Span), u64, u32, _P(DigestOut)]),
     "mxb_block_hashes": (i32, [_vp, i32, u64, u64, u64]),
     "mxb_digest_noalloc": (i32, [i32, _P(Span), u64, u32, _P(DigestOut), _vp]),
+    "mxb_convert_boxes": (i32, [_vp, i32, _P(ConvertBox), u64, u32, _P(u64)]),
     "mxb_fanout_plan": (i32, [_P(Span), u64, u64, _P(FanoutPiece), u64, _P(u64), _P(u32), u64, _P(u64)]),
     "mxb_fanout_create": (i32, [_vp, i32, _P(Span), u64, u64, _P(_vp)]),
     "mxb_fanout_counters": (u64, [_vp]),
     "mxb_fanout_set_child": (i32, [_vp, i32, _P(Span), u64, u64]),
+    "mxb_fanout_set_engine": (i32, [_vp, i32]),
     "mxb_fanout_run": (i32, [_vp, i32, u32]),
     "mxb_fanout_wait": (i32, [_vp, _P(ctypes.c_float)]),
     "mxb_fanout_destroy": (i32, [_vp]),

@@ -1,0 +1,458 @@
+// Kernel 5: box convert (sm_100a).  A staged source box (contiguous, in the source's own
+// dimension order) lands in a live parameter with the destination's strides, cast on the way
+// when the served dtype differs.  It replaces the per-tensor `dst.copy_(src)` the reference
+// leaves to torch after a pull (refit/reshard/receiver.py:964-971) and the transposed boxes
+// of slice_plan.py:170-224, with one persistent launch for the whole list.
+//
+// Each box is canonicalised on the host (extent-1 dims dropped, dims merged where the
+// destination walks them like the source does) into at most four dims.  Two tile shapes:
+//   rows       the destination is unit-stride along the source's inner dim: a tile is up to
+//              16384 elements of one row; 16-byte vectors when both sides are aligned.
+//   transpose  some other dim is the destination's unit-stride dim: a tile is 64 x 64 elements,
+//              read along the source's inner dim, turned in shared memory, written along the
+//              destination's inner dim (element pairs when both sides allow 4-byte accesses).
+// HBM-bound: one read of the source element and one write of the destination element, nothing
+// else.  Casts use the conversions torch's own device code uses (__float2bfloat16_rn,
+// __float2half_rn, widening by bit placement), so results equal torch's bit for bit.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace mxb {
+
+constexpr int kCvtThreads = 256;
+constexpr uint32_t kRowTile = 16384;
+constexpr uint32_t kTT = 64;  // transpose tile edge
+
+struct CvtItem {
+    uint64_t src, dst;
+    uint32_t n[4];     // canonical extents, n[3] = the source's inner dim
+    int64_t ds[4];     // destination strides (elements)
+    uint64_t tile0;    // first tile of this item
+    uint32_t mode;     // 0 rows, 1 transpose
+    uint32_t bdim;     // transpose: the dim the destination walks with stride 1
+    uint32_t pair;     // pair (4-byte / 8-byte) accesses allowed on both sides
+    uint32_t kind;     // conversion, see CvtKind
+    uint32_t tiles_a, tiles_b;  // tiles along n[3] and along n[bdim] (rows: tiles_b = 1)
+    uint64_t n_tiles;
+};
+
+enum CvtKind : uint32_t {
+    kRaw1, kRaw2, kRaw4, kRaw8, kBf16ToF32, kF16ToF32, kF32ToBf16, kF32ToF16, kBf16ToF16, kF16ToBf16,
+    kKinds
+};
+
+// Element tags: how a value is stored and how it passes through float.
+template <typename U>
+struct Raw {
+    using store = U;
+};
+struct F32 {
+    using store = uint32_t;
+    __device__ static __forceinline__ float to_float(store v) { return __uint_as_float(v); }
+    __device__ static __forceinline__ store from_float(float f) { return __float_as_uint(f); }
+};
+struct F16 {
+    using store = uint16_t;
+    __device__ static __forceinline__ float to_float(store v) { return __half2float(__ushort_as_half(v)); }
+    __device__ static __forceinline__ store from_float(float f) { return __half_as_ushort(__float2half_rn(f)); }
+};
+struct BF16 {
+    using store = uint16_t;
+    __device__ static __forceinline__ float to_float(store v) { return __uint_as_float((uint32_t)v << 16); }
+    __device__ static __forceinline__ store from_float(float f) {
+        return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+    }
+};
+
+template <typename S, typename D>
+struct Cast {
+    __device__ static __forceinline__ typename D::store run(typename S::store v) {
+        return D::from_float(S::to_float(v));
+    }
+};
+template <typename U>
+struct Cast<Raw<U>, Raw<U>> {
+    __device__ static __forceinline__ U run(U v) { return v; }
+};
+
+template <int N>
+struct Bytes;
+template <>
+struct Bytes<2> { using type = uint16_t; };
+template <>
+struct Bytes<4> { using type = uint32_t; };
+template <>
+struct Bytes<8> { using type = uint2; };
+template <>
+struct Bytes<16> { using type = uint4; };
+
+// V elements of S -> V elements of D through registers; addresses aligned to their vectors
+template <typename S, typename D, int V>
+__device__ __forceinline__ void cast_vec(const typename S::store *__restrict__ s,
+                                         typename D::store *__restrict__ d) {
+    using SE = typename S::store;
+    using DE = typename D::store;
+    using SV = typename Bytes<sizeof(SE) * V>::type;
+    using DV = typename Bytes<sizeof(DE) * V>::type;
+    union { SV v; SE e[V]; } in;
+    union { DV v; DE e[V]; } out;
+    in.v = *reinterpret_cast<const SV *>(s);
+#pragma unroll
+    for (int i = 0; i < V; ++i) out.e[i] = Cast<S, D>::run(in.e[i]);
+    *reinterpret_cast<DV *>(d) = out.v;
+}
+
+template <typename S, typename D>
+__device__ void rows_tile(const CvtItem &it, uint64_t t, unsigned char *) {
+    using SE = typename S::store;
+    using DE = typename D::store;
+    const uint32_t ta = (uint32_t)(t % it.tiles_a);
+    uint64_t row = t / it.tiles_a;
+    const uint32_t a0 = ta * kRowTile;
+    const uint32_t len = min(kRowTile, it.n[3] - a0);
+    const SE *s = reinterpret_cast<const SE *>(it.src) + row * it.n[3] + a0;
+    int64_t off = 0;
+    for (int d = 2; d >= 0; --d) {
+        off += (int64_t)(row % it.n[d]) * it.ds[d];
+        row /= it.n[d];
+    }
+    const int64_t step = it.ds[3];
+    DE *dbase = reinterpret_cast<DE *>(it.dst) + off + (int64_t)a0 * step;
+    uint32_t done = 0;
+    if (step == 1 && (reinterpret_cast<uintptr_t>(s) & 15u) == 0 &&
+        (reinterpret_cast<uintptr_t>(dbase) & 15u) == 0) {
+        // W elements per access: 16 bytes on the wider side
+        constexpr int kWide = sizeof(SE) > sizeof(DE) ? sizeof(SE) : sizeof(DE);
+        constexpr int W = 16 / kWide;
+        using SV = typename Bytes<sizeof(SE) * W>::type;
+        using DV = typename Bytes<sizeof(DE) * W>::type;
+        const uint32_t nv = len / W;
+        const SV *sv = reinterpret_cast<const SV *>(s);
+        DV *dv = reinterpret_cast<DV *>(dbase);
+        uint32_t i = threadIdx.x;
+        for (; i + 7 * kCvtThreads < nv; i += 8 * kCvtThreads) {   // eight independent loads in flight
+            SV in[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) in[k] = sv[i + k * kCvtThreads];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                union { SV v; SE e[W]; } a;
+                union { DV v; DE e[W]; } b;
+                a.v = in[k];
+#pragma unroll
+                for (int e = 0; e < W; ++e) b.e[e] = Cast<S, D>::run(a.e[e]);
+                dv[i + k * kCvtThreads] = b.v;
+            }
+        }
+        for (; i < nv; i += kCvtThreads) cast_vec<S, D, W>(s + (size_t)i * W, dbase + (size_t)i * W);
+        done = nv * W;
+    }
+    for (uint32_t i = done + threadIdx.x; i < len; i += kCvtThreads)
+        dbase[(int64_t)i * step] = Cast<S, D>::run(s[i]);
+}
+
+template <typename S, typename D>
+__device__ void transpose_tile(const CvtItem &it, uint64_t t, unsigned char *smem_raw) {
+    using SE = typename S::store;
+    using DE = typename D::store;
+    DE(*tile)[kTT + 1] = reinterpret_cast<DE(*)[kTT + 1]>(smem_raw);
+    const uint32_t b = it.bdim;
+    const uint32_t ta = (uint32_t)(t % it.tiles_a);
+    t /= it.tiles_a;
+    const uint32_t tb = (uint32_t)(t % it.tiles_b);
+    uint64_t rest = t / it.tiles_b;
+    // the two dims that are neither the source's inner dim nor the destination's
+    uint32_t idx[3] = {0, 0, 0};
+    for (int d = 2; d >= 0; --d) {
+        if ((uint32_t)d == b) continue;
+        idx[d] = (uint32_t)(rest % it.n[d]);
+        rest /= it.n[d];
+    }
+    const uint32_t a0 = ta * kTT, b0 = tb * kTT;
+    const uint32_t na = min(kTT, it.n[3] - a0), nb = min(kTT, it.n[b] - b0);
+    // source element (idx with idx[b] = b0 + j, a0 + i)
+    uint64_t srow = 0;
+    int64_t doff = 0;
+    for (int d = 0; d < 3; ++d) {
+        const uint32_t v = (uint32_t)d == b ? b0 : idx[d];
+        srow = srow * it.n[d] + v;
+        doff += (int64_t)v * it.ds[d];
+    }
+    uint64_t sstride_b = it.n[3];  // elements between consecutive b in the source
+    for (uint32_t d = b + 1; d < 3; ++d) sstride_b *= it.n[d];
+    const SE *s = reinterpret_cast<const SE *>(it.src) + srow * it.n[3] + a0;
+    DE *dp = reinterpret_cast<DE *>(it.dst) + doff + (int64_t)a0 * it.ds[3];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr uint32_t kWarps = kCvtThreads / 32;
+    if constexpr (sizeof(SE) <= 4 && sizeof(DE) <= 4) {
+      if (it.pair && na == kTT && nb == kTT) {
+        // a full tile: the warp's eight rows are loaded before any of them is turned
+        using S2 = typename Bytes<2 * sizeof(SE)>::type;
+        using D2 = typename Bytes<2 * sizeof(DE)>::type;
+        constexpr int kRows = kTT / kWarps;
+        S2 in[kRows];
+#pragma unroll
+        for (int k = 0; k < kRows; ++k)
+            in[k] = *reinterpret_cast<const S2 *>(s + (uint64_t)(warp + k * kWarps) * sstride_b + 2 * lane);
+#pragma unroll
+        for (int k = 0; k < kRows; ++k) {
+            union { S2 v; SE e[2]; } a;
+            a.v = in[k];
+            tile[warp + k * kWarps][2 * lane] = Cast<S, D>::run(a.e[0]);
+            tile[warp + k * kWarps][2 * lane + 1] = Cast<S, D>::run(a.e[1]);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < kRows; ++k) {
+            const uint32_t i = warp + k * kWarps;
+            union { D2 v; DE e[2]; } out;
+            out.e[0] = tile[2 * lane][i];
+            out.e[1] = tile[2 * lane + 1][i];
+            *reinterpret_cast<D2 *>(dp + (int64_t)i * it.ds[3] + 2 * lane) = out.v;
+        }
+        __syncthreads();  // the tile is reused by this CTA's next tile
+        return;
+      }
+      if (it.pair) {
+        using S2 = typename Bytes<2 * sizeof(SE)>::type;
+        using D2 = typename Bytes<2 * sizeof(DE)>::type;
+        for (uint32_t j = warp; j < nb; j += kWarps) {
+            const uint32_t i = 2 * lane;
+            if (i < na) {  // na is even when pairs are allowed
+                union { S2 v; SE e[2]; } in;
+                in.v = *reinterpret_cast<const S2 *>(s + (uint64_t)j * sstride_b + i);
+                tile[j][i] = Cast<S, D>::run(in.e[0]);
+                tile[j][i + 1] = Cast<S, D>::run(in.e[1]);
+            }
+        }
+        __syncthreads();
+        for (uint32_t i = warp; i < na; i += kWarps) {
+            const uint32_t j = 2 * lane;
+            if (j < nb) {
+                union { D2 v; DE e[2]; } out;
+                out.e[0] = tile[j][i];
+                out.e[1] = tile[j + 1][i];
+                *reinterpret_cast<D2 *>(dp + (int64_t)i * it.ds[3] + j) = out.v;
+            }
+        }
+        __syncthreads();  // the tile is reused by this CTA's next tile
+        return;
+      }
+    }
+    {
+        for (uint32_t j = warp; j < nb; j += kWarps)
+            for (uint32_t i = lane; i < na; i += 32)
+                tile[j][i] = Cast<S, D>::run(s[(uint64_t)j * sstride_b + i]);
+        __syncthreads();
+        for (uint32_t i = warp; i < na; i += kWarps)
+            for (uint32_t j = lane; j < nb; j += 32) dp[(int64_t)i * it.ds[3] + j] = tile[j][i];
+    }
+    __syncthreads();  // the tile is reused by this CTA's next tile
+}
+
+template <typename S, typename D>
+__device__ __forceinline__ void one_tile(const CvtItem &it, uint64_t t, unsigned char *smem) {
+    if (it.mode == 0) rows_tile<S, D>(it, t, smem);
+    else transpose_tile<S, D>(it, t, smem);
+}
+
+__global__ void __launch_bounds__(kCvtThreads) convert_kernel(const CvtItem *__restrict__ items,
+                                                             uint32_t n_items, uint64_t n_tiles) {
+    __shared__ __align__(16) unsigned char smem[kTT * (kTT + 1) * 8];
+    __shared__ CvtItem cur;
+    __shared__ uint32_t cur_index;
+    if (threadIdx.x == 0) cur_index = 0xffffffffu;
+    __syncthreads();
+    for (uint64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+        // the item that owns tile t: usually still the one this CTA holds; else the last item
+        // whose first tile is <= t
+        uint32_t lo = cur_index;
+        if (lo == 0xffffffffu || t < cur.tile0 || t >= cur.tile0 + cur.n_tiles) {
+            lo = 0;
+            uint32_t hi = n_items - 1;
+            while (lo < hi) {
+                const uint32_t mid = (lo + hi + 1) >> 1;
+                if (items[mid].tile0 <= t) lo = mid;
+                else hi = mid - 1;
+            }
+        }
+        if (cur_index != lo) {
+            __syncthreads();
+            if (threadIdx.x < sizeof(CvtItem) / 8)
+                reinterpret_cast<uint64_t *>(&cur)[threadIdx.x] =
+                    reinterpret_cast<const uint64_t *>(items + lo)[threadIdx.x];
+            if (threadIdx.x == 0) cur_index = lo;
+            __syncthreads();
+        }
+        const uint64_t local = t - cur.tile0;
+        switch (cur.kind) {
+            case kRaw1: one_tile<Raw<uint8_t>, Raw<uint8_t>>(cur, local, smem); break;
+            case kRaw2: one_tile<Raw<uint16_t>, Raw<uint16_t>>(cur, local, smem); break;
+            case kRaw4: one_tile<Raw<uint32_t>, Raw<uint32_t>>(cur, local, smem); break;
+            case kRaw8: one_tile<Raw<uint64_t>, Raw<uint64_t>>(cur, local, smem); break;
+            case kBf16ToF32: one_tile<BF16, F32>(cur, local, smem); break;
+            case kF16ToF32: one_tile<F16, F32>(cur, local, smem); break;
+            case kF32ToBf16: one_tile<F32, BF16>(cur, local, smem); break;
+            case kF32ToF16: one_tile<F32, F16>(cur, local, smem); break;
+            case kBf16ToF16: one_tile<BF16, F16>(cur, local, smem); break;
+            case kF16ToBf16: one_tile<F16, BF16>(cur, local, smem); break;
+            default: break;
+        }
+        __syncthreads();  // `cur` may be replaced for the next tile
+    }
+}
+
+}  // namespace mxb
+
+using namespace mxb;
+
+namespace {
+
+uint32_t kind_size(uint32_t kind, uint32_t raw_bytes) {
+    switch (kind) {
+        case MXB_ELEM_RAW: return raw_bytes;
+        case MXB_ELEM_F32: return 4;
+        case MXB_ELEM_F16: case MXB_ELEM_BF16: return 2;
+        default: return 0;
+    }
+}
+
+// MXB_OK and a filled item, or MXB_ERR_UNSUPPORTED / MXB_ERR_ARG
+int32_t canonical(const mxb_convert &c, CvtItem *out, uint64_t *bytes) {
+    const uint32_t ssz = kind_size(c.src_kind, c.elem_bytes), dsz = kind_size(c.dst_kind, c.elem_bytes);
+    if (!ssz || !dsz || c.ndim > MXB_MAX_DIMS) return MXB_ERR_ARG;
+    uint32_t kind;
+    if (c.src_kind == c.dst_kind) {
+        kind = ssz == 1 ? kRaw1 : ssz == 2 ? kRaw2 : ssz == 4 ? kRaw4 : ssz == 8 ? kRaw8 : (uint32_t)kKinds;
+    } else if (c.src_kind == MXB_ELEM_BF16 && c.dst_kind == MXB_ELEM_F32) kind = kBf16ToF32;
+    else if (c.src_kind == MXB_ELEM_F16 && c.dst_kind == MXB_ELEM_F32) kind = kF16ToF32;
+    else if (c.src_kind == MXB_ELEM_F32 && c.dst_kind == MXB_ELEM_BF16) kind = kF32ToBf16;
+    else if (c.src_kind == MXB_ELEM_F32 && c.dst_kind == MXB_ELEM_F16) kind = kF32ToF16;
+    else if (c.src_kind == MXB_ELEM_BF16 && c.dst_kind == MXB_ELEM_F16) kind = kBf16ToF16;
+    else if (c.src_kind == MXB_ELEM_F16 && c.dst_kind == MXB_ELEM_BF16) kind = kF16ToBf16;
+    else kind = kKinds;
+    if (kind == kKinds) return MXB_ERR_UNSUPPORTED;
+    if ((c.src % ssz) || (c.dst % dsz)) return MXB_ERR_ALIGN;
+    // drop extent-1 dims, merge dims the destination walks like the (contiguous) source does
+    uint64_t n[MXB_MAX_DIMS];
+    int64_t ds[MXB_MAX_DIMS];
+    uint32_t nd = 0;
+    uint64_t total = 1;
+    for (uint32_t d = 0; d < c.ndim; ++d) {
+        if (c.extent[d] == 0) { total = 0; break; }
+        if (c.dst_stride[d] < 0) return MXB_ERR_ARG;
+        total *= c.extent[d];
+        if (c.extent[d] == 1) continue;
+        if (nd && ds[nd - 1] == c.dst_stride[d] * (int64_t)c.extent[d]) {
+            n[nd - 1] *= c.extent[d];
+            ds[nd - 1] = c.dst_stride[d];
+        } else {
+            n[nd] = c.extent[d];
+            ds[nd] = c.dst_stride[d];
+            ++nd;
+        }
+    }
+    memset(out, 0, sizeof *out);
+    *bytes = total * (ssz + dsz);
+    if (total == 0) return MXB_OK;  // nothing to move: zero tiles
+    if (nd == 0) { n[0] = 1; ds[0] = 1; nd = 1; }
+    if (nd > 4) return MXB_ERR_UNSUPPORTED;
+    for (uint32_t d = 0; d < nd; ++d)
+        if (n[d] > 0xffffffffull) return MXB_ERR_UNSUPPORTED;
+    out->src = c.src;
+    out->dst = c.dst;
+    for (uint32_t d = 0; d < 4; ++d) { out->n[d] = 1; out->ds[d] = 0; }
+    for (uint32_t d = 0; d < nd; ++d) {
+        out->n[4 - nd + d] = (uint32_t)n[d];
+        out->ds[4 - nd + d] = ds[d];
+    }
+    out->kind = kind;
+    out->bdim = 3;
+    if (out->ds[3] != 1)
+        for (uint32_t d = 0; d < 3; ++d)
+            if (out->n[d] > 1 && out->ds[d] == 1) out->bdim = d;
+    uint64_t tiles;
+    if (out->bdim == 3) {
+        out->mode = 0;
+        out->tiles_a = (out->n[3] + kRowTile - 1) / kRowTile;
+        out->tiles_b = 1;
+        tiles = (uint64_t)out->tiles_a * out->n[0] * out->n[1] * out->n[2];
+    } else {
+        out->mode = 1;
+        const uint32_t b = out->bdim;
+        out->tiles_a = (out->n[3] + kTT - 1) / kTT;
+        out->tiles_b = (out->n[b] + kTT - 1) / kTT;
+        tiles = (uint64_t)out->tiles_a * out->tiles_b;
+        for (uint32_t d = 0; d < 3; ++d)
+            if (d != b) tiles *= out->n[d];
+        // pairs: every pair of source elements along the inner dim and every pair of destination
+        // elements along its unit-stride dim must be a naturally aligned 2-element word
+        bool pair = ssz <= 4 && dsz <= 4 && out->n[3] % 2 == 0 && out->n[b] % 2 == 0 &&
+                    c.src % (2 * ssz) == 0 && c.dst % (2 * dsz) == 0;
+        for (uint32_t d = 0; d < 4 && pair; ++d)
+            if (d != b && out->n[d] > 1 && out->ds[d] % 2) pair = false;
+        out->pair = pair ? 1u : 0u;
+    }
+    out->tile0 = tiles;  // the caller turns counts into a prefix
+    return MXB_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t mxb_convert_boxes(mxb_ctx *ctx, int32_t dev, const mxb_convert *items, uint64_t n,
+                                     uint32_t flags, uint64_t *bytes_out) {
+    if (!ctx || (!items && n)) {
+        set_error("mxb_convert_boxes: bad arguments");
+        return MXB_ERR_ARG;
+    }
+    DeviceState *d = ctx->find(dev);
+    if (!d) {
+        set_error("device %d is not part of this context", dev);
+        return MXB_ERR_ARG;
+    }
+    std::vector<CvtItem> table;
+    table.reserve(n);
+    uint64_t tiles = 0, bytes = 0;
+    for (uint64_t i = 0; i < n; ++i) {
+        CvtItem it;
+        uint64_t b = 0;
+        const int32_t rc = canonical(items[i], &it, &b);
+        if (rc != MXB_OK) {
+            set_error("mxb_convert_boxes: box %llu: %s", (unsigned long long)i,
+                      rc == MXB_ERR_UNSUPPORTED ? "element kinds or rank not supported"
+                      : rc == MXB_ERR_ALIGN     ? "address not aligned to its element"
+                                                : "bad geometry");
+            return rc;
+        }
+        bytes += b;
+        const uint64_t count = it.tile0;
+        if (!count) continue;
+        it.tile0 = tiles;
+        it.n_tiles = count;
+        tiles += count;
+        table.push_back(it);
+    }
+    if (bytes_out) *bytes_out = bytes;
+    if (table.empty()) return MXB_OK;
+    DeviceGuard g(dev);
+    std::lock_guard<std::mutex> lk(*d->mu);
+    const size_t table_bytes = table.size() * sizeof(CvtItem);
+    int32_t rc = ensure_table(d, table_bytes);
+    if (rc != MXB_OK) return rc;
+    MXB_CUDA(cudaStreamSynchronize(d->stream));  // the pinned staging copy is shared by every call
+    d->table_tag = 0;
+    memcpy(d->table_host, table.data(), table_bytes);
+    MXB_CUDA(cudaMemcpyAsync(d->table, d->table_host, table_bytes, cudaMemcpyHostToDevice, d->stream));
+    uint64_t grid = (uint64_t)d->sm_count * 4;  // 64 registers x 256 threads: four resident CTAs per SM
+    if (grid > tiles) grid = tiles;
+    convert_kernel<<<(unsigned)grid, kCvtThreads, 0, d->stream>>>(
+        reinterpret_cast<const CvtItem *>(d->table), (uint32_t)table.size(), tiles);
+    MXB_CUDA(cudaGetLastError());
+    ctx->launches.fetch_add(1);
+    if (flags & MXB_SCATTER_NO_SYNC) return MXB_OK;
+    return check_status(d);
+}

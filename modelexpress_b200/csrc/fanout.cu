@@ -272,6 +272,7 @@ struct mxb_fanout {
     bool dirty = true;
     uint32_t run_index = 0;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    int32_t engine = MXB_FANOUT_ENGINE_VECTOR;
 };
 
 namespace {
@@ -282,6 +283,13 @@ namespace {
 // broadcast (same sizes, own addresses) cuts the same pieces and counts the same chunks.
 void plan_pieces(const mxb_span *local, uint64_t n, uint64_t chunk_bytes,
                  std::vector<mxb_fanout_piece> &pieces, std::vector<uint32_t> &chunk_pieces) {
+    uint64_t piece_max = kFanPiece;
+    // Measurement aid (must be the same in every process of a broadcast): pieces of 16, 32, 128
+    // or 256 KiB instead of 64.  Pieces above 64 KiB run on the store kernel only.
+    if (const char *e = getenv("MXB_FANOUT_PIECE_KIB")) {
+        const long v = atol(e);
+        if (v == 16 || v == 32 || v == 128 || v == 256) piece_max = (uint64_t)v << 10;
+    }
     uint64_t vpos = 0;
     for (uint64_t i = 0; i < n; ++i) {
         uint64_t off = 0;
@@ -290,7 +298,7 @@ void plan_pieces(const mxb_span *local, uint64_t n, uint64_t chunk_bytes,
             const uint64_t to_chunk_end = (chunk + 1) * chunk_bytes - vpos;
             uint64_t len = local[i].nbytes - off;
             if (len > to_chunk_end) len = to_chunk_end;
-            if (len > kFanPiece) len = kFanPiece;
+            if (len > piece_max) len = piece_max;
             if (len < local[i].nbytes - off) len &= ~uint64_t(15);
             if (len == 0) len = local[i].nbytes - off < 16 ? local[i].nbytes - off : 16;
             pieces.push_back({i, off, (uint32_t)len, (uint32_t)chunk});
@@ -359,6 +367,9 @@ int32_t mxb_fanout_create(mxb_ctx *ctx, int32_t dev, const mxb_span *local, uint
         f->piece_range.push_back(p.range);
         f->piece_off.push_back(p.offset);
     }
+    if (const char *eng = getenv("MXB_FANOUT_ENGINE")) {
+        if (!strcmp(eng, "bulk")) f->engine = MXB_FANOUT_ENGINE_BULK;
+    }
     DeviceGuard g(dev);
     const size_t nchunks = f->chunk_pieces.size() ? f->chunk_pieces.size() : 1;
     // a whole 2 MiB allocation of its own, so that an IPC handle of the counters
@@ -375,6 +386,15 @@ int32_t mxb_fanout_create(mxb_ctx *ctx, int32_t dev, const mxb_span *local, uint
         return MXB_ERR_CUDA;
     }
     *out = f;
+    return MXB_OK;
+}
+
+int32_t mxb_fanout_set_engine(mxb_fanout *f, int32_t engine) {
+    if (!f || (engine != MXB_FANOUT_ENGINE_VECTOR && engine != MXB_FANOUT_ENGINE_BULK)) {
+        set_error("mxb_fanout_set_engine: unknown engine");
+        return MXB_ERR_ARG;
+    }
+    f->engine = engine;
     return MXB_OK;
 }
 
@@ -454,8 +474,13 @@ int32_t mxb_fanout_run(mxb_fanout *f, int32_t is_root, uint32_t timeout_ms) {
     if (np == 0) return MXB_OK;
     // all CTAs must be co-resident: they wait on data, never on each other, but a
     // CTA that is not scheduled cannot forward its pieces
-    const char *eng = getenv("MXB_FANOUT_ENGINE");  // "bulk": shared-memory staged bulk copies
-    const bool bulk = eng && !strcmp(eng, "bulk");
+    const bool bulk = f->engine == MXB_FANOUT_ENGINE_BULK;
+    if (bulk)
+        for (const FanPiece &pc : f->pieces)
+            if (pc.nbytes > kFanPiece) {
+                set_error("mxb_fanout_run: the bulk engine stages pieces of at most 64 KiB");
+                return MXB_ERR_ARG;
+            }
     MXB_CUDA(cudaEventRecord(f->ev0, dv->stream));
     if (bulk) {
         const size_t smem = (size_t)kFanStages * kFanPiece;

@@ -107,11 +107,14 @@ class Broadcast:
     every GPU."""
 
     def __init__(self, ctx: Context, devices: list, spans: list, chunk_bytes: int,
-                 kind: str = "chain", root_index: int = 0):
+                 kind: str = "chain", root_index: int = 0, engine: str | None = None):
         self.devices = devices
         self.root = root_index
         self.children = topology(kind, len(devices), root_index)
         self.nodes = [Fanout(ctx, dev, spans[i], chunk_bytes) for i, dev in enumerate(devices)]
+        if engine is not None:
+            for node in self.nodes:
+                node.set_engine(engine)
         for i, kids in enumerate(self.children):
             for k in kids:
                 self.nodes[i].add_child(spans[k], self.nodes[k].counters)
@@ -244,7 +247,7 @@ class FanoutSource:
     replicas that ask (``serve``).  ``tensors`` is ``{name: CUDA tensor}``."""
 
     def __init__(self, tensors: dict, rendezvous_dir: str, source_id: str, ctx: Context | None = None,
-                 device: int | None = None, chunk_bytes: int = 256 << 10, digests: bool = True):
+                 device: int | None = None, chunk_bytes: int = 64 << 10, digests: bool = True):
         import torch
 
         from .runtime import default_context

@@ -769,7 +769,7 @@ def place_captured(model, model_path: str, device=None, *, load_weights=None,
         timings["place_wait"] = time.perf_counter() - tc
         seconds = time.perf_counter() - t0
         for converts, buf in stagings:
-            apply_converts(converts, buf, dests)
+            apply_converts(converts, buf, dests, ctx)
         reasons = {}
         for cap in parts:
             reasons.update(cap.reasons)

@@ -458,13 +458,70 @@ def convert_staging_bytes(copies, sources: dict) -> int:
     return total
 
 
-def apply_converts(converts, staging, params: dict) -> None:
+_FLOAT_KINDS = {"torch.float32": "f32", "torch.float16": "f16", "torch.bfloat16": "bf16"}
+
+
+def convert_box(c, staging_ptr: int, param) -> tuple | None:
+    """The ``mxb_convert`` box of one ConvertSpec: ``(src, dst, extents, dst_strides, src_kind,
+    dst_kind, elem_bytes)``, or ``None`` when the pair of dtypes is outside the kernel's table."""
+    sk, dk = _FLOAT_KINDS.get(str(c.src_dtype)), _FLOAT_KINDS.get(str(param.dtype))
+    elem = int(param.element_size())
+    if c.src_dtype == param.dtype:
+        if elem not in (1, 2, 4, 8):
+            return None
+        sk = dk = "raw"
+    elif sk is None or dk is None:
+        return None
+    if c.box_shape is None:
+        extents, strides = list(c.dest_shape), list(c.dest_stride)
+    else:
+        # the staged box keeps the source's dim order; destination dim d walks staging dim box_perm[d]
+        extents = list(c.box_shape)
+        strides = [0] * len(extents)
+        for d, s_dim in enumerate(c.box_perm):
+            if s_dim is not None:
+                strides[s_dim] = int(c.dest_stride[d])
+    if len(extents) > 8:
+        return None
+    return (staging_ptr + int(c.staging_offset), param.data_ptr() + int(c.dest_offset) * elem,
+            extents, strides, sk, dk, elem)
+
+
+def apply_converts(converts, staging, params: dict, ctx=None) -> None:
     """Cast (and, for staged boxes, transpose) the staged sources into their parameters
-    (receiver.py:964-971): the one step left to torch, for the few tensors that need it
-    (a bf16-served router feeding an fp32 parameter; weights stored transposed)."""
+    (receiver.py:964-971).  On the GPU all of them go through one launch of the box-convert
+    kernel; a pair of dtypes outside its table (and host tensors, which only the planner's own
+    tests use) takes torch's strided copy."""
     import torch
 
-    for c in converts:
+    leftover = list(converts)
+    if converts and staging.is_cuda:
+        from ._lib import MxbError
+        from .runtime import default_context
+
+        ctx = ctx or default_context(staging.device.index)
+        boxes, leftover = [], []
+        for c in converts:
+            box = convert_box(c, staging.data_ptr(), params[c.param_name])
+            if box is None:
+                leftover.append(c)
+            else:
+                boxes.append((c, box))
+        try:
+            if boxes:
+                torch.cuda.current_stream(staging.device).synchronize()   # the parameters may be torch's
+                ctx.convert_boxes([b for _c, b in boxes], staging.device.index)
+        except MxbError as e:
+            if getattr(e, "code", None) != -9:   # MXB_ERR_UNSUPPORTED: more than four dims after merging
+                raise
+            for c, b in boxes:
+                try:
+                    ctx.convert_boxes([b], staging.device.index)
+                except MxbError as e1:
+                    if getattr(e1, "code", None) != -9:
+                        raise
+                    leftover.append(c)
+    for c in leftover:
         src = staging[c.staging_offset: c.staging_offset + c.nbytes].view(c.src_dtype)
         if c.box_shape is None:
             src = src.reshape(c.dest_shape)

@@ -382,7 +382,7 @@ class ReshardReceiver:
         check_throughput_ceiling(int(step), int(self.plan.get("bytes_per_step", 0)), stages["read_s"])
         t2 = time.perf_counter()
         if self._converts:
-            apply_converts(self._converts, self._staging, self._dests)
+            apply_converts(self._converts, self._staging, self._dests, self.ctx)
         if self._install is not None:
             self._install(self.model)
         torch.cuda.current_stream(self.device).synchronize()

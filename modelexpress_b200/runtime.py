@@ -124,6 +124,36 @@ class Context:
         arr, n = _lib.desc_array(descs)
         check(self._lib.mxb_scatter(self._h, self._dev(dev), arr, n, flags), "mxb_scatter")
 
+    ELEM_KINDS = {"raw": 0, "f32": 1, "f16": 2, "bf16": 3}
+
+    @classmethod
+    def convert_array(cls, boxes):
+        """Marshal ``(src, dst, extents, dst_strides, src_kind, dst_kind, elem_bytes)`` tuples once
+        (a list that is replayed every step need not be marshalled every step)."""
+        boxes = list(boxes)
+        arr = (_lib.ConvertBox * max(1, len(boxes)))()
+        for i, (src, dst, extents, strides, sk, dk, eb) in enumerate(boxes):
+            if len(extents) != len(strides) or len(extents) > _lib.MAX_DIMS:
+                raise ValueError("convert box: extents and strides must have the same rank, at most 8")
+            b = arr[i]
+            b.src, b.dst, b.ndim = int(src), int(dst), len(extents)
+            b.src_kind, b.dst_kind, b.elem_bytes = cls.ELEM_KINDS[sk], cls.ELEM_KINDS[dk], int(eb)
+            for d, (e, st) in enumerate(zip(extents, strides)):
+                b.extent[d], b.dst_stride[d] = int(e), int(st)
+        return arr, len(boxes)
+
+    def convert_boxes(self, boxes, dev: int | None = None, flags: int = SCATTER_DEFAULT) -> int:
+        """boxes: iterable of (src, dst, extents, dst_strides, src_kind, dst_kind, elem_bytes), or
+        what ``convert_array`` returned: each contiguous staged box lands with the destination's
+        strides (in elements), cast when the kinds ("raw", "f32", "f16", "bf16") differ.
+        One launch; returns bytes read + written."""
+        prepared = isinstance(boxes, tuple) and len(boxes) == 2 and isinstance(boxes[0], ctypes.Array)
+        arr, n = boxes if prepared else self.convert_array(boxes)
+        moved = ctypes.c_uint64(0)
+        check(self._lib.mxb_convert_boxes(self._h, self._dev(dev), arr, n, flags, ctypes.byref(moved)),
+              "mxb_convert_boxes")
+        return int(moved.value)
+
     def read_runs(self, runs, dev: int | None = None) -> None:
         """runs: iterable of (src, dst, nbytes); returns when the bytes are visible."""
         arr, n = _lib.run_array(runs)
@@ -384,6 +414,15 @@ class Fanout:
               "mxb_fanout_create")
         self._h = h
         self.children = 0
+
+    ENGINES = {"vector": 0, "bulk": 1}
+
+    def set_engine(self, engine: str) -> None:
+        """"vector" (16-byte peer stores straight from HBM) or "bulk" (staged through shared memory
+        with bulk copies); the nodes of one broadcast may differ."""
+        if engine not in self.ENGINES:
+            raise ValueError(f"unknown fan-out engine {engine!r}")
+        check(self.ctx._lib.mxb_fanout_set_engine(self._h, self.ENGINES[engine]), "mxb_fanout_set_engine")
 
     @property
     def counters(self) -> int:

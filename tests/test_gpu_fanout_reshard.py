@@ -19,7 +19,7 @@ def _spans(torch, tensors):
 @pytest.mark.parametrize("engine", ["vector", "bulk"])
 def test_fanout_single_gpu_loopback(engine, monkeypatch):
     """Root pushes to a 'child' on the same device; then the child's kernel runs
-    and finds every chunk counter already satisfied.  Both copy engines; the ranges
+    and finds every chunk counter already satisfied.  Every engine; the ranges
     whose size is not a multiple of 16 are followed by a range of a thousand pieces,
     so that every CTA of the bulk engine reuses each of its shared-memory stages
     after a piece that took a stage without loading into it."""
@@ -56,7 +56,8 @@ def test_fanout_single_gpu_loopback(engine, monkeypatch):
     ctx.close()
 
 
-def test_fanout_wait_runs_out_cleanly():
+@pytest.mark.parametrize("engine", ["vector", "bulk"])
+def test_fanout_wait_runs_out_cleanly(engine):
     """A node whose parent never delivers: the bounded wait ends, the call
     reports a timeout and the context keeps working."""
     import torch
@@ -68,6 +69,7 @@ def test_fanout_wait_runs_out_cleanly():
     buf = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
     torch.cuda.synchronize()
     node = ctx.fanout(_spans(torch, [buf]), 1 << 16, 0)
+    node.set_engine(engine)
     node.run(False, 50)
     with pytest.raises(MxbTimeout):
         node.wait()
@@ -101,8 +103,9 @@ def test_manifest_matching_rules():
     assert topology("flat", 3, root=1) == [[], [0, 2], []]
 
 
-@pytest.mark.parametrize("kind", ["chain", "tree", "flat"])
-def test_fanout_across_gpus(kind):
+@pytest.mark.parametrize("kind,engine", [("chain", "vector"), ("tree", "vector"), ("flat", "vector"),
+                                         ("chain", "bulk"), ("tree", "bulk")])
+def test_fanout_across_gpus(kind, engine):
     import torch
 
     n = torch.cuda.device_count()
@@ -122,8 +125,14 @@ def test_fanout_across_gpus(kind):
             bufs.append([torch.zeros(s, dtype=torch.uint8, device=f"cuda:{d}") for s in sizes])
     for d in devs:
         torch.cuda.synchronize(d)
-    bc = Broadcast(ctx, devs, [_spans(torch, b) for b in bufs], 1 << 20, kind)
-    bc.run(5000)
+    bc = Broadcast(ctx, devs, [_spans(torch, b) for b in bufs], 1 << 20, kind, engine=engine)
+    for _ in range(2):
+        for b in bufs[1:]:
+            for t in b:
+                t.zero_()
+        for d in devs:
+            torch.cuda.synchronize(d)
+        bc.run(5000)
     for b in bufs[1:]:
         for s, t in zip(bufs[0], b):
             assert torch.equal(s.cpu(), t.cpu())
