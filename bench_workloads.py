@@ -830,7 +830,8 @@ def run_vllm(args):
 def run_convert(args):
     """The box-convert kernel on the parameter list of a Llama-3-8B-shaped model (every 2-D
     weight and the norms): cast fp32 -> bf16 (a trainer that serves fp32 masters), transposed
-    bf16 (weights stored transposed) and both at once, one launch per case; beside each the
+    bf16 (weights stored transposed) and both at once, one launch per case (every case holds one
+    pair of dtypes); beside each the
     per-tensor ``dst.copy_(src)`` loop the reference leaves to torch (receiver.py:964-971).
     Every case is compared bit for bit with torch's result before it is timed."""
     import torch

@@ -389,8 +389,8 @@ typedef struct {
     int64_t dst_stride[MXB_MAX_DIMS]; /* destination elements, >= 0 */
 } mxb_convert;
 
-/* One launch over `n` boxes on the context's stream of `dev`; waits unless
- * MXB_SCATTER_NO_SYNC.  Casts round to nearest even like torch's device copy.
+/* All `n` boxes on the context's stream of `dev`, one launch per conversion
+ * (pair of kinds) present in the list; waits unless MXB_SCATTER_NO_SYNC.  Casts round to nearest even like torch's device copy.
  * *bytes_out (optional) = bytes read + written.  MXB_ERR_UNSUPPORTED for a pair
  * of kinds outside the table above or a box that needs more than four dims after
  * merging; MXB_ERR_ALIGN for an address not aligned to its element. */

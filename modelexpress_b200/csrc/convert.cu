@@ -12,7 +12,7 @@
 //              read along the source's inner dim, turned in shared memory, written along the
 //              destination's inner dim (element pairs when both sides allow 4-byte accesses).
 // HBM-bound: one read of the source element and one write of the destination element, nothing
-// else.  Casts use the conversions torch's own device code uses (__float2bfloat16_rn,
+// else.  One launch per conversion present in the list.  Casts use the conversions torch's own device code uses (__float2bfloat16_rn,
 // __float2half_rn, widening by bit placement), so results equal torch's bit for bit.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -32,7 +32,7 @@ struct CvtItem {
     uint32_t n[4];     // canonical extents, n[3] = the source's inner dim
     int64_t ds[4];     // destination strides (elements)
     uint64_t tile0;    // first tile of this item
-    uint32_t mode;     // 0 rows, 1 transpose
+    uint32_t mode;     // 0 rows, 1 transpose (64 x 64), 2 transpose, wide accesses
     uint32_t bdim;     // transpose: the dim the destination walks with stride 1
     uint32_t pair;     // pair (4-byte / 8-byte) accesses allowed on both sides
     uint32_t kind;     // conversion, see CvtKind
@@ -155,11 +155,16 @@ __device__ void rows_tile(const CvtItem &it, uint64_t t, unsigned char *) {
         dbase[(int64_t)i * step] = Cast<S, D>::run(s[i]);
 }
 
-template <typename S, typename D>
-__device__ void transpose_tile(const CvtItem &it, uint64_t t, unsigned char *smem_raw) {
-    using SE = typename S::store;
-    using DE = typename D::store;
-    DE(*tile)[kTT + 1] = reinterpret_cast<DE(*)[kTT + 1]>(smem_raw);
+// Where tile t of a transposed item lies: `edge_a` x `edge_b` elements along the source's
+// inner dim (a) and the destination's unit-stride dim (b).
+struct TileAt {
+    uint64_t src_elem;   // source element of the tile's corner
+    int64_t dst_elem;    // destination element of the tile's corner
+    uint64_t sstride_b;  // source elements between consecutive b
+    uint32_t na, nb;     // valid extent of this tile
+};
+
+__device__ __forceinline__ TileAt tile_at(const CvtItem &it, uint64_t t, uint32_t edge_a, uint32_t edge_b) {
     const uint32_t b = it.bdim;
     const uint32_t ta = (uint32_t)(t % it.tiles_a);
     t /= it.tiles_a;
@@ -172,9 +177,10 @@ __device__ void transpose_tile(const CvtItem &it, uint64_t t, unsigned char *sme
         idx[d] = (uint32_t)(rest % it.n[d]);
         rest /= it.n[d];
     }
-    const uint32_t a0 = ta * kTT, b0 = tb * kTT;
-    const uint32_t na = min(kTT, it.n[3] - a0), nb = min(kTT, it.n[b] - b0);
-    // source element (idx with idx[b] = b0 + j, a0 + i)
+    const uint32_t a0 = ta * edge_a, b0 = tb * edge_b;
+    TileAt at;
+    at.na = min(edge_a, it.n[3] - a0);
+    at.nb = min(edge_b, it.n[b] - b0);
     uint64_t srow = 0;
     int64_t doff = 0;
     for (int d = 0; d < 3; ++d) {
@@ -182,10 +188,84 @@ __device__ void transpose_tile(const CvtItem &it, uint64_t t, unsigned char *sme
         srow = srow * it.n[d] + v;
         doff += (int64_t)v * it.ds[d];
     }
-    uint64_t sstride_b = it.n[3];  // elements between consecutive b in the source
-    for (uint32_t d = b + 1; d < 3; ++d) sstride_b *= it.n[d];
-    const SE *s = reinterpret_cast<const SE *>(it.src) + srow * it.n[3] + a0;
-    DE *dp = reinterpret_cast<DE *>(it.dst) + doff + (int64_t)a0 * it.ds[3];
+    at.sstride_b = it.n[3];
+    for (uint32_t d = b + 1; d < 3; ++d) at.sstride_b *= it.n[d];
+    at.src_elem = srow * it.n[3] + a0;
+    at.dst_elem = doff + (int64_t)a0 * it.ds[3];
+    return at;
+}
+
+// Elements a lane moves per access in the wide transposed path: 8 bytes (4 for one-byte elements)
+template <typename E>
+struct Group {
+    static constexpr int n = sizeof(E) >= 4 ? 8 / sizeof(E) : 4;
+};
+
+// Transposed tile, wide: every lane reads Group<source> elements along the source's inner dim
+// and writes Group<destination> elements along the destination's, eight rows in flight per
+// warp.  The host selects it only when every such group is naturally aligned on both sides.
+template <typename S, typename D>
+__device__ void wide_tile(const CvtItem &it, uint64_t t, unsigned char *smem_raw) {
+    using SE = typename S::store;
+    using DE = typename D::store;
+    constexpr int GS = Group<SE>::n, GD = Group<DE>::n;
+    constexpr uint32_t TA = 32 * GS, TB = 32 * GD;
+    using SG = typename Bytes<GS * sizeof(SE)>::type;
+    using DG = typename Bytes<GD * sizeof(DE)>::type;
+    DE(*tile)[TA + 1] = reinterpret_cast<DE(*)[TA + 1]>(smem_raw);
+    const TileAt at = tile_at(it, t, TA, TB);
+    const SE *s = reinterpret_cast<const SE *>(it.src) + at.src_elem;
+    DE *dp = reinterpret_cast<DE *>(it.dst) + at.dst_elem;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr uint32_t kWarps = kCvtThreads / 32;
+    constexpr int kBatch = 8;
+    const bool lane_a = GS * lane < at.na, lane_b = GD * lane < at.nb;
+#pragma unroll 1
+    for (uint32_t j0 = 0; j0 < at.nb; j0 += kBatch * kWarps) {
+        SG in[kBatch];
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+            const uint32_t j = j0 + warp + k * kWarps;
+            if (lane_a && j < at.nb) in[k] = *reinterpret_cast<const SG *>(s + (uint64_t)j * at.sstride_b + GS * lane);
+        }
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+            const uint32_t j = j0 + warp + k * kWarps;
+            if (lane_a && j < at.nb) {
+                union { SG v; SE e[GS]; } a;
+                a.v = in[k];
+#pragma unroll
+                for (int g = 0; g < GS; ++g) tile[j][GS * lane + g] = Cast<S, D>::run(a.e[g]);
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll 1
+    for (uint32_t i0 = 0; i0 < at.na; i0 += kBatch * kWarps) {
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+            const uint32_t i = i0 + warp + k * kWarps;
+            if (lane_b && i < at.na) {
+                union { DG v; DE e[GD]; } o;
+#pragma unroll
+                for (int g = 0; g < GD; ++g) o.e[g] = tile[GD * lane + g][i];
+                *reinterpret_cast<DG *>(dp + (int64_t)i * it.ds[3] + GD * lane) = o.v;
+            }
+        }
+    }
+    __syncthreads();  // the tile is reused by this CTA's next tile
+}
+
+template <typename S, typename D>
+__device__ void transpose_tile(const CvtItem &it, uint64_t t, unsigned char *smem_raw) {
+    using SE = typename S::store;
+    using DE = typename D::store;
+    DE(*tile)[kTT + 1] = reinterpret_cast<DE(*)[kTT + 1]>(smem_raw);
+    const TileAt at = tile_at(it, t, kTT, kTT);
+    const uint32_t na = at.na, nb = at.nb;
+    const uint64_t sstride_b = at.sstride_b;
+    const SE *s = reinterpret_cast<const SE *>(it.src) + at.src_elem;
+    DE *dp = reinterpret_cast<DE *>(it.dst) + at.dst_elem;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr uint32_t kWarps = kCvtThreads / 32;
     if constexpr (sizeof(SE) <= 4 && sizeof(DE) <= 4) {
@@ -257,12 +337,19 @@ __device__ void transpose_tile(const CvtItem &it, uint64_t t, unsigned char *sme
 template <typename S, typename D>
 __device__ __forceinline__ void one_tile(const CvtItem &it, uint64_t t, unsigned char *smem) {
     if (it.mode == 0) rows_tile<S, D>(it, t, smem);
+    else if (it.mode == 2) wide_tile<S, D>(it, t, smem);
     else transpose_tile<S, D>(it, t, smem);
 }
 
-__global__ void __launch_bounds__(kCvtThreads) convert_kernel(const CvtItem *__restrict__ items,
+// One instantiation per conversion: a single kernel switching over all of them needs the
+// registers of every case at once (243 per thread against 48-77 for any one of them).
+template <typename S, typename D>
+__global__ void __launch_bounds__(kCvtThreads, 4) convert_kernel(const CvtItem *__restrict__ items,
                                                              uint32_t n_items, uint64_t n_tiles) {
-    __shared__ __align__(16) unsigned char smem[kTT * (kTT + 1) * 8];
+    constexpr uint32_t kElem = sizeof(typename D::store);
+    constexpr uint32_t kEdgeA = 32 * Group<typename S::store>::n, kEdgeB = 32 * Group<typename D::store>::n;
+    constexpr uint32_t kWide = kEdgeB * (kEdgeA + 1) * kElem, kPlain = kTT * (kTT + 1) * kElem;
+    __shared__ __align__(16) unsigned char smem[kWide > kPlain ? kWide : kPlain];
     __shared__ CvtItem cur;
     __shared__ uint32_t cur_index;
     if (threadIdx.x == 0) cur_index = 0xffffffffu;
@@ -288,21 +375,38 @@ __global__ void __launch_bounds__(kCvtThreads) convert_kernel(const CvtItem *__r
             if (threadIdx.x == 0) cur_index = lo;
             __syncthreads();
         }
-        const uint64_t local = t - cur.tile0;
-        switch (cur.kind) {
-            case kRaw1: one_tile<Raw<uint8_t>, Raw<uint8_t>>(cur, local, smem); break;
-            case kRaw2: one_tile<Raw<uint16_t>, Raw<uint16_t>>(cur, local, smem); break;
-            case kRaw4: one_tile<Raw<uint32_t>, Raw<uint32_t>>(cur, local, smem); break;
-            case kRaw8: one_tile<Raw<uint64_t>, Raw<uint64_t>>(cur, local, smem); break;
-            case kBf16ToF32: one_tile<BF16, F32>(cur, local, smem); break;
-            case kF16ToF32: one_tile<F16, F32>(cur, local, smem); break;
-            case kF32ToBf16: one_tile<F32, BF16>(cur, local, smem); break;
-            case kF32ToF16: one_tile<F32, F16>(cur, local, smem); break;
-            case kBf16ToF16: one_tile<BF16, F16>(cur, local, smem); break;
-            case kF16ToBf16: one_tile<F16, BF16>(cur, local, smem); break;
-            default: break;
-        }
+        one_tile<S, D>(cur, t - cur.tile0, smem);
         __syncthreads();  // `cur` may be replaced for the next tile
+    }
+}
+
+template <typename S, typename D>
+cudaError_t launch_convert(const CvtItem *items, uint32_t n_items, uint64_t tiles, int sm_count,
+                           cudaStream_t stream) {
+    // as many resident CTAs per SM as registers and shared memory allow
+    int per_sm = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, convert_kernel<S, D>, kCvtThreads, 0);
+    if (e != cudaSuccess) return e;
+    uint64_t grid = (uint64_t)sm_count * (per_sm > 0 ? per_sm : 1);
+    if (grid > tiles) grid = tiles;
+    convert_kernel<S, D><<<(unsigned)grid, kCvtThreads, 0, stream>>>(items, n_items, tiles);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_kind(uint32_t kind, const CvtItem *items, uint32_t n_items, uint64_t tiles, int sm_count,
+                        cudaStream_t stream) {
+    switch (kind) {
+        case kRaw1: return launch_convert<Raw<uint8_t>, Raw<uint8_t>>(items, n_items, tiles, sm_count, stream);
+        case kRaw2: return launch_convert<Raw<uint16_t>, Raw<uint16_t>>(items, n_items, tiles, sm_count, stream);
+        case kRaw4: return launch_convert<Raw<uint32_t>, Raw<uint32_t>>(items, n_items, tiles, sm_count, stream);
+        case kRaw8: return launch_convert<Raw<uint64_t>, Raw<uint64_t>>(items, n_items, tiles, sm_count, stream);
+        case kBf16ToF32: return launch_convert<BF16, F32>(items, n_items, tiles, sm_count, stream);
+        case kF16ToF32: return launch_convert<F16, F32>(items, n_items, tiles, sm_count, stream);
+        case kF32ToBf16: return launch_convert<F32, BF16>(items, n_items, tiles, sm_count, stream);
+        case kF32ToF16: return launch_convert<F32, F16>(items, n_items, tiles, sm_count, stream);
+        case kBf16ToF16: return launch_convert<BF16, F16>(items, n_items, tiles, sm_count, stream);
+        case kF16ToBf16: return launch_convert<F16, BF16>(items, n_items, tiles, sm_count, stream);
+        default: return cudaErrorInvalidValue;
     }
 }
 
@@ -384,8 +488,16 @@ int32_t canonical(const mxb_convert &c, CvtItem *out, uint64_t *bytes) {
     } else {
         out->mode = 1;
         const uint32_t b = out->bdim;
-        out->tiles_a = (out->n[3] + kTT - 1) / kTT;
-        out->tiles_b = (out->n[b] + kTT - 1) / kTT;
+        // wide accesses: groups of 8 bytes (4 for one-byte elements) naturally aligned on both sides
+        const uint32_t gs = ssz >= 4 ? 8 / ssz : 4, gd = dsz >= 4 ? 8 / dsz : 4;
+        bool wide = ssz < 8 && dsz < 8 && out->n[3] % gs == 0 && out->n[b] % gd == 0 &&
+                    c.src % (gs * ssz) == 0 && c.dst % (gd * dsz) == 0;
+        for (uint32_t d = 0; d < 4 && wide; ++d)
+            if (d != b && out->n[d] > 1 && out->ds[d] % gd) wide = false;
+        const uint32_t edge_a = wide ? 32 * gs : kTT, edge_b = wide ? 32 * gd : kTT;
+        if (wide) out->mode = 2;
+        out->tiles_a = (out->n[3] + edge_a - 1) / edge_a;
+        out->tiles_b = (out->n[b] + edge_b - 1) / edge_b;
         tiles = (uint64_t)out->tiles_a * out->tiles_b;
         for (uint32_t d = 0; d < 3; ++d)
             if (d != b) tiles *= out->n[d];
@@ -414,9 +526,11 @@ extern "C" int32_t mxb_convert_boxes(mxb_ctx *ctx, int32_t dev, const mxb_conver
         set_error("device %d is not part of this context", dev);
         return MXB_ERR_ARG;
     }
-    std::vector<CvtItem> table;
-    table.reserve(n);
-    uint64_t tiles = 0, bytes = 0;
+    // boxes grouped by conversion: one launch per conversion present (usually one or two)
+    std::vector<CvtItem> groups[kKinds];
+    uint64_t group_tiles[kKinds] = {};
+    uint64_t bytes = 0;
+    size_t live = 0;
     for (uint64_t i = 0; i < n; ++i) {
         CvtItem it;
         uint64_t b = 0;
@@ -431,28 +545,36 @@ extern "C" int32_t mxb_convert_boxes(mxb_ctx *ctx, int32_t dev, const mxb_conver
         bytes += b;
         const uint64_t count = it.tile0;
         if (!count) continue;
-        it.tile0 = tiles;
+        it.tile0 = group_tiles[it.kind];
         it.n_tiles = count;
-        tiles += count;
-        table.push_back(it);
+        group_tiles[it.kind] += count;
+        groups[it.kind].push_back(it);
+        ++live;
     }
     if (bytes_out) *bytes_out = bytes;
-    if (table.empty()) return MXB_OK;
+    if (!live) return MXB_OK;
     DeviceGuard g(dev);
     std::lock_guard<std::mutex> lk(*d->mu);
-    const size_t table_bytes = table.size() * sizeof(CvtItem);
+    const size_t table_bytes = live * sizeof(CvtItem);
     int32_t rc = ensure_table(d, table_bytes);
     if (rc != MXB_OK) return rc;
     MXB_CUDA(cudaStreamSynchronize(d->stream));  // the pinned staging copy is shared by every call
     d->table_tag = 0;
-    memcpy(d->table_host, table.data(), table_bytes);
+    CvtItem *host = reinterpret_cast<CvtItem *>(d->table_host);
+    size_t at = 0;
+    for (uint32_t k = 0; k < kKinds; ++k) {
+        memcpy(host + at, groups[k].data(), groups[k].size() * sizeof(CvtItem));
+        at += groups[k].size();
+    }
     MXB_CUDA(cudaMemcpyAsync(d->table, d->table_host, table_bytes, cudaMemcpyHostToDevice, d->stream));
-    uint64_t grid = (uint64_t)d->sm_count * 4;  // 64 registers x 256 threads: four resident CTAs per SM
-    if (grid > tiles) grid = tiles;
-    convert_kernel<<<(unsigned)grid, kCvtThreads, 0, d->stream>>>(
-        reinterpret_cast<const CvtItem *>(d->table), (uint32_t)table.size(), tiles);
-    MXB_CUDA(cudaGetLastError());
-    ctx->launches.fetch_add(1);
+    at = 0;
+    for (uint32_t k = 0; k < kKinds; ++k) {
+        if (groups[k].empty()) continue;
+        MXB_CUDA(launch_kind(k, reinterpret_cast<const CvtItem *>(d->table) + at, (uint32_t)groups[k].size(),
+                             group_tiles[k], d->sm_count, d->stream));
+        at += groups[k].size();
+        ctx->launches.fetch_add(1);
+    }
     if (flags & MXB_SCATTER_NO_SYNC) return MXB_OK;
     return check_status(d);
 }

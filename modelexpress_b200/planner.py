@@ -489,8 +489,8 @@ def convert_box(c, staging_ptr: int, param) -> tuple | None:
 
 def apply_converts(converts, staging, params: dict, ctx=None) -> None:
     """Cast (and, for staged boxes, transpose) the staged sources into their parameters
-    (receiver.py:964-971).  On the GPU all of them go through one launch of the box-convert
-    kernel; a pair of dtypes outside its table (and host tensors, which only the planner's own
+    (receiver.py:964-971).  On the GPU all of them go through one call of the box-convert
+    kernel (one launch per pair of dtypes present); a pair of dtypes outside its table (and host tensors, which only the planner's own
     tests use) takes torch's strided copy."""
     import torch
 

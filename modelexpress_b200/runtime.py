@@ -146,7 +146,7 @@ class Context:
         """boxes: iterable of (src, dst, extents, dst_strides, src_kind, dst_kind, elem_bytes), or
         what ``convert_array`` returned: each contiguous staged box lands with the destination's
         strides (in elements), cast when the kinds ("raw", "f32", "f16", "bf16") differ.
-        One launch; returns bytes read + written."""
+        One launch per pair of kinds present; returns bytes read + written."""
         prepared = isinstance(boxes, tuple) and len(boxes) == 2 and isinstance(boxes[0], ctypes.Array)
         arr, n = boxes if prepared else self.convert_array(boxes)
         moved = ctypes.c_uint64(0)
