@@ -842,7 +842,7 @@ def run_convert(args):
     rank, world, local = _dist()
     ctx = Context([local])
     layers = _env_int("MXB_CONVERT_LAYERS", 8)
-    cfg = synth.scaled(synth.LLAMA3_8B, layers=layers)
+    cfg = synth.scaled(synth.LLAMA3_8B, layers=layers, vocab=_env_int("MXB_CONVERT_VOCAB", synth.LLAMA3_8B.vocab))
     shapes = [tuple(s) for _n, s, _d, _k in synth.dense_tensors(cfg)]
     elems = sum(int(torch.Size(s).numel()) for s in shapes)
     g = torch.Generator(device="cuda")
