@@ -120,6 +120,37 @@ def test_transposed_casts_and_higher_ranks():
     ctx.close()
 
 
+def test_kernel_matches_the_oracle():
+    """Through the C ABI against the CPU restatement (oracle.ref_port.box_convert): a permuted
+    rank-3 box of two-byte elements and a transposed fp32 -> bf16 window of a wider parameter."""
+    import torch
+
+    from oracle import ref_port as R
+
+    ctx = _ctx()
+    rng = np.random.default_rng(12)
+    shape = (5, 70, 130)
+    src = rng.integers(0, 1 << 15, size=int(np.prod(shape)), dtype=np.int16)
+    strides = [70, 1, 5 * 70]                       # destination laid out [130, 5, 70]
+    want = np.zeros(src.size, dtype=np.int16)
+    R.box_convert(src, shape, strides, want)
+    d_src = torch.from_numpy(src).cuda()
+    d_dst = torch.zeros(src.size, dtype=torch.int16, device="cuda")
+    torch.cuda.synchronize()
+    ctx.convert_boxes([(d_src.data_ptr(), d_dst.data_ptr(), list(shape), strides, "raw", "raw", 2)], 0)
+    assert np.array_equal(d_dst.cpu().numpy(), want)
+    m, n = 300, 516
+    x = rng.standard_normal(m * n).astype(np.float32)
+    want = np.zeros(n * (m + 4), dtype=np.uint16)
+    R.box_convert(x, (m, n), (1, m + 4), want, dst_offset=4, cast=R.f32_to_bf16_bits)
+    d_x = torch.from_numpy(x).cuda()
+    d_out = torch.zeros(n * (m + 4), dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize()
+    ctx.convert_boxes([(d_x.data_ptr(), d_out.data_ptr() + 8, [m, n], [1, m + 4], "f32", "bf16", 4)], 0)
+    assert np.array_equal(d_out.view(torch.int16).cpu().numpy().view(np.uint16), want)
+    ctx.close()
+
+
 def test_many_boxes_one_call_and_rejections():
     import torch
 
