@@ -256,6 +256,73 @@ __device__ void wide_tile(const CvtItem &it, uint64_t t, unsigned char *smem_raw
     __syncthreads();  // the tile is reused by this CTA's next tile
 }
 
+// Transposed tile for two-byte destinations, packed: shared memory holds 32-bit words of two
+// elements that are neighbours along the destination's inner dim (source rows 2p and 2p+1, same
+// column), so neither phase touches shared memory in two-byte units.  A warp loads a pair of
+// source rows (8 bytes per lane from each), zips them into words and stores word g of every lane
+// at column g*32 + lane (conflict-free); on the way out lane l fetches the words of row pairs l
+// and l + 32 at one column (conflict-free with the odd pitch) and writes 4 bytes each, 128
+// contiguous bytes per warp instruction.  Same tile shape and alignment rules as wide_tile.
+template <typename S, typename D>
+__device__ void packed_tile(const CvtItem &it, uint64_t t, unsigned char *smem_raw) {
+    using SE = typename S::store;
+    using DE = typename D::store;
+    static_assert(sizeof(DE) == 2, "packed tiles hold two-byte destination elements");
+    constexpr int GS = Group<SE>::n;
+    constexpr uint32_t TA = 32 * GS, TB = 128, kPairs = TB / 2;
+    using SG = typename Bytes<GS * sizeof(SE)>::type;
+    uint32_t(*words)[TA + 1] = reinterpret_cast<uint32_t(*)[TA + 1]>(smem_raw);
+    const TileAt at = tile_at(it, t, TA, TB);
+    const SE *s = reinterpret_cast<const SE *>(it.src) + at.src_elem;
+    DE *dp = reinterpret_cast<DE *>(it.dst) + at.dst_elem;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr uint32_t kWarps = kCvtThreads / 32;
+    constexpr int kBatch = 4;   // row pairs in flight per warp: eight 8-byte loads per lane
+    const bool lane_a = GS * lane < at.na;
+    const uint32_t pairs = at.nb / 2;  // nb is a multiple of 4 here
+#pragma unroll 1
+    for (uint32_t p0 = 0; p0 < pairs; p0 += kBatch * kWarps) {
+        SG in0[kBatch], in1[kBatch];
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+            const uint32_t p = p0 + warp + k * kWarps;
+            if (lane_a && p < pairs) {
+                const SE *row = s + (uint64_t)(2 * p) * at.sstride_b + GS * lane;
+                in0[k] = *reinterpret_cast<const SG *>(row);
+                in1[k] = *reinterpret_cast<const SG *>(row + at.sstride_b);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+            const uint32_t p = p0 + warp + k * kWarps;
+            if (lane_a && p < pairs) {
+                union { SG v; SE e[GS]; } a, b;
+                a.v = in0[k];
+                b.v = in1[k];
+#pragma unroll
+                for (int g = 0; g < GS; ++g)
+                    words[p][g * 32 + lane] = (uint32_t)Cast<S, D>::run(a.e[g]) |
+                                              ((uint32_t)Cast<S, D>::run(b.e[g]) << 16);
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll 1
+    for (uint32_t i0 = 0; i0 < at.na; i0 += 8 * kWarps) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t i = i0 + warp + k * kWarps;
+            if (i < at.na) {
+                const uint32_t col = (i % GS) * 32 + i / GS;   // where the load phase put column i
+                uint32_t *out = reinterpret_cast<uint32_t *>(dp + (int64_t)i * it.ds[3]);
+                if (lane < pairs) out[lane] = words[lane][col];
+                if (lane + 32 < pairs) out[lane + 32] = words[lane + 32][col];
+            }
+        }
+    }
+    __syncthreads();  // the tile is reused by this CTA's next tile
+}
+
 template <typename S, typename D>
 __device__ void transpose_tile(const CvtItem &it, uint64_t t, unsigned char *smem_raw) {
     using SE = typename S::store;
@@ -337,7 +404,11 @@ __device__ void transpose_tile(const CvtItem &it, uint64_t t, unsigned char *sme
 template <typename S, typename D>
 __device__ __forceinline__ void one_tile(const CvtItem &it, uint64_t t, unsigned char *smem) {
     if (it.mode == 0) rows_tile<S, D>(it, t, smem);
-    else if (it.mode == 2) wide_tile<S, D>(it, t, smem);
+    else if (it.mode == 2) {
+        if constexpr (sizeof(typename D::store) == 2 && sizeof(typename S::store) >= 2 &&
+                      sizeof(typename S::store) <= 4) packed_tile<S, D>(it, t, smem);
+        else wide_tile<S, D>(it, t, smem);
+    }
     else transpose_tile<S, D>(it, t, smem);
 }
 

@@ -53,7 +53,7 @@ def test_noalloc_digest_matches_the_allocating_entry_point():
         rc2 = lib.mxb_digest_noalloc(0, arr, n, 2, out2, ctypes.c_void_p(s.cuda_stream))
         free_after = torch.cuda.mem_get_info(0)[0]
         assert rc == 0 and rc2 == 0, lib.mxb_last_error()
-        if call == 1:   # round 0 loaded the kernels; from here on the device's free memory must not move
+        if call == 1:   # the first call loaded the kernels; from here on the device's free memory must not move
             assert free_after == free_before, (free_before, free_after)
         for i in range(n):
             assert _records_equal(out[i], want[i]), (call, i, sizes[i] if i < len(sizes) else "view")
