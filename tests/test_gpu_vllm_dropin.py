@@ -217,3 +217,74 @@ def test_place_captured_loads_a_vllm_moe_model_with_no_layout_rules(tmp_path):
             assert torch.equal(params[n].detach().view(torch.uint8), t.view(torch.uint8)), n
     finally:
         ctx.__exit__(None, None, None)
+
+
+GPT2_CFG = {"architectures": ["GPT2LMHeadModel"], "model_type": "gpt2", "n_embd": 256, "n_head": 8,
+            "n_layer": 2, "n_positions": 512, "n_inner": 1024, "vocab_size": 1024,
+            "layer_norm_epsilon": 1e-5, "activation_function": "gelu_new", "tie_word_embeddings": True,
+            "torch_dtype": "bfloat16", "bos_token_id": 1, "eos_token_id": 2}
+
+
+def _gpt2_tensors():
+    """Conv1D weights are stored (in, out); vLLM's loader transposes them on the way in."""
+    out = [("wte.weight", (1024, 256), "BF16", "matrix"), ("wpe.weight", (512, 256), "BF16", "matrix")]
+    for i in range(2):
+        p = f"h.{i}."
+        out += [(p + "ln_1.weight", (256,), "BF16", "matrix"), (p + "ln_1.bias", (256,), "BF16", "matrix"),
+                (p + "attn.c_attn.weight", (256, 768), "BF16", "matrix"),
+                (p + "attn.c_attn.bias", (768,), "BF16", "matrix"),
+                (p + "attn.c_proj.weight", (256, 256), "BF16", "matrix"),
+                (p + "attn.c_proj.bias", (256,), "BF16", "matrix"),
+                (p + "ln_2.weight", (256,), "BF16", "matrix"), (p + "ln_2.bias", (256,), "BF16", "matrix"),
+                (p + "mlp.c_fc.weight", (256, 1024), "BF16", "matrix"),
+                (p + "mlp.c_fc.bias", (1024,), "BF16", "matrix"),
+                (p + "mlp.c_proj.weight", (1024, 256), "BF16", "matrix"),
+                (p + "mlp.c_proj.bias", (256,), "BF16", "matrix")]
+    return out + [("ln_f.weight", (256,), "BF16", "matrix"), ("ln_f.bias", (256,), "BF16", "matrix")]
+
+
+def test_transposed_checkpoint_weights_go_through_the_convert_kernel(tmp_path):
+    """vLLM's ``GPT2LMHeadModel`` on the GPU: its loader transposes every Conv1D weight.  The
+    capture stages those sources as the boxes they read, the box-convert kernel turns them, and
+    every parameter equals what vLLM's own ``load_weights`` produces; nothing is left to it."""
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from modelexpress_b200 import synth
+    from modelexpress_b200.loader import place_captured
+    from modelexpress_b200.runtime import default_context
+
+    d = str(tmp_path)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(GPT2_CFG, f)
+    synth.write_checkpoint(d, _gpt2_tensors(), 44, 2)
+    try:
+        model, ctx, vc, mc = _build_vllm_model(d)
+    except Exception as e:
+        pytest.skip(f"vLLM could not build a GPT-2 model here: {type(e).__name__}: {e}")
+    try:
+        from safetensors import safe_open
+
+        weights = []
+        for fn in sorted(os.listdir(d)):
+            if fn.endswith(".safetensors"):
+                with safe_open(os.path.join(d, fn), framework="pt", device="cpu") as f:
+                    weights += [(k, f.get_tensor(k)) for k in f.keys()]
+        model.load_weights(iter(weights))
+        torch.cuda.synchronize()
+        params = dict(model.named_parameters())
+        truth = {n: p.detach().clone() for n, p in params.items()}
+        for p in params.values():
+            p.data.zero_()
+        torch.cuda.synchronize()
+        before = default_context(0).launch_count
+        got = place_captured(model, d, "cuda:0", ring_bytes=16 << 20, ring_slots=4, host_threads=2)
+        assert got.engine_loaded == [], got.reasons
+        turned = [n for n in got.converted if n.endswith(("c_attn.weight", "c_proj.weight", "c_fc.weight"))]
+        assert len(turned) >= 8, got.converted       # four Conv1D weights per layer
+        assert default_context(0).launch_count > before
+        for n, t in truth.items():
+            assert torch.equal(params[n].detach().view(torch.uint8), t.view(torch.uint8)), n
+    finally:
+        ctx.__exit__(None, None, None)
