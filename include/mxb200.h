@@ -21,6 +21,7 @@
 
 #include <stddef.h>
 #include <stdint.h>
+#include <sys/types.h> /* ssize_t: the torch allocator entry points */
 
 #ifdef __cplusplus
 extern "C" {
@@ -141,6 +142,56 @@ int32_t mxb_clear_extents(mxb_ctx *ctx);
 int32_t mxb_ipc_export(uint64_t ptr, uint8_t handle[64], uint64_t *offset);
 int32_t mxb_ipc_open(const uint8_t handle[64], uint64_t offset, uint64_t *out_ptr);
 int32_t mxb_ipc_close(uint64_t ptr, uint64_t offset);
+
+/* ---- device arena on CUDA virtual memory management --------------------- */
+
+/* One reserved address range per arena; every allocation is one physical block
+ * mapped at the next free offset (never reused).  Another process on the box
+ * imports the blocks at the same offsets of a range of its own, so that an
+ * address there is `its base + the same offset`: a whole model crosses the
+ * process boundary as one layout instead of one IPC handle per allocation.
+ * Lifecycle and names follow the reference's VmmArena (vmm/arena.py:155-350;
+ * backend calls vmm/backend.py); what the reference registers with its NIC
+ * once per load (arena.py:322-330, `registered_range`) is here exported to
+ * NVLink peers.  Process-wide, no context needed. */
+typedef struct mxb_arena mxb_arena;
+typedef struct {
+    uint64_t offset; /* from the arena's base; a multiple of the granularity */
+    uint64_t size;   /* a multiple of the granularity */
+} mxb_arena_block;
+
+/* Reserve `reserve_bytes` of address space for device `dev` (no memory yet). */
+int32_t mxb_arena_create(int32_t dev, uint64_t reserve_bytes, mxb_arena **out);
+/* One new block of at least `nbytes` (rounded up to the granularity), mapped
+ * read/write for the arena's device.  MXB_ERR_NOMEM when the range or the
+ * device is exhausted. */
+int32_t mxb_arena_malloc(mxb_arena *a, uint64_t nbytes, uint64_t *out_ptr);
+/* `ptr` as returned by mxb_arena_malloc: unmaps and releases that block. */
+int32_t mxb_arena_free(mxb_arena *a, uint64_t ptr);
+/* Base address, bytes bumped through so far and bytes reserved. */
+int32_t mxb_arena_range(mxb_arena *a, uint64_t *base, uint64_t *used, uint64_t *span);
+/* The live blocks in address order; *n_out = how many there are
+ * (MXB_ERR_NOMEM if `cap` is smaller). */
+int32_t mxb_arena_blocks(mxb_arena *a, mxb_arena_block *out, uint64_t cap, uint64_t *n_out);
+/* A POSIX file descriptor naming the block at `offset` (send it over a unix
+ * socket with SCM_RIGHTS; the caller closes its copy). */
+int32_t mxb_arena_export_fd(mxb_arena *a, uint64_t offset, int32_t *fd_out);
+/* Map another process's blocks (descriptors received from it) at the same
+ * offsets of a fresh range of `span` bytes, read/write for device `dev`
+ * (MXB_ERR_PEER if `dev` has no peer access to the blocks' device).  The
+ * result answers mxb_arena_range / mxb_arena_blocks / mxb_arena_destroy only. */
+int32_t mxb_arena_import(int32_t dev, uint64_t span, const mxb_arena_block *blocks, const int32_t *fds,
+                         uint64_t n, mxb_arena **out);
+/* Unmaps and releases every block and the range.  No tensor or kernel may
+ * still use the addresses. */
+int32_t mxb_arena_destroy(mxb_arena *a);
+/* Entry points for torch.cuda.CUDAPluggableAllocator(path, "mxb_arena_torch_malloc",
+ * "mxb_arena_torch_free"): memory for a device comes from the arena that
+ * mxb_arena_set_default named for it (NULL: none; allocations then fail), as
+ * vmm/hook.py:82-109 routes torch's calls into the reference's arena. */
+int32_t mxb_arena_set_default(int32_t dev, mxb_arena *a);
+void *mxb_arena_torch_malloc(ssize_t size, int device, void *stream);
+void mxb_arena_torch_free(void *ptr, ssize_t size, int device, void *stream);
 
 /* ---- descriptor compiler (host) ---------------------------------------- */
 

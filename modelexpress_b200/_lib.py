@@ -66,6 +66,10 @@ class ConvertBox(ctypes.Structure):
                 ("elem_bytes", u32), ("extent", u64 * MAX_DIMS), ("dst_stride", i64 * MAX_DIMS)]
 
 
+class ArenaBlock(ctypes.Structure):
+    _fields_ = [("offset", u64), ("size", u64)]
+
+
 class PlaceStats(ctypes.Structure):
     _fields_ = [("bytes_placed", u64), ("chunks", u64), ("launches", u64),
                 ("seconds_total", ctypes.c_double), ("seconds_gather", ctypes.c_double),
@@ -118,6 +122,17 @@ SIGNATURES = {
     "mxb_digest": (i32, [_vp, i32, _P(Span), u64, u32, _P(DigestOut)]),
     "mxb_block_hashes": (i32, [_vp, i32, u64, u64, u64]),
     "mxb_digest_noalloc": (i32, [i32, _P(Span), u64, u32, _P(DigestOut), _vp]),
+    "mxb_arena_create": (i32, [i32, u64, _P(_vp)]),
+    "mxb_arena_malloc": (i32, [_vp, u64, _P(u64)]),
+    "mxb_arena_free": (i32, [_vp, u64]),
+    "mxb_arena_range": (i32, [_vp, _P(u64), _P(u64), _P(u64)]),
+    "mxb_arena_blocks": (i32, [_vp, _P(ArenaBlock), u64, _P(u64)]),
+    "mxb_arena_export_fd": (i32, [_vp, u64, _P(i32)]),
+    "mxb_arena_import": (i32, [i32, u64, _P(ArenaBlock), _P(i32), u64, _P(_vp)]),
+    "mxb_arena_destroy": (i32, [_vp]),
+    "mxb_arena_set_default": (i32, [i32, _vp]),
+    "mxb_arena_torch_malloc": (_vp, [ctypes.c_ssize_t, ctypes.c_int, _vp]),
+    "mxb_arena_torch_free": (None, [_vp, ctypes.c_ssize_t, ctypes.c_int, _vp]),
     "mxb_convert_boxes": (i32, [_vp, i32, _P(ConvertBox), u64, u32, _P(u64)]),
     "mxb_fanout_plan": (i32, [_P(Span), u64, u64, _P(FanoutPiece), u64, _P(u64), _P(u32), u64, _P(u64)]),
     "mxb_fanout_create": (i32, [_vp, i32, _P(Span), u64, u64, _P(_vp)]),

@@ -15,7 +15,7 @@ import sys
 
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
-SOURCES = ["api.cu", "scatter.cu", "digest.cu", "ring.cu", "fanout.cu", "convert.cu", "hostcopy.cpp", "planner.cpp"]
+SOURCES = ["api.cu", "scatter.cu", "digest.cu", "ring.cu", "fanout.cu", "convert.cu", "arena.cu", "hostcopy.cpp", "planner.cpp"]
 HEADERS = ["common.cuh", "bulk.cuh", os.path.join("..", "..", "include", "mxb200.h")]
 LIB = os.path.join(PKG, "libmxb200.so")
 
