@@ -95,6 +95,12 @@ class Arena:
 
     def close(self) -> None:
         if getattr(self, "_h", None):
+            if getattr(self, "_pool", None) is not None:
+                # torch hands back what its pool still caches (through the free entry point)
+                import torch
+
+                self._pool = None
+                torch.cuda.empty_cache()
             self._lib.mxb_arena_destroy(self._h)
             self._h = None
 
@@ -243,12 +249,12 @@ def fetch_arena(path: str, device: int, timeout_s: float = 5.0) -> Arena:
 
 _pool_lock = threading.Lock()
 _allocator = None
-_pools: dict = {}
 
 
-def _mem_pool(device: int):
-    """One pluggable allocator per process, one pool per device; both live as long as the
-    process (torch keeps raw pointers to them)."""
+def _mem_pool(arena: Arena, device: int):
+    """One pluggable allocator per process (torch keeps a raw pointer to it) and one torch
+    memory pool per arena: torch caches what it frees inside a pool, so a pool shared between
+    arenas would hand a later arena's tensors the cached blocks of an earlier one."""
     global _allocator
     import torch
     from torch.cuda.memory import CUDAPluggableAllocator, MemPool
@@ -256,10 +262,10 @@ def _mem_pool(device: int):
     with _pool_lock:
         if _allocator is None:
             _allocator = CUDAPluggableAllocator(_lib.LIB_PATH, "mxb_arena_torch_malloc", "mxb_arena_torch_free")
-        if device not in _pools:
+        if getattr(arena, "_pool", None) is None:
             with torch.cuda.device(device):
-                _pools[device] = MemPool(_allocator.allocator())
-        return _pools[device]
+                arena._pool = MemPool(_allocator.allocator())
+        return arena._pool
 
 
 @contextlib.contextmanager
@@ -270,10 +276,83 @@ def use_arena(arena: Arena, device: int | None = None):
     import torch
 
     dev = arena.device if device is None else int(device)
-    pool = _mem_pool(dev)
+    pool = _mem_pool(arena, dev)
     check(_lib.load().mxb_arena_set_default(dev, arena._h), "mxb_arena_set_default")
     try:
         with torch.cuda.use_mem_pool(pool, device=torch.device("cuda", dev)):
             yield arena
     finally:
         _lib.load().mxb_arena_set_default(dev, None)
+
+
+# ---------------------------------------------------------------------------
+# the arenas of this process that peers may map
+# ---------------------------------------------------------------------------
+
+_published: dict = {}   # socket path -> (Arena, ArenaServer)
+_by_device: dict = {}   # device -> socket path of the arena the last load on it filled
+
+
+def publish_arena(arena: Arena, socket_path: str) -> str:
+    """Serve ``arena`` on ``socket_path``; manifests and requests written by this process from
+    now on name tensors inside it by that path and their offset (``lookup``)."""
+    with _pool_lock:
+        if socket_path in _published:
+            return socket_path
+        _published[socket_path] = (arena, ArenaServer(arena, socket_path))
+    return socket_path
+
+
+def withdraw_arena(socket_path: str) -> None:
+    with _pool_lock:
+        entry = _published.pop(socket_path, None)
+    if entry is not None:
+        entry[1].close()
+
+
+def lookup(ptr: int, nbytes: int):
+    """``(socket path, offset)`` when ``[ptr, ptr + nbytes)`` lies in a published arena."""
+    with _pool_lock:
+        items = list(_published.items())
+    for path, (arena, _server) in items:
+        if arena._h and arena.contains(ptr, max(1, nbytes)):
+            return path, ptr - arena.base
+    return None
+
+
+def _env_on() -> bool:
+    return (os.environ.get("MXB_VMM_ARENA") or os.environ.get("MX_VMM_ARENA") or "0") == "1"
+
+
+@contextlib.contextmanager
+def maybe_enter_arena(device: int, socket_dir: str | None = None):
+    """With ``MXB_VMM_ARENA=1`` (or the reference's ``MX_VMM_ARENA=1``): what the engine
+    allocates inside the block comes out of a fresh arena, which is published for peers once the
+    block has completed (the load envelope of vmm/runtime.py:40-135: a failed body closes the
+    arena; a second load on the device replaces the first arena, whose tensors must be gone).
+    Otherwise a no-op.  Yields the arena or ``None``."""
+    if not _env_on():
+        yield None
+        return
+    import logging
+    import tempfile
+
+    log = logging.getLogger(__name__)
+    arena = Arena(int(device))
+    try:
+        with use_arena(arena, int(device)):
+            yield arena
+    except BaseException:
+        arena.close()
+        raise
+    prior = _by_device.pop(int(device), None)
+    if prior is not None:
+        log.warning("device %d: a second load replaces the arena of the first; its tensors must be gone", device)
+        old = _published.get(prior)
+        withdraw_arena(prior)
+        if old is not None:
+            old[0].close()
+    path = os.path.join(socket_dir or tempfile.gettempdir(), f"mxb-arena-{os.getpid()}-{int(device)}.sock")
+    _by_device[int(device)] = publish_arena(arena, path)
+    log.info("device %d: arena published at %s (%d blocks, %d bytes mapped)", device, path,
+             arena.live_allocation_count, arena.mapped_bytes)

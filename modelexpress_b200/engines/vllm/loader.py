@@ -121,9 +121,16 @@ class MxModelLoader(BaseModelLoader):
                                                             process_weights_after_loading)
         from vllm.utils.torch_utils import set_default_torch_dtype
 
+        from ...arena import maybe_enter_arena
+
         device_config = vllm_config.device_config
         target_device = torch.device(device_config.device)
-        with set_default_torch_dtype(model_config.dtype):
+        dev_index = target_device.index if target_device.index is not None else (
+            torch.cuda.current_device() if target_device.type == "cuda" else 0)
+        # MXB_VMM_ARENA=1: the model is allocated in one arena that peers can map through a single
+        # descriptor exchange (the load envelope of the reference's loader.py:107-127)
+        with maybe_enter_arena(dev_index, os.environ.get("MXB_FANOUT_DIR")), \
+                set_default_torch_dtype(model_config.dtype):
             def fresh_model():
                 with target_device:
                     return initialize_model(vllm_config=vllm_config, model_config=model_config, prefix=prefix)

@@ -200,31 +200,60 @@ def _tensor_rows(tensors: dict, device_id: int) -> list:
 
 
 def _export_rows(rows: list) -> list:
-    """JSON-able manifest: every row with the CUDA IPC handle of the allocation it lies
-    in and its offset inside that allocation."""
+    """JSON-able manifest: every row with the way a peer reaches it: the socket of the
+    published arena it lies in and its offset there (one mapping for all such rows), else the
+    CUDA IPC handle of its allocation and its offset inside that allocation."""
+    from . import arena as arena_mod
     from .runtime import ipc_export
 
     out = []
     for d in rows:
-        handle, off = (ipc_export(d.addr) if d.size else (b"", 0))
-        out.append({"name": d.name, "size": d.size, "device_id": d.device_id, "dtype": d.dtype,
-                    "handle": handle.hex(), "offset": off})
+        row = {"name": d.name, "size": d.size, "device_id": d.device_id, "dtype": d.dtype,
+               "handle": "", "offset": 0}
+        hit = arena_mod.lookup(d.addr, d.size) if d.size else None
+        if hit is not None:
+            row["arena"], row["offset"] = hit
+        elif d.size:
+            handle, row["offset"] = ipc_export(d.addr)
+            row["handle"] = handle.hex()
+        out.append(row)
     return out
 
 
 class _PeerMemory:
-    """IPC mappings opened by this process: one per allocation, however many tensors lie in it."""
+    """A peer's memory as mapped by this process: one IPC mapping per allocation, however many
+    tensors lie in it, or one imported arena per socket, however many allocations it holds."""
 
-    def __init__(self):
+    def __init__(self, device: int = 0):
+        self.device = int(device)
         self._base: dict = {}
+        self._arenas: dict = {}
 
-    def address(self, handle_hex: str, offset: int) -> int:
+    def address(self, handle_hex: str, offset: int, arena: str | None = None, nbytes: int = 1) -> int:
+        if arena:
+            return self._arena_address(arena, int(offset), int(nbytes))
         from .runtime import ipc_open
 
         base = self._base.get(handle_hex)
         if base is None:
             base = self._base[handle_hex] = ipc_open(bytes.fromhex(handle_hex), 0)
         return base + int(offset)
+
+    def row_address(self, row: dict) -> int:
+        return self.address(row.get("handle", ""), row["offset"], row.get("arena"), int(row.get("size", 1)) or 1)
+
+    def _arena_address(self, path: str, offset: int, nbytes: int) -> int:
+        from .arena import fetch_arena
+
+        mapped = self._arenas.get(path)
+        if mapped is not None and offset + nbytes > mapped.used_bytes:
+            mapped.close()        # the peer's arena has grown since it was mapped
+            mapped = None
+        if mapped is None:
+            mapped = self._arenas[path] = fetch_arena(path, self.device)
+        if offset + nbytes > mapped.used_bytes:
+            raise ManifestMismatchError(f"offset {offset} + {nbytes} lies outside the arena served at {path}")
+        return mapped.base + offset
 
     def close(self) -> None:
         from . import _lib
@@ -233,6 +262,9 @@ class _PeerMemory:
         for base in self._base.values():
             lib.mxb_ipc_close(int(base), 0)
         self._base = {}
+        for mapped in self._arenas.values():
+            mapped.close()
+        self._arenas = {}
 
 
 def _write_json(path: str, obj) -> None:
@@ -264,7 +296,7 @@ class FanoutSource:
             recs = self.ctx.digest([(d.addr, d.size) for d in self.rows], DIGEST_SAFE32 | DIGEST_ROWS, self.dev)
             self._digests = [[int(r.safe_checksum), int(r.row_sum), int(r.row_sum_w), int(r.tail_sum),
                               int(r.tail_sum_w), int(r.ragged_sum)] for r in recs]
-        self._peers = _PeerMemory()
+        self._peers = _PeerMemory(self.dev)
 
     @property
     def manifest_path(self) -> str:
@@ -320,7 +352,7 @@ class FanoutSource:
             if not d.size:
                 continue
             local.append((d.addr, d.size))
-            child.append((self._peers.address(row["handle"], row["offset"]), d.size))
+            child.append((self._peers.row_address(row), d.size))
         counters = self._peers.address(req["counters"]["handle"], req["counters"]["offset"])
         node = self.ctx.fanout(local, int(req["chunk_bytes"]), self.dev)
         try:

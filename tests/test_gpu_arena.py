@@ -80,8 +80,16 @@ def test_torch_allocates_inside_use_arena():
     w.normal_()
     assert torch.isfinite(w.float()).all() and float(v.sum()) == 0.0
     assert arena.mapped_bytes >= w.numel() * 2
-    del w, v
+    # a second arena gets its own torch pool: nothing of the first arena's cache leaks into it
+    second = Arena(0, 4 << 30)
+    del v
+    with use_arena(second):
+        v2 = torch.zeros(17, dtype=torch.float32, device="cuda")
+    assert second.contains(v2.data_ptr(), 68) and not arena.contains(v2.data_ptr())
+    del w, v2
     torch.cuda.synchronize()
+    second.close()
+    arena.close()
 
 
 def _peer(tmp_path, peer_dev, my_dev):

@@ -167,3 +167,51 @@ def test_retry_reinitialises_after_a_mutating_failure(monkeypatch, tmp_path):
     with pytest.raises(StrategyFailed) as e:
         fanout.B200FanoutStrategy(str(tmp_path)).load(LoadResult(value="m", model=None), Ctx())
     assert e.value.mutated is True and str(e.value).count("x") == 3
+
+
+@pytest.mark.gpu
+def test_push_into_a_target_whose_parameters_live_in_a_published_arena(tmp_path):
+    """The target allocated its parameters through torch inside ``use_arena`` and published the
+    arena: its request names every tensor by the arena's socket and an offset, and the serving
+    process maps the whole arena once (descriptors over the socket) instead of opening one IPC
+    handle per allocation.  Same push, same digests."""
+    import torch
+
+    from fanout_source_proc import seeded_tensors
+    from modelexpress_b200 import fanout
+    from modelexpress_b200.arena import Arena, lookup, publish_arena, use_arena, withdraw_arena
+    from modelexpress_b200.fanout import B200FanoutStrategy
+    from modelexpress_b200.loader import LoadResult
+
+    rendezvous = str(tmp_path)
+    arena = Arena(0, 4 << 30)
+    shapes = seeded_tensors(0, "cpu")
+    with use_arena(arena):
+        dests = {n: torch.zeros_like(t, device="cuda") for n, t in shapes.items()}
+    sock = publish_arena(arena, os.path.join(rendezvous, "target-arena.sock"))
+    try:
+        assert all(lookup(t.data_ptr(), t.numel() * t.element_size()) is not None for t in dests.values())
+        rows = fanout._export_rows(fanout._tensor_rows(dests, 0))
+        assert all(r["arena"] == sock and r["handle"] == "" for r in rows if r["size"])
+
+        class Adapter:
+            def named_destinations(self, result):
+                return dests
+
+        ctx = _Ctx()
+        ctx.adapter = Adapter()
+        live = _spawn(rendezvous, "arena_src", 8, "serve")
+        try:
+            res = B200FanoutStrategy(rendezvous, timeout_ms=5000, wait_for_push=True).load(
+                LoadResult(value=None, model=None), ctx)
+            assert res.metadata["b200_fanout"]["tensors"] == len(dests)
+            for n, t in seeded_tensors(8, "cuda").items():
+                assert torch.equal(dests[n].view(torch.uint8), t.view(torch.uint8)), n
+            assert live.stdout.readline().strip() == "served 1"
+        finally:
+            _stop(live)
+    finally:
+        withdraw_arena(sock)
+        del dests
+        torch.cuda.synchronize()
+        arena.close()
