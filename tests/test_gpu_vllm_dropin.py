@@ -128,6 +128,26 @@ def test_place_checkpoint_equals_vllm_load_weights(tmp_path):
             inner.load_weights(model, mc)
             for n, t in truth.items():
                 assert torch.equal(params[n].detach().view(torch.int16), t.view(torch.int16)), n
+            # MXB_VMM_ARENA=1 (the reference's MX_VMM_ARENA envelope, engines/vllm/loader.py:107-127):
+            # the same load with the model allocated in an arena that is published for peers
+            from modelexpress_b200 import arena as arena_mod
+
+            os.environ["MXB_VMM_ARENA"] = "1"
+            try:
+                vc3 = VllmConfig(model_config=mc, device_config=DeviceConfig(device="cuda"),
+                                 load_config=LoadConfig(load_format="auto"))
+                with set_current_vllm_config(vc3):
+                    model3 = wrapper.load_model(vllm_config=vc3, model_config=mc)
+            finally:
+                del os.environ["MXB_VMM_ARENA"]
+            hits = [arena_mod.lookup(p.data_ptr(), p.numel() * p.element_size()) for p in model3.parameters()]
+            assert all(h is not None for h in hits) and len({h[0] for h in hits}) == 1
+            for n, p in model3.named_parameters():
+                assert torch.equal(p.detach().view(torch.int16), truth[n].view(torch.int16)), n
+            served = arena_mod._published[hits[0][0]][0]
+            assert served.live_allocation_count >= 1 and served.mapped_bytes >= sum(
+                p.numel() * p.element_size() for p in model3.parameters())
+            arena_mod.withdraw_arena(hits[0][0])
         finally:
             sys.path.remove(shim)
             for k in [k for k in sys.modules if k == "modelexpress" or k.startswith("modelexpress.")]:
