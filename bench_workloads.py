@@ -827,6 +827,62 @@ def run_vllm(args):
     print(json.dumps(out), flush=True)
 
 
+def _refit_cast_step(torch, local) -> dict:
+    """One refit step whose trainer publishes fp32 and whose engine holds bf16: eight 8192 x 8192
+    parameters, each source in eight row shards on this GPU, through ``ReshardReceiver``.  Fused:
+    the convert kernel reads the shards in place.  Staged: the reference's order (pull the served
+    dtype into a staging buffer, cast afterwards; transfer_plan.py:49-60, receiver.py:964-971)."""
+    from modelexpress_b200.planner import ShardSpec, SourceSpec
+    from modelexpress_b200.refit import ReshardReceiver
+
+    rows, cols, layers = 8192, 8192, 8
+
+    class Engine(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.w = torch.nn.ParameterList(
+                [torch.nn.Parameter(torch.zeros(rows, cols, dtype=torch.bfloat16)) for _ in range(layers)])
+
+        def load_weights(self, weights):
+            for name, w in weights:
+                self.w[int(name[1:])].data.copy_(w)
+
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1)
+    srcs = [torch.randn(rows, cols, device="cuda", generator=g) for _ in range(layers)]
+    per = rows // 8
+    sources = {f"w{i}": SourceSpec((rows, cols), torch.float32, 4,
+                                   [ShardSpec((s * per, 0), (per, cols), "t0", t.data_ptr() + s * per * cols * 4, 4)
+                                    for s in range(8)]) for i, t in enumerate(srcs)}
+    out = {"elements": rows * cols * layers, "bytes_read_plus_written": rows * cols * layers * 6}
+    saved = os.environ.get("MXB_RESHARD_FUSED_CASTS")
+    try:
+        for label, fused in (("fused", "1"), ("staged", "0")):
+            os.environ["MXB_RESHARD_FUSED_CASTS"] = fused
+            model = Engine().to(f"cuda:{local}")
+            rx = ReshardReceiver(model, device=f"cuda:{local}")
+            rx.prepare(sources)
+            staging = int(rx._staging.numel())
+            steps = [rx.update_weights(k) for k in range(6)]
+            for i, t in enumerate(srcs):
+                if not torch.equal(model.w[i].data, t.to(torch.bfloat16)):
+                    raise SystemExit(f"refit cast step ({label}): parameter {i} differs from torch's cast")
+            best = min(steps[2:], key=lambda st: st["total_s"])
+            out[label] = {"ms_per_step": round(best["total_s"] * 1e3, 3), "read_ms": round(best["read_s"] * 1e3, 3),
+                          "install_ms": round(best["install_s"] * 1e3, 3), "staging_bytes": staging if staging > 1 else 0,
+                          "gbs": round(out["bytes_read_plus_written"] / best["total_s"] / 1e9, 1)}
+            rx.close()
+            del model, rx
+            torch.cuda.empty_cache()
+    finally:
+        if saved is None:
+            os.environ.pop("MXB_RESHARD_FUSED_CASTS", None)
+        else:
+            os.environ["MXB_RESHARD_FUSED_CASTS"] = saved
+    out["check"] = "every parameter bit-identical to torch's cast, both ways"
+    return out
+
+
 def run_convert(args):
     """The box-convert kernel on the parameter list of a Llama-3-8B-shaped model (every 2-D
     weight and the norms): cast fp32 -> bf16 (a trainer that serves fp32 masters), transposed
@@ -902,11 +958,15 @@ def run_convert(args):
                         "bytes_read_plus_written": moved, "launches_per_step": 1,
                         "torch_copy_loop_ms": round(torch_ms, 4), "torch_launches_per_step": len(views),
                         "torch_gbs": round(moved / (torch_ms * 1e-3) / 1e9, 1), "check": "bit-identical to torch"}
+    del src32, src16, dst16, want
+    torch.cuda.empty_cache()
+    refit = _refit_cast_step(torch, local)
     head = cases["cast fp32 -> bf16"]
     out = _base("GB/s converted (bytes read + written, box-convert kernel, one launch)", head["gbs"] * world,
                 "GB/s", world, args, head["ms"],
                 {"workload": f"Llama-3-8B parameter list, {layers} layers, {len(shapes)} tensors, "
-                             f"{elems} elements resident in HBM", "l2": "input larger than L2", "cases": cases},
+                             f"{elems} elements resident in HBM", "l2": "input larger than L2", "cases": cases,
+                 "refit_step_fp32_shards_to_bf16_params": refit},
                 dtype="f32->bf16")
     out["gpu_launches"] = steps * len(cases)
     out["roofline"] = {"bound": "hbm", "achieved": head["gbs"], "peak": peak, "unit": "GB/s",

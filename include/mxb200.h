@@ -422,9 +422,9 @@ int32_t mxb_digest_noalloc(int32_t dev, const mxb_span *spans, uint64_t n, uint3
 #define MXB_ELEM_F16 2
 #define MXB_ELEM_BF16 3
 
-/* One staged box.  `src` holds the box contiguously, row-major over
- * extent[0..ndim) (the source tensor's own dim order, element size given by
- * `src_kind`); the element at box index (i0, i1, ...) lands at
+/* One box.  `src` holds the box row-major over extent[0..ndim) (the source
+ * tensor's own dim order, element size given by `src_kind`), contiguously
+ * unless `src_stride` says otherwise; the element at box index (i0, i1, ...) lands at
  * dst + sum(i_d * dst_stride[d]) destination elements (`dst_kind`).  This is the
  * copy the reference leaves to torch after a pull: `dst.copy_(staged)` for a
  * served dtype that differs from the parameter's (refit/reshard/receiver.py:964-971)
@@ -438,6 +438,9 @@ typedef struct {
     uint32_t elem_bytes; /* MXB_ELEM_RAW only */
     uint64_t extent[MXB_MAX_DIMS];
     int64_t dst_stride[MXB_MAX_DIMS]; /* destination elements, >= 0 */
+    int64_t src_stride[MXB_MAX_DIMS]; /* source elements; all zero: the box is contiguous.  Otherwise the
+                                       * innermost dim with extent > 1 must have stride 1 (a strided slice
+                                       * of a shard read in place, e.g. straight from a peer's memory) */
 } mxb_convert;
 
 /* All `n` boxes on the context's stream of `dev`, one launch per conversion

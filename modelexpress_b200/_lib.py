@@ -63,7 +63,8 @@ class FanoutPiece(ctypes.Structure):
 
 class ConvertBox(ctypes.Structure):
     _fields_ = [("src", u64), ("dst", u64), ("ndim", u32), ("src_kind", u32), ("dst_kind", u32),
-                ("elem_bytes", u32), ("extent", u64 * MAX_DIMS), ("dst_stride", i64 * MAX_DIMS)]
+                ("elem_bytes", u32), ("extent", u64 * MAX_DIMS), ("dst_stride", i64 * MAX_DIMS),
+                ("src_stride", i64 * MAX_DIMS)]
 
 
 class ArenaBlock(ctypes.Structure):

@@ -31,6 +31,7 @@ struct CvtItem {
     uint64_t src, dst;
     uint32_t n[4];     // canonical extents, n[3] = the source's inner dim
     int64_t ds[4];     // destination strides (elements)
+    int64_t ss[3];     // source strides of the three outer dims (elements); the inner dim's is 1
     uint64_t tile0;    // first tile of this item
     uint32_t mode;     // 0 rows, 1 transpose (64 x 64), 2 transpose, wide accesses
     uint32_t bdim;     // transpose: the dim the destination walks with stride 1
@@ -114,12 +115,14 @@ __device__ void rows_tile(const CvtItem &it, uint64_t t, unsigned char *) {
     uint64_t row = t / it.tiles_a;
     const uint32_t a0 = ta * kRowTile;
     const uint32_t len = min(kRowTile, it.n[3] - a0);
-    const SE *s = reinterpret_cast<const SE *>(it.src) + row * it.n[3] + a0;
-    int64_t off = 0;
+    int64_t off = 0, soff = 0;
     for (int d = 2; d >= 0; --d) {
-        off += (int64_t)(row % it.n[d]) * it.ds[d];
+        const int64_t idx = (int64_t)(row % it.n[d]);
+        off += idx * it.ds[d];
+        soff += idx * it.ss[d];
         row /= it.n[d];
     }
+    const SE *s = reinterpret_cast<const SE *>(it.src) + soff + a0;
     const int64_t step = it.ds[3];
     DE *dbase = reinterpret_cast<DE *>(it.dst) + off + (int64_t)a0 * step;
     uint32_t done = 0;
@@ -181,16 +184,14 @@ __device__ __forceinline__ TileAt tile_at(const CvtItem &it, uint64_t t, uint32_
     TileAt at;
     at.na = min(edge_a, it.n[3] - a0);
     at.nb = min(edge_b, it.n[b] - b0);
-    uint64_t srow = 0;
-    int64_t doff = 0;
+    int64_t soff = 0, doff = 0;
     for (int d = 0; d < 3; ++d) {
         const uint32_t v = (uint32_t)d == b ? b0 : idx[d];
-        srow = srow * it.n[d] + v;
+        soff += (int64_t)v * it.ss[d];
         doff += (int64_t)v * it.ds[d];
     }
-    at.sstride_b = it.n[3];
-    for (uint32_t d = b + 1; d < 3; ++d) at.sstride_b *= it.n[d];
-    at.src_elem = srow * it.n[3] + a0;
+    at.sstride_b = (uint64_t)it.ss[b];
+    at.src_elem = (uint64_t)soff + a0;
     at.dst_elem = doff + (int64_t)a0 * it.ds[3];
     return at;
 }
@@ -512,9 +513,21 @@ int32_t canonical(const mxb_convert &c, CvtItem *out, uint64_t *bytes) {
     else kind = kKinds;
     if (kind == kKinds) return MXB_ERR_UNSUPPORTED;
     if ((c.src % ssz) || (c.dst % dsz)) return MXB_ERR_ALIGN;
-    // drop extent-1 dims, merge dims the destination walks like the (contiguous) source does
+    // source strides: as given, or those of a contiguous row-major box when all are zero
+    int64_t given[MXB_MAX_DIMS];
+    bool strided = false;
+    for (uint32_t d = 0; d < c.ndim; ++d) strided = strided || c.src_stride[d] != 0;
+    {
+        int64_t run = 1;
+        for (int d = (int)c.ndim - 1; d >= 0; --d) {
+            given[d] = strided ? c.src_stride[d] : run;
+            if (given[d] < 0) return MXB_ERR_ARG;
+            run *= (int64_t)(c.extent[d] ? c.extent[d] : 1);
+        }
+    }
+    // drop extent-1 dims, merge dims that source and destination both walk as one
     uint64_t n[MXB_MAX_DIMS];
-    int64_t ds[MXB_MAX_DIMS];
+    int64_t ds[MXB_MAX_DIMS], ss[MXB_MAX_DIMS];
     uint32_t nd = 0;
     uint64_t total = 1;
     for (uint32_t d = 0; d < c.ndim; ++d) {
@@ -522,28 +535,34 @@ int32_t canonical(const mxb_convert &c, CvtItem *out, uint64_t *bytes) {
         if (c.dst_stride[d] < 0) return MXB_ERR_ARG;
         total *= c.extent[d];
         if (c.extent[d] == 1) continue;
-        if (nd && ds[nd - 1] == c.dst_stride[d] * (int64_t)c.extent[d]) {
+        if (nd && ds[nd - 1] == c.dst_stride[d] * (int64_t)c.extent[d] &&
+            ss[nd - 1] == given[d] * (int64_t)c.extent[d]) {
             n[nd - 1] *= c.extent[d];
             ds[nd - 1] = c.dst_stride[d];
+            ss[nd - 1] = given[d];
         } else {
             n[nd] = c.extent[d];
             ds[nd] = c.dst_stride[d];
+            ss[nd] = given[d];
             ++nd;
         }
     }
     memset(out, 0, sizeof *out);
     *bytes = total * (ssz + dsz);
     if (total == 0) return MXB_OK;  // nothing to move: zero tiles
-    if (nd == 0) { n[0] = 1; ds[0] = 1; nd = 1; }
+    if (nd == 0) { n[0] = 1; ds[0] = 1; ss[0] = 1; nd = 1; }
     if (nd > 4) return MXB_ERR_UNSUPPORTED;
+    if (ss[nd - 1] != 1) return MXB_ERR_UNSUPPORTED;  // the source's inner dim must be unit-stride
     for (uint32_t d = 0; d < nd; ++d)
         if (n[d] > 0xffffffffull) return MXB_ERR_UNSUPPORTED;
     out->src = c.src;
     out->dst = c.dst;
     for (uint32_t d = 0; d < 4; ++d) { out->n[d] = 1; out->ds[d] = 0; }
+    for (uint32_t d = 0; d < 3; ++d) out->ss[d] = 0;
     for (uint32_t d = 0; d < nd; ++d) {
         out->n[4 - nd + d] = (uint32_t)n[d];
         out->ds[4 - nd + d] = ds[d];
+        if (4 - nd + d < 3) out->ss[4 - nd + d] = ss[d];
     }
     out->kind = kind;
     out->bdim = 3;
@@ -565,6 +584,8 @@ int32_t canonical(const mxb_convert &c, CvtItem *out, uint64_t *bytes) {
                     c.src % (gs * ssz) == 0 && c.dst % (gd * dsz) == 0;
         for (uint32_t d = 0; d < 4 && wide; ++d)
             if (d != b && out->n[d] > 1 && out->ds[d] % gd) wide = false;
+        for (uint32_t d = 0; d < 3 && wide; ++d)
+            if (out->n[d] > 1 && out->ss[d] % gs) wide = false;
         const uint32_t edge_a = wide ? 32 * gs : kTT, edge_b = wide ? 32 * gd : kTT;
         if (wide) out->mode = 2;
         out->tiles_a = (out->n[3] + edge_a - 1) / edge_a;
@@ -578,6 +599,8 @@ int32_t canonical(const mxb_convert &c, CvtItem *out, uint64_t *bytes) {
                     c.src % (2 * ssz) == 0 && c.dst % (2 * dsz) == 0;
         for (uint32_t d = 0; d < 4 && pair; ++d)
             if (d != b && out->n[d] > 1 && out->ds[d] % 2) pair = false;
+        for (uint32_t d = 0; d < 3 && pair; ++d)
+            if (out->n[d] > 1 && out->ss[d] % 2) pair = false;
         out->pair = pair ? 1u : 0u;
     }
     out->tile0 = tiles;  // the caller turns counts into a prefix

@@ -343,6 +343,18 @@ class ConvertSpec:
     box_perm: tuple | None = None    # per destination dim, the staging dim it walks (None: extent 1)
 
 
+@dataclass
+class DirectCast:
+    """A dtype-changing copy whose sources are device memory this GPU can read (local or a
+    mapped peer): every record of the pull becomes one box of the convert kernel, read in place
+    from the shard and written cast into the live parameter.  No staging buffer, no second pass
+    (the reference stages the served dtype and casts afterwards, transfer_plan.py:49-60)."""
+
+    param_name: str
+    boxes: list   # (src, dst, extents, dst_strides, src_kind, dst_kind, elem_bytes, src_strides)
+    nbytes: int   # source bytes read
+
+
 TRANSPOSE_MIN_ELEMENTS = 4096   # below this a transposing copy stays a list of narrow records
 
 
@@ -383,7 +395,32 @@ def _box_copy(copy, src, box_shape, corner: int):
     return staged
 
 
-def plan_transfer_2d(copies, sources: dict, resolve_param_ptr, convert_base: int | None = None) -> tuple:
+def direct_cast(copy, src, param_ptr: int, dst_elsize: int) -> DirectCast | None:
+    """``copy`` (served dtype != destination dtype, walking its source with the grain) as boxes
+    read straight from the shards; ``None`` when the pair of dtypes is outside the convert
+    kernel's table.  The pull is planned as for a same-dtype copy against a destination at
+    address 0 measured in source elements, then every record's destination is rescaled to the
+    parameter's element size."""
+    sk, dk = _FLOAT_KINDS.get(str(src.dtype)), _FLOAT_KINDS.get(str(copy.dest_dtype))
+    if sk is None or dk is None:
+        return None
+    ssz = int(src.elsize)
+    virtual = _copy.copy(copy)
+    virtual.dest_dtype = src.dtype
+    parts = plan_pull_2d(virtual, src.global_shape, src.dtype, ssz, src.shards, 0)
+    boxes, nbytes = [], 0
+    for _sess, recs in parts:
+        for s_addr, d_virtual, rows, row_bytes, sp, dp in np.asarray(recs, dtype=np.uint64).tolist():
+            if row_bytes % ssz or d_virtual % ssz or sp % ssz or dp % ssz:
+                raise UnsupportedReshard(f"{copy.param_name}: a record is not element-granular")
+            boxes.append((int(s_addr), int(param_ptr) + d_virtual // ssz * int(dst_elsize),
+                          [int(rows), row_bytes // ssz], [dp // ssz, 1], sk, dk, ssz, [sp // ssz, 1]))
+            nbytes += int(rows) * int(row_bytes)
+    return DirectCast(copy.param_name, boxes, nbytes)
+
+
+def plan_transfer_2d(copies, sources: dict, resolve_param_ptr, convert_base: int | None = None,
+                     fuse_casts: bool = False, dst_elsize=None) -> tuple:
     """All copies of a capture -> one record array.
 
     Returns ``(records, unsupported, converts)``.  Same-dtype copies write
@@ -391,7 +428,10 @@ def plan_transfer_2d(copies, sources: dict, resolve_param_ptr, convert_base: int
     the destination's is planned into a contiguous staging buffer at
     ``convert_base`` (served dtype, row-major) and listed in ``converts`` for
     the caller to cast, as the reference does; without ``convert_base`` such
-    copies are reported unsupported.  Sources that are missing or not
+    copies are reported unsupported.  With ``fuse_casts`` (sources in device memory;
+    ``dst_elsize(param_name)`` gives the parameter's element size) a cast that walks its
+    source with the grain is not staged at all: it comes back as a ``DirectCast`` whose
+    boxes the convert kernel reads in place.  Sources that are missing or not
     box-shaped are returned by name so the caller can fail closed
     (transfer_plan.py:192-299 keeps the same outcomes; there is no descriptor
     bound here because a strided slice costs one record, not one per row)."""
@@ -415,6 +455,11 @@ def plan_transfer_2d(copies, sources: dict, resolve_param_ptr, convert_base: int
                                             tuple(copy.dest_stride), int(copy.dest_offset), src.dtype,
                                             off, n * int(src.elsize), box_shape, box_perm))
                 staged = off + n * int(src.elsize)
+            elif src.dtype != copy.dest_dtype and fuse_casts and dst_elsize is not None and (
+                    fused := direct_cast(copy, src, resolve_param_ptr(copy.param_name),
+                                         dst_elsize(copy.param_name))) is not None:
+                converts.append(fused)
+                parts = []
             elif src.dtype != copy.dest_dtype:
                 if convert_base is None:
                     raise UnsupportedReshard("dtype conversion required and no staging given")
@@ -442,8 +487,9 @@ def plan_transfer_2d(copies, sources: dict, resolve_param_ptr, convert_base: int
     return table, unsupported, converts
 
 
-def convert_staging_bytes(copies, sources: dict) -> int:
-    """Size of the staging buffer ``plan_transfer_2d`` needs for dtype converts."""
+def convert_staging_bytes(copies, sources: dict, fuse_casts: bool = False) -> int:
+    """Size of the staging buffer ``plan_transfer_2d`` needs for dtype converts
+    (``fuse_casts``: casts between the convert kernel's float dtypes are read in place)."""
     total = 0
     for copy in copies:
         src = sources.get(copy.src_name)
@@ -452,6 +498,9 @@ def convert_staging_bytes(copies, sources: dict) -> int:
         tbox = transposed_box(copy, src.global_shape)
         if tbox is not None:
             total = (total + 255) // 256 * 256 + int(np.prod(tbox[0])) * int(src.elsize)
+        elif src.dtype != copy.dest_dtype and fuse_casts and str(src.dtype) in _FLOAT_KINDS and str(
+                copy.dest_dtype) in _FLOAT_KINDS:
+            continue
         elif src.dtype != copy.dest_dtype:
             n = int(np.prod(copy.dest_shape)) if len(copy.dest_shape) else 1
             total = (total + 255) // 256 * 256 + n * int(src.elsize)
@@ -502,6 +551,9 @@ def apply_converts(converts, staging, params: dict, ctx=None) -> None:
         ctx = ctx or default_context(staging.device.index)
         boxes, leftover = [], []
         for c in converts:
+            if isinstance(c, DirectCast):
+                boxes += [(c, b) for b in c.boxes]
+                continue
             box = convert_box(c, staging.data_ptr(), params[c.param_name])
             if box is None:
                 leftover.append(c)
@@ -518,7 +570,7 @@ def apply_converts(converts, staging, params: dict, ctx=None) -> None:
                 try:
                     ctx.convert_boxes([b], staging.device.index)
                 except MxbError as e1:
-                    if getattr(e1, "code", None) != -9:
+                    if getattr(e1, "code", None) != -9 or isinstance(c, DirectCast):
                         raise
                     leftover.append(c)
     for c in leftover:

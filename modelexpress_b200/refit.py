@@ -40,7 +40,7 @@ import time
 from dataclasses import dataclass, field
 from typing import Callable
 
-from .planner import (ShardSpec, SourceSpec, apply_converts, convert_staging_bytes,
+from .planner import (DirectCast, ShardSpec, SourceSpec, apply_converts, convert_staging_bytes,
                       plan_transfer_2d)
 from .runtime import Context, Table, default_context
 
@@ -268,6 +268,8 @@ class ReshardReceiver:
         self._table: Table | None = None
         self._sources: dict = {}
         self._converts: list = []
+        self._staged: list = []
+        self._direct = None
         self._staging = None
         self._dests: dict = {}
         self.plan: dict = {}
@@ -290,10 +292,14 @@ class ReshardReceiver:
         cap = capture_geometry(self.model, manifest, self._load_weights, device=self.device)
         t_capture = time.perf_counter() - t0
         dests = model_destinations(self.model)
-        nbytes = convert_staging_bytes(cap.copies, sources)
+        # shards are device memory this GPU reads in place: a cast between float dtypes needs no
+        # staging (MXB_RESHARD_FUSED_CASTS=0 stages the served dtype and casts afterwards)
+        fuse = _env("RESHARD_FUSED_CASTS", "1") != "0"
+        nbytes = convert_staging_bytes(cap.copies, sources, fuse_casts=fuse)
         staging = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=self.device)
         table, not_planned, converts = plan_transfer_2d(
-            cap.copies, sources, lambda n: dests[n].data_ptr(), staging.data_ptr() if nbytes else None)
+            cap.copies, sources, lambda n: dests[n].data_ptr(), staging.data_ptr() if nbytes else None,
+            fuse_casts=fuse, dst_elsize=lambda n: dests[n].element_size())
         reasons = dict(cap.unsupported_reasons)
         for n in not_planned:
             reasons.setdefault(n, "the copied window is not a box of the source tensor")
@@ -304,16 +310,22 @@ class ReshardReceiver:
         self.close()
         self._table = self.ctx.table(table, self._dev) if len(table) else None
         self._sources, self._converts, self._staging, self._dests = sources, converts, staging, dests
+        self._staged = [c for c in converts if not isinstance(c, DirectCast)]
+        direct = [b for c in converts if isinstance(c, DirectCast) for b in c.boxes]
+        self._direct = self.ctx.convert_array(direct) if direct else None   # marshalled once, replayed every step
         planned = {c.param_name for c in cap.copies}
         total = sum(t.numel() * t.element_size() for t in
                     {id(p): p for p in self.model.parameters()}.values())
         moved = int((table[:, 2] * table[:, 3]).sum()) if len(table) else 0
+        moved += sum(c.nbytes for c in converts if isinstance(c, DirectCast))
         used = {c.src_name for c in cap.copies}
         all_params = {id(p): n for n, p in self.model.named_parameters()}
         missed = sorted(set(all_params.values()) - planned)
         self.plan = {
             "copies": len(cap.copies), "records": int(len(table)), "bytes_per_step": moved,
-            "converts": [c.param_name for c in converts], "params_written": len(planned),
+            "converts": [c.param_name for c in converts],
+            "fused_casts": [c.param_name for c in converts if isinstance(c, DirectCast)],
+            "params_written": len(planned),
             "coverage": (moved / total) if total else 1.0,
             "sources_unused": sorted(set(sources) - used),
             "engine": self._table.engine() if self._table is not None else "none",
@@ -374,15 +386,19 @@ class ReshardReceiver:
         t1 = time.perf_counter()
         if self._table is not None:
             self._table.launch()
-            # the launch only queues the kernel on the library's own stream: wait for it (and
-            # learn of a device-side wait that ran out) before anything reads what it wrote
+        if self._direct is not None:
+            # casts read in place from the shards: part of the pull, on the same stream
+            self.ctx.convert_boxes(self._direct, self._dev)
+        if self._table is not None or self._direct is not None:
+            # the launches only queue kernels on the library's own stream: wait for them (and
+            # learn of a device-side wait that ran out) before anything reads what they wrote
             self.ctx.sync(self._dev)
         stages["read_s"] = time.perf_counter() - t1
         # before anything reads or installs what the step wrote
         check_throughput_ceiling(int(step), int(self.plan.get("bytes_per_step", 0)), stages["read_s"])
         t2 = time.perf_counter()
-        if self._converts:
-            apply_converts(self._converts, self._staging, self._dests, self.ctx)
+        if self._staged:
+            apply_converts(self._staged, self._staging, self._dests, self.ctx)
         if self._install is not None:
             self._install(self.model)
         torch.cuda.current_stream(self.device).synchronize()
@@ -393,6 +409,7 @@ class ReshardReceiver:
         return stages
 
     def close(self) -> None:
+        self._direct = None
         if self._table is not None:
             self._table.close()
             self._table = None

@@ -128,18 +128,23 @@ class Context:
 
     @classmethod
     def convert_array(cls, boxes):
-        """Marshal ``(src, dst, extents, dst_strides, src_kind, dst_kind, elem_bytes)`` tuples once
-        (a list that is replayed every step need not be marshalled every step)."""
+        """Marshal ``(src, dst, extents, dst_strides, src_kind, dst_kind, elem_bytes[, src_strides])``
+        tuples once (a list that is replayed every step need not be marshalled every step).
+        Without ``src_strides`` the source box is contiguous."""
         boxes = list(boxes)
         arr = (_lib.ConvertBox * max(1, len(boxes)))()
-        for i, (src, dst, extents, strides, sk, dk, eb) in enumerate(boxes):
-            if len(extents) != len(strides) or len(extents) > _lib.MAX_DIMS:
+        for i, box in enumerate(boxes):
+            src, dst, extents, strides, sk, dk, eb = box[:7]
+            src_strides = box[7] if len(box) > 7 and box[7] is not None else None
+            if len(extents) != len(strides) or len(extents) > _lib.MAX_DIMS or (
+                    src_strides is not None and len(src_strides) != len(extents)):
                 raise ValueError("convert box: extents and strides must have the same rank, at most 8")
             b = arr[i]
             b.src, b.dst, b.ndim = int(src), int(dst), len(extents)
             b.src_kind, b.dst_kind, b.elem_bytes = cls.ELEM_KINDS[sk], cls.ELEM_KINDS[dk], int(eb)
             for d, (e, st) in enumerate(zip(extents, strides)):
                 b.extent[d], b.dst_stride[d] = int(e), int(st)
+                b.src_stride[d] = int(src_strides[d]) if src_strides is not None else 0
         return arr, len(boxes)
 
     def convert_boxes(self, boxes, dev: int | None = None, flags: int = SCATTER_DEFAULT) -> int:

@@ -120,6 +120,42 @@ def test_transposed_casts_and_higher_ranks():
     ctx.close()
 
 
+def test_strided_sources_are_read_in_place():
+    """A box whose source is a strided slice of a larger tensor (a shard read where it lies):
+    a column window of a wider fp32 matrix cast into a bf16 parameter, the same window
+    transposed, and a window whose rows start off every vector boundary."""
+    import torch
+
+    ctx = _ctx()
+    rows, width = 700, 1000
+    full = _random_values(torch, rows * width, torch.float32, 21).reshape(rows, width)
+    for c0, cols in ((0, 1000), (8, 512), (3, 333), (996, 4)):
+        win = full[:, c0: c0 + cols]
+        src_ptr = full.data_ptr() + c0 * 4
+        # plain cast into a window of a wider bf16 parameter
+        dst = torch.zeros(rows, width + 24, dtype=torch.bfloat16, device="cuda")
+        want = dst.clone()
+        want[:, 16: 16 + cols].copy_(win)
+        ctx.convert_boxes([(src_ptr, dst.data_ptr() + 16 * 2, [rows, cols], [width + 24, 1], "f32", "bf16", 4,
+                            [width, 1])], 0)
+        assert torch.equal(_bits(torch, dst), _bits(torch, want)), (c0, cols)
+        # transposed on the way
+        dst_t = torch.zeros(cols, rows, dtype=torch.bfloat16, device="cuda")
+        ctx.convert_boxes([(src_ptr, dst_t.data_ptr(), [rows, cols], [1, rows], "f32", "bf16", 4, [width, 1])], 0)
+        assert torch.equal(_bits(torch, dst_t), _bits(torch, win.t().to(torch.bfloat16)))
+        # moved unchanged
+        raw = torch.zeros(rows, cols, dtype=torch.float32, device="cuda")
+        ctx.convert_boxes([(src_ptr, raw.data_ptr(), [rows, cols], [cols, 1], "raw", "raw", 4, [width, 1])], 0)
+        assert torch.equal(_bits(torch, raw), _bits(torch, win))
+    # a source whose inner dim is not unit-stride is refused
+    from modelexpress_b200._lib import MxbError
+
+    with pytest.raises(MxbError) as e:
+        ctx.convert_boxes([(full.data_ptr(), full.data_ptr(), [10, 10], [10, 1], "raw", "raw", 4, [1, width])], 0)
+    assert e.value.code == -9
+    ctx.close()
+
+
 def test_kernel_matches_the_oracle():
     """Through the C ABI against the CPU restatement (oracle.ref_port.box_convert): a permuted
     rank-3 box of two-byte elements and a transposed fp32 -> bf16 window of a wider parameter."""

@@ -357,12 +357,16 @@ def test_reshard_receiver_prepare_once_update_every_step():
 
 
 @pytest.mark.gpu
-def test_update_weights_returns_with_the_bytes_in_place():
-    """update_weights must not return before the scatter kernel has finished: a
-    payload of several hundred MB with a dtype-changing source (staged, then cast)
-    is compared right after the call returns, and the reported read time must be
-    that of the copy, not of its enqueue."""
+@pytest.mark.parametrize("fused", ["1", "0"])
+def test_update_weights_returns_with_the_bytes_in_place(fused, monkeypatch):
+    """update_weights must not return before the kernels have finished: a payload of
+    several hundred MB with a dtype-changing source (read in place and cast by the
+    convert kernel, or staged in the served dtype and cast afterwards) is compared
+    right after the call returns, and the reported read time must be that of the
+    copy, not of its enqueue."""
     import torch
+
+    monkeypatch.setenv("MXB_RESHARD_FUSED_CASTS", fused)
 
     from modelexpress_b200.planner import ShardSpec, SourceSpec
     from modelexpress_b200.refit import IncompleteRefit, ReshardReceiver
@@ -399,6 +403,9 @@ def test_update_weights_returns_with_the_bytes_in_place():
     rx = ReshardReceiver(model, device="cuda:0")
     plan = rx.prepare(sources)
     assert plan["converts"] == ["gate"] and plan["params_missed"] == ["untouched"]
+    assert plan["fused_casts"] == (["gate"] if fused == "1" else [])
+    assert plan["bytes_per_step"] == big.numel() * 2 + gate.numel() * 2
+    assert (rx._staging.numel() <= 1) == (fused == "1")      # nothing is staged when the cast is fused
     for step in range(3):
         model.big.data.zero_()
         model.gate.data.zero_()
