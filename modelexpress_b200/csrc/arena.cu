@@ -17,6 +17,7 @@
 #include <cuda.h>
 #include <unistd.h>
 
+#include <cstdio>
 #include <map>
 #include <vector>
 
@@ -340,7 +341,12 @@ void *mxb_arena_torch_malloc(ssize_t size, int device, void *) {
         if (device >= 0 && device < 64) a = g_default[device];
     }
     uint64_t p = 0;
-    if (!a || size <= 0 || mxb_arena_malloc(a, (uint64_t)size, &p) != MXB_OK) return nullptr;
+    if (!a || size <= 0 || mxb_arena_malloc(a, (uint64_t)size, &p) != MXB_OK) {
+        // the caller (torch's allocator) has no error channel but the null pointer: say why
+        fprintf(stderr, "mxb arena: %zd bytes for device %d could not be allocated: %s\n", size, device,
+                a ? mxb_last_error() : "no arena is set for the device");
+        return nullptr;
+    }
     return (void *)(uintptr_t)p;
 }
 
