@@ -377,7 +377,8 @@ def fanout_measure(args, ctx, rank, world, local, nv=None) -> dict:
             g.manual_seed(100 + rank)
             arena[:pay].copy_(torch.randint(0, 256, (pay,), dtype=torch.uint8, device="cuda", generator=g))
         torch.cuda.synchronize()
-        node = ctx.fanout(pspans, 16 << 20, local)
+        # one hop: 256 KiB pieces (fewer system-scope fences per byte than the chain's 64 KiB)
+        node = ctx.fanout(pspans, 16 << 20, local, 256 << 10)
         ctrs = _open_peers(ctx, node.counters, world)
         if rank < half:
             node.add_child([(peers[rank + half], pay)], ctrs[rank + half])
@@ -399,7 +400,7 @@ def fanout_measure(args, ctx, rank, world, local, nv=None) -> dict:
             if alld[r] != alld[r + half]:
                 raise SystemExit(f"pair copy: GPU {r + half} differs from GPU {r}")
         pms = sum(times) / len(times)
-        pairs = {"pairs": half, "bytes_per_pair": pay, "device_ms": round(pms, 3),
+        pairs = {"pairs": half, "bytes_per_pair": pay, "piece_bytes": 256 << 10, "device_ms": round(pms, 3),
                  "gbs_per_pair": round(pay / (pms * 1e-3) / 1e9, 1),
                  "gbs_aggregate": round(pay * half / (pms * 1e-3) / 1e9, 1)}
         _barrier(world)

@@ -455,7 +455,7 @@ int32_t mxb_convert_boxes(mxb_ctx *ctx, int32_t dev, const mxb_convert *items, u
 
 #define MXB_FANOUT_MAX_CHILDREN 7
 
-/* One piece of a fan-out payload: `nbytes` (<= 64 KiB) at `offset` inside range
+/* One piece of a fan-out payload: `nbytes` (<= the piece size, 64 KiB by default) at `offset` inside range
  * `range`, belonging to chunk `chunk`. */
 typedef struct {
     uint64_t range;
@@ -475,6 +475,16 @@ typedef struct {
 int32_t mxb_fanout_plan(const mxb_span *local, uint64_t n, uint64_t chunk_bytes,
                         mxb_fanout_piece *pieces, uint64_t piece_cap, uint64_t *n_pieces,
                         uint32_t *chunk_pieces, uint64_t chunk_cap, uint64_t *n_chunks);
+/* The same with pieces of at most `piece_bytes` instead of 64 KiB (a multiple of
+ * 16, 4 KiB .. MXB_FANOUT_PIECE_MAX).  A piece is what one CTA stores before it
+ * releases a counter: larger pieces mean fewer system-scope fences per byte
+ * (faster on a single hop), smaller ones let the next hop of a chain start
+ * sooner.  Every node of a broadcast must use the same value; pieces above
+ * 64 KiB run on the VECTOR engine only. */
+#define MXB_FANOUT_PIECE_MAX (1u << 20)
+int32_t mxb_fanout_plan_pieces(const mxb_span *local, uint64_t n, uint64_t chunk_bytes, uint64_t piece_bytes,
+                               mxb_fanout_piece *pieces, uint64_t piece_cap, uint64_t *n_pieces,
+                               uint32_t *chunk_pieces, uint64_t chunk_cap, uint64_t *n_chunks);
 
 /* A fan-out node: this GPU's copy of the payload is the ranges
  * `local[0..n)`, cut into chunks of `chunk_bytes`.  The node waits for each
@@ -484,6 +494,9 @@ int32_t mxb_fanout_plan(const mxb_span *local, uint64_t n, uint64_t chunk_bytes,
  * one box. */
 int32_t mxb_fanout_create(mxb_ctx *ctx, int32_t dev, const mxb_span *local, uint64_t n,
                           uint64_t chunk_bytes, mxb_fanout **out);
+/* The same with the piece size of mxb_fanout_plan_pieces. */
+int32_t mxb_fanout_create_pieces(mxb_ctx *ctx, int32_t dev, const mxb_span *local, uint64_t n,
+                                 uint64_t chunk_bytes, uint64_t piece_bytes, mxb_fanout **out);
 /* Device address of this node's arrival counters (export it to the parent). */
 uint64_t mxb_fanout_counters(mxb_fanout *f);
 /* Ranges (same count and sizes as `local`) and counter address of child `k`,

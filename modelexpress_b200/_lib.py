@@ -137,6 +137,8 @@ SIGNATURES = {
     "mxb_convert_boxes": (i32, [_vp, i32, _P(ConvertBox), u64, u32, _P(u64)]),
     "mxb_fanout_plan": (i32, [_P(Span), u64, u64, _P(FanoutPiece), u64, _P(u64), _P(u32), u64, _P(u64)]),
     "mxb_fanout_create": (i32, [_vp, i32, _P(Span), u64, u64, _P(_vp)]),
+    "mxb_fanout_create_pieces": (i32, [_vp, i32, _P(Span), u64, u64, u64, _P(_vp)]),
+    "mxb_fanout_plan_pieces": (i32, [_P(Span), u64, u64, u64, _P(FanoutPiece), u64, _P(u64), _P(u32), u64, _P(u64)]),
     "mxb_fanout_counters": (u64, [_vp]),
     "mxb_fanout_set_child": (i32, [_vp, i32, _P(Span), u64, u64]),
     "mxb_fanout_set_engine": (i32, [_vp, i32]),

@@ -278,18 +278,11 @@ struct mxb_fanout {
 namespace {
 
 // Pieces of a payload: walk the concatenated byte space of the ranges; cut at range ends,
-// chunk ends and 64 KiB.  Every piece start stays 16-byte aligned inside its range: only a
+// chunk ends and the piece size (64 KiB unless the caller names another).  Every piece start stays 16-byte aligned inside its range: only a
 // range's last piece may be ragged.  Depends on the range sizes alone, so every GPU of a
 // broadcast (same sizes, own addresses) cuts the same pieces and counts the same chunks.
-void plan_pieces(const mxb_span *local, uint64_t n, uint64_t chunk_bytes,
+void plan_pieces(const mxb_span *local, uint64_t n, uint64_t chunk_bytes, uint64_t piece_max,
                  std::vector<mxb_fanout_piece> &pieces, std::vector<uint32_t> &chunk_pieces) {
-    uint64_t piece_max = kFanPiece;
-    // Measurement aid (must be the same in every process of a broadcast): pieces of 16, 32, 128
-    // or 256 KiB instead of 64.  Pieces above 64 KiB run on the store kernel only.
-    if (const char *e = getenv("MXB_FANOUT_PIECE_KIB")) {
-        const long v = atol(e);
-        if (v == 16 || v == 32 || v == 128 || v == 256) piece_max = (uint64_t)v << 10;
-    }
     uint64_t vpos = 0;
     for (uint64_t i = 0; i < n; ++i) {
         uint64_t off = 0;
@@ -314,17 +307,29 @@ void plan_pieces(const mxb_span *local, uint64_t n, uint64_t chunk_bytes,
 
 extern "C" {
 
+static bool piece_ok(uint64_t piece_bytes) {
+    return piece_bytes >= 4096 && piece_bytes <= MXB_FANOUT_PIECE_MAX && !(piece_bytes & 15u);
+}
+
 int32_t mxb_fanout_plan(const mxb_span *local, uint64_t n, uint64_t chunk_bytes,
                         mxb_fanout_piece *pieces, uint64_t piece_cap, uint64_t *n_pieces,
                         uint32_t *chunk_pieces, uint64_t chunk_cap, uint64_t *n_chunks) {
+    return mxb_fanout_plan_pieces(local, n, chunk_bytes, kFanPiece, pieces, piece_cap, n_pieces, chunk_pieces,
+                                  chunk_cap, n_chunks);
+}
+
+int32_t mxb_fanout_plan_pieces(const mxb_span *local, uint64_t n, uint64_t chunk_bytes, uint64_t piece_bytes,
+                               mxb_fanout_piece *pieces, uint64_t piece_cap, uint64_t *n_pieces,
+                               uint32_t *chunk_pieces, uint64_t chunk_cap, uint64_t *n_chunks) {
     if ((!local && n) || !n_pieces || !n_chunks || chunk_bytes < 4096 || (chunk_bytes & 15u) ||
-        (!pieces && piece_cap) || (!chunk_pieces && chunk_cap)) {
-        set_error("mxb_fanout_plan: bad arguments (chunk must be a multiple of 16, >= 4096)");
+        !piece_ok(piece_bytes) || (!pieces && piece_cap) || (!chunk_pieces && chunk_cap)) {
+        set_error("mxb_fanout_plan: bad arguments (chunk and piece must be multiples of 16, >= 4096; "
+                  "a piece at most 1 MiB)");
         return MXB_ERR_ARG;
     }
     std::vector<mxb_fanout_piece> plan;
     std::vector<uint32_t> per_chunk;
-    plan_pieces(local, n, chunk_bytes, plan, per_chunk);
+    plan_pieces(local, n, chunk_bytes, piece_bytes, plan, per_chunk);
     *n_pieces = plan.size();
     *n_chunks = per_chunk.size();
     for (uint64_t i = 0; i < plan.size() && i < piece_cap; ++i) pieces[i] = plan[i];
@@ -340,8 +345,14 @@ int32_t mxb_fanout_plan(const mxb_span *local, uint64_t n, uint64_t chunk_bytes,
 
 int32_t mxb_fanout_create(mxb_ctx *ctx, int32_t dev, const mxb_span *local, uint64_t n,
                           uint64_t chunk_bytes, mxb_fanout **out) {
-    if (!ctx || !local || !n || !out || chunk_bytes < 4096 || (chunk_bytes & 15u)) {
-        set_error("mxb_fanout_create: bad arguments (chunk must be a multiple of 16, >= 4096)");
+    return mxb_fanout_create_pieces(ctx, dev, local, n, chunk_bytes, kFanPiece, out);
+}
+
+int32_t mxb_fanout_create_pieces(mxb_ctx *ctx, int32_t dev, const mxb_span *local, uint64_t n,
+                                 uint64_t chunk_bytes, uint64_t piece_bytes, mxb_fanout **out) {
+    if (!ctx || !local || !n || !out || chunk_bytes < 4096 || (chunk_bytes & 15u) || !piece_ok(piece_bytes)) {
+        set_error("mxb_fanout_create: bad arguments (chunk and piece must be multiples of 16, >= 4096; "
+                  "a piece at most 1 MiB)");
         return MXB_ERR_ARG;
     }
     DeviceState *dv = ctx->find(dev);
@@ -361,7 +372,7 @@ int32_t mxb_fanout_create(mxb_ctx *ctx, int32_t dev, const mxb_span *local, uint
     f->local.assign(local, local + n);
     f->chunk_bytes = chunk_bytes;
     std::vector<mxb_fanout_piece> plan;
-    plan_pieces(local, n, chunk_bytes, plan, f->chunk_pieces);
+    plan_pieces(local, n, chunk_bytes, piece_bytes, plan, f->chunk_pieces);
     for (const mxb_fanout_piece &p : plan) {
         f->pieces.push_back({local[p.range].ptr + p.offset, p.nbytes, p.chunk});
         f->piece_range.push_back(p.range);

@@ -78,9 +78,9 @@ def topology(kind: str, n: int, root: int = 0) -> list:
     return children
 
 
-def plan_pieces(sizes, chunk_bytes: int) -> tuple:
-    """Host only (``mxb_fanout_plan``): how ranges of the given sizes are cut into pieces
-    and chunks.  Returns ``(pieces, chunk_pieces)``: ``pieces`` is a list of
+def plan_pieces(sizes, chunk_bytes: int, piece_bytes: int = 65536) -> tuple:
+    """Host only (``mxb_fanout_plan_pieces``): how ranges of the given sizes are cut into pieces
+    (of at most ``piece_bytes``) and chunks.  Returns ``(pieces, chunk_pieces)``: ``pieces`` is a list of
     ``(range, offset, nbytes, chunk)``, ``chunk_pieces[c]`` what a child's arrival
     counter ``c`` reaches per broadcast."""
     import ctypes
@@ -90,13 +90,15 @@ def plan_pieces(sizes, chunk_bytes: int) -> tuple:
     lib = _lib.load()
     spans, n = _lib.span_array([(4096, int(s)) for s in sizes])
     np_, nc = ctypes.c_uint64(), ctypes.c_uint64()
-    rc = lib.mxb_fanout_plan(spans, n, int(chunk_bytes), None, 0, ctypes.byref(np_), None, 0, ctypes.byref(nc))
+    rc = lib.mxb_fanout_plan_pieces(spans, n, int(chunk_bytes), int(piece_bytes), None, 0, ctypes.byref(np_),
+                                    None, 0, ctypes.byref(nc))
     if rc not in (0, -7):
         _lib.check(rc, "mxb_fanout_plan")
     pieces = (_lib.FanoutPiece * max(1, np_.value))()
     per_chunk = (ctypes.c_uint32 * max(1, nc.value))()
-    _lib.check(lib.mxb_fanout_plan(spans, n, int(chunk_bytes), pieces, np_.value, ctypes.byref(np_),
-                                   per_chunk, nc.value, ctypes.byref(nc)), "mxb_fanout_plan")
+    _lib.check(lib.mxb_fanout_plan_pieces(spans, n, int(chunk_bytes), int(piece_bytes), pieces, np_.value,
+                                          ctypes.byref(np_), per_chunk, nc.value, ctypes.byref(nc)),
+               "mxb_fanout_plan")
     return ([(int(p.range), int(p.offset), int(p.nbytes), int(p.chunk)) for p in pieces[: np_.value]],
             [int(x) for x in per_chunk[: nc.value]])
 
@@ -107,11 +109,12 @@ class Broadcast:
     every GPU."""
 
     def __init__(self, ctx: Context, devices: list, spans: list, chunk_bytes: int,
-                 kind: str = "chain", root_index: int = 0, engine: str | None = None):
+                 kind: str = "chain", root_index: int = 0, engine: str | None = None,
+                 piece_bytes: int = 65536):
         self.devices = devices
         self.root = root_index
         self.children = topology(kind, len(devices), root_index)
-        self.nodes = [Fanout(ctx, dev, spans[i], chunk_bytes) for i, dev in enumerate(devices)]
+        self.nodes = [Fanout(ctx, dev, spans[i], chunk_bytes, piece_bytes) for i, dev in enumerate(devices)]
         if engine is not None:
             for node in self.nodes:
                 node.set_engine(engine)
@@ -279,7 +282,8 @@ class FanoutSource:
     replicas that ask (``serve``).  ``tensors`` is ``{name: CUDA tensor}``."""
 
     def __init__(self, tensors: dict, rendezvous_dir: str, source_id: str, ctx: Context | None = None,
-                 device: int | None = None, chunk_bytes: int = 64 << 10, digests: bool = True):
+                 device: int | None = None, chunk_bytes: int = 256 << 10, digests: bool = True,
+                 piece_bytes: int = 256 << 10):
         import torch
 
         from .runtime import default_context
@@ -287,6 +291,8 @@ class FanoutSource:
         self.dev = torch.cuda.current_device() if device is None else int(device)
         self.ctx = ctx if ctx is not None else default_context(self.dev)
         self.dir, self.id, self.chunk_bytes = rendezvous_dir, source_id, int(chunk_bytes)
+        # a push is one hop: larger pieces (fewer system-scope fences per byte) are faster there
+        self.piece_bytes = min(int(piece_bytes), int(chunk_bytes))
         self.rows = _tensor_rows(tensors, self.dev)
         self._keep = tensors
         self._digests = None
@@ -312,7 +318,8 @@ class FanoutSource:
             for r, d in zip(rows, self._digests):
                 r["digest"] = d
         _write_json(self.manifest_path, {"source_id": self.id, "status": "READY", "device_id": self.dev,
-                                         "chunk_bytes": self.chunk_bytes, "tensors": rows})
+                                         "chunk_bytes": self.chunk_bytes, "piece_bytes": self.piece_bytes,
+                                         "tensors": rows})
         return self.manifest_path
 
     def withdraw(self) -> None:
@@ -354,7 +361,7 @@ class FanoutSource:
             local.append((d.addr, d.size))
             child.append((self._peers.row_address(row), d.size))
         counters = self._peers.address(req["counters"]["handle"], req["counters"]["offset"])
-        node = self.ctx.fanout(local, int(req["chunk_bytes"]), self.dev)
+        node = self.ctx.fanout(local, int(req["chunk_bytes"]), self.dev, int(req.get("piece_bytes", 65536)))
         try:
             node.add_child(child, counters)
             node.run(True, int(req.get("timeout_ms", 5000)))
@@ -479,8 +486,9 @@ class B200FanoutStrategy:
         rows = [d for d in target if d.size]
         spans = [(d.addr, d.size) for d in rows]
         chunk = int(manifest.get("chunk_bytes", 1 << 20))
+        piece = int(manifest.get("piece_bytes", 65536))
         torch.cuda.synchronize(dev)
-        node = mx.fanout(spans, chunk, dev)
+        node = mx.fanout(spans, chunk, dev, piece)
         d = self._dir(ctx)
         req_id = uuid.uuid4().hex
         done = os.path.join(d, f"{manifest['source_id']}.done.{req_id}.json")
@@ -488,7 +496,7 @@ class B200FanoutStrategy:
             from .runtime import ipc_export
 
             ch, coff = ipc_export(node.counters)
-            request = {"chunk_bytes": chunk, "timeout_ms": self.timeout_ms, "done": done,
+            request = {"chunk_bytes": chunk, "piece_bytes": piece, "timeout_ms": self.timeout_ms, "done": done,
                        "counters": {"handle": ch.hex(), "offset": coff},
                        "tensors": [r for r in _export_rows(rows)]}
             request_path = os.path.join(d, f"{manifest['source_id']}.request.{req_id}.json")

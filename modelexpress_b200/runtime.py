@@ -197,8 +197,8 @@ class Context:
     def ring(self, ring_bytes: int = 2 << 30, slots: int = 32, dev: int | None = None) -> "Ring":
         return Ring(self, self._dev(dev), ring_bytes, slots)
 
-    def fanout(self, local_spans, chunk_bytes: int, dev: int | None = None) -> "Fanout":
-        return Fanout(self, self._dev(dev), local_spans, chunk_bytes)
+    def fanout(self, local_spans, chunk_bytes: int, dev: int | None = None, piece_bytes: int = 65536) -> "Fanout":
+        return Fanout(self, self._dev(dev), local_spans, chunk_bytes, piece_bytes)
 
 
 def coalesce_runs(runs) -> np.ndarray:
@@ -410,13 +410,13 @@ class PackedImage:
 class Fanout:
     """One node of a chunked, pipelined broadcast (see ``fanout.py`` for topologies)."""
 
-    def __init__(self, ctx: Context, dev: int, local_spans, chunk_bytes: int):
+    def __init__(self, ctx: Context, dev: int, local_spans, chunk_bytes: int, piece_bytes: int = 65536):
         self.ctx, self.dev = ctx, dev
         arr, n = _lib.span_array(local_spans)
         self.n = n
         h = ctypes.c_void_p()
-        check(ctx._lib.mxb_fanout_create(ctx._h, dev, arr, n, int(chunk_bytes), ctypes.byref(h)),
-              "mxb_fanout_create")
+        check(ctx._lib.mxb_fanout_create_pieces(ctx._h, dev, arr, n, int(chunk_bytes), int(piece_bytes),
+                                                ctypes.byref(h)), "mxb_fanout_create")
         self._h = h
         self.children = 0
 

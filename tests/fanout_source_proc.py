@@ -3,8 +3,8 @@
     python tests/fanout_source_proc.py <rendezvous dir> <source id> <seed> <mode>
 
 Builds the seeded tensors on cuda:0, publishes the manifest, prints ``ready``, then
-(mode ``serve``) answers one request and prints ``served``, or (mode ``silent``) answers
-nothing.  Stays alive, keeping its memory mapped for the peer, until a line arrives on
+(mode ``serve``, or ``serve256`` with the default chunk and piece sizes) answers one request
+and prints ``served``, or (mode ``silent``) answers nothing.  Stays alive, keeping its memory mapped for the peer, until a line arrives on
 stdin."""
 
 import os
@@ -37,10 +37,14 @@ def main():
     rendezvous, source_id, seed, mode = sys.argv[1], sys.argv[2], int(sys.argv[3]), sys.argv[4]
     torch.cuda.set_device(0)
     tensors = seeded_tensors(seed)
-    src = FanoutSource(tensors, rendezvous, source_id, chunk_bytes=64 << 10)
+    if mode == "serve256":      # the defaults of a one-hop push: 256 KiB chunks of one 256 KiB piece
+        src = FanoutSource(tensors, rendezvous, source_id)
+        assert src.piece_bytes == 256 << 10
+    else:
+        src = FanoutSource(tensors, rendezvous, source_id, chunk_bytes=64 << 10)
     src.publish()
     print("ready", flush=True)
-    if mode == "serve":
+    if mode in ("serve", "serve256"):
         n = src.serve(timeout_s=60.0, max_requests=1)
         print(f"served {n}", flush=True)
     sys.stdin.readline()

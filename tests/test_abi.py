@@ -248,3 +248,35 @@ def test_plan_reshard_agrees_with_the_python_clip(lib):
                          0, 1 << 23, 0)
     assert len(big) > len(whole) and int((big[:, 2] * big[:, 3]).max()) <= 1 << 20
     assert int((big[:, 2] * big[:, 3]).sum()) == int((whole[:, 2] * whole[:, 3]).sum())
+
+
+def test_fanout_plan_piece_sizes():
+    """``mxb_fanout_plan_pieces`` (host only): pieces tile every range exactly once, stay inside
+    the chunk they start in (but for a 16-byte alignment piece) and within the piece size, start on 16-byte boundaries inside their range, and only a
+    range's last piece is ragged; the plan depends on the sizes alone."""
+    import pytest
+
+    from modelexpress_b200 import _lib
+    from modelexpress_b200.fanout import plan_pieces
+
+    sizes = [3 << 20, 4096 + 16, 100, 333 * 16, 1 << 20, 52, 700_000, 0, 48]
+    for chunk, piece in ((1 << 20, 64 << 10), (1 << 20, 256 << 10), (256 << 10, 256 << 10), (64 << 10, 64 << 10),
+                         (64 << 10, 256 << 10), (4096, 4096)):
+        pieces, per_chunk = plan_pieces(sizes, chunk, piece)
+        assert sum(per_chunk) == len(pieces)
+        at, vpos = [0] * len(sizes), 0
+        for rng, off, n, ch in pieces:
+            assert off == at[rng] and 0 < n <= min(piece, chunk) and off % 16 == 0
+            # a piece belongs to the chunk it starts in; only a 16-byte piece that keeps a range's
+            # 16-byte phase may reach past the chunk's end
+            assert vpos // chunk == ch and ((vpos + n - 1) // chunk == ch or n <= 16)
+            assert n % 16 == 0 or off + n == sizes[rng]                     # only a last piece is ragged
+            at[rng] += n
+            vpos += n
+        assert at == sizes
+        if piece >= chunk:
+            assert all(c >= 1 for c in per_chunk)
+    assert plan_pieces(sizes, 1 << 20) == plan_pieces(sizes, 1 << 20, 64 << 10)   # the default piece
+    for bad in (100, 2 << 20, 65536 + 8):
+        with pytest.raises(_lib.MxbError):
+            plan_pieces(sizes, 1 << 20, bad)

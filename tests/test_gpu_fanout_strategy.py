@@ -200,7 +200,7 @@ def test_push_into_a_target_whose_parameters_live_in_a_published_arena(tmp_path)
 
         ctx = _Ctx()
         ctx.adapter = Adapter()
-        live = _spawn(rendezvous, "arena_src", 8, "serve")
+        live = _spawn(rendezvous, "arena_src", 8, "serve256")
         try:
             res = B200FanoutStrategy(rendezvous, timeout_ms=5000, wait_for_push=True).load(
                 LoadResult(value=None, model=None), ctx)
