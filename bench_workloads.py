@@ -294,8 +294,11 @@ def fanout_measure(args, ctx, rank, world, local, nv=None) -> dict:
     kinds = os.environ.get("MXB_FANOUT_TOPOLOGY", "chain").split(",")
     # the sweep the benchmark configuration names (1, 4, 16, 64 MiB) plus two finer points (a chunk
     # of one 64 KiB piece is the finest the counters resolve)
-    chunks_mib = {"vector": [float(x) for x in os.environ.get("MXB_FANOUT_CHUNKS", "0.0625,0.25,1,4,16,64").split(",")]}
-    engines = os.environ.get("MXB_FANOUT_ENGINES", "vector").split(",")
+    chunks_mib = {"vector": [float(x) for x in os.environ.get("MXB_FANOUT_CHUNKS", "0.0625,0.25,1,4,16,64").split(",")],
+                  "dma": [64.0]}
+    # the copy-engine push announces everything at the end: it is measured where the broadcast is
+    # one hop (two GPUs); on a longer chain every hop would wait for the whole payload
+    engines = os.environ.get("MXB_FANOUT_ENGINES", "vector,dma" if world == 2 else "vector").split(",")
     launches = 0
     for kind in kinds:
         children = topology(kind, world, 0)
@@ -377,34 +380,40 @@ def fanout_measure(args, ctx, rank, world, local, nv=None) -> dict:
             g.manual_seed(100 + rank)
             arena[:pay].copy_(torch.randint(0, 256, (pay,), dtype=torch.uint8, device="cuda", generator=g))
         torch.cuda.synchronize()
-        # one hop: 256 KiB pieces (fewer system-scope fences per byte than the chain's 64 KiB)
-        node = ctx.fanout(pspans, 16 << 20, local, 256 << 10)
-        ctrs = _open_peers(ctx, node.counters, world)
-        if rank < half:
-            node.add_child([(peers[rank + half], pay)], ctrs[rank + half])
-        _barrier(world)
-        times = []
-        for it in range(warmup + steps):
-            if rank >= half:
-                arena[:pay].zero_()
-                torch.cuda.synchronize()
+        # one hop: 256 KiB pieces (fewer system-scope fences per byte than the chain's 64 KiB) for the
+        # store kernel; the copy-engine push beside it (every range one peer copy, one announcement)
+        pairs = {"pairs": half, "bytes_per_pair": pay, "piece_bytes": 256 << 10}
+        for engine in ("vector", "dma"):
+            node = ctx.fanout(pspans, 16 << 20, local, 256 << 10)
+            node.set_engine(engine)
+            ctrs = _open_peers(ctx, node.counters, world)
+            if rank < half:
+                node.add_child([(peers[rank + half], pay)], ctrs[rank + half])
             _barrier(world)
-            node.run(rank < half, 20000)
-            ms = _max(node.wait(), world)
-            launches += 1
-            if it >= warmup:
-                times.append(ms)
-        recs = ctx.digest(pspans, DIGEST_SAFE32 | DIGEST_BLOCK64, local)
-        alld = _gather_objects((int(recs[0].safe_checksum), int(recs[0].block_hash)), world)
-        for r in range(half):
-            if alld[r] != alld[r + half]:
-                raise SystemExit(f"pair copy: GPU {r + half} differs from GPU {r}")
-        pms = sum(times) / len(times)
-        pairs = {"pairs": half, "bytes_per_pair": pay, "piece_bytes": 256 << 10, "device_ms": round(pms, 3),
-                 "gbs_per_pair": round(pay / (pms * 1e-3) / 1e9, 1),
-                 "gbs_aggregate": round(pay * half / (pms * 1e-3) / 1e9, 1)}
-        _barrier(world)
-        node.close()
+            times = []
+            for it in range(warmup + steps):
+                if rank >= half:
+                    arena[:pay].zero_()
+                    torch.cuda.synchronize()
+                _barrier(world)
+                node.run(rank < half, 20000)
+                ms = _max(node.wait(), world)
+                launches += 1
+                if it >= warmup:
+                    times.append(ms)
+            recs = ctx.digest(pspans, DIGEST_SAFE32 | DIGEST_BLOCK64, local)
+            alld = _gather_objects((int(recs[0].safe_checksum), int(recs[0].block_hash)), world)
+            for r in range(half):
+                if alld[r] != alld[r + half]:
+                    raise SystemExit(f"pair copy ({engine}): GPU {r + half} differs from GPU {r}")
+            pms = sum(times) / len(times)
+            res_e = {"device_ms": round(pms, 3), "gbs_per_pair": round(pay / (pms * 1e-3) / 1e9, 1),
+                     "gbs_aggregate": round(pay * half / (pms * 1e-3) / 1e9, 1)}
+            pairs[engine] = res_e
+            _barrier(world)
+            node.close()
+        best = max(("vector", "dma"), key=lambda e: pairs[e]["gbs_per_pair"])
+        pairs.update(pairs[best], engine=best)
     first = topologies[kinds[0]]
     peak = (nv or {}).get("peak_gbs")
     res = {"workload": "configs[2]: 16.06 GB TP=1 copy on GPU 0 broadcast over NVLink P2P stores",

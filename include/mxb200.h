@@ -504,14 +504,19 @@ uint64_t mxb_fanout_counters(mxb_fanout *f);
 int32_t mxb_fanout_set_child(mxb_fanout *f, int32_t k, const mxb_span *child, uint64_t n,
                              uint64_t child_counters);
 /* How a node moves its chunks (default: VECTOR, or what the environment variable
- * MXB_FANOUT_ENGINE = "vector" | "bulk" names when the node is created).
+ * MXB_FANOUT_ENGINE = "vector" | "bulk" | "dma" names when the node is created).
  *   VECTOR  one persistent kernel, 16-byte peer stores straight from HBM;
- *   BULK    one persistent kernel, pieces staged through shared memory with bulk copies.
- * Both speak the same counters, so the nodes of one broadcast may differ.  The
+ *   BULK    one persistent kernel, pieces staged through shared memory with bulk copies;
+ *   DMA     for a root: the copy engines move every range to every child (one peer copy
+ *           each, children side by side), then one launch announces all chunks at once.
+ *           Nothing is announced before everything has arrived, so it suits pushes whose
+ *           children only receive (one hop); a node that has a parent runs VECTOR.
+ * All speak the same counters, so the nodes of one broadcast may differ.  The
  * reference has no counterpart: its pull is one RDMA READ per tensor with no
  * forwarding (nixl_transfer.py:769-952). */
 #define MXB_FANOUT_ENGINE_VECTOR 0
 #define MXB_FANOUT_ENGINE_BULK 1
+#define MXB_FANOUT_ENGINE_DMA 2
 int32_t mxb_fanout_set_engine(mxb_fanout *f, int32_t engine);
 /* Launch this node's kernel for one broadcast.  `is_root`: has no parent.
  * `timeout_ms` bounds every device-side wait. */

@@ -38,6 +38,7 @@ struct FanArgs {
     uint32_t *counters;               // this GPU's arrival counters, one per chunk
     uint64_t child_counters[MXB_FANOUT_MAX_CHILDREN];
     uint64_t n_pieces;
+    uint32_t n_chunks;
     uint32_t n_children;
     uint32_t is_root;
     uint32_t run_index;  // 1-based
@@ -62,6 +63,26 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 __global__ void __launch_bounds__(kFanThreads) fanout_kernel(FanArgs a) {
     __shared__ uint32_t s_abort;
     const uint32_t tid = threadIdx.x;
+    if (a.n_children == 0) {
+        // a leaf forwards nothing: it only has to see every chunk arrive, one thread per chunk
+        if (a.is_root) return;
+        const uint64_t t0 = globaltimer_ns();
+        for (uint64_t c = (uint64_t)blockIdx.x * kFanThreads + tid; c < a.n_chunks;
+             c += (uint64_t)gridDim.x * kFanThreads) {
+            const uint32_t want = a.run_index * a.chunk_pieces[c];
+            uint32_t spins = 0;
+            while ((int32_t)(ld_acquire_sys(a.counters + c) - want) < 0) {
+                if ((++spins & 63u) == 0) {
+                    if (globaltimer_ns() - t0 > a.timeout_ns) {
+                        atomicExch(a.status, DEV_TIMEOUT);
+                        return;
+                    }
+                    __nanosleep(200);
+                }
+            }
+        }
+        return;
+    }
     if (tid == 0) s_abort = 0;
     __syncthreads();
     for (uint64_t p = blockIdx.x; p < a.n_pieces; p += gridDim.x) {
@@ -251,6 +272,17 @@ __global__ void __launch_bounds__(32) fanout_bulk_kernel(FanArgs a) {
     }
 }
 
+// Copy-engine push (root only): after the peer copies of every range have completed in stream
+// order, one launch announces every chunk to every child at once.
+__global__ void __launch_bounds__(256) fanout_announce_kernel(FanArgs a, uint32_t n_chunks) {
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= n_chunks) return;
+    __threadfence_system();
+    const uint32_t add = a.chunk_pieces[c];
+    for (uint32_t k = 0; k < a.n_children; ++k)
+        red_release_sys_add(reinterpret_cast<uint32_t *>(a.child_counters[k]) + c, add);
+}
+
 }  // namespace mxb
 
 using namespace mxb;
@@ -273,6 +305,9 @@ struct mxb_fanout {
     uint32_t run_index = 0;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     int32_t engine = MXB_FANOUT_ENGINE_VECTOR;
+    // copy-engine push: one stream and one completion event per child
+    cudaStream_t child_stream[MXB_FANOUT_MAX_CHILDREN] = {};
+    cudaEvent_t child_done[MXB_FANOUT_MAX_CHILDREN] = {};
 };
 
 namespace {
@@ -380,6 +415,7 @@ int32_t mxb_fanout_create_pieces(mxb_ctx *ctx, int32_t dev, const mxb_span *loca
     }
     if (const char *eng = getenv("MXB_FANOUT_ENGINE")) {
         if (!strcmp(eng, "bulk")) f->engine = MXB_FANOUT_ENGINE_BULK;
+        else if (!strcmp(eng, "dma")) f->engine = MXB_FANOUT_ENGINE_DMA;
     }
     DeviceGuard g(dev);
     const size_t nchunks = f->chunk_pieces.size() ? f->chunk_pieces.size() : 1;
@@ -401,7 +437,8 @@ int32_t mxb_fanout_create_pieces(mxb_ctx *ctx, int32_t dev, const mxb_span *loca
 }
 
 int32_t mxb_fanout_set_engine(mxb_fanout *f, int32_t engine) {
-    if (!f || (engine != MXB_FANOUT_ENGINE_VECTOR && engine != MXB_FANOUT_ENGINE_BULK)) {
+    if (!f || (engine != MXB_FANOUT_ENGINE_VECTOR && engine != MXB_FANOUT_ENGINE_BULK &&
+               engine != MXB_FANOUT_ENGINE_DMA)) {
         set_error("mxb_fanout_set_engine: unknown engine");
         return MXB_ERR_ARG;
     }
@@ -477,6 +514,7 @@ int32_t mxb_fanout_run(mxb_fanout *f, int32_t is_root, uint32_t timeout_ms) {
     a.counters = f->counters;
     for (uint32_t c = 0; c < f->n_children; ++c) a.child_counters[c] = f->child_counters[c];
     a.n_pieces = np;
+    a.n_chunks = (uint32_t)f->chunk_pieces.size();
     a.n_children = f->n_children;
     a.is_root = is_root ? 1u : 0u;
     a.run_index = ++f->run_index;
@@ -486,6 +524,44 @@ int32_t mxb_fanout_run(mxb_fanout *f, int32_t is_root, uint32_t timeout_ms) {
     // all CTAs must be co-resident: they wait on data, never on each other, but a
     // CTA that is not scheduled cannot forward its pieces
     const bool bulk = f->engine == MXB_FANOUT_ENGINE_BULK;
+    if (f->engine == MXB_FANOUT_ENGINE_DMA && is_root && f->n_children) {
+        // Copy-engine push: every range to every child with one peer copy (children on streams
+        // of their own, so their links run side by side), then one launch that announces all
+        // chunks.  Nothing is announced before everything has arrived, which suits a root whose
+        // children only receive; a node that waits for a parent keeps the store kernel.
+        MXB_CUDA(cudaEventRecord(f->ev0, dv->stream));
+        const uint32_t nchunks = (uint32_t)f->chunk_pieces.size();
+        for (uint32_t c = 0; c < f->n_children; ++c) {
+            if (!f->child_stream[c]) MXB_CUDA(cudaStreamCreateWithFlags(&f->child_stream[c], cudaStreamNonBlocking));
+            if (!f->child_done[c]) MXB_CUDA(cudaEventCreateWithFlags(&f->child_done[c], cudaEventDisableTiming));
+            MXB_CUDA(cudaStreamWaitEvent(f->child_stream[c], f->ev0, 0));
+            // ranges that follow one another in memory on both sides travel as one copy
+            uint64_t run_src = 0, run_dst = 0, run_len = 0;
+            for (size_t p = 0; p <= np; ++p) {
+                if (p < np && f->piece_off[p] != 0) continue;  // the first piece of a range stands for the range
+                const uint64_t src = p < np ? f->pieces[p].local : 0;
+                const uint64_t dst = p < np ? f->child_ptr[c][p] : 0;
+                const uint64_t len = p < np ? f->local[f->piece_range[p]].nbytes : 0;
+                if (p < np && run_len && src == run_src + run_len && dst == run_dst + run_len) {
+                    run_len += len;
+                    continue;
+                }
+                if (run_len)
+                    MXB_CUDA(cudaMemcpyAsync(reinterpret_cast<void *>(run_dst), reinterpret_cast<const void *>(run_src),
+                                             run_len, cudaMemcpyDeviceToDevice, f->child_stream[c]));
+                run_src = src;
+                run_dst = dst;
+                run_len = len;
+            }
+            MXB_CUDA(cudaEventRecord(f->child_done[c], f->child_stream[c]));
+            MXB_CUDA(cudaStreamWaitEvent(dv->stream, f->child_done[c], 0));
+        }
+        fanout_announce_kernel<<<(nchunks + 255) / 256, 256, 0, dv->stream>>>(a, nchunks);
+        MXB_CUDA(cudaGetLastError());
+        MXB_CUDA(cudaEventRecord(f->ev1, dv->stream));
+        f->ctx->launches.fetch_add(1);
+        return MXB_OK;
+    }
     if (bulk)
         for (const FanPiece &pc : f->pieces)
             if (pc.nbytes > kFanPiece) {
@@ -533,6 +609,13 @@ int32_t mxb_fanout_destroy(mxb_fanout *f) {
     if (!f) return MXB_OK;
     DeviceGuard g(f->dv->device);
     cudaStreamSynchronize(f->dv->stream);
+    for (int c = 0; c < MXB_FANOUT_MAX_CHILDREN; ++c) {
+        if (f->child_stream[c]) {
+            cudaStreamSynchronize(f->child_stream[c]);
+            cudaStreamDestroy(f->child_stream[c]);
+        }
+        if (f->child_done[c]) cudaEventDestroy(f->child_done[c]);
+    }
     if (f->counters) cudaFree(f->counters);
     if (f->dev_tables) cudaFree(f->dev_tables);
     if (f->ev0) cudaEventDestroy(f->ev0);

@@ -283,7 +283,7 @@ class FanoutSource:
 
     def __init__(self, tensors: dict, rendezvous_dir: str, source_id: str, ctx: Context | None = None,
                  device: int | None = None, chunk_bytes: int = 256 << 10, digests: bool = True,
-                 piece_bytes: int = 256 << 10):
+                 piece_bytes: int = 256 << 10, engine: str | None = "dma"):
         import torch
 
         from .runtime import default_context
@@ -291,8 +291,11 @@ class FanoutSource:
         self.dev = torch.cuda.current_device() if device is None else int(device)
         self.ctx = ctx if ctx is not None else default_context(self.dev)
         self.dir, self.id, self.chunk_bytes = rendezvous_dir, source_id, int(chunk_bytes)
-        # a push is one hop: larger pieces (fewer system-scope fences per byte) are faster there
+        # a push is one hop: larger pieces (fewer system-scope fences per byte) are faster there,
+        # and the copy engines faster still ("dma"; None: the library's default, the store kernel,
+        # or what MXB_FANOUT_ENGINE names)
         self.piece_bytes = min(int(piece_bytes), int(chunk_bytes))
+        self.engine = None if os.environ.get("MXB_FANOUT_ENGINE") else engine
         self.rows = _tensor_rows(tensors, self.dev)
         self._keep = tensors
         self._digests = None
@@ -363,6 +366,8 @@ class FanoutSource:
         counters = self._peers.address(req["counters"]["handle"], req["counters"]["offset"])
         node = self.ctx.fanout(local, int(req["chunk_bytes"]), self.dev, int(req.get("piece_bytes", 65536)))
         try:
+            if self.engine:
+                node.set_engine(self.engine)
             node.add_child(child, counters)
             node.run(True, int(req.get("timeout_ms", 5000)))
             ms = node.wait()

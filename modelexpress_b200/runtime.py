@@ -420,11 +420,12 @@ class Fanout:
         self._h = h
         self.children = 0
 
-    ENGINES = {"vector": 0, "bulk": 1}
+    ENGINES = {"vector": 0, "bulk": 1, "dma": 2}
 
     def set_engine(self, engine: str) -> None:
-        """"vector" (16-byte peer stores straight from HBM) or "bulk" (staged through shared memory
-        with bulk copies); the nodes of one broadcast may differ."""
+        """"vector" (16-byte peer stores straight from HBM), "bulk" (staged through shared memory
+        with bulk copies) or, for a root whose children only receive, "dma" (copy engines, then one
+        launch that announces every chunk); the nodes of one broadcast may differ."""
         if engine not in self.ENGINES:
             raise ValueError(f"unknown fan-out engine {engine!r}")
         check(self.ctx._lib.mxb_fanout_set_engine(self._h, self.ENGINES[engine]), "mxb_fanout_set_engine")

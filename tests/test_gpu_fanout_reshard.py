@@ -16,7 +16,7 @@ def _spans(torch, tensors):
     return [(t.data_ptr(), t.numel() * t.element_size()) for t in tensors]
 
 
-@pytest.mark.parametrize("engine", ["vector", "bulk"])
+@pytest.mark.parametrize("engine", ["vector", "bulk", "dma"])
 def test_fanout_single_gpu_loopback(engine, monkeypatch):
     """Root pushes to a 'child' on the same device; then the child's kernel runs
     and finds every chunk counter already satisfied.  Every engine; the ranges
@@ -106,7 +106,7 @@ def test_manifest_matching_rules():
 
 
 @pytest.mark.parametrize("kind,engine", [("chain", "vector"), ("tree", "vector"), ("flat", "vector"),
-                                         ("chain", "bulk"), ("tree", "bulk")])
+                                         ("chain", "bulk"), ("tree", "bulk"), ("flat", "dma"), ("chain", "dma")])
 def test_fanout_across_gpus(kind, engine):
     import torch
 
