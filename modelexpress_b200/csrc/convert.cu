@@ -108,11 +108,11 @@ __device__ __forceinline__ void cast_vec(const typename S::store *__restrict__ s
 }
 
 template <typename S, typename D>
-__device__ void rows_tile(const CvtItem &it, uint64_t t, unsigned char *) {
+__device__ void rows_tile(const CvtItem &it, uint32_t t, unsigned char *) {
     using SE = typename S::store;
     using DE = typename D::store;
-    const uint32_t ta = (uint32_t)(t % it.tiles_a);
-    uint64_t row = t / it.tiles_a;
+    const uint32_t ta = t % it.tiles_a;
+    uint32_t row = t / it.tiles_a;   // a box's tile count fits 32 bits (checked on the host)
     const uint32_t a0 = ta * kRowTile;
     const uint32_t len = min(kRowTile, it.n[3] - a0);
     int64_t off = 0, soff = 0;
@@ -167,17 +167,17 @@ struct TileAt {
     uint32_t na, nb;     // valid extent of this tile
 };
 
-__device__ __forceinline__ TileAt tile_at(const CvtItem &it, uint64_t t, uint32_t edge_a, uint32_t edge_b) {
+__device__ __forceinline__ TileAt tile_at(const CvtItem &it, uint32_t t, uint32_t edge_a, uint32_t edge_b) {
     const uint32_t b = it.bdim;
-    const uint32_t ta = (uint32_t)(t % it.tiles_a);
+    const uint32_t ta = t % it.tiles_a;
     t /= it.tiles_a;
-    const uint32_t tb = (uint32_t)(t % it.tiles_b);
-    uint64_t rest = t / it.tiles_b;
+    const uint32_t tb = t % it.tiles_b;
+    uint32_t rest = t / it.tiles_b;
     // the two dims that are neither the source's inner dim nor the destination's
     uint32_t idx[3] = {0, 0, 0};
     for (int d = 2; d >= 0; --d) {
         if ((uint32_t)d == b) continue;
-        idx[d] = (uint32_t)(rest % it.n[d]);
+        idx[d] = rest % it.n[d];
         rest /= it.n[d];
     }
     const uint32_t a0 = ta * edge_a, b0 = tb * edge_b;
@@ -206,7 +206,7 @@ struct Group {
 // and writes Group<destination> elements along the destination's, eight rows in flight per
 // warp.  The host selects it only when every such group is naturally aligned on both sides.
 template <typename S, typename D>
-__device__ void wide_tile(const CvtItem &it, uint64_t t, unsigned char *smem_raw) {
+__device__ void wide_tile(const CvtItem &it, uint32_t t, unsigned char *smem_raw) {
     using SE = typename S::store;
     using DE = typename D::store;
     constexpr int GS = Group<SE>::n, GD = Group<DE>::n;
@@ -265,12 +265,12 @@ __device__ void wide_tile(const CvtItem &it, uint64_t t, unsigned char *smem_raw
 // and l + 32 at one column (conflict-free with the odd pitch) and writes 4 bytes each, 128
 // contiguous bytes per warp instruction.  Same tile shape and alignment rules as wide_tile.
 template <typename S, typename D>
-__device__ void packed_tile(const CvtItem &it, uint64_t t, unsigned char *smem_raw) {
+__device__ void packed_tile(const CvtItem &it, uint32_t t, unsigned char *smem_raw) {
     using SE = typename S::store;
     using DE = typename D::store;
     static_assert(sizeof(DE) == 2, "packed tiles hold two-byte destination elements");
     constexpr int GS = Group<SE>::n;
-    constexpr uint32_t TA = 32 * GS, TB = 128, kPairs = TB / 2;
+    constexpr uint32_t TA = 32 * GS, TB = 128;
     using SG = typename Bytes<GS * sizeof(SE)>::type;
     uint32_t(*words)[TA + 1] = reinterpret_cast<uint32_t(*)[TA + 1]>(smem_raw);
     const TileAt at = tile_at(it, t, TA, TB);
@@ -325,7 +325,7 @@ __device__ void packed_tile(const CvtItem &it, uint64_t t, unsigned char *smem_r
 }
 
 template <typename S, typename D>
-__device__ void transpose_tile(const CvtItem &it, uint64_t t, unsigned char *smem_raw) {
+__device__ void transpose_tile(const CvtItem &it, uint32_t t, unsigned char *smem_raw) {
     using SE = typename S::store;
     using DE = typename D::store;
     DE(*tile)[kTT + 1] = reinterpret_cast<DE(*)[kTT + 1]>(smem_raw);
@@ -403,7 +403,7 @@ __device__ void transpose_tile(const CvtItem &it, uint64_t t, unsigned char *sme
 }
 
 template <typename S, typename D>
-__device__ __forceinline__ void one_tile(const CvtItem &it, uint64_t t, unsigned char *smem) {
+__device__ __forceinline__ void one_tile(const CvtItem &it, uint32_t t, unsigned char *smem) {
     if (it.mode == 0) rows_tile<S, D>(it, t, smem);
     else if (it.mode == 2) {
         if constexpr (sizeof(typename D::store) == 2 && sizeof(typename S::store) >= 2 &&
@@ -447,7 +447,7 @@ __global__ void __launch_bounds__(kCvtThreads, 4) convert_kernel(const CvtItem *
             if (threadIdx.x == 0) cur_index = lo;
             __syncthreads();
         }
-        one_tile<S, D>(cur, t - cur.tile0, smem);
+        one_tile<S, D>(cur, (uint32_t)(t - cur.tile0), smem);
         __syncthreads();  // `cur` may be replaced for the next tile
     }
 }
@@ -603,6 +603,7 @@ int32_t canonical(const mxb_convert &c, CvtItem *out, uint64_t *bytes) {
             if (out->n[d] > 1 && out->ss[d] % 2) pair = false;
         out->pair = pair ? 1u : 0u;
     }
+    if (tiles > 0xffffffffull) return MXB_ERR_UNSUPPORTED;  // the kernel indexes a box's tiles with 32 bits
     out->tile0 = tiles;  // the caller turns counts into a prefix
     return MXB_OK;
 }
