@@ -224,8 +224,8 @@ class ArenaServer:
             with conn:
                 try:
                     send_arena(conn, self.arena)
-                except OSError:
-                    pass
+                except (OSError, _lib.MxbError):
+                    pass      # a peer that hung up, or an arena closed under us: serve the next one
 
     def close(self) -> None:
         self._stop.set()
