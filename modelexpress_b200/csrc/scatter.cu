@@ -384,7 +384,9 @@ static bool bulk_shape_ok(const mxb_desc2d &d) {
 // from the vector engine (many warps posting 16-byte stores) than from the bulk
 // engine (one warp per SM issuing bulk copies), so records that touch peer memory
 // are routed to the vector engine.  Allocations are few (one arena per peer), so
-// a small cache of ranges answers per record.
+// a small cache of ranges answers per record.  (A peer range mapped through CUDA IPC
+// answers the pointer query with the device that opened it and so counts as local:
+// its records take the bulk engine, whose bulk stores cross NVLink as well.)
 class PeerRanges {
   public:
     explicit PeerRanges(int device) : device_(device) {
