@@ -418,7 +418,11 @@ def bench_place(args):
         dev_buf.copy_(pin, non_blocking=True)
     ev1.record()
     torch.cuda.synchronize()
-    pcie_gbs = sum_over_ranks(3 * (1 << 30) / (ev0.elapsed_time(ev1) * 1e-3) / 1e9, world)
+    copy_ms = ev0.elapsed_time(ev1)
+    pcie_gbs = sum_over_ranks(3 * (1 << 30) / (copy_ms * 1e-3) / 1e9, world)
+    # the same copies on the basis `value` is measured on: all bytes over the slowest rank's time
+    # (ranks whose links get a smaller share finish later; the sum of rates does not show that)
+    pcie_all_done_gbs = world * 3 * (1 << 30) / (max_over_ranks(copy_ms, world) * 1e-3) / 1e9
     pcie_single = None
     if world > 1:
         barrier(world)
@@ -546,7 +550,9 @@ def bench_place(args):
                       "device_s_per_step": round(sum(p.stats.seconds_device for p in mem["stats"]) / args.steps, 4),
                       "host_copy_bytes_per_step": 0,
                       "chunks_per_step": int(mem["stats"][0].stats.chunks),
-                      "binding_roofline": dict(pcie, frac=round(value / pcie_gbs, 4))}
+                      "binding_roofline": dict(pcie, frac=round(value / pcie_gbs, 4),
+                                               peak_until_the_slowest_rank_is_done=round(pcie_all_done_gbs, 1),
+                                               frac_until_the_slowest_rank_is_done=round(value / pcie_all_done_gbs, 4))}
         if world > 1 and mem["single_s"]:
             single = bytes_placed / mem["single_s"] / 1e9
             out["e2e"]["one_rank_alone_gbs"] = round(single, 2)
