@@ -510,7 +510,9 @@ int32_t mxb_fanout_set_child(mxb_fanout *f, int32_t k, const mxb_span *child, ui
  *   DMA     for a root: the copy engines move every range to every child (one peer copy
  *           each, children side by side), then one launch announces all chunks at once.
  *           Nothing is announced before everything has arrived, so it suits pushes whose
- *           children only receive (one hop); a node that has a parent runs VECTOR.
+ *           children only receive (one hop); a node that has a parent runs VECTOR, and so
+ *           does a root whose copies would average under 4 MiB (thousands of scattered
+ *           tensors: copy setup would cost more than the engines gain).
  * All speak the same counters, so the nodes of one broadcast may differ.  The
  * reference has no counterpart: its pull is one RDMA READ per tensor with no
  * forwarding (nixl_transfer.py:769-952). */

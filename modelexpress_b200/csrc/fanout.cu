@@ -29,6 +29,9 @@ struct FanPiece {
 };
 
 constexpr int kFanThreads = 512;
+// the copy-engine push is used when its copies average at least this much (about 7 us of setup
+// per peer copy were measured: 4 MiB at 750 GB/s take 5.6 us)
+constexpr uint64_t kDmaMinMeanCopy = 4ull << 20;
 constexpr uint32_t kFanPiece = 64 * 1024;
 
 struct FanArgs {
@@ -529,38 +532,51 @@ int32_t mxb_fanout_run(mxb_fanout *f, int32_t is_root, uint32_t timeout_ms) {
         // of their own, so their links run side by side), then one launch that announces all
         // chunks.  Nothing is announced before everything has arrived, which suits a root whose
         // children only receive; a node that waits for a parent keeps the store kernel.
-        MXB_CUDA(cudaEventRecord(f->ev0, dv->stream));
-        const uint32_t nchunks = (uint32_t)f->chunk_pieces.size();
+        // Ranges that follow one another in memory on both sides travel as one copy; a payload
+        // that still comes to many small copies (thousands of scattered tensors) costs more in
+        // copy setup than the engines gain, and goes to the store kernel below instead.
+        struct Run {
+            uint64_t src, dst, len;
+        };
+        std::vector<Run> runs[MXB_FANOUT_MAX_CHILDREN];
+        uint64_t total = 0, copies = 0;
         for (uint32_t c = 0; c < f->n_children; ++c) {
-            if (!f->child_stream[c]) MXB_CUDA(cudaStreamCreateWithFlags(&f->child_stream[c], cudaStreamNonBlocking));
-            if (!f->child_done[c]) MXB_CUDA(cudaEventCreateWithFlags(&f->child_done[c], cudaEventDisableTiming));
-            MXB_CUDA(cudaStreamWaitEvent(f->child_stream[c], f->ev0, 0));
-            // ranges that follow one another in memory on both sides travel as one copy
-            uint64_t run_src = 0, run_dst = 0, run_len = 0;
-            for (size_t p = 0; p <= np; ++p) {
-                if (p < np && f->piece_off[p] != 0) continue;  // the first piece of a range stands for the range
-                const uint64_t src = p < np ? f->pieces[p].local : 0;
-                const uint64_t dst = p < np ? f->child_ptr[c][p] : 0;
-                const uint64_t len = p < np ? f->local[f->piece_range[p]].nbytes : 0;
-                if (p < np && run_len && src == run_src + run_len && dst == run_dst + run_len) {
-                    run_len += len;
+            Run cur{0, 0, 0};
+            for (size_t p = 0; p < np; ++p) {
+                if (f->piece_off[p] != 0) continue;  // the first piece of a range stands for the range
+                const Run r{f->pieces[p].local, f->child_ptr[c][p], f->local[f->piece_range[p]].nbytes};
+                if (cur.len && r.src == cur.src + cur.len && r.dst == cur.dst + cur.len) {
+                    cur.len += r.len;
                     continue;
                 }
-                if (run_len)
-                    MXB_CUDA(cudaMemcpyAsync(reinterpret_cast<void *>(run_dst), reinterpret_cast<const void *>(run_src),
-                                             run_len, cudaMemcpyDeviceToDevice, f->child_stream[c]));
-                run_src = src;
-                run_dst = dst;
-                run_len = len;
+                if (cur.len) runs[c].push_back(cur);
+                cur = r;
             }
-            MXB_CUDA(cudaEventRecord(f->child_done[c], f->child_stream[c]));
-            MXB_CUDA(cudaStreamWaitEvent(dv->stream, f->child_done[c], 0));
+            if (cur.len) runs[c].push_back(cur);
+            for (const Run &r : runs[c]) total += r.len;
+            copies += runs[c].size();
         }
-        fanout_announce_kernel<<<(nchunks + 255) / 256, 256, 0, dv->stream>>>(a, nchunks);
-        MXB_CUDA(cudaGetLastError());
-        MXB_CUDA(cudaEventRecord(f->ev1, dv->stream));
-        f->ctx->launches.fetch_add(1);
-        return MXB_OK;
+        if (copies && total / copies >= kDmaMinMeanCopy) {
+            MXB_CUDA(cudaEventRecord(f->ev0, dv->stream));
+            const uint32_t nchunks = (uint32_t)f->chunk_pieces.size();
+            for (uint32_t c = 0; c < f->n_children; ++c) {
+                if (!f->child_stream[c])
+                    MXB_CUDA(cudaStreamCreateWithFlags(&f->child_stream[c], cudaStreamNonBlocking));
+                if (!f->child_done[c])
+                    MXB_CUDA(cudaEventCreateWithFlags(&f->child_done[c], cudaEventDisableTiming));
+                MXB_CUDA(cudaStreamWaitEvent(f->child_stream[c], f->ev0, 0));
+                for (const Run &r : runs[c])
+                    MXB_CUDA(cudaMemcpyAsync(reinterpret_cast<void *>(r.dst), reinterpret_cast<const void *>(r.src),
+                                             r.len, cudaMemcpyDeviceToDevice, f->child_stream[c]));
+                MXB_CUDA(cudaEventRecord(f->child_done[c], f->child_stream[c]));
+                MXB_CUDA(cudaStreamWaitEvent(dv->stream, f->child_done[c], 0));
+            }
+            fanout_announce_kernel<<<(nchunks + 255) / 256, 256, 0, dv->stream>>>(a, nchunks);
+            MXB_CUDA(cudaGetLastError());
+            MXB_CUDA(cudaEventRecord(f->ev1, dv->stream));
+            f->ctx->launches.fetch_add(1);
+            return MXB_OK;
+        }
     }
     if (bulk)
         for (const FanPiece &pc : f->pieces)

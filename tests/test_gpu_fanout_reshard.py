@@ -118,7 +118,8 @@ def test_fanout_across_gpus(kind, engine):
 
     devs = list(range(min(n, 4)))
     ctx = Context(devs)
-    sizes = [3 << 20, 4096 + 16, 7 << 20, 160]
+    # large enough on average (>= 4 MiB per range) for the copy-engine push to be taken when asked for
+    sizes = [3 << 20, 4096 + 16, 7 << 20, 160, 24 << 20]
     bufs = []
     for i, d in enumerate(devs):
         if i == 0:
