@@ -431,6 +431,57 @@ def fanout_measure(args, ctx, rank, world, local, nv=None) -> dict:
     return res
 
 
+def _fanout_loopback(args, local):
+    """One GPU: the root's kernel pushes into a second buffer of the same device, then the leaf's
+    kernel finds every chunk arrived (kernels that wait on one another never share a GPU).  The
+    same ``fanout_kernel`` as between GPUs with HBM in place of the link: what a profiler can be
+    pointed at, since a multi-rank command cannot be profiled."""
+    import torch
+
+    from modelexpress_b200.runtime import DIGEST_BLOCK64, DIGEST_SAFE32, Context
+
+    ctx = Context([local])
+    mib = _env_int("MXB_FANOUT_LOOPBACK_MIB", 2048)
+    sizes = [(mib << 20) // 40 // 256 * 256] * 40
+    offs, total = _layout_ranges(sizes)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(3)
+    src = torch.randint(0, 256, (total,), dtype=torch.uint8, device="cuda", generator=g)
+    dst = torch.zeros(total, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    s_spans = [(src.data_ptr() + o, n) for o, n in zip(offs, sizes)]
+    d_spans = [(dst.data_ptr() + o, n) for o, n in zip(offs, sizes)]
+    root, leaf = ctx.fanout(s_spans, 64 << 10, local), ctx.fanout(d_spans, 64 << 10, local)
+    root.add_child(d_spans, leaf.counters)
+    times = []
+    for it in range(max(3, args.warmup) + args.steps):
+        root.run(True, 5000)
+        ms = root.wait()
+        leaf.run(False, 5000)
+        leaf.wait()
+        if it >= max(3, args.warmup):
+            times.append(ms)
+    a = [(int(r.safe_checksum), int(r.block_hash)) for r in ctx.digest(s_spans, DIGEST_SAFE32 | DIGEST_BLOCK64, local)]
+    b = [(int(r.safe_checksum), int(r.block_hash)) for r in ctx.digest(d_spans, DIGEST_SAFE32 | DIGEST_BLOCK64, local)]
+    if a != b:
+        raise SystemExit("fan-out loopback: destination digests differ from the source")
+    ms = sum(times) / len(times)
+    payload = sum(sizes)
+    peak, peak_src = _peaks()
+    gbs = 2 * payload / (ms * 1e-3) / 1e9
+    out = _base("fan-out loopback GB/s read+write (root kernel into a buffer of the same GPU)", gbs, "GB/s", 1, args, ms,
+                {"workload": f"{payload} B in 40 ranges, 64 KiB chunks of one piece, same-device child",
+                 "l2": "input larger than L2", "check": "digests of every destination range equal the source"})
+    out["gpu_launches"] = 2 * (max(3, args.warmup) + args.steps)
+    out["roofline"] = {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s",
+                       "frac": round(gbs / peak, 4), "traffic": None, "kernel": "fanout_kernel",
+                       "peak_source": peak_src, "algorithmic_bytes_per_launch": 2 * payload}
+    print(json.dumps(out), flush=True)
+    root.close()
+    leaf.close()
+    ctx.close()
+
+
 def run_fanout(args):
     import torch.distributed as dist
 
@@ -438,10 +489,7 @@ def run_fanout(args):
 
     rank, world, local = _dist()
     if world < 2:
-        if rank == 0:
-            print(json.dumps({"metric": "fan-out GB/s per target", "unavailable":
-                              "needs at least 2 GPUs (one process per GPU)"}))
-        return
+        return _fanout_loopback(args, local)
     ctx = Context([local])
     nv = nvlink_peaks(ctx, rank, world, local)
     res = fanout_measure(args, ctx, rank, world, local, nv)
