@@ -15,6 +15,9 @@
 // run the same kernel with no children: it returns once every chunk arrived.
 // No wait is unbounded: when the time budget runs out the kernel records
 // DEV_TIMEOUT in its status word and returns.
+// A leaf only watches its counters (one thread per chunk).  A root whose children only
+// receive may hand the bytes to the copy engines instead (MXB_FANOUT_ENGINE_DMA: one peer
+// copy per run of adjacent ranges, then one launch that raises every counter).
 #include <cstdlib>
 
 #include "bulk.cuh"
